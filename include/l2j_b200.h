@@ -1,0 +1,227 @@
+/*
+ * l2j_b200.h -- C ABI of libl2j_b200.so: llama2j's `--mode CUDA` token-decode path for NVIDIA B200.
+ *
+ * The library replaces what the reference's Java code reaches through JCuda for one token:
+ * the device runtime (ContextCUDA.java), the run state (RunState.java), the device copies of the
+ * weights (TransformerWeights.java) and the per-token forward (Run.transformerCUDA,
+ * Run.java:315-519).  The Java host keeps its checkpoint reader, quant cache, tokenizer, sampler
+ * and command line, and drives this ABI with java.lang.foreign downcalls.
+ *
+ * Paths in the comments are relative to the reference's src/main/java/com/lastbot/llama2j/.
+ *
+ * Conventions: every function returns 0 on success or a negative L2J_E_* code; the message of the
+ * last failure of a context is available from l2j_last_error().  Nothing aborts or throws across
+ * the ABI.  Host pointers only need to stay valid for the duration of the call.  There is no CPU
+ * fallback: without a CUDA device l2j_create() fails.
+ */
+#ifndef L2J_B200_H
+#define L2J_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define L2J_OK 0
+#define L2J_E_INVALID (-1)   /* bad argument, unsupported shape, wrong size */
+#define L2J_E_CUDA (-2)      /* a CUDA runtime call failed */
+#define L2J_E_STATE (-3)     /* call out of order (e.g. forward before finalize) */
+#define L2J_E_DEVICE (-4)    /* a kernel reported a fault through the device status word */
+#define L2J_E_NOMEM (-5)     /* device or host allocation failed */
+
+/* Device status bits (l2j_stats.device_status): set by kernels, never by a trap. */
+#define L2J_DS_WAIT_TIMEOUT 0x1  /* a bounded wait on a copy barrier ran out */
+#define L2J_DS_BAD_POS 0x2       /* pos outside [0, seq_len) reached a kernel */
+#define L2J_DS_BAD_TOKEN 0x4     /* token outside [0, vocab) reached a kernel */
+
+/* Quantisation group of the reference: Run.QUANT_GROUP_SIZE / QUANT_BITS, Run.java:27-28;
+ * encoded group = 8-byte header (min, max as big-endian floats) + 256 bytes, Quant.java:35-37. */
+#define L2J_QUANT_GROUP 256
+#define L2J_QUANT_GROUP_BYTES 264
+
+/* Config.java:6-13, plus the sign of vocab_size in the checkpoint header (Run.java:571-573). */
+typedef struct l2j_config {
+    int32_t dim;
+    int32_t hidden_dim;
+    int32_t n_layers;
+    int32_t n_heads;
+    int32_t n_kv_heads;
+    int32_t vocab_size;        /* always positive here */
+    int32_t seq_len;
+    int32_t shared_classifier; /* 1: wcls is the embedding table (positive vocab in the file) */
+} l2j_config;
+
+/* Tensor ids, in checkpoint file order (TransformerWeights.java:50-122). */
+enum l2j_tensor {
+    L2J_T_TOKEN_EMBEDDING = 0, /* f32 (vocab, dim) */
+    L2J_T_RMS_ATT = 1,         /* quant (layer, dim) */
+    L2J_T_WQ = 2,              /* quant (layer, dim, dim) */
+    L2J_T_WK = 3,              /* quant (layer, kv_dim, dim) */
+    L2J_T_WV = 4,              /* quant (layer, kv_dim, dim) */
+    L2J_T_WO = 5,              /* quant (layer, dim, dim) */
+    L2J_T_RMS_FFN = 6,         /* quant (layer, dim) */
+    L2J_T_W1 = 7,              /* quant (layer, hidden, dim) */
+    L2J_T_W2 = 8,              /* quant (layer, dim, hidden) */
+    L2J_T_W3 = 9,              /* quant (layer, hidden, dim) */
+    L2J_T_RMS_FINAL = 10,      /* quant (dim) */
+    L2J_T_WCLS = 11,           /* f32 (vocab, dim), only when not shared */
+    L2J_T_COUNT = 12
+};
+
+/* l2j_create flags */
+#define L2J_F_NO_GRAPH 0x1    /* launch kernels directly instead of replaying a CUDA graph */
+#define L2J_F_NO_PDL 0x2      /* no programmatic dependent launch between consecutive kernels */
+#define L2J_F_SIMPLE 0x4      /* plain direct-load matvec kernels (cross-check path, slower) */
+
+typedef struct l2j_ctx l2j_ctx;
+
+typedef struct l2j_stats {
+    int64_t forwards;          /* forwards launched since create/reset */
+    int64_t kernels_per_forward;
+    int64_t device_bytes;      /* device memory held by the context */
+    int32_t device_status;     /* L2J_DS_* bits accumulated since create/reset */
+    int32_t last_pos;
+    int32_t last_token;        /* token chosen by the device argmax of the last forward */
+    int32_t sm_count;
+} l2j_stats;
+
+/* ---- context ------------------------------------------------------------------------------- */
+
+/* One context = one device and one contiguous layer range [first_layer, last_layer] of the model,
+ * the unit LayerAllocation.java:67-95 assigns to a GPU.  A context that starts at layer 0 owns the
+ * embedding gather (Run.java:362-363); one that ends at the last layer owns the final RMSNorm,
+ * the classifier (Run.java:514-518) and the greedy pick (Sampler.java:46-57).
+ * Replaces ContextCUDA's constructor (ContextCUDA.java:75-100) and RunState's device half
+ * (RunState.java:107-166). */
+int l2j_create(const l2j_config *cfg, int device, int first_layer, int last_layer, uint32_t flags, l2j_ctx **out);
+
+/* ContextCUDA.close(), ContextCUDA.java:311-323. */
+void l2j_destroy(l2j_ctx *ctx);
+
+/* Message of the most recent failure on this context ("" if none).  ctx may be NULL for a
+ * failure of l2j_create. */
+const char *l2j_last_error(const l2j_ctx *ctx);
+
+/* ---- weights ------------------------------------------------------------------------------- */
+
+/* Uploads (part of) a quantised tensor in the reference's group format, exactly the bytes of a
+ * `.quant` cache file after its length field (BinFileWriter.java:20-34).  `float_offset` is the
+ * index of the part's first element in the whole tensor and must be a multiple of 256; `n_floats`
+ * is the number of elements in the part; `bytes` must equal ceil(n_floats/256)*264.  Parts outside
+ * the context's layer range are ignored, parts that overlap it are clipped.  Replaces
+ * ContextCUDA.allocateQuantAndCopyToDevice (ContextCUDA.java:138-158) and the SPLIT_TO_LAYERS /
+ * LAST_DEVICE_ONLY policies (TransformerWeights.java:238-350).  Thread-safe per context. */
+int l2j_upload_quant(l2j_ctx *ctx, int tensor, int64_t float_offset, const void *groups, int64_t bytes,
+                     int64_t n_floats);
+
+/* Uploads (part of) an FP32 tensor: the embedding table or the unshared classifier
+ * (TransformerWeights.java:119-135). */
+int l2j_upload_f32(l2j_ctx *ctx, int tensor, int64_t float_offset, const float *data, int64_t n_floats);
+
+/* Checks that every tensor the layer range needs has arrived, builds the derived tables and
+ * captures the per-token graph.  Must follow the uploads and precede the first forward. */
+int l2j_finalize(l2j_ctx *ctx);
+
+/* ---- per-token forward --------------------------------------------------------------------- */
+
+/* One decode step: Run.transformerCUDA(token, pos, ...) (Run.java:315-519) followed by the
+ * logits read-back of the run loop (Run.java:628-632).  For a context that holds the whole model.
+ * `logits` (vocab floats) and `argmax` may each be NULL.  Blocks until the results are on the host. */
+int l2j_forward(l2j_ctx *ctx, int token, int pos, float *logits, int *argmax);
+
+/* The same step for one stage of a layer split.  A first stage takes `token`; later stages take
+ * the activation vector x (dim floats, host memory) that the previous stage returned, the hand-off
+ * of Run.java:368-413.  A stage that is not the last writes its x to `x_out`; the last stage fills
+ * `logits` / `argmax`.  Unused pointers may be NULL. */
+int l2j_forward_stage(l2j_ctx *ctx, int token, int pos, const float *x_in, float *x_out, float *logits, int *argmax);
+
+/* Device addresses of the stage's activation vector x (dim floats) and of its logits, for callers
+ * that move them with their own device-to-device transport. */
+int l2j_device_buffers(l2j_ctx *ctx, void **x_dev, void **logits_dev);
+
+/* The stage step without host copies: enqueues the kernels on the context's stream and returns.
+ * x must already be in the device buffer (or token given for a first stage). */
+int l2j_forward_stage_async(l2j_ctx *ctx, int token, int pos);
+
+/* Waits for the context's stream and returns L2J_E_DEVICE if a kernel raised a status bit. */
+int l2j_sync(l2j_ctx *ctx);
+
+/* The run loop of Run.java:609-685 with greedy selection, kept on the device: position 0 is fed
+ * BOS (token 1), positions 1..n_prompt are fed the prompt, later positions the previous argmax.
+ * `out_tokens[p]` receives the token chosen after position p (the forced prompt token while the
+ * prompt lasts), for p in [0, steps).  No host round trip between tokens; the early stop on a
+ * sampled BOS (Run.java:670-672) is left to the caller, who truncates. */
+int l2j_generate_greedy(l2j_ctx *ctx, const int32_t *prompt, int n_prompt, int steps, int32_t *out_tokens);
+
+/* Clears the KV cache position bookkeeping and the statistics (a new sequence). */
+int l2j_reset(l2j_ctx *ctx);
+
+int l2j_get_stats(l2j_ctx *ctx, l2j_stats *out);
+
+/* How the per-token work is issued: bit 0 CUDA graph replay, bit 1 programmatic dependent launch
+ * between kernels, bit 2 the bulk-copy ring kernels (else the plain kernels).  The reference issues
+ * every kernel with its own cuLaunchKernel (kernel/MatMul.java:338-354). */
+int l2j_launch_mode(l2j_ctx *ctx);
+
+/* Reads a run-state buffer after a forward, the device half of RunState.java:38-50, for
+ * stage-by-stage comparison in the spirit of the reference's TEST mode (Run.java:186-303):
+ * which = 0 x, 1 attention output xb, 2 q, 3 hb, 4 logits (layer/pos ignored);
+ * 5 K row, 6 V row of (layer, pos) in the reference's (kv_dim) order, n must be kv_dim. */
+int l2j_read_buffer(l2j_ctx *ctx, int which, int layer, int pos, float *out, int n);
+
+/* Average device time in microseconds of the last l2j_generate_greedy call per forward, measured
+ * with CUDA events on the context's stream. */
+int l2j_last_generate_us(l2j_ctx *ctx, double *total_us);
+
+/* ---- load-time helpers on the device ------------------------------------------------------- */
+
+/* Quant.encode (Quant.java:156-193) on the device, bit-exact: `in` host floats -> `out` host
+ * bytes (ceil(n/256)*264).  `device` selects the GPU. */
+int l2j_quant_encode(int device, const float *in, int64_t n_floats, void *out);
+
+/* Synthetic checkpoint tensors (no counterpart in the reference, which loads real checkpoints):
+ * element i of stream `stream` is a counter-based N(0,1) draw times `scale`.  The f32 form writes
+ * host floats; the quant form generates and encodes on the device and writes the group format. */
+int l2j_synth_f32(int device, uint64_t seed, uint32_t stream, int64_t start, int64_t n_floats, float scale,
+                  float *out);
+int l2j_synth_quant(int device, uint64_t seed, uint32_t stream, int64_t n_floats, float scale, void *out);
+
+/* ---- single-kernel entry points (TEST-mode counterparts, Run.java:186-303) ------------------ */
+
+/* xout = W x with fused dequantisation: MatMul.callI8 (kernel/MatMul.java:314-358).
+ * `groups` is the whole tensor in group format on the host, `weight_index` the element index of
+ * W's first entry (l * d * n in the reference's call sites), n the row length, d the row count. */
+int l2j_k_matvec_i8(int device, uint32_t flags, const void *groups, int64_t tensor_floats, int64_t weight_index,
+                    int n, int d, const float *x, float *xout);
+
+/* xout = W x, FP32 weights: MatMul.callFP32 (kernel/MatMul.java:289-312). */
+int l2j_k_matvec_f32(int device, uint32_t flags, const float *w, int n, int d, const float *x, float *xout,
+                     int *argmax);
+
+/* out = deq(w) * (rsqrt(mean(x^2) + 1e-5) * x): RootMeanSquare.call + WeightNormalizeAndScale.callI8
+ * (kernel/RootMeanSquare.java:57-118, kernel/WeightNormalizeAndScale.java:141-189). */
+int l2j_k_rmsnorm(int device, const void *groups, int64_t tensor_floats, int64_t weight_index, int n,
+                  const float *x, float *out);
+
+/* ApplyRope.call (kernel/ApplyRope.java:114-142): rotates q (dim) and k (kv_dim) in place. */
+int l2j_k_rope(int device, float *q, float *k, int pos, int dim, int kv_dim, int head_size);
+
+/* AttentionLoop + ExpSumNormalize + AccumWeightedValue for every head (Run.java:450-478).
+ * key/value caches are in the reference's layout (seq, kv_dim) for one layer; positions 0..pos
+ * are read.  out receives n_heads * head_size floats. */
+int l2j_k_attention(int device, const float *q, const float *key_cache, const float *value_cache, int pos,
+                    int n_heads, int n_kv_heads, int head_size, int seq_len, float *out);
+
+/* Silu.call (kernel/Silu.java:97-135): hb = hb * sigmoid(hb) * hb2. */
+int l2j_k_swiglu(int device, float *hb, const float *hb2, int n);
+
+/* Copies n bytes device-to-device repeatedly and returns the best time; the denominator check of
+ * the roofline (no counterpart in the reference). */
+int l2j_k_copy_bandwidth(int device, int64_t bytes, int iters, double *best_gbs);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* L2J_B200_H */

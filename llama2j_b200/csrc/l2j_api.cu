@@ -1,0 +1,1392 @@
+// Host side of libl2j_b200: the context (device memory, weights, per-token CUDA graph) and the
+// C ABI declared in include/l2j_b200.h.  No Torch, no CPU compute path: everything a token needs
+// runs in the kernels of l2j_kernels.cu.
+
+#include "../../include/l2j_b200.h"
+#include "l2j_internal.h"
+
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <vector>
+
+using namespace l2j;
+
+namespace {
+
+thread_local std::string g_create_error;
+
+constexpr int kCmdRing = 256;
+
+struct LayerLaunch {
+    MvParams qkv, wo, w13, w2;
+    AttnParams attn;
+};
+
+}  // namespace
+
+struct l2j_ctx {
+    l2j_config cfg{};
+    int device = 0;
+    int first_layer = 0, last_layer = 0, nl = 0;
+    uint32_t flags = 0;
+    bool is_first = false, is_last = false;
+    int dim = 0, kv_dim = 0, head = 0, hidden = 0, kv_mul = 1;
+    int sm_count = 0;
+    cudaStream_t stream = nullptr;
+    std::mutex mu;
+    std::string err;
+    std::vector<void *> allocs;
+    int64_t device_bytes = 0;
+
+    QTensor qt[L2J_T_COUNT];
+    int64_t per_layer[L2J_T_COUNT] = {0};
+    bool needed[L2J_T_COUNT] = {false};
+    float *rms_att = nullptr, *rms_ffn = nullptr, *rms_final = nullptr;   // dequantised
+    float *emb = nullptr, *wcls = nullptr;
+    int64_t emb_received = 0, wcls_received = 0;
+
+    float *x = nullptr, *xb = nullptr, *q = nullptr, *hb = nullptr, *logits = nullptr;
+    float *y0 = nullptr, *y1 = nullptr, *y2 = nullptr, *xn = nullptr;
+    float *kc = nullptr, *vc = nullptr;
+    float *rope_cos = nullptr, *rope_sin = nullptr;
+    float *attn_part = nullptr;
+    unsigned int *attn_counters = nullptr;
+    int nsplit = 1, chunk_max = 1;
+    float *blk_val = nullptr;
+    int *blk_idx = nullptr;
+    int *prompt_dev = nullptr, *out_tokens_dev = nullptr;
+    SeqState *state = nullptr;
+    Cmd *cmd_dev = nullptr;
+    Cmd *cmd_host = nullptr;       // pinned ring
+    float *logits_host = nullptr;  // pinned
+    float *x_host = nullptr;       // pinned
+    SeqState *state_host = nullptr;
+
+    MvPlan plan_dim{}, plan_hidden{}, plan_cls{};
+    bool use_ring = false;
+    std::vector<LayerLaunch> layers;
+    MvParams cls{};
+    bool finalized = false;
+    bool pdl_on = false;
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    int kernels_per_forward = 0;
+    int64_t forwards = 0;
+    int32_t status_accum = 0;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    double last_generate_us = 0.0;
+};
+
+namespace {
+
+int fail(l2j_ctx *ctx, int code, const char *fmt, ...)
+{
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    if (ctx)
+        ctx->err = buf;
+    else
+        g_create_error = buf;
+    return code;
+}
+
+#define CK(ctx, call)                                                                                       \
+    do {                                                                                                    \
+        cudaError_t e__ = (call);                                                                           \
+        if (e__ != cudaSuccess)                                                                             \
+            return fail(ctx, L2J_E_CUDA, "%s failed: %s (%s:%d)", #call, cudaGetErrorString(e__), __FILE__, \
+                        __LINE__);                                                                          \
+    } while (0)
+
+template <typename T>
+int dev_alloc(l2j_ctx *ctx, T **out, int64_t count, bool zero)
+{
+    void *p = nullptr;
+    const size_t bytes = (size_t)(count > 0 ? count : 1) * sizeof(T);
+    cudaError_t e = cudaMalloc(&p, bytes);
+    if (e != cudaSuccess)
+        return fail(ctx, L2J_E_NOMEM, "cudaMalloc of %zu bytes failed: %s", bytes, cudaGetErrorString(e));
+    if (zero) {
+        e = cudaMemset(p, 0, bytes);
+        if (e != cudaSuccess) {
+            cudaFree(p);
+            return fail(ctx, L2J_E_CUDA, "cudaMemset failed: %s", cudaGetErrorString(e));
+        }
+    }
+    ctx->allocs.push_back(p);
+    ctx->device_bytes += (int64_t)bytes;
+    *out = static_cast<T *>(p);
+    return L2J_OK;
+}
+
+bool is_quant_tensor(int t)
+{
+    return t == L2J_T_RMS_ATT || t == L2J_T_WQ || t == L2J_T_WK || t == L2J_T_WV || t == L2J_T_WO || t == L2J_T_RMS_FFN ||
+           t == L2J_T_W1 || t == L2J_T_W2 || t == L2J_T_W3 || t == L2J_T_RMS_FINAL;
+}
+
+bool is_rms_tensor(int t)
+{
+    return t == L2J_T_RMS_ATT || t == L2J_T_RMS_FFN || t == L2J_T_RMS_FINAL;
+}
+
+// The reference's RoPE table (ApplyRope.init, kernel/ApplyRope.java:34-59), one row per position
+// and one entry per rotated pair of a head.
+void build_rope_tables(int seq_len, int head, std::vector<float> &cs, std::vector<float> &sn)
+{
+    const int half = head / 2;
+    cs.resize((size_t)seq_len * half);
+    sn.resize((size_t)seq_len * half);
+    for (int j = 0; j < half; ++j) {
+        const float e = (float)(2 * j) / (float)head;
+        const float freq = (float)(1.0 / std::pow((double)10000.0f, (double)e));
+        for (int pos = 0; pos < seq_len; ++pos) {
+            const float val = (float)pos * freq;
+            cs[(size_t)pos * half + j] = (float)std::cos((double)val);
+            sn[(size_t)pos * half + j] = (float)std::sin((double)val);
+        }
+    }
+}
+
+int choose_nsplit(int sm_count, int n_heads, int seq_len)
+{
+    int ns = (2 * sm_count + n_heads - 1) / n_heads;
+    if (ns > 32)
+        ns = 32;
+    const int cap = seq_len / 16 > 0 ? seq_len / 16 : 1;
+    if (ns > cap)
+        ns = cap;
+    if (ns < 1)
+        ns = 1;
+    return ns;
+}
+
+MvSeg make_seg(const QTensor &t, int64_t weight_index, int rows)
+{
+    MvSeg s;
+    s.payload = t.payload;
+    s.hdr = t.hdr;
+    s.flat0 = weight_index - t.base_float;
+    s.rows = rows;
+    return s;
+}
+
+void fill_plan(MvParams &p, const MvPlan &pl)
+{
+    p.rpp = pl.rpp;
+    p.wpr = pl.wpr;
+    p.nstage = pl.nstage;
+    p.slot_bytes = pl.slot_bytes;
+    p.hdr_off = pl.hdr_off;
+    p.half_hdr = pl.half_hdr;
+    p.timeout_polls = 1 << 22;
+}
+
+// Builds the static kernel parameter blocks of every layer this context owns.
+void build_launch_params(l2j_ctx *c)
+{
+    const int dim = c->dim, kv_dim = c->kv_dim, hidden = c->hidden;
+    c->layers.assign((size_t)c->nl, LayerLaunch{});
+    for (int li = 0; li < c->nl; ++li) {
+        const int64_t l = c->first_layer + li;
+        LayerLaunch &L = c->layers[(size_t)li];
+        float *kc = c->kc + (int64_t)li * c->cfg.n_kv_heads * c->cfg.seq_len * c->head;
+        float *vc = c->vc + (int64_t)li * c->cfg.n_kv_heads * c->cfg.seq_len * c->head;
+
+        MvParams base{};
+        base.dim = dim;
+        base.kv_dim = kv_dim;
+        base.head = c->head;
+        base.seq_len = c->cfg.seq_len;
+        base.state = c->state;
+        base.rope_cos = c->rope_cos;
+        base.rope_sin = c->rope_sin;
+
+        // q, k, v = W(rmsnorm(x)); RoPE; KV append            (Run.java:418-446)
+        MvParams &a = L.qkv;
+        a = base;
+        a.seg[0] = make_seg(c->qt[L2J_T_WQ], l * dim * dim, dim);
+        a.seg[1] = make_seg(c->qt[L2J_T_WK], l * (int64_t)kv_dim * dim, kv_dim);
+        a.seg[2] = make_seg(c->qt[L2J_T_WV], l * (int64_t)kv_dim * dim, kv_dim);
+        a.nseg = 3;
+        a.paired = 0;
+        a.n = dim;
+        fill_plan(a, c->plan_dim);
+        a.x_in = c->x;
+        a.rms_w = c->rms_att + (int64_t)li * dim;
+        a.epilogue = EPI_QKV_ROPE;
+        a.q_out = c->q;
+        a.k_cache = kc;
+        a.v_cache = vc;
+
+        // attention over positions 0..pos                      (Run.java:450-478)
+        AttnParams &t = L.attn;
+        t.q = c->q;
+        t.k_cache = kc;
+        t.v_cache = vc;
+        t.out = c->xb;
+        t.part = c->attn_part;
+        t.counters = c->attn_counters;
+        t.state = c->state;
+        t.n_heads = c->cfg.n_heads;
+        t.kv_mul = c->kv_mul;
+        t.head = c->head;
+        t.seq_len = c->cfg.seq_len;
+        t.nsplit = c->nsplit;
+        t.chunk_max = c->chunk_max;
+        t.pos_override = -1;
+
+        // x += Wo att                                          (Run.java:483-485)
+        MvParams &o = L.wo;
+        o = base;
+        o.seg[0] = make_seg(c->qt[L2J_T_WO], l * dim * dim, dim);
+        o.nseg = 1;
+        o.n = dim;
+        fill_plan(o, c->plan_dim);
+        o.x_in = c->xb;
+        o.rms_w = nullptr;
+        o.epilogue = EPI_RESIDUAL;
+        o.y = c->x;
+
+        // hb = silu(W1 rmsnorm(x)) * W3 rmsnorm(x)              (Run.java:490-502)
+        MvParams &f = L.w13;
+        f = base;
+        f.seg[0] = make_seg(c->qt[L2J_T_W1], l * (int64_t)hidden * dim, hidden);
+        f.seg[1] = make_seg(c->qt[L2J_T_W3], l * (int64_t)hidden * dim, hidden);
+        f.nseg = 1;
+        f.paired = 1;
+        f.n = dim;
+        fill_plan(f, c->plan_dim);
+        f.x_in = c->x;
+        f.rms_w = c->rms_ffn + (int64_t)li * dim;
+        f.epilogue = EPI_SWIGLU;
+        f.y = c->hb;
+
+        // x += W2 hb                                           (Run.java:505-508)
+        MvParams &w = L.w2;
+        w = base;
+        w.seg[0] = make_seg(c->qt[L2J_T_W2], l * (int64_t)hidden * dim, dim);
+        w.nseg = 1;
+        w.n = hidden;
+        fill_plan(w, c->plan_hidden);
+        w.x_in = c->hb;
+        w.rms_w = nullptr;
+        w.epilogue = EPI_RESIDUAL;
+        w.y = c->x;
+    }
+    if (c->is_last) {
+        // logits = Wcls rmsnorm(x); arg-max                    (Run.java:514-518, Sampler.java:46-57)
+        MvParams &k = c->cls;
+        k = MvParams{};
+        k.dim = c->dim;
+        k.kv_dim = c->kv_dim;
+        k.head = c->head;
+        k.seq_len = c->cfg.seq_len;
+        k.state = c->state;
+        k.seg[0].payload = reinterpret_cast<const uint8_t *>(c->wcls);
+        k.seg[0].hdr = nullptr;
+        k.seg[0].flat0 = 0;
+        k.seg[0].rows = c->cfg.vocab_size;
+        k.nseg = 1;
+        k.n = c->dim;
+        fill_plan(k, c->plan_cls);
+        k.x_in = c->x;
+        k.rms_w = c->rms_final;
+        k.epilogue = EPI_LOGITS;
+        k.y = c->logits;
+        k.blk_val = c->blk_val;
+        k.blk_idx = c->blk_idx;
+        k.prompt = c->prompt_dev;
+        k.out_tokens = c->out_tokens_dev;
+    }
+}
+
+// Enqueues the kernels of one forward of this context's layer range on its stream.
+cudaError_t enqueue_forward(l2j_ctx *c, bool pdl, int *n_kernels)
+{
+    cudaError_t e;
+    int nk = 0;
+    LaunchCfg lc{c->stream, false, c->sm_count};
+    // The first kernel of a forward follows a memcpy (or the previous graph launch): plain edge.
+    e = launch_begin(lc, c->state, c->cmd_dev, c->emb, c->x, c->dim, c->cfg.vocab_size, c->cfg.seq_len, c->is_first ? 1 : 0);
+    if (e != cudaSuccess)
+        return e;
+    ++nk;
+    lc.pdl = pdl;
+    const int dim = c->dim, hidden = c->hidden;
+    for (int li = 0; li < c->nl; ++li) {
+        LayerLaunch &L = c->layers[(size_t)li];
+        if (c->use_ring) {
+            if ((e = launch_matvec_ring(lc, c->plan_dim, false, L.qkv)) != cudaSuccess) return e;
+            if ((e = launch_attention(lc, L.attn)) != cudaSuccess) return e;
+            if ((e = launch_matvec_ring(lc, c->plan_dim, false, L.wo)) != cudaSuccess) return e;
+            if ((e = launch_matvec_ring(lc, c->plan_dim, false, L.w13)) != cudaSuccess) return e;
+            if ((e = launch_matvec_ring(lc, c->plan_hidden, false, L.w2)) != cudaSuccess) return e;
+            nk += 5;
+        } else {
+            LaunchCfg plain{c->stream, false, c->sm_count};
+            if ((e = launch_rmsnorm_plain(c->stream, c->x, L.qkv.rms_w, c->xn, dim)) != cudaSuccess) return e;
+            if ((e = launch_matvec_plain_u8(c->stream, L.qkv.seg[0], dim, c->xn, c->y0)) != cudaSuccess) return e;
+            if ((e = launch_matvec_plain_u8(c->stream, L.qkv.seg[1], dim, c->xn, c->y1)) != cudaSuccess) return e;
+            if ((e = launch_matvec_plain_u8(c->stream, L.qkv.seg[2], dim, c->xn, c->y2)) != cudaSuccess) return e;
+            if ((e = launch_epilogue_plain(c->stream, L.qkv, c->y0, c->y1, c->y2)) != cudaSuccess) return e;
+            if ((e = launch_attention(plain, L.attn)) != cudaSuccess) return e;
+            if ((e = launch_matvec_plain_u8(c->stream, L.wo.seg[0], dim, c->xb, c->y0)) != cudaSuccess) return e;
+            if ((e = launch_epilogue_plain(c->stream, L.wo, c->y0, nullptr, nullptr)) != cudaSuccess) return e;
+            if ((e = launch_rmsnorm_plain(c->stream, c->x, L.w13.rms_w, c->xn, dim)) != cudaSuccess) return e;
+            if ((e = launch_matvec_plain_u8(c->stream, L.w13.seg[0], dim, c->xn, c->y0)) != cudaSuccess) return e;
+            if ((e = launch_matvec_plain_u8(c->stream, L.w13.seg[1], dim, c->xn, c->y1)) != cudaSuccess) return e;
+            if ((e = launch_epilogue_plain(c->stream, L.w13, c->y0, c->y1, nullptr)) != cudaSuccess) return e;
+            if ((e = launch_matvec_plain_u8(c->stream, L.w2.seg[0], hidden, c->hb, c->y0)) != cudaSuccess) return e;
+            if ((e = launch_epilogue_plain(c->stream, L.w2, c->y0, nullptr, nullptr)) != cudaSuccess) return e;
+            nk += 14;
+        }
+    }
+    if (c->is_last) {
+        if (c->use_ring) {
+            if ((e = launch_matvec_ring(lc, c->plan_cls, true, c->cls)) != cudaSuccess) return e;
+            nk += 1;
+        } else {
+            if ((e = launch_rmsnorm_plain(c->stream, c->x, c->rms_final, c->xn, dim)) != cudaSuccess) return e;
+            if ((e = launch_matvec_plain_f32(c->stream, c->wcls, dim, c->cfg.vocab_size, c->xn, c->y0)) != cudaSuccess) return e;
+            if ((e = launch_epilogue_plain(c->stream, c->cls, c->y0, nullptr, nullptr)) != cudaSuccess) return e;
+            nk += 3;
+        }
+    }
+    if (n_kernels)
+        *n_kernels = nk;
+    return cudaSuccess;
+}
+
+bool try_capture(l2j_ctx *c, bool pdl)
+{
+    cudaGraph_t g = nullptr;
+    if (cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    int nk = 0;
+    cudaError_t e = enqueue_forward(c, pdl, &nk);
+    cudaError_t e2 = cudaStreamEndCapture(c->stream, &g);
+    if (e != cudaSuccess || e2 != cudaSuccess || !g) {
+        if (g)
+            cudaGraphDestroy(g);
+        cudaGetLastError();
+        return false;
+    }
+    cudaGraphExec_t ex = nullptr;
+    if (cudaGraphInstantiate(&ex, g, 0) != cudaSuccess || !ex) {
+        cudaGraphDestroy(g);
+        cudaGetLastError();
+        return false;
+    }
+    c->graph = g;
+    c->exec = ex;
+    c->kernels_per_forward = nk;
+    return true;
+}
+
+int launch_forward(l2j_ctx *c)
+{
+    if (c->exec) {
+        CK(c, cudaGraphLaunch(c->exec, c->stream));
+    } else {
+        int nk = 0;
+        CK(c, enqueue_forward(c, c->pdl_on, &nk));
+        c->kernels_per_forward = nk;
+    }
+    c->forwards++;
+    return L2J_OK;
+}
+
+int check_range(l2j_ctx *c, int token, int pos, bool need_token)
+{
+    if (pos < 0 || pos >= c->cfg.seq_len)
+        return fail(c, L2J_E_INVALID, "pos %d outside [0, %d)", pos, c->cfg.seq_len);
+    if (need_token && (token < 0 || token >= c->cfg.vocab_size))
+        return fail(c, L2J_E_INVALID, "token %d outside [0, %d)", token, c->cfg.vocab_size);
+    return L2J_OK;
+}
+
+int post_cmd(l2j_ctx *c, int mode, int token, int pos)
+{
+    Cmd *slot = c->cmd_host + (c->forwards % kCmdRing);
+    slot->mode = mode;
+    slot->token = token;
+    slot->pos = pos;
+    slot->pad = 0;
+    CK(c, cudaMemcpyAsync(c->cmd_dev, slot, sizeof(Cmd), cudaMemcpyHostToDevice, c->stream));
+    return L2J_OK;
+}
+
+int finish_status(l2j_ctx *c)
+{
+    const int st = c->state_host->status;
+    c->status_accum |= st;
+    if (st != 0)
+        return fail(c, L2J_E_DEVICE, "device status 0x%x (1: copy wait timed out, 2: bad pos, 4: bad token)", st);
+    return L2J_OK;
+}
+
+}  // namespace
+
+// ===============================================================================================
+// context
+// ===============================================================================================
+
+extern "C" int l2j_create(const l2j_config *cfg, int device, int first_layer, int last_layer, uint32_t flags, l2j_ctx **out)
+{
+    if (!cfg || !out)
+        return fail(nullptr, L2J_E_INVALID, "null argument");
+    *out = nullptr;
+    if (cfg->dim <= 0 || cfg->hidden_dim <= 0 || cfg->n_layers <= 0 || cfg->n_heads <= 0 || cfg->n_kv_heads <= 0 ||
+        cfg->vocab_size <= 0 || cfg->seq_len <= 0)
+        return fail(nullptr, L2J_E_INVALID, "config fields must be positive");
+    if (cfg->dim % cfg->n_heads != 0 || cfg->n_heads % cfg->n_kv_heads != 0)
+        return fail(nullptr, L2J_E_INVALID, "dim must divide by n_heads and n_heads by n_kv_heads");
+    const int head = cfg->dim / cfg->n_heads;
+    if (head % 4 != 0 || head > 128)
+        return fail(nullptr, L2J_E_INVALID, "head size %d unsupported (needs a multiple of 4, at most 128)", head);
+    if (cfg->dim % 4 != 0)
+        return fail(nullptr, L2J_E_INVALID, "dim must be a multiple of 4");
+    if (first_layer < 0 || last_layer >= cfg->n_layers || first_layer > last_layer)
+        return fail(nullptr, L2J_E_INVALID, "layer range [%d, %d] outside the model", first_layer, last_layer);
+    int ndev = 0;
+    cudaError_t e = cudaGetDeviceCount(&ndev);
+    if (e != cudaSuccess || ndev <= 0)
+        return fail(nullptr, L2J_E_CUDA, "no CUDA device: %s (this library has no CPU path)", cudaGetErrorString(e));
+    if (device < 0 || device >= ndev)
+        return fail(nullptr, L2J_E_INVALID, "device %d not present (%d devices)", device, ndev);
+    e = cudaSetDevice(device);
+    if (e != cudaSuccess)
+        return fail(nullptr, L2J_E_CUDA, "cudaSetDevice failed: %s", cudaGetErrorString(e));
+
+    l2j_ctx *c = new l2j_ctx();
+    c->cfg = *cfg;
+    c->device = device;
+    c->first_layer = first_layer;
+    c->last_layer = last_layer;
+    c->nl = last_layer - first_layer + 1;
+    c->flags = flags;
+    c->is_first = first_layer == 0;
+    c->is_last = last_layer == cfg->n_layers - 1;
+    c->dim = cfg->dim;
+    c->hidden = cfg->hidden_dim;
+    c->head = head;
+    c->kv_dim = cfg->dim * cfg->n_kv_heads / cfg->n_heads;
+    c->kv_mul = cfg->n_heads / cfg->n_kv_heads;
+
+#define CREATE_CK(call)                     \
+    do {                                    \
+        int rc__ = (call);                  \
+        if (rc__ != L2J_OK) {               \
+            g_create_error = c->err;        \
+            l2j_destroy(c);                 \
+            return rc__;                    \
+        }                                   \
+    } while (0)
+#define CREATE_CUDA(call)                                                                          \
+    do {                                                                                           \
+        cudaError_t e__ = (call);                                                                  \
+        if (e__ != cudaSuccess) {                                                                  \
+            fail(nullptr, L2J_E_CUDA, "%s failed: %s", #call, cudaGetErrorString(e__));            \
+            l2j_destroy(c);                                                                        \
+            return L2J_E_CUDA;                                                                     \
+        }                                                                                          \
+    } while (0)
+
+    cudaDeviceProp prop{};
+    CREATE_CUDA(cudaGetDeviceProperties(&prop, device));
+    c->sm_count = prop.multiProcessorCount;
+    CREATE_CUDA(prepare_kernels());
+    CREATE_CUDA(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
+    CREATE_CUDA(cudaEventCreate(&c->ev0));
+    CREATE_CUDA(cudaEventCreate(&c->ev1));
+
+    // quantised tensors: element counts per layer, TransformerWeights.java:54-111
+    const int64_t dim = c->dim, kvd = c->kv_dim, hid = c->hidden;
+    c->per_layer[L2J_T_RMS_ATT] = dim;
+    c->per_layer[L2J_T_WQ] = dim * dim;
+    c->per_layer[L2J_T_WK] = kvd * dim;
+    c->per_layer[L2J_T_WV] = kvd * dim;
+    c->per_layer[L2J_T_WO] = dim * dim;
+    c->per_layer[L2J_T_RMS_FFN] = dim;
+    c->per_layer[L2J_T_W1] = hid * dim;
+    c->per_layer[L2J_T_W2] = dim * hid;
+    c->per_layer[L2J_T_W3] = hid * dim;
+    for (int t = 0; t < L2J_T_COUNT; ++t) {
+        if (!is_quant_tensor(t))
+            continue;
+        int64_t f0, f1;
+        if (t == L2J_T_RMS_FINAL) {
+            if (!c->is_last)
+                continue;
+            f0 = 0;
+            f1 = dim;
+        } else {
+            f0 = c->per_layer[t] * first_layer;
+            f1 = c->per_layer[t] * (last_layer + 1);
+        }
+        c->needed[t] = true;
+        QTensor &q = c->qt[t];
+        const int64_t g0 = f0 / kGroup, g1 = (f1 + kGroup - 1) / kGroup;
+        q.base_float = g0 * kGroup;
+        q.n_groups = g1 - g0;
+        CREATE_CK(dev_alloc(c, &q.payload, q.n_groups * kGroup + 512, true));
+        CREATE_CK(dev_alloc(c, &q.hdr, q.n_groups + 8, true));
+    }
+    const bool need_emb = c->is_first || (c->is_last && cfg->shared_classifier);
+    if (need_emb) {
+        CREATE_CK(dev_alloc(c, &c->emb, (int64_t)cfg->vocab_size * dim, false));
+        c->needed[L2J_T_TOKEN_EMBEDDING] = true;
+    }
+    if (c->is_last) {
+        if (cfg->shared_classifier) {
+            c->wcls = c->emb;
+        } else {
+            CREATE_CK(dev_alloc(c, &c->wcls, (int64_t)cfg->vocab_size * dim, false));
+            c->needed[L2J_T_WCLS] = true;
+        }
+    }
+    CREATE_CK(dev_alloc(c, &c->rms_att, (int64_t)c->nl * dim, true));
+    CREATE_CK(dev_alloc(c, &c->rms_ffn, (int64_t)c->nl * dim, true));
+    CREATE_CK(dev_alloc(c, &c->rms_final, dim, true));
+
+    // run state, RunState.java:107-166 (q/k/v and att scratch are internal to the fused kernels)
+    int64_t ymax = dim > hid ? dim : hid;
+    if (cfg->vocab_size > ymax)
+        ymax = cfg->vocab_size;
+    CREATE_CK(dev_alloc(c, &c->x, dim, true));
+    CREATE_CK(dev_alloc(c, &c->xb, dim, true));
+    CREATE_CK(dev_alloc(c, &c->xn, dim, true));
+    CREATE_CK(dev_alloc(c, &c->q, dim, true));
+    CREATE_CK(dev_alloc(c, &c->hb, hid, true));
+    CREATE_CK(dev_alloc(c, &c->logits, cfg->vocab_size, true));
+    CREATE_CK(dev_alloc(c, &c->y0, ymax, true));
+    CREATE_CK(dev_alloc(c, &c->y1, ymax, true));
+    CREATE_CK(dev_alloc(c, &c->y2, ymax, true));
+    const int64_t kv_floats = (int64_t)c->nl * cfg->n_kv_heads * cfg->seq_len * head;
+    CREATE_CK(dev_alloc(c, &c->kc, kv_floats, true));
+    CREATE_CK(dev_alloc(c, &c->vc, kv_floats, true));
+
+    std::vector<float> cs, sn;
+    build_rope_tables(cfg->seq_len, head, cs, sn);
+    CREATE_CK(dev_alloc(c, &c->rope_cos, (int64_t)cs.size(), false));
+    CREATE_CK(dev_alloc(c, &c->rope_sin, (int64_t)sn.size(), false));
+    CREATE_CUDA(cudaMemcpy(c->rope_cos, cs.data(), cs.size() * sizeof(float), cudaMemcpyHostToDevice));
+    CREATE_CUDA(cudaMemcpy(c->rope_sin, sn.data(), sn.size() * sizeof(float), cudaMemcpyHostToDevice));
+
+    c->nsplit = choose_nsplit(c->sm_count, cfg->n_heads, cfg->seq_len);
+    c->chunk_max = (cfg->seq_len + c->nsplit - 1) / c->nsplit;
+    CREATE_CK(dev_alloc(c, &c->attn_part, (int64_t)cfg->n_heads * c->nsplit * (head + 2), true));
+    CREATE_CK(dev_alloc(c, &c->attn_counters, cfg->n_heads, true));
+    CREATE_CK(dev_alloc(c, &c->blk_val, c->sm_count + 8, true));
+    CREATE_CK(dev_alloc(c, &c->blk_idx, c->sm_count + 8, true));
+    CREATE_CK(dev_alloc(c, &c->prompt_dev, cfg->seq_len, true));
+    CREATE_CK(dev_alloc(c, &c->out_tokens_dev, cfg->seq_len, true));
+    CREATE_CK(dev_alloc(c, &c->state, 1, true));
+    CREATE_CK(dev_alloc(c, &c->cmd_dev, 1, true));
+    CREATE_CUDA(cudaHostAlloc((void **)&c->cmd_host, sizeof(Cmd) * kCmdRing, cudaHostAllocDefault));
+    CREATE_CUDA(cudaHostAlloc((void **)&c->logits_host, sizeof(float) * (size_t)cfg->vocab_size, cudaHostAllocDefault));
+    CREATE_CUDA(cudaHostAlloc((void **)&c->x_host, sizeof(float) * (size_t)dim, cudaHostAllocDefault));
+    CREATE_CUDA(cudaHostAlloc((void **)&c->state_host, sizeof(SeqState), cudaHostAllocDefault));
+    memset(c->state_host, 0, sizeof(SeqState));
+
+    c->plan_dim = plan_matvec(c->dim, false, false);
+    c->plan_hidden = plan_matvec(c->hidden, false, false);
+    c->plan_cls = plan_matvec(c->dim, true, false);
+    c->use_ring = !(flags & L2J_F_SIMPLE) && c->plan_dim.ok && c->plan_hidden.ok && c->plan_cls.ok && (head % 2 == 0);
+    CREATE_CUDA(cudaStreamSynchronize(c->stream));
+    CREATE_CUDA(cudaDeviceSynchronize());
+#undef CREATE_CK
+#undef CREATE_CUDA
+    *out = c;
+    return L2J_OK;
+}
+
+extern "C" void l2j_destroy(l2j_ctx *c)
+{
+    if (!c)
+        return;
+    cudaSetDevice(c->device);
+    if (c->stream)
+        cudaStreamSynchronize(c->stream);
+    if (c->exec)
+        cudaGraphExecDestroy(c->exec);
+    if (c->graph)
+        cudaGraphDestroy(c->graph);
+    for (void *p : c->allocs)
+        cudaFree(p);
+    if (c->cmd_host)
+        cudaFreeHost(c->cmd_host);
+    if (c->logits_host)
+        cudaFreeHost(c->logits_host);
+    if (c->x_host)
+        cudaFreeHost(c->x_host);
+    if (c->state_host)
+        cudaFreeHost(c->state_host);
+    if (c->ev0)
+        cudaEventDestroy(c->ev0);
+    if (c->ev1)
+        cudaEventDestroy(c->ev1);
+    if (c->stream)
+        cudaStreamDestroy(c->stream);
+    delete c;
+}
+
+extern "C" const char *l2j_last_error(const l2j_ctx *c)
+{
+    return c ? c->err.c_str() : g_create_error.c_str();
+}
+
+// ===============================================================================================
+// weights
+// ===============================================================================================
+
+extern "C" int l2j_upload_quant(l2j_ctx *c, int tensor, int64_t float_offset, const void *groups, int64_t bytes,
+                                int64_t n_floats)
+{
+    if (!c)
+        return L2J_E_INVALID;
+    std::lock_guard<std::mutex> lock(c->mu);
+    if (tensor < 0 || tensor >= L2J_T_COUNT || !is_quant_tensor(tensor))
+        return fail(c, L2J_E_INVALID, "tensor %d is not a quantised tensor", tensor);
+    if (!groups || n_floats <= 0 || float_offset < 0 || float_offset % kGroup != 0)
+        return fail(c, L2J_E_INVALID, "bad part: offset %lld must be a non-negative multiple of 256, n_floats %lld positive",
+                    (long long)float_offset, (long long)n_floats);
+    const int64_t part_groups = (n_floats + kGroup - 1) / kGroup;
+    if (bytes != part_groups * kGroupBytes)
+        return fail(c, L2J_E_INVALID, "bytes %lld != ceil(n_floats/256)*264 = %lld", (long long)bytes,
+                    (long long)(part_groups * kGroupBytes));
+    if (c->finalized)
+        return fail(c, L2J_E_STATE, "upload after finalize");
+    if (!c->needed[tensor])
+        return L2J_OK;   // e.g. the final norm on a stage that is not the last
+    QTensor &q = c->qt[tensor];
+    const int64_t pg0 = float_offset / kGroup, pg1 = pg0 + part_groups;
+    const int64_t g0 = q.base_float / kGroup, g1 = g0 + q.n_groups;
+    const int64_t i0 = pg0 > g0 ? pg0 : g0, i1 = pg1 < g1 ? pg1 : g1;
+    if (i1 <= i0)
+        return L2J_OK;
+    CK(c, cudaSetDevice(c->device));
+    const int64_t count = i1 - i0;
+    const uint8_t *src = static_cast<const uint8_t *>(groups) + (i0 - pg0) * kGroupBytes;
+    // stage through device memory in pieces so that a 1.5 GB tensor does not need a second copy of itself
+    const int64_t piece = 1 << 18;   // groups per piece (66 MiB)
+    uint8_t *stage = nullptr;
+    const int64_t stage_groups = count < piece ? count : piece;
+    cudaError_t e = cudaMalloc((void **)&stage, (size_t)stage_groups * kGroupBytes);
+    if (e != cudaSuccess)
+        return fail(c, L2J_E_NOMEM, "staging allocation failed: %s", cudaGetErrorString(e));
+    int rc = L2J_OK;
+    for (int64_t done = 0; done < count && rc == L2J_OK; done += piece) {
+        const int64_t ng = count - done < piece ? count - done : piece;
+        e = cudaMemcpyAsync(stage, src + done * kGroupBytes, (size_t)ng * kGroupBytes, cudaMemcpyHostToDevice, c->stream);
+        if (e == cudaSuccess) {
+            uint8_t *dp = q.payload + (i0 - g0 + done) * kGroup;
+            float2 *dh = q.hdr + (i0 - g0 + done);
+            e = is_rms_tensor(tensor) ? launch_repack_minmax(c->stream, stage, ng, dp, dh)
+                                      : launch_repack(c->stream, stage, ng, dp, dh);
+        }
+        if (e == cudaSuccess)
+            e = cudaStreamSynchronize(c->stream);
+        if (e != cudaSuccess)
+            rc = fail(c, L2J_E_CUDA, "upload of tensor %d failed: %s", tensor, cudaGetErrorString(e));
+    }
+    cudaFree(stage);
+    if (rc == L2J_OK)
+        q.groups_received += count;
+    return rc;
+}
+
+extern "C" int l2j_upload_f32(l2j_ctx *c, int tensor, int64_t float_offset, const float *data, int64_t n_floats)
+{
+    if (!c)
+        return L2J_E_INVALID;
+    std::lock_guard<std::mutex> lock(c->mu);
+    if (tensor != L2J_T_TOKEN_EMBEDDING && tensor != L2J_T_WCLS)
+        return fail(c, L2J_E_INVALID, "tensor %d is not an FP32 tensor", tensor);
+    const int64_t total = (int64_t)c->cfg.vocab_size * c->dim;
+    if (!data || float_offset < 0 || n_floats <= 0 || float_offset + n_floats > total)
+        return fail(c, L2J_E_INVALID, "bad FP32 part [%lld, +%lld) of %lld", (long long)float_offset, (long long)n_floats,
+                    (long long)total);
+    if (c->finalized)
+        return fail(c, L2J_E_STATE, "upload after finalize");
+    if (tensor == L2J_T_WCLS && c->cfg.shared_classifier)
+        return fail(c, L2J_E_INVALID, "the classifier is shared with the embedding in this configuration");
+    if (!c->needed[tensor])
+        return L2J_OK;
+    CK(c, cudaSetDevice(c->device));
+    float *dst = tensor == L2J_T_TOKEN_EMBEDDING ? c->emb : c->wcls;
+    CK(c, cudaMemcpy(dst + float_offset, data, (size_t)n_floats * sizeof(float), cudaMemcpyHostToDevice));
+    if (tensor == L2J_T_TOKEN_EMBEDDING)
+        c->emb_received += n_floats;
+    else
+        c->wcls_received += n_floats;
+    return L2J_OK;
+}
+
+extern "C" int l2j_finalize(l2j_ctx *c)
+{
+    if (!c)
+        return L2J_E_INVALID;
+    std::lock_guard<std::mutex> lock(c->mu);
+    if (c->finalized)
+        return L2J_OK;
+    CK(c, cudaSetDevice(c->device));
+    for (int t = 0; t < L2J_T_COUNT; ++t) {
+        if (!c->needed[t])
+            continue;
+        if (is_quant_tensor(t)) {
+            if (c->qt[t].groups_received != c->qt[t].n_groups)
+                return fail(c, L2J_E_STATE, "tensor %d: %lld of %lld groups uploaded", t, (long long)c->qt[t].groups_received,
+                            (long long)c->qt[t].n_groups);
+        } else {
+            const int64_t total = (int64_t)c->cfg.vocab_size * c->dim;
+            const int64_t got = t == L2J_T_TOKEN_EMBEDDING ? c->emb_received : c->wcls_received;
+            if (got != total)
+                return fail(c, L2J_E_STATE, "tensor %d: %lld of %lld floats uploaded", t, (long long)got, (long long)total);
+        }
+    }
+    const int64_t dim = c->dim;
+    CK(c, launch_dequant_rms(c->stream, c->qt[L2J_T_RMS_ATT], dim * c->first_layer, dim * c->nl, c->rms_att));
+    CK(c, launch_dequant_rms(c->stream, c->qt[L2J_T_RMS_FFN], dim * c->first_layer, dim * c->nl, c->rms_ffn));
+    if (c->is_last)
+        CK(c, launch_dequant_rms(c->stream, c->qt[L2J_T_RMS_FINAL], 0, dim, c->rms_final));
+    CK(c, cudaStreamSynchronize(c->stream));
+    build_launch_params(c);
+
+    c->pdl_on = c->use_ring && !(c->flags & L2J_F_NO_PDL);
+    if (!(c->flags & L2J_F_NO_GRAPH)) {
+        if (!try_capture(c, c->pdl_on)) {
+            if (c->pdl_on) {
+                c->pdl_on = false;
+                try_capture(c, false);
+            }
+        }
+    }
+    c->finalized = true;
+    return L2J_OK;
+}
+
+// ===============================================================================================
+// forward
+// ===============================================================================================
+
+extern "C" int l2j_forward_stage_async(l2j_ctx *c, int token, int pos)
+{
+    if (!c)
+        return L2J_E_INVALID;
+    if (!c->finalized)
+        return fail(c, L2J_E_STATE, "forward before finalize");
+    int rc = check_range(c, token, pos, c->is_first);
+    if (rc != L2J_OK)
+        return rc;
+    CK(c, cudaSetDevice(c->device));
+    rc = post_cmd(c, 1, c->is_first ? token : 0, pos);
+    if (rc != L2J_OK)
+        return rc;
+    return launch_forward(c);
+}
+
+extern "C" int l2j_sync(l2j_ctx *c)
+{
+    if (!c)
+        return L2J_E_INVALID;
+    CK(c, cudaSetDevice(c->device));
+    CK(c, cudaMemcpyAsync(c->state_host, c->state, sizeof(SeqState), cudaMemcpyDeviceToHost, c->stream));
+    CK(c, cudaStreamSynchronize(c->stream));
+    return finish_status(c);
+}
+
+extern "C" int l2j_forward_stage(l2j_ctx *c, int token, int pos, const float *x_in, float *x_out, float *logits, int *argmax)
+{
+    if (!c)
+        return L2J_E_INVALID;
+    std::lock_guard<std::mutex> lock(c->mu);
+    if (!c->finalized)
+        return fail(c, L2J_E_STATE, "forward before finalize");
+    if (!c->is_first && !x_in)
+        return fail(c, L2J_E_INVALID, "a stage that does not start at layer 0 needs x_in");
+    int rc = check_range(c, token, pos, c->is_first);
+    if (rc != L2J_OK)
+        return rc;
+    CK(c, cudaSetDevice(c->device));
+    if (!c->is_first) {
+        memcpy(c->x_host, x_in, sizeof(float) * (size_t)c->dim);
+        CK(c, cudaMemcpyAsync(c->x, c->x_host, sizeof(float) * (size_t)c->dim, cudaMemcpyHostToDevice, c->stream));
+    }
+    rc = post_cmd(c, 1, c->is_first ? token : 0, pos);
+    if (rc != L2J_OK)
+        return rc;
+    rc = launch_forward(c);
+    if (rc != L2J_OK)
+        return rc;
+    if (c->is_last && logits)
+        CK(c, cudaMemcpyAsync(c->logits_host, c->logits, sizeof(float) * (size_t)c->cfg.vocab_size, cudaMemcpyDeviceToHost,
+                              c->stream));
+    if (!c->is_last && x_out)
+        CK(c, cudaMemcpyAsync(c->x_host, c->x, sizeof(float) * (size_t)c->dim, cudaMemcpyDeviceToHost, c->stream));
+    CK(c, cudaMemcpyAsync(c->state_host, c->state, sizeof(SeqState), cudaMemcpyDeviceToHost, c->stream));
+    CK(c, cudaStreamSynchronize(c->stream));
+    if (c->is_last && logits)
+        memcpy(logits, c->logits_host, sizeof(float) * (size_t)c->cfg.vocab_size);
+    if (!c->is_last && x_out)
+        memcpy(x_out, c->x_host, sizeof(float) * (size_t)c->dim);
+    if (c->is_last && argmax)
+        *argmax = c->state_host->argmax;
+    return finish_status(c);
+}
+
+extern "C" int l2j_forward(l2j_ctx *c, int token, int pos, float *logits, int *argmax)
+{
+    if (!c)
+        return L2J_E_INVALID;
+    if (!(c->is_first && c->is_last))
+        return fail(c, L2J_E_STATE, "l2j_forward needs a context that holds every layer; use l2j_forward_stage");
+    return l2j_forward_stage(c, token, pos, nullptr, nullptr, logits, argmax);
+}
+
+extern "C" int l2j_device_buffers(l2j_ctx *c, void **x_dev, void **logits_dev)
+{
+    if (!c)
+        return L2J_E_INVALID;
+    if (x_dev)
+        *x_dev = c->x;
+    if (logits_dev)
+        *logits_dev = c->logits;
+    return L2J_OK;
+}
+
+extern "C" int l2j_generate_greedy(l2j_ctx *c, const int32_t *prompt, int n_prompt, int steps, int32_t *out_tokens)
+{
+    if (!c)
+        return L2J_E_INVALID;
+    std::lock_guard<std::mutex> lock(c->mu);
+    if (!c->finalized)
+        return fail(c, L2J_E_STATE, "generate before finalize");
+    if (!(c->is_first && c->is_last))
+        return fail(c, L2J_E_STATE, "l2j_generate_greedy needs a context that holds every layer");
+    if (steps <= 0 || steps > c->cfg.seq_len || n_prompt < 0 || n_prompt > c->cfg.seq_len || (n_prompt > 0 && !prompt) ||
+        !out_tokens)
+        return fail(c, L2J_E_INVALID, "bad arguments: steps %d (seq_len %d), n_prompt %d", steps, c->cfg.seq_len, n_prompt);
+    for (int i = 0; i < n_prompt; ++i)
+        if (prompt[i] < 0 || prompt[i] >= c->cfg.vocab_size)
+            return fail(c, L2J_E_INVALID, "prompt token %d outside the vocabulary", prompt[i]);
+    CK(c, cudaSetDevice(c->device));
+    if (n_prompt > 0)
+        CK(c, cudaMemcpyAsync(c->prompt_dev, prompt, sizeof(int32_t) * (size_t)n_prompt, cudaMemcpyHostToDevice, c->stream));
+    SeqState init{};
+    init.token = 1;   // BOS, Run.java:614
+    init.pos = 0;
+    init.n_prompt = n_prompt;
+    CK(c, cudaMemcpyAsync(c->state, &init, sizeof(SeqState), cudaMemcpyHostToDevice, c->stream));
+    CK(c, cudaStreamSynchronize(c->stream));   // `init` and a pageable `prompt` must not be read later
+    int rc = post_cmd(c, 0, 0, 0);
+    if (rc != L2J_OK)
+        return rc;
+    CK(c, cudaEventRecord(c->ev0, c->stream));
+    for (int s = 0; s < steps; ++s) {
+        rc = launch_forward(c);
+        if (rc != L2J_OK)
+            return rc;
+    }
+    CK(c, cudaEventRecord(c->ev1, c->stream));
+    CK(c, cudaMemcpyAsync(c->state_host, c->state, sizeof(SeqState), cudaMemcpyDeviceToHost, c->stream));
+    CK(c, cudaStreamSynchronize(c->stream));
+    CK(c, cudaMemcpy(out_tokens, c->out_tokens_dev, sizeof(int32_t) * (size_t)steps, cudaMemcpyDeviceToHost));
+    float ms = 0.f;
+    CK(c, cudaEventElapsedTime(&ms, c->ev0, c->ev1));
+    c->last_generate_us = (double)ms * 1000.0;
+    return finish_status(c);
+}
+
+extern "C" int l2j_last_generate_us(l2j_ctx *c, double *total_us)
+{
+    if (!c || !total_us)
+        return L2J_E_INVALID;
+    *total_us = c->last_generate_us;
+    return L2J_OK;
+}
+
+extern "C" int l2j_reset(l2j_ctx *c)
+{
+    if (!c)
+        return L2J_E_INVALID;
+    std::lock_guard<std::mutex> lock(c->mu);
+    CK(c, cudaSetDevice(c->device));
+    CK(c, cudaStreamSynchronize(c->stream));
+    CK(c, cudaMemset(c->state, 0, sizeof(SeqState)));
+    CK(c, cudaMemset(c->attn_counters, 0, sizeof(unsigned int) * (size_t)c->cfg.n_heads));
+    CK(c, cudaDeviceSynchronize());
+    c->forwards = 0;
+    c->status_accum = 0;
+    c->err.clear();
+    return L2J_OK;
+}
+
+extern "C" int l2j_get_stats(l2j_ctx *c, l2j_stats *out)
+{
+    if (!c || !out)
+        return L2J_E_INVALID;
+    out->forwards = c->forwards;
+    out->kernels_per_forward = c->kernels_per_forward;
+    out->device_bytes = c->device_bytes;
+    out->device_status = c->status_accum;
+    out->last_pos = c->state_host ? c->state_host->cur_pos : 0;
+    out->last_token = c->state_host ? c->state_host->argmax : 0;
+    out->sm_count = c->sm_count;
+    return L2J_OK;
+}
+
+// Flags that describe how the per-token work is issued (bit 0: CUDA graph, bit 1: programmatic
+// dependent launch, bit 2: ring kernels), for reports.
+extern "C" int l2j_launch_mode(l2j_ctx *c)
+{
+    if (!c)
+        return 0;
+    return (c->exec ? 1 : 0) | (c->pdl_on ? 2 : 0) | (c->use_ring ? 4 : 0);
+}
+
+// Reads an internal buffer after a forward (debugging and per-stage parity checks):
+// 0 x, 1 attention output (xb), 2 q, 3 hb, 4 logits, 5 K row (layer, pos), 6 V row (layer, pos)
+// in the reference's (kv_dim) order.
+extern "C" int l2j_read_buffer(l2j_ctx *c, int which, int layer, int pos, float *out, int n)
+{
+    if (!c || !out || n <= 0)
+        return L2J_E_INVALID;
+    std::lock_guard<std::mutex> lock(c->mu);
+    CK(c, cudaSetDevice(c->device));
+    CK(c, cudaStreamSynchronize(c->stream));
+    const float *src = nullptr;
+    int len = 0;
+    switch (which) {
+    case 0: src = c->x; len = c->dim; break;
+    case 1: src = c->xb; len = c->dim; break;
+    case 2: src = c->q; len = c->dim; break;
+    case 3: src = c->hb; len = c->hidden; break;
+    case 4: src = c->logits; len = c->cfg.vocab_size; break;
+    case 5:
+    case 6: {
+        const int li = layer - c->first_layer;
+        if (li < 0 || li >= c->nl || pos < 0 || pos >= c->cfg.seq_len || n != c->kv_dim)
+            return fail(c, L2J_E_INVALID, "bad KV row request");
+        const float *base = (which == 5 ? c->kc : c->vc) + (int64_t)li * c->cfg.n_kv_heads * c->cfg.seq_len * c->head;
+        for (int h = 0; h < c->cfg.n_kv_heads; ++h)
+            CK(c, cudaMemcpy(out + (int64_t)h * c->head, base + ((int64_t)h * c->cfg.seq_len + pos) * c->head,
+                             sizeof(float) * (size_t)c->head, cudaMemcpyDeviceToHost));
+        return L2J_OK;
+    }
+    default: return fail(c, L2J_E_INVALID, "unknown buffer %d", which);
+    }
+    if (n > len)
+        return fail(c, L2J_E_INVALID, "buffer %d holds %d floats", which, len);
+    CK(c, cudaMemcpy(out, src, sizeof(float) * (size_t)n, cudaMemcpyDeviceToHost));
+    return L2J_OK;
+}
+
+// ===============================================================================================
+// load-time helpers and single-kernel entry points
+// ===============================================================================================
+
+namespace {
+
+struct Scratch {   // device allocations of a one-shot entry point, freed on scope exit
+    std::vector<void *> ptrs;
+    ~Scratch()
+    {
+        for (void *p : ptrs)
+            cudaFree(p);
+    }
+    template <typename T>
+    cudaError_t alloc(T **out, int64_t count, bool zero = false)
+    {
+        void *p = nullptr;
+        const size_t bytes = (size_t)(count > 0 ? count : 1) * sizeof(T);
+        cudaError_t e = cudaMalloc(&p, bytes);
+        if (e != cudaSuccess)
+            return e;
+        ptrs.push_back(p);
+        if (zero)
+            e = cudaMemset(p, 0, bytes);
+        *out = static_cast<T *>(p);
+        return e;
+    }
+};
+
+#define KCK(call)                                                                                      \
+    do {                                                                                               \
+        cudaError_t e__ = (call);                                                                      \
+        if (e__ != cudaSuccess)                                                                        \
+            return fail(nullptr, L2J_E_CUDA, "%s failed: %s (%s:%d)", #call, cudaGetErrorString(e__),  \
+                        __FILE__, __LINE__);                                                           \
+    } while (0)
+
+int set_device_checked(int device)
+{
+    int ndev = 0;
+    cudaError_t e = cudaGetDeviceCount(&ndev);
+    if (e != cudaSuccess || ndev <= 0)
+        return fail(nullptr, L2J_E_CUDA, "no CUDA device: %s (this library has no CPU path)", cudaGetErrorString(e));
+    if (device < 0 || device >= ndev)
+        return fail(nullptr, L2J_E_INVALID, "device %d not present", device);
+    KCK(cudaSetDevice(device));
+    KCK(prepare_kernels());
+    return L2J_OK;
+}
+
+int status_of(SeqState *dev_state)
+{
+    SeqState h{};
+    KCK(cudaMemcpy(&h, dev_state, sizeof(SeqState), cudaMemcpyDeviceToHost));
+    if (h.status != 0)
+        return fail(nullptr, L2J_E_DEVICE, "device status 0x%x", h.status);
+    return L2J_OK;
+}
+
+}  // namespace
+
+extern "C" int l2j_quant_encode(int device, const float *in, int64_t n_floats, void *out)
+{
+    if (!in || !out || n_floats <= 0)
+        return fail(nullptr, L2J_E_INVALID, "bad arguments");
+    int rc = set_device_checked(device);
+    if (rc != L2J_OK)
+        return rc;
+    Scratch s;
+    const int64_t piece = (int64_t)kGroup << 18;   // 64 Mi floats per piece
+    float *din = nullptr;
+    uint8_t *dout = nullptr;
+    const int64_t pn = n_floats < piece ? n_floats : piece;
+    KCK(s.alloc(&din, pn));
+    KCK(s.alloc(&dout, ((pn + kGroup - 1) / kGroup) * kGroupBytes));
+    for (int64_t done = 0; done < n_floats; done += piece) {
+        const int64_t n = n_floats - done < piece ? n_floats - done : piece;
+        const int64_t ob = ((n + kGroup - 1) / kGroup) * kGroupBytes;
+        KCK(cudaMemcpy(din, in + done, (size_t)n * sizeof(float), cudaMemcpyHostToDevice));
+        KCK(launch_quant_encode(nullptr, din, n, dout));
+        KCK(cudaMemcpy(static_cast<uint8_t *>(out) + (done / kGroup) * kGroupBytes, dout, (size_t)ob, cudaMemcpyDeviceToHost));
+    }
+    return L2J_OK;
+}
+
+extern "C" int l2j_synth_f32(int device, uint64_t seed, uint32_t stream, int64_t start, int64_t n_floats, float scale,
+                             float *out)
+{
+    if (!out || n_floats <= 0 || start < 0)
+        return fail(nullptr, L2J_E_INVALID, "bad arguments");
+    int rc = set_device_checked(device);
+    if (rc != L2J_OK)
+        return rc;
+    Scratch s;
+    const int64_t piece = (int64_t)1 << 26;
+    float *d = nullptr;
+    KCK(s.alloc(&d, n_floats < piece ? n_floats : piece));
+    for (int64_t done = 0; done < n_floats; done += piece) {
+        const int64_t n = n_floats - done < piece ? n_floats - done : piece;
+        KCK(launch_synth_normal(nullptr, d, n, seed, stream, start + done, scale));
+        KCK(cudaMemcpy(out + done, d, (size_t)n * sizeof(float), cudaMemcpyDeviceToHost));
+    }
+    return L2J_OK;
+}
+
+extern "C" int l2j_synth_quant(int device, uint64_t seed, uint32_t stream, int64_t n_floats, float scale, void *out)
+{
+    if (!out || n_floats <= 0)
+        return fail(nullptr, L2J_E_INVALID, "bad arguments");
+    int rc = set_device_checked(device);
+    if (rc != L2J_OK)
+        return rc;
+    Scratch s;
+    const int64_t piece = (int64_t)kGroup << 18;
+    float *d = nullptr;
+    uint8_t *dq = nullptr;
+    const int64_t pn = n_floats < piece ? n_floats : piece;
+    KCK(s.alloc(&d, pn));
+    KCK(s.alloc(&dq, ((pn + kGroup - 1) / kGroup) * kGroupBytes));
+    for (int64_t done = 0; done < n_floats; done += piece) {
+        const int64_t n = n_floats - done < piece ? n_floats - done : piece;
+        const int64_t ob = ((n + kGroup - 1) / kGroup) * kGroupBytes;
+        KCK(launch_synth_normal(nullptr, d, n, seed, stream, done, scale));
+        KCK(launch_quant_encode(nullptr, d, n, dq));
+        KCK(cudaMemcpy(static_cast<uint8_t *>(out) + (done / kGroup) * kGroupBytes, dq, (size_t)ob, cudaMemcpyDeviceToHost));
+    }
+    return L2J_OK;
+}
+
+extern "C" int l2j_k_matvec_i8(int device, uint32_t flags, const void *groups, int64_t tensor_floats, int64_t weight_index,
+                               int n, int d, const float *x, float *xout)
+{
+    if (!groups || !x || !xout || n <= 0 || d <= 0 || weight_index < 0 || weight_index + (int64_t)n * d > tensor_floats)
+        return fail(nullptr, L2J_E_INVALID, "bad arguments");
+    int rc = set_device_checked(device);
+    if (rc != L2J_OK)
+        return rc;
+    Scratch s;
+    const int64_t ng = (tensor_floats + kGroup - 1) / kGroup;
+    uint8_t *raw = nullptr, *payload = nullptr;
+    float2 *hdr = nullptr;
+    float *dx = nullptr, *dy = nullptr;
+    SeqState *st = nullptr;
+    KCK(s.alloc(&raw, ng * kGroupBytes));
+    KCK(s.alloc(&payload, ng * kGroup + 512, true));
+    KCK(s.alloc(&hdr, ng + 8, true));
+    KCK(s.alloc(&dx, n));
+    KCK(s.alloc(&dy, d, true));
+    KCK(s.alloc(&st, 1, true));
+    KCK(cudaMemcpy(raw, groups, (size_t)ng * kGroupBytes, cudaMemcpyHostToDevice));
+    KCK(cudaMemcpy(dx, x, (size_t)n * sizeof(float), cudaMemcpyHostToDevice));
+    KCK(launch_repack(nullptr, raw, ng, payload, hdr));
+    MvSeg seg{payload, hdr, weight_index, d};
+    const MvPlan pl = plan_matvec(n, false, false);
+    if (!(flags & L2J_F_SIMPLE) && pl.ok) {
+        cudaDeviceProp prop{};
+        KCK(cudaGetDeviceProperties(&prop, device));
+        MvParams p{};
+        p.seg[0] = seg;
+        p.nseg = 1;
+        p.n = n;
+        fill_plan(p, pl);
+        p.x_in = dx;
+        p.epilogue = EPI_STORE;
+        p.y = dy;
+        p.state = st;
+        LaunchCfg lc{nullptr, false, prop.multiProcessorCount};
+        KCK(launch_matvec_ring(lc, pl, false, p));
+    } else {
+        KCK(launch_matvec_plain_u8(nullptr, seg, n, dx, dy));
+    }
+    KCK(cudaDeviceSynchronize());
+    KCK(cudaMemcpy(xout, dy, (size_t)d * sizeof(float), cudaMemcpyDeviceToHost));
+    return status_of(st);
+}
+
+extern "C" int l2j_k_matvec_f32(int device, uint32_t flags, const float *w, int n, int d, const float *x, float *xout,
+                                int *argmax)
+{
+    if (!w || !x || !xout || n <= 0 || d <= 0)
+        return fail(nullptr, L2J_E_INVALID, "bad arguments");
+    int rc = set_device_checked(device);
+    if (rc != L2J_OK)
+        return rc;
+    Scratch s;
+    cudaDeviceProp prop{};
+    KCK(cudaGetDeviceProperties(&prop, device));
+    float *dw = nullptr, *dx = nullptr, *dy = nullptr, *bv = nullptr;
+    int *bi = nullptr, *outtok = nullptr;
+    SeqState *st = nullptr;
+    KCK(s.alloc(&dw, (int64_t)n * d + 64));
+    KCK(s.alloc(&dx, n));
+    KCK(s.alloc(&dy, d, true));
+    KCK(s.alloc(&bv, prop.multiProcessorCount + 8, true));
+    KCK(s.alloc(&bi, prop.multiProcessorCount + 8, true));
+    KCK(s.alloc(&outtok, 8, true));
+    KCK(s.alloc(&st, 1, true));
+    KCK(cudaMemcpy(dw, w, (size_t)n * d * sizeof(float), cudaMemcpyHostToDevice));
+    KCK(cudaMemcpy(dx, x, (size_t)n * sizeof(float), cudaMemcpyHostToDevice));
+    MvParams p{};
+    p.seg[0].payload = reinterpret_cast<const uint8_t *>(dw);
+    p.seg[0].rows = d;
+    p.nseg = 1;
+    p.n = n;
+    p.x_in = dx;
+    p.epilogue = argmax ? EPI_LOGITS : EPI_STORE;
+    p.y = dy;
+    p.blk_val = bv;
+    p.blk_idx = bi;
+    p.out_tokens = outtok;
+    p.state = st;
+    const MvPlan pl = plan_matvec(n, true, false);
+    if (!(flags & L2J_F_SIMPLE) && pl.ok) {
+        fill_plan(p, pl);
+        LaunchCfg lc{nullptr, false, prop.multiProcessorCount};
+        KCK(launch_matvec_ring(lc, pl, true, p));
+    } else {
+        float *tmp = nullptr;
+        KCK(s.alloc(&tmp, d, true));
+        KCK(launch_matvec_plain_f32(nullptr, dw, n, d, dx, tmp));
+        KCK(launch_epilogue_plain(nullptr, p, tmp, nullptr, nullptr));
+    }
+    KCK(cudaDeviceSynchronize());
+    KCK(cudaMemcpy(xout, dy, (size_t)d * sizeof(float), cudaMemcpyDeviceToHost));
+    SeqState h{};
+    KCK(cudaMemcpy(&h, st, sizeof(SeqState), cudaMemcpyDeviceToHost));
+    if (argmax)
+        *argmax = h.argmax;
+    if (h.status != 0)
+        return fail(nullptr, L2J_E_DEVICE, "device status 0x%x", h.status);
+    return L2J_OK;
+}
+
+extern "C" int l2j_k_rmsnorm(int device, const void *groups, int64_t tensor_floats, int64_t weight_index, int n, const float *x,
+                             float *out)
+{
+    if (!groups || !x || !out || n <= 0 || weight_index < 0 || weight_index + n > tensor_floats)
+        return fail(nullptr, L2J_E_INVALID, "bad arguments");
+    int rc = set_device_checked(device);
+    if (rc != L2J_OK)
+        return rc;
+    Scratch s;
+    const int64_t ng = (tensor_floats + kGroup - 1) / kGroup;
+    uint8_t *raw = nullptr;
+    QTensor t;
+    float *w = nullptr, *dx = nullptr, *dy = nullptr;
+    KCK(s.alloc(&raw, ng * kGroupBytes));
+    KCK(s.alloc(&t.payload, ng * kGroup + 512, true));
+    KCK(s.alloc(&t.hdr, ng + 8, true));
+    KCK(s.alloc(&w, n));
+    KCK(s.alloc(&dx, n));
+    KCK(s.alloc(&dy, n));
+    t.base_float = 0;
+    t.n_groups = ng;
+    KCK(cudaMemcpy(raw, groups, (size_t)ng * kGroupBytes, cudaMemcpyHostToDevice));
+    KCK(cudaMemcpy(dx, x, (size_t)n * sizeof(float), cudaMemcpyHostToDevice));
+    KCK(launch_repack_minmax(nullptr, raw, ng, t.payload, t.hdr));
+    KCK(launch_dequant_rms(nullptr, t, weight_index, n, w));
+    KCK(launch_rmsnorm_plain(nullptr, dx, w, dy, n));
+    KCK(cudaDeviceSynchronize());
+    KCK(cudaMemcpy(out, dy, (size_t)n * sizeof(float), cudaMemcpyDeviceToHost));
+    return L2J_OK;
+}
+
+extern "C" int l2j_k_rope(int device, float *q, float *k, int pos, int dim, int kv_dim, int head_size)
+{
+    if (!q || !k || pos < 0 || dim <= 0 || kv_dim <= 0 || kv_dim > dim || head_size <= 0 || head_size % 2 != 0 ||
+        dim % head_size != 0 || kv_dim % head_size != 0)
+        return fail(nullptr, L2J_E_INVALID, "bad arguments");
+    int rc = set_device_checked(device);
+    if (rc != L2J_OK)
+        return rc;
+    Scratch s;
+    std::vector<float> cs, sn;
+    build_rope_tables(pos + 1, head_size, cs, sn);
+    float *dq = nullptr, *dk = nullptr, *dcs = nullptr, *dsn = nullptr;
+    KCK(s.alloc(&dq, dim));
+    KCK(s.alloc(&dk, kv_dim));
+    KCK(s.alloc(&dcs, (int64_t)cs.size()));
+    KCK(s.alloc(&dsn, (int64_t)sn.size()));
+    KCK(cudaMemcpy(dq, q, (size_t)dim * sizeof(float), cudaMemcpyHostToDevice));
+    KCK(cudaMemcpy(dk, k, (size_t)kv_dim * sizeof(float), cudaMemcpyHostToDevice));
+    KCK(cudaMemcpy(dcs, cs.data(), cs.size() * sizeof(float), cudaMemcpyHostToDevice));
+    KCK(cudaMemcpy(dsn, sn.data(), sn.size() * sizeof(float), cudaMemcpyHostToDevice));
+    KCK(launch_rope_plain(nullptr, dq, dk, dcs, dsn, pos, dim, kv_dim, head_size));
+    KCK(cudaDeviceSynchronize());
+    KCK(cudaMemcpy(q, dq, (size_t)dim * sizeof(float), cudaMemcpyDeviceToHost));
+    KCK(cudaMemcpy(k, dk, (size_t)kv_dim * sizeof(float), cudaMemcpyDeviceToHost));
+    return L2J_OK;
+}
+
+extern "C" int l2j_k_attention(int device, const float *q, const float *key_cache, const float *value_cache, int pos,
+                               int n_heads, int n_kv_heads, int head_size, int seq_len, float *out)
+{
+    if (!q || !key_cache || !value_cache || !out || pos < 0 || pos >= seq_len || n_heads <= 0 || n_kv_heads <= 0 ||
+        n_heads % n_kv_heads != 0 || head_size % 4 != 0 || head_size > 128 || head_size <= 0)
+        return fail(nullptr, L2J_E_INVALID, "bad arguments");
+    int rc = set_device_checked(device);
+    if (rc != L2J_OK)
+        return rc;
+    Scratch s;
+    cudaDeviceProp prop{};
+    KCK(cudaGetDeviceProperties(&prop, device));
+    const int kv_dim = n_kv_heads * head_size;
+    const int64_t used = (int64_t)(pos + 1) * kv_dim;
+    const int64_t cache = (int64_t)seq_len * kv_dim;
+    float *dq = nullptr, *ksrc = nullptr, *vsrc = nullptr, *kc = nullptr, *vc = nullptr, *dout = nullptr, *part = nullptr;
+    unsigned int *counters = nullptr;
+    SeqState *st = nullptr;
+    AttnParams p{};
+    p.nsplit = choose_nsplit(prop.multiProcessorCount, n_heads, seq_len);
+    p.chunk_max = (seq_len + p.nsplit - 1) / p.nsplit;
+    KCK(s.alloc(&dq, (int64_t)n_heads * head_size));
+    KCK(s.alloc(&ksrc, used));
+    KCK(s.alloc(&vsrc, used));
+    KCK(s.alloc(&kc, cache, true));
+    KCK(s.alloc(&vc, cache, true));
+    KCK(s.alloc(&dout, (int64_t)n_heads * head_size, true));
+    KCK(s.alloc(&part, (int64_t)n_heads * p.nsplit * (head_size + 2), true));
+    KCK(s.alloc(&counters, n_heads, true));
+    KCK(s.alloc(&st, 1, true));
+    KCK(cudaMemcpy(dq, q, (size_t)n_heads * head_size * sizeof(float), cudaMemcpyHostToDevice));
+    KCK(cudaMemcpy(ksrc, key_cache, (size_t)used * sizeof(float), cudaMemcpyHostToDevice));
+    KCK(cudaMemcpy(vsrc, value_cache, (size_t)used * sizeof(float), cudaMemcpyHostToDevice));
+    KCK(launch_kv_relayout(nullptr, ksrc, kc, n_kv_heads, head_size, seq_len, pos + 1));
+    KCK(launch_kv_relayout(nullptr, vsrc, vc, n_kv_heads, head_size, seq_len, pos + 1));
+    p.q = dq;
+    p.k_cache = kc;
+    p.v_cache = vc;
+    p.out = dout;
+    p.part = part;
+    p.counters = counters;
+    p.state = st;
+    p.n_heads = n_heads;
+    p.kv_mul = n_heads / n_kv_heads;
+    p.head = head_size;
+    p.seq_len = seq_len;
+    p.pos_override = pos;
+    LaunchCfg lc{nullptr, false, prop.multiProcessorCount};
+    KCK(launch_attention(lc, p));
+    KCK(cudaDeviceSynchronize());
+    KCK(cudaMemcpy(out, dout, (size_t)n_heads * head_size * sizeof(float), cudaMemcpyDeviceToHost));
+    return L2J_OK;
+}
+
+extern "C" int l2j_k_swiglu(int device, float *hb, const float *hb2, int n)
+{
+    if (!hb || !hb2 || n <= 0)
+        return fail(nullptr, L2J_E_INVALID, "bad arguments");
+    int rc = set_device_checked(device);
+    if (rc != L2J_OK)
+        return rc;
+    Scratch s;
+    float *a = nullptr, *b = nullptr;
+    KCK(s.alloc(&a, n));
+    KCK(s.alloc(&b, n));
+    KCK(cudaMemcpy(a, hb, (size_t)n * sizeof(float), cudaMemcpyHostToDevice));
+    KCK(cudaMemcpy(b, hb2, (size_t)n * sizeof(float), cudaMemcpyHostToDevice));
+    KCK(launch_swiglu_plain(nullptr, a, b, n));
+    KCK(cudaDeviceSynchronize());
+    KCK(cudaMemcpy(hb, a, (size_t)n * sizeof(float), cudaMemcpyDeviceToHost));
+    return L2J_OK;
+}
+
+extern "C" int l2j_k_copy_bandwidth(int device, int64_t bytes, int iters, double *best_gbs)
+{
+    if (bytes <= 0 || iters <= 0 || !best_gbs)
+        return fail(nullptr, L2J_E_INVALID, "bad arguments");
+    int rc = set_device_checked(device);
+    if (rc != L2J_OK)
+        return rc;
+    Scratch s;
+    uint8_t *a = nullptr, *b = nullptr;
+    KCK(s.alloc(&a, bytes, true));
+    KCK(s.alloc(&b, bytes, true));
+    cudaEvent_t e0, e1;
+    KCK(cudaEventCreate(&e0));
+    KCK(cudaEventCreate(&e1));
+    double best = 0.0;
+    for (int i = 0; i < iters + 2; ++i) {
+        cudaEventRecord(e0, nullptr);
+        cudaMemcpyAsync(b, a, (size_t)bytes, cudaMemcpyDeviceToDevice, nullptr);
+        cudaEventRecord(e1, nullptr);
+        cudaEventSynchronize(e1);
+        float ms = 0.f;
+        cudaEventElapsedTime(&ms, e0, e1);
+        if (i >= 2 && ms > 0.f) {
+            const double gbs = 2.0 * (double)bytes / ((double)ms * 1e6);
+            if (gbs > best)
+                best = gbs;
+        }
+    }
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    *best_gbs = best;
+    return L2J_OK;
+}

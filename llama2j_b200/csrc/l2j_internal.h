@@ -1,0 +1,149 @@
+// Host/device shared declarations of libl2j_b200: device-side tensor views, kernel parameter
+// blocks and the launch wrappers the context code calls.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace l2j {
+
+constexpr int kGroup = 256;        // elements per quantisation group
+constexpr int kGroupBytes = 264;   // encoded bytes per group in the file format
+constexpr int kMaxSmemRing = 100 * 1024;  // ring budget per CTA; two kernels must fit on one SM
+
+// Device-resident sequence state, advanced by the kernels themselves so that consecutive tokens
+// can be queued without a host round trip.
+struct SeqState {
+    int cur_token;   // token fed to the forward in flight
+    int cur_pos;     // its position
+    int token;       // token to feed next (greedy loop)
+    int pos;         // next position (greedy loop)
+    int n_prompt;    // forced tokens after BOS
+    int status;      // L2J_DS_* bits
+    int argmax;      // device argmax of the last forward
+    unsigned int cls_counter;   // arrival counter of the classifier's argmax reduction
+};
+
+struct Cmd {
+    int mode;    // 1: feed (token, pos) from the host; 0: continue the device-side greedy loop
+    int token;
+    int pos;
+    int pad;
+};
+
+// One quantised tensor (or the slice of it a context owns) after the upload re-layout:
+// bytes and group headers in separate arrays so that every row starts on a 16-byte boundary.
+struct QTensor {
+    uint8_t *payload = nullptr;   // one byte per element, element e at payload[e - base_float]
+    float2 *hdr = nullptr;        // (min, scale) of group g at hdr[g - base_float/256]
+    int64_t base_float = 0;       // first element held (multiple of 256)
+    int64_t n_groups = 0;         // groups held
+    int64_t groups_received = 0;
+};
+
+enum MvEpilogue {
+    EPI_STORE = 0,      // y[i] = v
+    EPI_QKV_ROPE = 1,   // rotate q/k pairs, write q and the KV cache
+    EPI_RESIDUAL = 2,   // x[i] += v
+    EPI_SWIGLU = 3,     // hb[i] = silu(v1) * v3  (paired W1/W3 rows)
+    EPI_LOGITS = 4      // logits[i] = v, block argmax, grid argmax by the last block
+};
+
+struct MvSeg {
+    const uint8_t *payload;   // u8 payload, or the float rows for FP32 weights
+    const float2 *hdr;
+    int64_t flat0;            // element offset of row 0 relative to payload
+    int rows;
+};
+
+// Parameters of the ring matvec kernel.
+struct MvParams {
+    MvSeg seg[3];
+    int nseg;          // sequential segments (1, or 3 for QKV); paired mode uses seg[0], seg[1]
+    int paired;        // 1: a stage holds RPP rows of seg[0] and the same rows of seg[1]
+    int n;             // row length in elements
+    int rpp;           // rows per pass and half
+    int wpr;           // warps per row
+    int nstage;        // ring depth
+    int slot_bytes;    // bytes per ring slot
+    int hdr_off;       // offset of the header area inside a slot
+    int half_hdr;      // bytes of one half's header area (paired mode)
+    int timeout_polls;
+    // prologue
+    const float *x_in;       // input vector (n floats)
+    const float *rms_w;      // dequantised RMSNorm weights (n floats) or nullptr
+    // epilogue
+    int epilogue;
+    float *y;                // STORE / RESIDUAL / SWIGLU / LOGITS target
+    float *q_out;            // QKV: q (dim)
+    float *k_cache;          // QKV: layer base of the K cache [kv_head][seq][head]
+    float *v_cache;
+    const float *rope_cos;   // [seq][head/2]
+    const float *rope_sin;
+    int dim, kv_dim, head, seq_len;
+    // logits
+    float *blk_val;          // per-block argmax candidates
+    int *blk_idx;
+    const int *prompt;       // device prompt tokens
+    int *out_tokens;
+    SeqState *state;
+};
+
+struct AttnParams {
+    const float *q;          // (n_heads * head)
+    const float *k_cache;    // layer base, [kv_head][seq][head]
+    const float *v_cache;
+    float *out;              // (n_heads * head)
+    float *part;             // scratch: [n_heads][nsplit][head + 2]
+    unsigned int *counters;  // [n_heads], zero between launches
+    SeqState *state;
+    int n_heads, kv_mul, head, seq_len, nsplit, chunk_max;
+    int pos_override;        // >= 0: use this position instead of state->cur_pos (tests)
+};
+
+struct MvPlan {
+    int cpt;       // chunks per thread (template selector)
+    int rpp, wpr;
+    int nstage, slot_bytes, hdr_off, half_hdr;
+    int threads;   // block size including the producer warp
+    int smem_bytes;
+    bool ok;
+};
+
+// Chooses the thread mapping and ring geometry for a row length; ok=false if the ring kernel
+// cannot take the shape (the caller then uses the plain kernels).
+MvPlan plan_matvec(int n, bool f32, bool paired);
+
+// ---- launch wrappers (all asynchronous on `stream`) ---------------------------------------
+struct LaunchCfg {
+    cudaStream_t stream;
+    bool pdl;       // launch with the programmatic-stream-serialization attribute
+    int grid;       // number of blocks for the ring kernels (SM count)
+};
+
+cudaError_t prepare_kernels();
+cudaError_t launch_matvec_ring(const LaunchCfg &lc, const MvPlan &plan, bool f32, const MvParams &p);
+cudaError_t launch_attention(const LaunchCfg &lc, const AttnParams &p);
+cudaError_t launch_begin(const LaunchCfg &lc, SeqState *state, const Cmd *cmd, const float *emb, float *x, int dim,
+                         int vocab, int seq_len, int gather);
+
+// plain (cross-check) kernels
+cudaError_t launch_rmsnorm_plain(cudaStream_t s, const float *x, const float *w, float *out, int n);
+cudaError_t launch_matvec_plain_u8(cudaStream_t s, const MvSeg &seg, int n, const float *x, float *y);
+cudaError_t launch_matvec_plain_f32(cudaStream_t s, const float *w, int n, int d, const float *x, float *y);
+cudaError_t launch_epilogue_plain(cudaStream_t s, const MvParams &p, const float *y0, const float *y1, const float *y2);
+cudaError_t launch_rope_plain(cudaStream_t s, float *q, float *k, const float *cs, const float *sn, int pos, int dim,
+                              int kv_dim, int head);
+cudaError_t launch_swiglu_plain(cudaStream_t s, float *hb, const float *hb2, int n);
+
+// load-time kernels
+cudaError_t launch_repack(cudaStream_t s, const uint8_t *groups, int64_t n_groups, uint8_t *payload, float2 *hdr);
+cudaError_t launch_repack_minmax(cudaStream_t s, const uint8_t *groups, int64_t n_groups, uint8_t *payload, float2 *hdr);
+cudaError_t launch_dequant_rms(cudaStream_t s, const QTensor &t, int64_t first_float, int64_t n, float *out);
+cudaError_t launch_quant_encode(cudaStream_t s, const float *in, int64_t n, uint8_t *out);
+cudaError_t launch_synth_normal(cudaStream_t s, float *out, int64_t n, uint64_t seed, uint32_t stream_id, int64_t start,
+                                float scale);
+cudaError_t launch_kv_relayout(cudaStream_t s, const float *src, float *dst, int n_kv_heads, int head, int seq_len,
+                               int npos);
+
+}  // namespace l2j

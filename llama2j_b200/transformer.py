@@ -1,0 +1,180 @@
+"""Host-side mirror of the reference's CUDA-mode objects over the C ABI.
+
+`Transformer` plays the part of TransformerWeights + RunState + Run.transformerCUDA for one device
+and one contiguous layer range (paths relative to src/main/java/com/lastbot/llama2j/):
+
+  Transformer.upload_quant / upload_f32   TransformerWeights.readAsQuant upload half, :238-350
+  Transformer.forward(token, pos)         Run.transformer(token, pos, Mode.CUDA, ...), Run.java:44-51,315-519
+                                          plus the logits read-back of Run.java:628-632
+  Transformer.generate_greedy             the token loop of Run.java:609-685 with --temp 0.0
+  argmax                                  Sampler.argmax, Sampler.java:46-57
+
+Everything numerical happens in libl2j_b200.so; this module only moves host buffers across the ABI.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import lib as _lib
+from .model_files import ModelConfig, quant_bytes
+
+
+def argmax(logits: np.ndarray) -> int:
+    """First index of the maximum, as Sampler.argmax (Sampler.java:46-57)."""
+    return int(np.argmax(logits))
+
+
+class Transformer:
+    """One device, layers [first_layer, last_layer] of the model (LayerAllocation.java:67-95)."""
+
+    def __init__(self, cfg: ModelConfig, device: int = 0, first_layer: int = 0, last_layer: int | None = None,
+                 flags: int = 0):
+        self.cfg = cfg
+        self.device = device
+        self.first_layer = first_layer
+        self.last_layer = cfg.n_layers - 1 if last_layer is None else last_layer
+        self._lib = _lib.load()
+        self._ctx = C.c_void_p()
+        ccfg = cfg.to_c()
+        rc = self._lib.l2j_create(C.byref(ccfg), device, self.first_layer, self.last_layer, flags, C.byref(self._ctx))
+        _lib.check(rc, None)
+        self._logits = np.zeros(cfg.vocab_size, dtype=np.float32)
+
+    # ---- lifetime -----------------------------------------------------------------------------
+    def close(self) -> None:
+        if self._ctx:
+            self._lib.l2j_destroy(self._ctx)
+            self._ctx = C.c_void_p()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @property
+    def is_first(self) -> bool:
+        return self.first_layer == 0
+
+    @property
+    def is_last(self) -> bool:
+        return self.last_layer == self.cfg.n_layers - 1
+
+    # ---- weights ------------------------------------------------------------------------------
+    def upload_quant(self, tensor: int, groups: np.ndarray, n_floats: int | None = None, float_offset: int = 0) -> None:
+        """`groups`: bytes of the tensor (or of a part starting at `float_offset`) in the group format."""
+        data = np.ascontiguousarray(groups, dtype=np.uint8).reshape(-1)
+        if n_floats is None:
+            n_floats = self.cfg.tensor_floats(tensor) - float_offset
+        if data.size != quant_bytes(n_floats):
+            raise ValueError(f"tensor {tensor}: {data.size} bytes for {n_floats} floats, expected {quant_bytes(n_floats)}")
+        rc = self._lib.l2j_upload_quant(self._ctx, tensor, float_offset, data.ctypes.data, data.size, n_floats)
+        _lib.check(rc, self._ctx)
+
+    def upload_f32(self, tensor: int, values: np.ndarray, float_offset: int = 0) -> None:
+        data = np.ascontiguousarray(values, dtype=np.float32).reshape(-1)
+        rc = self._lib.l2j_upload_f32(self._ctx, tensor, float_offset, data.ctypes.data, data.size)
+        _lib.check(rc, self._ctx)
+
+    def upload_all(self, tensors: dict) -> None:
+        """Uploads a {tensor id: host array} checkpoint (quantised tensors in group format)."""
+        for t in _lib.QUANT_TENSORS:
+            self.upload_quant(t, tensors[t])
+        self.upload_f32(_lib.T_TOKEN_EMBEDDING, tensors[_lib.T_TOKEN_EMBEDDING])
+        if not self.cfg.shared_classifier and self.is_last:
+            self.upload_f32(_lib.T_WCLS, tensors[_lib.T_WCLS])
+
+    def finalize(self) -> None:
+        _lib.check(self._lib.l2j_finalize(self._ctx), self._ctx)
+
+    # ---- forward ------------------------------------------------------------------------------
+    def forward(self, token: int, pos: int, want_logits: bool = True):
+        """One decode step of a whole-model context; returns (logits or None, device argmax)."""
+        am = C.c_int(-1)
+        ptr = self._logits.ctypes.data if want_logits else None
+        rc = self._lib.l2j_forward(self._ctx, int(token), int(pos), ptr, C.byref(am))
+        _lib.check(rc, self._ctx)
+        return (self._logits if want_logits else None), am.value
+
+    def forward_stage(self, token: int, pos: int, x_in: np.ndarray | None = None, want_logits: bool = True):
+        """One step of a pipeline stage; returns x (not last stage) or (logits, argmax) (last stage)."""
+        xin = None
+        if x_in is not None:
+            x_in = np.ascontiguousarray(x_in, dtype=np.float32)
+            xin = x_in.ctypes.data
+        am = C.c_int(-1)
+        if self.is_last:
+            ptr = self._logits.ctypes.data if want_logits else None
+            rc = self._lib.l2j_forward_stage(self._ctx, int(token), int(pos), xin, None, ptr, C.byref(am))
+            _lib.check(rc, self._ctx)
+            return (self._logits if want_logits else None), am.value
+        x_out = np.empty(self.cfg.dim, dtype=np.float32)
+        rc = self._lib.l2j_forward_stage(self._ctx, int(token), int(pos), xin, x_out.ctypes.data, None, None)
+        _lib.check(rc, self._ctx)
+        return x_out
+
+    def generate_greedy(self, prompt, steps: int) -> np.ndarray:
+        """Greedy run loop on the device; element p is the token chosen after position p."""
+        prompt = np.ascontiguousarray(prompt, dtype=np.int32).reshape(-1)
+        out = np.zeros(steps, dtype=np.int32)
+        rc = self._lib.l2j_generate_greedy(self._ctx, prompt.ctypes.data if prompt.size else None, int(prompt.size),
+                                           int(steps), out.ctypes.data)
+        _lib.check(rc, self._ctx)
+        return out
+
+    def last_generate_us(self) -> float:
+        v = C.c_double(0.0)
+        _lib.check(self._lib.l2j_last_generate_us(self._ctx, C.byref(v)), self._ctx)
+        return v.value
+
+    def reset(self) -> None:
+        _lib.check(self._lib.l2j_reset(self._ctx), self._ctx)
+
+    def stats(self) -> _lib.Stats:
+        st = _lib.Stats()
+        _lib.check(self._lib.l2j_get_stats(self._ctx, C.byref(st)), self._ctx)
+        return st
+
+    def launch_mode(self) -> dict:
+        m = self._lib.l2j_launch_mode(self._ctx)
+        return {"graph": bool(m & 1), "pdl": bool(m & 2), "ring": bool(m & 4)}
+
+    def read_buffer(self, which: int, n: int, layer: int = 0, pos: int = 0) -> np.ndarray:
+        out = np.empty(n, dtype=np.float32)
+        _lib.check(self._lib.l2j_read_buffer(self._ctx, which, layer, pos, out.ctypes.data, n), self._ctx)
+        return out
+
+    def device_buffers(self):
+        x, lg = C.c_void_p(), C.c_void_p()
+        _lib.check(self._lib.l2j_device_buffers(self._ctx, C.byref(x), C.byref(lg)), self._ctx)
+        return x.value, lg.value
+
+
+def run_greedy_host_loop(model: Transformer, prompt, steps: int, stop_on_bos: bool = True):
+    """The reference's run loop (Run.java:609-685) with --temp 0.0, one blocking forward per token and
+    the arg-max on the host, exactly what the Java host does through the ABI.  Returns the chosen
+    tokens (forced ones included) and the logits of every step."""
+    prompt = [int(t) for t in prompt]
+    token, pos = 1, 0   # BOS, Run.java:614
+    chosen, all_logits = [], []
+    while pos < steps:
+        logits, _ = model.forward(token, pos)
+        if pos < len(prompt):
+            nxt = prompt[pos]          # Run.java:635-637
+        else:
+            nxt = argmax(logits)       # Run.java:640-642
+        all_logits.append(logits.copy())
+        chosen.append(nxt)
+        pos += 1
+        if stop_on_bos and nxt == 1:   # Run.java:670-672
+            break
+        token = nxt
+    return np.asarray(chosen, dtype=np.int32), np.stack(all_logits) if all_logits else np.zeros((0, model.cfg.vocab_size))

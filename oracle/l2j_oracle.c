@@ -1,0 +1,691 @@
+/*
+ * l2j_oracle.c -- CPU restatement of llama2j's CPU decode path.  TEST INFRASTRUCTURE ONLY.
+ *
+ * This file is the checker the CUDA path is compared against.  It is never linked into,
+ * imported by or called from the product library; only the test-suite, the smoke check and
+ * the CPU-baseline leg of the benchmark load it.
+ *
+ * PARITY UNPINNED: the reference project ships no golden vectors, no known-answer tests and
+ * no fixtures for this path, and it is a Java program that cannot be built where this file is
+ * developed (no JVM).  The restatement is therefore pinned only by the reference's source
+ * formulas (cited per function below, paths relative to the reference's
+ * src/main/java/com/lastbot/llama2j/), by the tolerance round trip of Quant.testEncode
+ * (Quant.java:118-154) and by an independent float64 numpy model in the test-suite.
+ *
+ * Java semantics that are honoured here:
+ *   - every float expression is IEEE binary32 without fused multiply-add (build with
+ *     -ffp-contract=off and without fast-math);
+ *   - every sum is one sequential float accumulator in ascending index order, so the result
+ *     does not depend on the number of threads (threads split output rows / heads only);
+ *   - Math.sqrt/exp/pow/cos/sin are evaluated in double and cast to float;
+ *   - Math.round(float) is floor(x + 1/2) computed without intermediate rounding, NaN -> 0;
+ *   - group headers are big-endian floats, everything else little-endian.
+ *
+ * Also here (not part of the reference): the counter-based synthetic weight generator that the
+ * benchmark and the tests use to make N(0, 0.02^2) checkpoints which are bit-identical on the
+ * CPU and on the GPU.
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+#define L2JO_GROUP 256
+#define L2JO_GROUP_BYTES 264 /* Quant.encodedBytesPerGroup(): 256*8/8 + 8, Quant.java:35-37 */
+
+#define EXPORT __attribute__((visibility("default")))
+
+/* ------------------------------------------------------------------------------------------
+ * helpers
+ * ---------------------------------------------------------------------------------------- */
+
+/* Quant.bytesToFloat, Quant.java:108-114: header floats are big-endian. */
+static inline float be_float(const uint8_t *p)
+{
+    uint32_t v = ((uint32_t)p[0] << 24) | ((uint32_t)p[1] << 16) | ((uint32_t)p[2] << 8) | (uint32_t)p[3];
+    float f;
+    memcpy(&f, &v, 4);
+    return f;
+}
+
+static inline void put_be_float(uint8_t *p, float f)
+{
+    uint32_t v;
+    memcpy(&v, &f, 4);
+    p[0] = (uint8_t)(v >> 24);
+    p[1] = (uint8_t)(v >> 16);
+    p[2] = (uint8_t)(v >> 8);
+    p[3] = (uint8_t)v;
+}
+
+/* Java's Math.round(float): floor(a + 1/2) evaluated exactly, NaN -> 0, saturating to int.
+ * The sum is exact in double for every float a, so no double rounding can occur. */
+static inline int32_t java_round_float(float a)
+{
+    if (a != a)
+        return 0;
+    double r = floor((double)a + 0.5);
+    if (r >= 2147483647.0)
+        return 2147483647;
+    if (r <= -2147483648.0)
+        return (int32_t)(-2147483647 - 1);
+    return (int32_t)r;
+}
+
+EXPORT int l2jo_num_threads(void)
+{
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
+
+EXPORT void l2jo_set_num_threads(int n)
+{
+#ifdef _OPENMP
+    if (n > 0)
+        omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
+/* ------------------------------------------------------------------------------------------
+ * Quant: group format, encode, decode                                    (Quant.java:30-197)
+ * ---------------------------------------------------------------------------------------- */
+
+/* Quant.numberOfBytesByFloatSize, Quant.java:39-48 (64-bit here). */
+EXPORT int64_t l2jo_quant_bytes(int64_t n_floats)
+{
+    int64_t groups = (n_floats + L2JO_GROUP - 1) / L2JO_GROUP;
+    return groups * L2JO_GROUP_BYTES;
+}
+
+/* Quant.encode, Quant.java:156-193.  min/max start at the group's first element and move only
+ * on a strict comparison; padding elements of the last group are ignored for min/max and are
+ * written as byte 0; a constant group gives 0/0 = NaN, Math.round(NaN) = 0. */
+EXPORT void l2jo_quant_encode(const float *in, int64_t n, uint8_t *out)
+{
+    int64_t groups = (n + L2JO_GROUP - 1) / L2JO_GROUP;
+#pragma omp parallel for schedule(static)
+    for (int64_t g = 0; g < groups; g++) {
+        int64_t i = g * L2JO_GROUP;
+        float mn = in[i];
+        float mx = mn;
+        for (int j = 1; j < L2JO_GROUP; j++) {
+            if (i + j < n) {
+                float v = in[i + j];
+                if (v < mn)
+                    mn = v;
+                if (v > mx)
+                    mx = v;
+            }
+        }
+        float range = mx - mn;
+        uint8_t *o = out + g * L2JO_GROUP_BYTES;
+        put_be_float(o, mn);
+        put_be_float(o + 4, mx);
+        for (int j = 0; j < L2JO_GROUP; j++) {
+            if (i + j < n) {
+                float t = in[i + j] - mn;
+                t = t / range;
+                t = t * 255.0f;
+                o[8 + j] = (uint8_t)(java_round_float(t) & 0xff);
+            } else {
+                o[8 + j] = 0;
+            }
+        }
+    }
+}
+
+/* Quant.decode, Quant.java:79-106: value = byte / 255f * range + min. */
+EXPORT void l2jo_quant_decode(const uint8_t *enc, int64_t float_index, int64_t size, float *out)
+{
+    for (int64_t k = 0; k < size; k++) {
+        int64_t idx = float_index + k;
+        int64_t g = idx / L2JO_GROUP;
+        const uint8_t *p = enc + g * L2JO_GROUP_BYTES;
+        float mn = be_float(p), mx = be_float(p + 4);
+        float range = mx - mn;
+        float b = (float)p[8 + (idx % L2JO_GROUP)];
+        float v = b / 255.0f;
+        v = v * range;
+        v = v + mn;
+        out[k] = v;
+    }
+}
+
+/* Quant.testEncode's acceptance rule (Quant.java:118-154): counts the elements whose decoded
+ * value is off by more than 1 % relative AND more than 1e-2 absolute. */
+EXPORT int64_t l2jo_quant_roundtrip_violations(const float *in, int64_t n)
+{
+    uint8_t *enc = (uint8_t *)malloc((size_t)l2jo_quant_bytes(n));
+    float *dec = (float *)malloc((size_t)n * sizeof(float));
+    l2jo_quant_encode(in, n, enc);
+    l2jo_quant_decode(enc, 0, n, dec);
+    int64_t bad = 0;
+    for (int64_t i = 0; i < n; i++) {
+        float diff = fabsf(in[i] - dec[i]);
+        double rel = (double)diff / (double)fabsf(in[i]);
+        if (rel > 0.01 && diff > 1e-2)
+            bad++;
+    }
+    free(enc);
+    free(dec);
+    return bad;
+}
+
+/* ------------------------------------------------------------------------------------------
+ * Per-op restatements (static CPU call() of each kernel class)
+ * ---------------------------------------------------------------------------------------- */
+
+/* RootMeanSquare.call, kernel/RootMeanSquare.java:25-35. */
+EXPORT void l2jo_rms(float *sum, const float *x, int size)
+{
+    float ss = 0.0f;
+    for (int j = 0; j < size; j++) {
+        float p = x[j] * x[j];
+        ss = ss + p;
+    }
+    ss = ss / (float)size;
+    ss = ss + 1e-5f;
+    ss = 1.0f / (float)sqrt((double)ss);
+    sum[0] = ss;
+}
+
+/* WeightNormalizeAndScale.callI8, kernel/WeightNormalizeAndScale.java:40-77:
+ * value = byte / 255f * range + min;  out = value * (ss * x).  out may alias x. */
+EXPORT void l2jo_weight_normalize_i8(float *out, const float *x, const uint8_t *enc, int64_t weight_index,
+                                     const float *sum_of_squares, int size)
+{
+    float ss = sum_of_squares[0];
+    for (int k = 0; k < size; k++) {
+        int64_t idx = weight_index + k;
+        const uint8_t *p = enc + (idx / L2JO_GROUP) * L2JO_GROUP_BYTES;
+        float mn = be_float(p), mx = be_float(p + 4);
+        float range = mx - mn;
+        float v = (float)p[8 + (idx % L2JO_GROUP)] / 255.0f;
+        v = v * range;
+        v = v + mn;
+        float sx = ss * x[k];
+        out[k] = v * sx;
+    }
+}
+
+/* MatMul.callI8 (both the group-aligned and the straddling variant perform the same
+ * arithmetic in the same order), kernel/MatMul.java:78-212:
+ * rangeMultiplier = (max - min) / 255f;  val += (byte * rangeMultiplier + min) * x[j]. */
+EXPORT void l2jo_matmul_i8(float *xout, const float *x, const uint8_t *enc, int64_t weight_index, int n, int d)
+{
+#pragma omp parallel for schedule(static)
+    for (int i = 0; i < d; i++) {
+        int64_t pos = weight_index + (int64_t)i * n;
+        float val = 0.0f;
+        int j = 0;
+        while (j < n) {
+            int64_t g = (pos + j) / L2JO_GROUP;
+            int off = (int)((pos + j) % L2JO_GROUP);
+            const uint8_t *p = enc + g * L2JO_GROUP_BYTES;
+            float mn = be_float(p), mx = be_float(p + 4);
+            float rm = (mx - mn) / 255.0f;
+            int lim = L2JO_GROUP - off;
+            if (lim > n - j)
+                lim = n - j;
+            const uint8_t *b = p + 8 + off;
+            for (int t = 0; t < lim; t++) {
+                float w = (float)b[t] * rm;
+                w = w + mn;
+                float pr = w * x[j + t];
+                val = val + pr;
+            }
+            j += lim;
+        }
+        xout[i] = val;
+    }
+}
+
+/* MatMul.callFP32, kernel/MatMul.java:29-60 (classifier). */
+EXPORT void l2jo_matmul_f32(float *xout, const float *x, const float *w, int64_t weight_index, int n, int d)
+{
+#pragma omp parallel for schedule(static)
+    for (int i = 0; i < d; i++) {
+        const float *row = w + weight_index + (int64_t)i * n;
+        float val = 0.0f;
+        for (int j = 0; j < n; j++) {
+            float pr = row[j] * x[j];
+            val = val + pr;
+        }
+        xout[i] = val;
+    }
+}
+
+/* ApplyRope.init + call, kernel/ApplyRope.java:34-92.  The reference precomputes a
+ * (pos, i/2) table; the entries are recomputed here with the same expressions. */
+static inline void rope_cs(int i, int pos, int head_size, float *c, float *s)
+{
+    int head_dim = i % head_size;
+    float e = (float)head_dim / (float)head_size;
+    float freq = (float)(1.0 / pow((double)10000.0f, (double)e));
+    float val = (float)pos * freq;
+    *c = (float)cos((double)val);
+    *s = (float)sin((double)val);
+}
+
+EXPORT void l2jo_rope(float *q, float *k, int pos, int dim, int kv_dim, int head_size)
+{
+    for (int i = 0; i < dim; i += 2) {
+        float fcr, fci;
+        rope_cs(i, pos, head_size, &fcr, &fci);
+        float v0 = q[i], v1 = q[i + 1];
+        float a = v0 * fcr, b = v1 * fci;
+        q[i] = a - b;
+        a = v0 * fci;
+        b = v1 * fcr;
+        q[i + 1] = a + b;
+    }
+    for (int i = 0; i < kv_dim; i += 2) {
+        float fcr, fci;
+        rope_cs(i, pos, head_size, &fcr, &fci);
+        float v0 = k[i], v1 = k[i + 1];
+        float a = v0 * fcr, b = v1 * fci;
+        k[i] = a - b;
+        a = v0 * fci;
+        b = v1 * fcr;
+        k[i + 1] = a + b;
+    }
+}
+
+/* AttentionLoop.call, kernel/AttentionLoop.java:29-54.  Besides the scores it keeps the
+ * running maximum of the element-wise products q_i*k_i in max_slot (never reset by the
+ * reference between layers or tokens). */
+EXPORT void l2jo_attention_scores(const float *q, const float *key_cache, float *att, float *max_slot, int64_t keybase,
+                                  int kv_dim, int pos, int head_size)
+{
+    float head_max = -3.4028234663852886e38f;
+    float scale = (float)sqrt((double)head_size);
+    for (int t = 0; t <= pos; t++) {
+        const float *k = key_cache + keybase + (int64_t)t * kv_dim;
+        float score = 0.0f;
+        for (int i = 0; i < head_size; i++) {
+            float value = q[i] * k[i];
+            score = score + value;
+            head_max = fmaxf(head_max, value);
+        }
+        att[t] = score / scale;
+        if (max_slot)
+            *max_slot = fmaxf(*max_slot, head_max);
+    }
+}
+
+/* ExpSumNormalize.call, kernel/ExpSumNormalize.java:25-38. */
+EXPORT void l2jo_exp_sum_normalize(float *x, float max_val, int size)
+{
+    float sum = 0.0f;
+    for (int i = 0; i < size; i++) {
+        x[i] = (float)exp((double)(x[i] - max_val));
+        sum = sum + x[i];
+    }
+    if (sum != 0.0f) {
+        for (int i = 0; i < size; i++)
+            x[i] = x[i] / sum;
+    }
+}
+
+/* AccumWeightedValue.call, kernel/AccumWeightedValue.java:40-88 (the unrolled and the plain
+ * variant have the same per-element order). */
+EXPORT void l2jo_accum_weighted_value(float *xb, const float *att, const float *value_cache, int pos, int64_t valuebase,
+                                      int head_size, int kv_dim)
+{
+    for (int i = 0; i < head_size; i++)
+        xb[i] = 0.0f;
+    for (int t = 0; t <= pos; t++) {
+        float a = att[t];
+        const float *v = value_cache + valuebase + (int64_t)t * kv_dim;
+        for (int i = 0; i < head_size; i++) {
+            float pr = a * v[i];
+            xb[i] = xb[i] + pr;
+        }
+    }
+}
+
+/* Accum.call, kernel/Accum.java:26-30. */
+EXPORT void l2jo_accum(float *a, const float *b, int size)
+{
+    for (int i = 0; i < size; i++)
+        a[i] = a[i] + b[i];
+}
+
+/* Silu, kernel/Silu.java:41-78.  Mode 0 ("lookup") is the CPU path with its 8192-entry
+ * sigmoid table whose index multiplier is the integer 8192/10 = 819; mode 1 ("exact") is a
+ * correctly rounded sigmoid combined in the order of the reference's CUDA kernel
+ * (kernel/Silu.java:122-132: (value * sigmoid) * hb2). */
+static float g_silu_table[8192];
+static int g_silu_table_ready = 0;
+
+static void silu_table_init(void)
+{
+    if (g_silu_table_ready)
+        return;
+    for (int i = 0; i < 8192; i++) {
+        double val = ((double)i / 8192.0) * 10.0 - 5.0;
+        g_silu_table[i] = (float)(1.0 / (1.0 + exp(-val)));
+    }
+    g_silu_table_ready = 1;
+}
+
+static inline float sigmoid_exact(float v)
+{
+    return (float)(1.0 / (1.0 + exp(-(double)v)));
+}
+
+static inline float sigmoid_lookup(float v)
+{
+    float position = (v + 5.0f) * 819.0f;
+    int index = (int)position;
+    if (position > 0.0f && position < 8191.0f) {
+        float lo = g_silu_table[index];
+        float frac = position - (float)index;
+        float d = g_silu_table[index + 1] - lo;
+        float t = frac * d;
+        return lo + t;
+    }
+    return sigmoid_exact(v);
+}
+
+EXPORT void l2jo_silu(float *hb, const float *hb2, int hidden_dim, int mode)
+{
+    if (mode == 0) {
+        silu_table_init();
+        for (int i = 0; i < hidden_dim; i++) {
+            float g = sigmoid_lookup(hb[i]) * hb2[i];
+            hb[i] = hb[i] * g;
+        }
+    } else {
+        for (int i = 0; i < hidden_dim; i++) {
+            float g = hb[i] * sigmoid_exact(hb[i]);
+            hb[i] = g * hb2[i];
+        }
+    }
+}
+
+/* Sampler.argmax, Sampler.java:46-57: the first maximum wins. */
+EXPORT int l2jo_argmax(const float *logits, int n)
+{
+    int max_i = 0;
+    float max_p = logits[0];
+    for (int i = 1; i < n; i++) {
+        if (logits[i] > max_p) {
+            max_i = i;
+            max_p = logits[i];
+        }
+    }
+    return max_i;
+}
+
+/* ------------------------------------------------------------------------------------------
+ * The forward pass                                   (Run.transformerCPU, Run.java:62-169)
+ * ---------------------------------------------------------------------------------------- */
+
+enum {
+    T_EMB = 0, T_RMS_ATT, T_WQ, T_WK, T_WV, T_WO, T_RMS_FFN, T_W1, T_W2, T_W3, T_RMS_FINAL, T_WCLS, T_COUNT
+};
+
+typedef struct {
+    int dim, hidden_dim, n_layers, n_heads, n_kv_heads, vocab_size, seq_len;
+    int silu_mode;    /* 0 lookup (CPU-faithful), 1 exact (CUDA-faithful order) */
+    int softmax_mode; /* 0 reference running max of products, 1 true maximum of the scores */
+    const void *w[T_COUNT];
+    /* run state, RunState.java:19-36 */
+    float *x, *xb, *xb2, *hb, *hb2, *q, *k, *v, *att, *logits, *tmp1;
+    float *key_cache, *value_cache;
+} l2jo_model;
+
+EXPORT l2jo_model *l2jo_model_create(int dim, int hidden_dim, int n_layers, int n_heads, int n_kv_heads, int vocab_size,
+                                     int seq_len, int silu_mode, int softmax_mode)
+{
+    l2jo_model *m = (l2jo_model *)calloc(1, sizeof(l2jo_model));
+    m->dim = dim;
+    m->hidden_dim = hidden_dim;
+    m->n_layers = n_layers;
+    m->n_heads = n_heads;
+    m->n_kv_heads = n_kv_heads;
+    m->vocab_size = vocab_size;
+    m->seq_len = seq_len;
+    m->silu_mode = silu_mode;
+    m->softmax_mode = softmax_mode;
+    int kv_dim = dim * n_kv_heads / n_heads;
+    int tmp = (dim > vocab_size ? dim : vocab_size);
+    m->x = (float *)calloc((size_t)dim, 4);
+    m->xb = (float *)calloc((size_t)dim, 4);
+    m->xb2 = (float *)calloc((size_t)dim, 4);
+    m->hb = (float *)calloc((size_t)hidden_dim, 4);
+    m->hb2 = (float *)calloc((size_t)hidden_dim, 4);
+    m->q = (float *)calloc((size_t)dim, 4);
+    m->k = (float *)calloc((size_t)kv_dim, 4);
+    m->v = (float *)calloc((size_t)kv_dim, 4);
+    m->att = (float *)calloc((size_t)n_heads * seq_len, 4);
+    m->logits = (float *)calloc((size_t)vocab_size, 4);
+    m->tmp1 = (float *)calloc((size_t)tmp, 4); /* Java arrays start at zero, RunState.java:86-87 */
+    m->key_cache = (float *)calloc((size_t)n_layers * seq_len * kv_dim, 4);
+    m->value_cache = (float *)calloc((size_t)n_layers * seq_len * kv_dim, 4);
+    silu_table_init();
+    return m;
+}
+
+EXPORT void l2jo_model_set_tensor(l2jo_model *m, int id, const void *data)
+{
+    if (id >= 0 && id < T_COUNT)
+        m->w[id] = data;
+}
+
+EXPORT void l2jo_model_reset(l2jo_model *m)
+{
+    int tmp = (m->dim > m->vocab_size ? m->dim : m->vocab_size);
+    memset(m->tmp1, 0, (size_t)tmp * 4);
+}
+
+EXPORT void l2jo_model_destroy(l2jo_model *m)
+{
+    if (!m)
+        return;
+    free(m->x); free(m->xb); free(m->xb2); free(m->hb); free(m->hb2); free(m->q); free(m->k); free(m->v);
+    free(m->att); free(m->logits); free(m->tmp1); free(m->key_cache); free(m->value_cache);
+    free(m);
+}
+
+EXPORT const float *l2jo_model_buffer(l2jo_model *m, int which)
+{
+    switch (which) {
+    case 0: return m->x;
+    case 1: return m->xb;
+    case 2: return m->q;
+    case 3: return m->k;
+    case 4: return m->v;
+    case 5: return m->hb;
+    case 6: return m->key_cache;
+    case 7: return m->value_cache;
+    case 8: return m->logits;
+    default: return 0;
+    }
+}
+
+EXPORT void l2jo_model_forward(l2jo_model *m, int token, int pos, float *logits_out)
+{
+    const int dim = m->dim;
+    const int kv_dim = dim * m->n_kv_heads / m->n_heads;
+    const int kv_mul = m->n_heads / m->n_kv_heads;
+    const int hidden_dim = m->hidden_dim;
+    const int head_size = dim / m->n_heads;
+    const uint8_t *rms_att = (const uint8_t *)m->w[T_RMS_ATT], *rms_ffn = (const uint8_t *)m->w[T_RMS_FFN];
+    const uint8_t *wq = (const uint8_t *)m->w[T_WQ], *wk = (const uint8_t *)m->w[T_WK], *wv = (const uint8_t *)m->w[T_WV];
+    const uint8_t *wo = (const uint8_t *)m->w[T_WO], *w1 = (const uint8_t *)m->w[T_W1], *w2 = (const uint8_t *)m->w[T_W2];
+    const uint8_t *w3 = (const uint8_t *)m->w[T_W3], *rms_final = (const uint8_t *)m->w[T_RMS_FINAL];
+    const float *emb = (const float *)m->w[T_EMB];
+    const float *wcls = (const float *)(m->w[T_WCLS] ? m->w[T_WCLS] : m->w[T_EMB]);
+
+    /* Run.java:72 */
+    memcpy(m->x, emb + (int64_t)token * dim, (size_t)dim * 4);
+
+    for (int l = 0; l < m->n_layers; l++) {
+        /* Run.java:78-80 */
+        l2jo_rms(m->tmp1, m->x, dim);
+        l2jo_weight_normalize_i8(m->xb, m->x, rms_att, (int64_t)l * dim, m->tmp1, dim);
+        /* Run.java:83-85 */
+        l2jo_matmul_i8(m->q, m->xb, wq, (int64_t)l * dim * dim, dim, dim);
+        l2jo_matmul_i8(m->k, m->xb, wk, (int64_t)l * dim * kv_dim, dim, kv_dim);
+        l2jo_matmul_i8(m->v, m->xb, wv, (int64_t)l * dim * kv_dim, dim, kv_dim);
+        /* Run.java:88 */
+        l2jo_rope(m->q, m->k, pos, dim, kv_dim, head_size);
+        /* Run.java:91-99 */
+        int64_t loff = (int64_t)l * m->seq_len * kv_dim;
+        memcpy(m->key_cache + loff + (int64_t)pos * kv_dim, m->k, (size_t)kv_dim * 4);
+        memcpy(m->value_cache + loff + (int64_t)pos * kv_dim, m->v, (size_t)kv_dim * 4);
+        /* Run.java:102-133; heads are independent (each owns att[h,:], tmp1[h], xb[h,:]) */
+#pragma omp parallel for schedule(static)
+        for (int h = 0; h < m->n_heads; h++) {
+            float *att = m->att + (int64_t)h * m->seq_len;
+            int64_t base = loff + (int64_t)(h / kv_mul) * head_size;
+            l2jo_attention_scores(m->q + h * head_size, m->key_cache, att, &m->tmp1[h], base, kv_dim, pos, head_size);
+            float shift = m->tmp1[h];
+            if (m->softmax_mode == 1) {
+                shift = att[0];
+                for (int t = 1; t <= pos; t++)
+                    if (att[t] > shift)
+                        shift = att[t];
+            }
+            l2jo_exp_sum_normalize(att, shift, pos + 1);
+            l2jo_accum_weighted_value(m->xb + h * head_size, att, m->value_cache, pos, base, head_size, kv_dim);
+        }
+        /* Run.java:136-138 */
+        l2jo_matmul_i8(m->xb2, m->xb, wo, (int64_t)l * dim * dim, dim, dim);
+        l2jo_accum(m->x, m->xb2, dim);
+        /* Run.java:144-145 */
+        l2jo_rms(m->tmp1, m->x, dim);
+        l2jo_weight_normalize_i8(m->xb, m->x, rms_ffn, (int64_t)l * dim, m->tmp1, dim);
+        /* Run.java:149-154 */
+        l2jo_matmul_i8(m->hb, m->xb, w1, (int64_t)l * dim * hidden_dim, dim, hidden_dim);
+        l2jo_matmul_i8(m->hb2, m->xb, w3, (int64_t)l * dim * hidden_dim, dim, hidden_dim);
+        l2jo_silu(m->hb, m->hb2, hidden_dim, m->silu_mode);
+        /* Run.java:157-160 */
+        l2jo_matmul_i8(m->xb, m->hb, w2, (int64_t)l * dim * hidden_dim, hidden_dim, dim);
+        l2jo_accum(m->x, m->xb, dim);
+    }
+    /* Run.java:164-168 */
+    l2jo_rms(m->tmp1, m->x, dim);
+    l2jo_weight_normalize_i8(m->x, m->x, rms_final, 0, m->tmp1, dim);
+    l2jo_matmul_f32(m->logits, m->x, wcls, 0, dim, m->vocab_size);
+    if (logits_out)
+        memcpy(logits_out, m->logits, (size_t)m->vocab_size * 4);
+}
+
+/* ------------------------------------------------------------------------------------------
+ * Synthetic weights (not from the reference): counter-based N(0,1) * scale.
+ *
+ * Element `index` of stream `stream` under `seed` is a pure function of (seed, stream, index):
+ *   key = mix64(seed ^ (0xA0761D6478BD642F * (stream + 1)))
+ *   h   = mix64(key + index * 0x9E3779B97F4A7C15)          (mix64 = splitmix64 finaliser)
+ *   k1  = h >> 40 (24 bits), k2 = (h >> 16) & 0xFFFFFF (24 bits)
+ *   u1  = (k1 + 1) / 2^24 in (0, 1],  u2 = k2 / 2^24 in [0, 1)
+ *   z   = sqrt(-2 ln u1) * cos(2 pi u2),  value = z * scale
+ * ln and cos are evaluated with the fixed float polynomials below, built from correctly rounded
+ * operations only (+, -, *, /, sqrt, fma), so a GPU that follows the same recipe produces the
+ * same bits.
+ * ---------------------------------------------------------------------------------------- */
+
+static inline uint64_t mix64(uint64_t z)
+{
+    z ^= z >> 30;
+    z *= 0xBF58476D1CE4E5B9ULL;
+    z ^= z >> 27;
+    z *= 0x94D049BB133111EBULL;
+    z ^= z >> 31;
+    return z;
+}
+
+static inline float synth_ln_u(uint32_t k /* 1..2^24, u = k / 2^24 */)
+{
+    int p = 31 - __builtin_clz(k);
+    float m = (float)k * (1.0f / (float)(1u << p)); /* exact: in [1, 2) */
+    if (m > 1.41421356f) {
+        m = m * 0.5f;
+        p += 1;
+    }
+    float s = (m - 1.0f) / (m + 1.0f);
+    float s2 = s * s;
+    float t = fmaf(s2, 0.11111111f, 0.14285715f);
+    t = fmaf(s2, t, 0.2f);
+    t = fmaf(s2, t, 0.33333334f);
+    t = fmaf(s2, t, 1.0f);
+    float poly = (2.0f * s) * t;
+    return fmaf((float)(p - 24), 0.69314718f, poly);
+}
+
+static inline float synth_cos_2pi(uint32_t k2 /* 24 bits, u2 = k2 / 2^24 */)
+{
+    uint32_t oct = k2 >> 21;
+    float f = (float)(k2 & 0x1FFFFFu) * (1.0f / 2097152.0f); /* exact, in [0, 1) */
+    if (oct & 1u)
+        f = 1.0f - f;                /* exact */
+    float phi = f * 0.78539816f;     /* in [0, pi/4] */
+    float p2 = phi * phi;
+    float c = fmaf(p2, -2.7557319e-7f, 2.4801587e-5f);
+    c = fmaf(p2, c, -1.3888889e-3f);
+    c = fmaf(p2, c, 4.1666668e-2f);
+    c = fmaf(p2, c, -0.5f);
+    c = fmaf(p2, c, 1.0f);
+    float s = fmaf(p2, 2.7557319e-6f, -1.9841270e-4f);
+    s = fmaf(p2, s, 8.3333338e-3f);
+    s = fmaf(p2, s, -0.16666667f);
+    s = fmaf(p2, s, 1.0f);
+    s = phi * s;
+    switch (oct) {
+    case 0: return c;
+    case 1: return s;
+    case 2: return -s;
+    case 3: return -c;
+    case 4: return -c;
+    case 5: return -s;
+    case 6: return s;
+    default: return c;
+    }
+}
+
+static inline float synth_normal(uint64_t key, uint64_t index)
+{
+    uint64_t h = mix64(key + index * 0x9E3779B97F4A7C15ULL);
+    uint32_t k1 = (uint32_t)(h >> 40);
+    uint32_t k2 = (uint32_t)(h >> 16) & 0xFFFFFFu;
+    float ln = synth_ln_u(k1 + 1u);
+    float r = sqrtf(-2.0f * ln);
+    float c = synth_cos_2pi(k2);
+    return r * c;
+}
+
+EXPORT void l2jo_synth_normal(float *out, int64_t n, uint64_t seed, uint32_t stream, int64_t start, float scale)
+{
+    uint64_t key = mix64(seed ^ (0xA0761D6478BD642FULL * ((uint64_t)stream + 1ULL)));
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < n; i++) {
+        float z = synth_normal(key, (uint64_t)(start + i));
+        out[i] = z * scale;
+    }
+}
+
+/* Generates a tensor chunk by chunk and quantises it straight into the group format, so that
+ * a 7B-sized tensor never exists in FP32 on the host.  n must be a multiple of the group size
+ * unless the call covers the tail of the tensor. */
+EXPORT void l2jo_synth_quant(uint8_t *out, int64_t n, uint64_t seed, uint32_t stream, float scale)
+{
+    const int64_t chunk = (int64_t)L2JO_GROUP * 4096;
+    float *buf = (float *)malloc((size_t)chunk * sizeof(float));
+    for (int64_t s = 0; s < n; s += chunk) {
+        int64_t len = (n - s < chunk) ? (n - s) : chunk;
+        l2jo_synth_normal(buf, len, seed, stream, s, scale);
+        l2jo_quant_encode(buf, len, out + (s / L2JO_GROUP) * L2JO_GROUP_BYTES);
+    }
+    free(buf);
+}
