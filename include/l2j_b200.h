@@ -23,6 +23,13 @@
 extern "C" {
 #endif
 
+/* Exported from the shared object (it is built with hidden default visibility). */
+#if defined(__GNUC__)
+#define L2J_API __attribute__((visibility("default")))
+#else
+#define L2J_API
+#endif
+
 #define L2J_OK 0
 #define L2J_E_INVALID (-1)   /* bad argument, unsupported shape, wrong size */
 #define L2J_E_CUDA (-2)      /* a CUDA runtime call failed */
@@ -94,14 +101,14 @@ typedef struct l2j_stats {
  * the classifier (Run.java:514-518) and the greedy pick (Sampler.java:46-57).
  * Replaces ContextCUDA's constructor (ContextCUDA.java:75-100) and RunState's device half
  * (RunState.java:107-166). */
-int l2j_create(const l2j_config *cfg, int device, int first_layer, int last_layer, uint32_t flags, l2j_ctx **out);
+L2J_API int l2j_create(const l2j_config *cfg, int device, int first_layer, int last_layer, uint32_t flags, l2j_ctx **out);
 
 /* ContextCUDA.close(), ContextCUDA.java:311-323. */
-void l2j_destroy(l2j_ctx *ctx);
+L2J_API void l2j_destroy(l2j_ctx *ctx);
 
 /* Message of the most recent failure on this context ("" if none).  ctx may be NULL for a
  * failure of l2j_create. */
-const char *l2j_last_error(const l2j_ctx *ctx);
+L2J_API const char *l2j_last_error(const l2j_ctx *ctx);
 
 /* ---- weights ------------------------------------------------------------------------------- */
 
@@ -112,113 +119,120 @@ const char *l2j_last_error(const l2j_ctx *ctx);
  * the context's layer range are ignored, parts that overlap it are clipped.  Replaces
  * ContextCUDA.allocateQuantAndCopyToDevice (ContextCUDA.java:138-158) and the SPLIT_TO_LAYERS /
  * LAST_DEVICE_ONLY policies (TransformerWeights.java:238-350).  Thread-safe per context. */
-int l2j_upload_quant(l2j_ctx *ctx, int tensor, int64_t float_offset, const void *groups, int64_t bytes,
+L2J_API int l2j_upload_quant(l2j_ctx *ctx, int tensor, int64_t float_offset, const void *groups, int64_t bytes,
                      int64_t n_floats);
 
 /* Uploads (part of) an FP32 tensor: the embedding table or the unshared classifier
  * (TransformerWeights.java:119-135). */
-int l2j_upload_f32(l2j_ctx *ctx, int tensor, int64_t float_offset, const float *data, int64_t n_floats);
+L2J_API int l2j_upload_f32(l2j_ctx *ctx, int tensor, int64_t float_offset, const float *data, int64_t n_floats);
 
 /* Checks that every tensor the layer range needs has arrived, builds the derived tables and
  * captures the per-token graph.  Must follow the uploads and precede the first forward. */
-int l2j_finalize(l2j_ctx *ctx);
+L2J_API int l2j_finalize(l2j_ctx *ctx);
 
 /* ---- per-token forward --------------------------------------------------------------------- */
 
 /* One decode step: Run.transformerCUDA(token, pos, ...) (Run.java:315-519) followed by the
  * logits read-back of the run loop (Run.java:628-632).  For a context that holds the whole model.
  * `logits` (vocab floats) and `argmax` may each be NULL.  Blocks until the results are on the host. */
-int l2j_forward(l2j_ctx *ctx, int token, int pos, float *logits, int *argmax);
+L2J_API int l2j_forward(l2j_ctx *ctx, int token, int pos, float *logits, int *argmax);
 
 /* The same step for one stage of a layer split.  A first stage takes `token`; later stages take
  * the activation vector x (dim floats, host memory) that the previous stage returned, the hand-off
  * of Run.java:368-413.  A stage that is not the last writes its x to `x_out`; the last stage fills
  * `logits` / `argmax`.  Unused pointers may be NULL. */
-int l2j_forward_stage(l2j_ctx *ctx, int token, int pos, const float *x_in, float *x_out, float *logits, int *argmax);
+L2J_API int l2j_forward_stage(l2j_ctx *ctx, int token, int pos, const float *x_in, float *x_out, float *logits, int *argmax);
 
 /* Device addresses of the stage's activation vector x (dim floats) and of its logits, for callers
  * that move them with their own device-to-device transport. */
-int l2j_device_buffers(l2j_ctx *ctx, void **x_dev, void **logits_dev);
+L2J_API int l2j_device_buffers(l2j_ctx *ctx, void **x_dev, void **logits_dev);
 
 /* The stage step without host copies: enqueues the kernels on the context's stream and returns.
  * x must already be in the device buffer (or token given for a first stage). */
-int l2j_forward_stage_async(l2j_ctx *ctx, int token, int pos);
+L2J_API int l2j_forward_stage_async(l2j_ctx *ctx, int token, int pos);
 
 /* Waits for the context's stream and returns L2J_E_DEVICE if a kernel raised a status bit. */
-int l2j_sync(l2j_ctx *ctx);
+L2J_API int l2j_sync(l2j_ctx *ctx);
 
 /* The run loop of Run.java:609-685 with greedy selection, kept on the device: position 0 is fed
  * BOS (token 1), positions 1..n_prompt are fed the prompt, later positions the previous argmax.
  * `out_tokens[p]` receives the token chosen after position p (the forced prompt token while the
  * prompt lasts), for p in [0, steps).  No host round trip between tokens; the early stop on a
  * sampled BOS (Run.java:670-672) is left to the caller, who truncates. */
-int l2j_generate_greedy(l2j_ctx *ctx, const int32_t *prompt, int n_prompt, int steps, int32_t *out_tokens);
+L2J_API int l2j_generate_greedy(l2j_ctx *ctx, const int32_t *prompt, int n_prompt, int steps, int32_t *out_tokens);
 
 /* Clears the KV cache position bookkeeping and the statistics (a new sequence). */
-int l2j_reset(l2j_ctx *ctx);
+L2J_API int l2j_reset(l2j_ctx *ctx);
 
-int l2j_get_stats(l2j_ctx *ctx, l2j_stats *out);
+L2J_API int l2j_get_stats(l2j_ctx *ctx, l2j_stats *out);
 
 /* How the per-token work is issued: bit 0 CUDA graph replay, bit 1 programmatic dependent launch
  * between kernels, bit 2 the bulk-copy ring kernels (else the plain kernels).  The reference issues
  * every kernel with its own cuLaunchKernel (kernel/MatMul.java:338-354). */
-int l2j_launch_mode(l2j_ctx *ctx);
+L2J_API int l2j_launch_mode(l2j_ctx *ctx);
 
 /* Reads a run-state buffer after a forward, the device half of RunState.java:38-50, for
  * stage-by-stage comparison in the spirit of the reference's TEST mode (Run.java:186-303):
  * which = 0 x, 1 attention output xb, 2 q, 3 hb, 4 logits (layer/pos ignored);
  * 5 K row, 6 V row of (layer, pos) in the reference's (kv_dim) order, n must be kv_dim. */
-int l2j_read_buffer(l2j_ctx *ctx, int which, int layer, int pos, float *out, int n);
+L2J_API int l2j_read_buffer(l2j_ctx *ctx, int which, int layer, int pos, float *out, int n);
 
 /* Average device time in microseconds of the last l2j_generate_greedy call per forward, measured
  * with CUDA events on the context's stream. */
-int l2j_last_generate_us(l2j_ctx *ctx, double *total_us);
+L2J_API int l2j_last_generate_us(l2j_ctx *ctx, double *total_us);
+
+/* Measurement aid (the reference only prints tok/s, Run.java:703-706): average device time in
+ * microseconds of one launch of each kernel of a layer at position `pos`, timed with CUDA events on
+ * the context's stream over `reps` sweeps through all layers (so consecutive launches never re-read
+ * the same weights).  us[0..5] = QKV+RoPE, attention, Wo+residual, W1/W3+SwiGLU, W2+residual,
+ * classifier+argmax.  Leaves the sequence state undefined: call l2j_reset afterwards. */
+L2J_API int l2j_time_kernels(l2j_ctx *ctx, int pos, int reps, double *us);
 
 /* ---- load-time helpers on the device ------------------------------------------------------- */
 
 /* Quant.encode (Quant.java:156-193) on the device, bit-exact: `in` host floats -> `out` host
  * bytes (ceil(n/256)*264).  `device` selects the GPU. */
-int l2j_quant_encode(int device, const float *in, int64_t n_floats, void *out);
+L2J_API int l2j_quant_encode(int device, const float *in, int64_t n_floats, void *out);
 
 /* Synthetic checkpoint tensors (no counterpart in the reference, which loads real checkpoints):
  * element i of stream `stream` is a counter-based N(0,1) draw times `scale`.  The f32 form writes
  * host floats; the quant form generates and encodes on the device and writes the group format. */
-int l2j_synth_f32(int device, uint64_t seed, uint32_t stream, int64_t start, int64_t n_floats, float scale,
+L2J_API int l2j_synth_f32(int device, uint64_t seed, uint32_t stream, int64_t start, int64_t n_floats, float scale,
                   float *out);
-int l2j_synth_quant(int device, uint64_t seed, uint32_t stream, int64_t n_floats, float scale, void *out);
+L2J_API int l2j_synth_quant(int device, uint64_t seed, uint32_t stream, int64_t n_floats, float scale, void *out);
 
 /* ---- single-kernel entry points (TEST-mode counterparts, Run.java:186-303) ------------------ */
 
 /* xout = W x with fused dequantisation: MatMul.callI8 (kernel/MatMul.java:314-358).
  * `groups` is the whole tensor in group format on the host, `weight_index` the element index of
  * W's first entry (l * d * n in the reference's call sites), n the row length, d the row count. */
-int l2j_k_matvec_i8(int device, uint32_t flags, const void *groups, int64_t tensor_floats, int64_t weight_index,
+L2J_API int l2j_k_matvec_i8(int device, uint32_t flags, const void *groups, int64_t tensor_floats, int64_t weight_index,
                     int n, int d, const float *x, float *xout);
 
 /* xout = W x, FP32 weights: MatMul.callFP32 (kernel/MatMul.java:289-312). */
-int l2j_k_matvec_f32(int device, uint32_t flags, const float *w, int n, int d, const float *x, float *xout,
+L2J_API int l2j_k_matvec_f32(int device, uint32_t flags, const float *w, int n, int d, const float *x, float *xout,
                      int *argmax);
 
 /* out = deq(w) * (rsqrt(mean(x^2) + 1e-5) * x): RootMeanSquare.call + WeightNormalizeAndScale.callI8
  * (kernel/RootMeanSquare.java:57-118, kernel/WeightNormalizeAndScale.java:141-189). */
-int l2j_k_rmsnorm(int device, const void *groups, int64_t tensor_floats, int64_t weight_index, int n,
+L2J_API int l2j_k_rmsnorm(int device, const void *groups, int64_t tensor_floats, int64_t weight_index, int n,
                   const float *x, float *out);
 
 /* ApplyRope.call (kernel/ApplyRope.java:114-142): rotates q (dim) and k (kv_dim) in place. */
-int l2j_k_rope(int device, float *q, float *k, int pos, int dim, int kv_dim, int head_size);
+L2J_API int l2j_k_rope(int device, float *q, float *k, int pos, int dim, int kv_dim, int head_size);
 
 /* AttentionLoop + ExpSumNormalize + AccumWeightedValue for every head (Run.java:450-478).
  * key/value caches are in the reference's layout (seq, kv_dim) for one layer; positions 0..pos
  * are read.  out receives n_heads * head_size floats. */
-int l2j_k_attention(int device, const float *q, const float *key_cache, const float *value_cache, int pos,
+L2J_API int l2j_k_attention(int device, const float *q, const float *key_cache, const float *value_cache, int pos,
                     int n_heads, int n_kv_heads, int head_size, int seq_len, float *out);
 
 /* Silu.call (kernel/Silu.java:97-135): hb = hb * sigmoid(hb) * hb2. */
-int l2j_k_swiglu(int device, float *hb, const float *hb2, int n);
+L2J_API int l2j_k_swiglu(int device, float *hb, const float *hb2, int n);
 
 /* Copies n bytes device-to-device repeatedly and returns the best time; the denominator check of
  * the roofline (no counterpart in the reference). */
-int l2j_k_copy_bandwidth(int device, int64_t bytes, int iters, double *best_gbs);
+L2J_API int l2j_k_copy_bandwidth(int device, int64_t bytes, int iters, double *best_gbs);
 
 #ifdef __cplusplus
 }

@@ -187,7 +187,7 @@ void fill_plan(MvParams &p, const MvPlan &pl)
     p.slot_bytes = pl.slot_bytes;
     p.hdr_off = pl.hdr_off;
     p.half_hdr = pl.half_hdr;
-    p.timeout_polls = 1 << 22;
+    p.timeout_us = 50000;
 }
 
 // Builds the static kernel parameter blocks of every layer this context owns.
@@ -585,7 +585,7 @@ extern "C" int l2j_create(const l2j_config *cfg, int device, int first_layer, in
     CREATE_CUDA(cudaMemcpy(c->rope_sin, sn.data(), sn.size() * sizeof(float), cudaMemcpyHostToDevice));
 
     c->nsplit = choose_nsplit(c->sm_count, cfg->n_heads, cfg->seq_len);
-    c->chunk_max = (cfg->seq_len + c->nsplit - 1) / c->nsplit;
+    c->chunk_max = (((cfg->seq_len + c->nsplit - 1) / c->nsplit) + 3) & ~3;   // keeps the float4 scratch behind it aligned
     CREATE_CK(dev_alloc(c, &c->attn_part, (int64_t)cfg->n_heads * c->nsplit * (head + 2), true));
     CREATE_CK(dev_alloc(c, &c->attn_counters, cfg->n_heads, true));
     CREATE_CK(dev_alloc(c, &c->blk_val, c->sm_count + 8, true));
@@ -947,6 +947,60 @@ extern "C" int l2j_get_stats(l2j_ctx *c, l2j_stats *out)
     return L2J_OK;
 }
 
+extern "C" int l2j_time_kernels(l2j_ctx *c, int pos, int reps, double *us)
+{
+    if (!c || !us || reps <= 0)
+        return L2J_E_INVALID;
+    std::lock_guard<std::mutex> lock(c->mu);
+    if (!c->finalized || !c->use_ring)
+        return fail(c, L2J_E_STATE, "kernel timing needs a finalized context on the ring kernels");
+    int rc = check_range(c, 1, pos, true);
+    if (rc != L2J_OK)
+        return rc;
+    CK(c, cudaSetDevice(c->device));
+    rc = post_cmd(c, 1, 1, pos);
+    if (rc != L2J_OK)
+        return rc;
+    LaunchCfg lc{c->stream, false, c->sm_count};
+    CK(c, launch_begin(lc, c->state, c->cmd_dev, c->emb, c->x, c->dim, c->cfg.vocab_size, c->cfg.seq_len, c->is_first ? 1 : 0));
+    for (int kind = 0; kind < 6; ++kind) {
+        us[kind] = 0.0;
+        if (kind == 5 && !c->is_last)
+            continue;
+        int launches = 0;
+        for (int phase = 0; phase < 2; ++phase) {   // phase 0 warms up, phase 1 is timed
+            if (phase == 1)
+                CK(c, cudaEventRecord(c->ev0, c->stream));
+            const int sweeps = phase == 0 ? 1 : reps;
+            for (int r = 0; r < sweeps; ++r) {
+                const int n = kind == 5 ? 1 : c->nl;
+                for (int li = 0; li < n; ++li) {
+                    LayerLaunch &L = c->layers[(size_t)(kind == 5 ? 0 : li)];
+                    cudaError_t e = cudaSuccess;
+                    switch (kind) {
+                    case 0: e = launch_matvec_ring(lc, c->plan_dim, false, L.qkv); break;
+                    case 1: e = launch_attention(lc, L.attn); break;
+                    case 2: e = launch_matvec_ring(lc, c->plan_dim, false, L.wo); break;
+                    case 3: e = launch_matvec_ring(lc, c->plan_dim, false, L.w13); break;
+                    case 4: e = launch_matvec_ring(lc, c->plan_hidden, false, L.w2); break;
+                    default: e = launch_matvec_ring(lc, c->plan_cls, true, c->cls); break;
+                    }
+                    CK(c, e);
+                    if (phase == 1)
+                        ++launches;
+                }
+            }
+        }
+        CK(c, cudaEventRecord(c->ev1, c->stream));
+        CK(c, cudaEventSynchronize(c->ev1));
+        float ms = 0.f;
+        CK(c, cudaEventElapsedTime(&ms, c->ev0, c->ev1));
+        us[kind] = launches > 0 ? (double)ms * 1000.0 / launches : 0.0;
+    }
+    CK(c, cudaStreamSynchronize(c->stream));
+    return L2J_OK;
+}
+
 // Flags that describe how the per-token work is issued (bit 0: CUDA graph, bit 1: programmatic
 // dependent launch, bit 2: ring kernels), for reports.
 extern "C" int l2j_launch_mode(l2j_ctx *c)
@@ -1304,7 +1358,7 @@ extern "C" int l2j_k_attention(int device, const float *q, const float *key_cach
     SeqState *st = nullptr;
     AttnParams p{};
     p.nsplit = choose_nsplit(prop.multiProcessorCount, n_heads, seq_len);
-    p.chunk_max = (seq_len + p.nsplit - 1) / p.nsplit;
+    p.chunk_max = (((seq_len + p.nsplit - 1) / p.nsplit) + 3) & ~3;
     KCK(s.alloc(&dq, (int64_t)n_heads * head_size));
     KCK(s.alloc(&ksrc, used));
     KCK(s.alloc(&vsrc, used));

@@ -52,15 +52,26 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
     return ok != 0;
 }
 
-// Bounded wait: gives up after `limit` polls and returns false; the caller records the fault in
-// the device status word and carries on, so a lost copy can never hang the GPU.
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, uint32_t limit)
+__device__ __forceinline__ uint64_t global_timer_ns()
 {
-    for (uint32_t i = 0; i < limit; ++i) {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Bounded wait: gives up `timeout_ns` after the first failed poll and returns false; the caller
+// records the fault in the device status word and carries on, so a lost copy can never hang the GPU.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, uint64_t timeout_ns)
+{
+    if (mbar_try_wait(bar, parity))
+        return true;
+    const uint64_t t0 = global_timer_ns();
+    for (;;) {
         if (mbar_try_wait(bar, parity))
             return true;
+        if (global_timer_ns() - t0 > timeout_ns)
+            return false;
     }
-    return false;
 }
 
 // L2 eviction policy for data that is read exactly once per token (the weights).

@@ -68,7 +68,7 @@ struct MvParams {
     int slot_bytes;    // bytes per ring slot
     int hdr_off;       // offset of the header area inside a slot
     int half_hdr;      // bytes of one half's header area (paired mode)
-    int timeout_polls;
+    int timeout_us;    // bound of every wait on a copy barrier
     // prologue
     const float *x_in;       // input vector (n floats)
     const float *rms_w;      // dequantised RMSNorm weights (n floats) or nullptr

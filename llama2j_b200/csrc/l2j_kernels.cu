@@ -145,6 +145,7 @@ constexpr int kSmemHeader = 1024;   // barriers + reduction scratch in front of 
 constexpr int kRedOff = 256;        // float red[2][2*rpp*wpr], at most 64 floats
 constexpr int kSsOff = 512;         // float ss[wpr]
 constexpr int kBestOff = 640;       // arg-max scratch: float[32] then int[32]
+constexpr uint64_t kShortWaitNs = 2000;
 
 template <bool F32, int CPT, int MAXT>
 __global__ void __launch_bounds__(MAXT, 2) matvec_ring_kernel(const __grid_constant__ MvParams p)
@@ -182,11 +183,12 @@ __global__ void __launch_bounds__(MAXT, 2) matvec_ring_kernel(const __grid_const
         if (lane == 0) {
             const uint64_t pol = policy_evict_first();
             bool lost = false;
+            const uint64_t wait_ns = (uint64_t)p.timeout_us * 1000ull;
             for (int i = 0, s = s_begin; s < s_end; ++s, ++i) {
                 const int slot = i % nstage;
                 if (i >= nstage) {
                     const uint32_t parity = (uint32_t)((i / nstage) - 1) & 1u;
-                    if (!mbar_wait_bounded(bar_base + 8 * (nstage + slot), parity, (uint32_t)p.timeout_polls))
+                    if (!mbar_wait_bounded(bar_base + 8 * (nstage + slot), parity, lost ? kShortWaitNs : wait_ns))
                         lost = true;
                 }
                 int seg, row0, nrows;
@@ -308,14 +310,18 @@ __global__ void __launch_bounds__(MAXT, 2) matvec_ring_kernel(const __grid_const
         xs[k] = s;
     }
 
-    bool lost = false;
+    // After one wait has run out (here or in an earlier kernel of the stream) later waits give up
+    // almost at once, so a broken copy costs one timeout, not one per stage.
+    bool lost = (__ldcg(&p.state->status) & L2J_DS_WAIT_TIMEOUT) != 0;
+    const bool lost_before = lost;
+    const uint64_t wait_ns = (uint64_t)p.timeout_us * 1000ull;
     float best_v = -FLT_MAX;   // arg-max candidates of the epilogue threads (EPI_LOGITS)
     int best_i = 0x7fffffff;
 
     for (int i = 0, s = s_begin; s < s_end; ++s, ++i) {
         const int slot = i % nstage;
         const uint32_t parity = (uint32_t)(i / nstage) & 1u;
-        if (!mbar_wait_bounded(bar_base + 8 * slot, parity, (uint32_t)p.timeout_polls))
+        if (!mbar_wait_bounded(bar_base + 8 * slot, parity, lost ? kShortWaitNs : wait_ns))
             lost = true;
         int seg, row0, nrows;
         decode_stage(p, rs, s, seg, row0, nrows);
@@ -416,12 +422,12 @@ __global__ void __launch_bounds__(MAXT, 2) matvec_ring_kernel(const __grid_const
         }
     }
 
-    if (lost) {
+    if (lost && !lost_before) {
         atomicOr(&p.state->status, L2J_DS_WAIT_TIMEOUT);
         // give copies that may still be in flight a last bounded chance to land before the block exits
         const int issued = s_end - s_begin;
         for (int i = max(0, issued - nstage); i < issued; ++i)
-            mbar_wait_bounded(bar_base + 8 * (i % nstage), (uint32_t)(i / nstage) & 1u, (uint32_t)p.timeout_polls);
+            mbar_wait_bounded(bar_base + 8 * (i % nstage), (uint32_t)(i / nstage) & 1u, wait_ns);
     }
 
     if (p.epilogue == EPI_LOGITS) {

@@ -135,6 +135,12 @@ class Transformer:
         _lib.check(self._lib.l2j_last_generate_us(self._ctx, C.byref(v)), self._ctx)
         return v.value
 
+    def time_kernels(self, pos: int, reps: int = 3) -> dict:
+        """Average device microseconds per launch of each kernel of a layer at position `pos`."""
+        arr = (C.c_double * 6)()
+        _lib.check(self._lib.l2j_time_kernels(self._ctx, int(pos), int(reps), arr), self._ctx)
+        return dict(zip(("qkv_rope", "attention", "wo_residual", "w13_swiglu", "w2_residual", "classifier_argmax"), arr))
+
     def reset(self) -> None:
         _lib.check(self._lib.l2j_reset(self._ctx), self._ctx)
 
