@@ -167,7 +167,8 @@ L2J_API int l2j_reset(l2j_ctx *ctx);
 L2J_API int l2j_get_stats(l2j_ctx *ctx, l2j_stats *out);
 
 /* How the per-token work is issued: bit 0 CUDA graph replay, bit 1 programmatic dependent launch
- * between kernels, bit 2 the bulk-copy ring kernels (else the plain kernels).  The reference issues
+ * between kernels, bit 2 the bulk-copy ring kernels (else the plain kernels); bits 8 and up hold the
+ * number of blocks a ring kernel is launched with.  The reference issues
  * every kernel with its own cuLaunchKernel (kernel/MatMul.java:338-354). */
 L2J_API int l2j_launch_mode(l2j_ctx *ctx);
 
@@ -187,6 +188,20 @@ L2J_API int l2j_last_generate_us(l2j_ctx *ctx, double *total_us);
  * the same weights).  us[0..5] = QKV+RoPE, attention, Wo+residual, W1/W3+SwiGLU, W2+residual,
  * classifier+argmax.  Leaves the sequence state undefined: call l2j_reset afterwards. */
 L2J_API int l2j_time_kernels(l2j_ctx *ctx, int pos, int reps, double *us);
+
+/* Measurement aid (no counterpart in the reference): the in-kernel timeline of one launch of a ring
+ * kernel (kind 0 QKV, 2 Wo, 3 W1/W3, 4 W2, 5 classifier; same numbering as l2j_time_kernels).
+ * out receives 16 values per block for up to max_blocks blocks: SM cycle counter at 0 block entry,
+ * 1 first bulk copy issued, 2 last bulk copy issued, 3 consumer prologue done, 4 first stage landed,
+ * 5 consumers done, 6 epilogue warp done; 7 / 8 = global timer in ns at block entry / epilogue done;
+ * 9-15 finer marks of the block set-up.
+ * Leaves the sequence state undefined: call l2j_reset afterwards. */
+L2J_API int l2j_trace_kernel(l2j_ctx *ctx, int kind, int layer, int pos, uint64_t *out, int max_blocks);
+
+/* The same timelines for every ring-kernel launch of the last forward, in launch order (per layer
+ * QKV, Wo, W1/W3, W2, then the classifier), 16 values per block and two blocks per SM.  Only
+ * recorded when the context was created with L2J_TRACE set in the environment. */
+L2J_API int l2j_read_trace(l2j_ctx *ctx, uint64_t *out, int64_t max_values);
 
 /* ---- load-time helpers on the device ------------------------------------------------------- */
 

@@ -60,6 +60,9 @@ struct l2j_ctx {
     float *blk_val = nullptr;
     int *blk_idx = nullptr;
     int *prompt_dev = nullptr, *out_tokens_dev = nullptr;
+    unsigned int *work = nullptr;   // two counters per ring-kernel launch of a forward
+    unsigned long long *trace = nullptr;   // per-launch timelines, only when L2J_TRACE is set
+    int ring_grid = 0;              // blocks per ring kernel: two per SM
     SeqState *state = nullptr;
     Cmd *cmd_dev = nullptr;
     Cmd *cmd_host = nullptr;       // pinned ring
@@ -188,6 +191,19 @@ void fill_plan(MvParams &p, const MvPlan &pl)
     p.hdr_off = pl.hdr_off;
     p.half_hdr = pl.half_hdr;
     p.timeout_us = 50000;
+    {   // stage bookkeeping: a stage advances rt*rpp rows (half of that per matrix in paired mode)
+        const int rs = p.paired ? (pl.rt * pl.rpp) / 2 : pl.rt * pl.rpp;
+        p.total_stages = 0;
+        const int nseg = p.paired ? 1 : p.nseg;
+        for (int i = 0; i < 3; ++i) {
+            p.seg_stages[i] = i < nseg ? (p.seg[i].rows + rs - 1) / rs : 0;
+            p.total_stages += p.seg_stages[i];
+        }
+    }
+    const char *pm = getenv("L2J_PDL_MODE");
+    p.pdl_mode = pm ? atoi(pm) : 0;
+    const char *pw = getenv("L2J_PRODUCER_WAIT");
+    p.producer_wait = pw ? atoi(pw) : 0;
 }
 
 // Builds the static kernel parameter blocks of every layer this context owns.
@@ -226,6 +242,8 @@ void build_launch_params(l2j_ctx *c)
         a.q_out = c->q;
         a.k_cache = kc;
         a.v_cache = vc;
+        a.work = c->work + 2 * (4 * li + 0);
+        a.trace = c->trace ? c->trace + (int64_t)(4 * li + 0) * c->ring_grid * 16 : nullptr;
 
         // attention over positions 0..pos                      (Run.java:450-478)
         AttnParams &t = L.attn;
@@ -255,6 +273,8 @@ void build_launch_params(l2j_ctx *c)
         o.rms_w = nullptr;
         o.epilogue = EPI_RESIDUAL;
         o.y = c->x;
+        o.work = c->work + 2 * (4 * li + 1);
+        o.trace = c->trace ? c->trace + (int64_t)(4 * li + 1) * c->ring_grid * 16 : nullptr;
 
         // hb = silu(W1 rmsnorm(x)) * W3 rmsnorm(x)              (Run.java:490-502)
         MvParams &f = L.w13;
@@ -269,6 +289,8 @@ void build_launch_params(l2j_ctx *c)
         f.rms_w = c->rms_ffn + (int64_t)li * dim;
         f.epilogue = EPI_SWIGLU;
         f.y = c->hb;
+        f.work = c->work + 2 * (4 * li + 2);
+        f.trace = c->trace ? c->trace + (int64_t)(4 * li + 2) * c->ring_grid * 16 : nullptr;
 
         // x += W2 hb                                           (Run.java:505-508)
         MvParams &w = L.w2;
@@ -281,6 +303,8 @@ void build_launch_params(l2j_ctx *c)
         w.rms_w = nullptr;
         w.epilogue = EPI_RESIDUAL;
         w.y = c->x;
+        w.work = c->work + 2 * (4 * li + 3);
+        w.trace = c->trace ? c->trace + (int64_t)(4 * li + 3) * c->ring_grid * 16 : nullptr;
     }
     if (c->is_last) {
         // logits = Wcls rmsnorm(x); arg-max                    (Run.java:514-518, Sampler.java:46-57)
@@ -306,6 +330,8 @@ void build_launch_params(l2j_ctx *c)
         k.blk_idx = c->blk_idx;
         k.prompt = c->prompt_dev;
         k.out_tokens = c->out_tokens_dev;
+        k.work = c->work + 2 * (4 * c->nl);
+        k.trace = c->trace ? c->trace + (int64_t)(4 * c->nl) * c->ring_grid * 16 : nullptr;
     }
 }
 
@@ -314,7 +340,7 @@ cudaError_t enqueue_forward(l2j_ctx *c, bool pdl, int *n_kernels)
 {
     cudaError_t e;
     int nk = 0;
-    LaunchCfg lc{c->stream, false, c->sm_count};
+    LaunchCfg lc{c->stream, false, c->ring_grid};
     // The first kernel of a forward follows a memcpy (or the previous graph launch): plain edge.
     e = launch_begin(lc, c->state, c->cmd_dev, c->emb, c->x, c->dim, c->cfg.vocab_size, c->cfg.seq_len, c->is_first ? 1 : 0);
     if (e != cudaSuccess)
@@ -332,7 +358,7 @@ cudaError_t enqueue_forward(l2j_ctx *c, bool pdl, int *n_kernels)
             if ((e = launch_matvec_ring(lc, c->plan_hidden, false, L.w2)) != cudaSuccess) return e;
             nk += 5;
         } else {
-            LaunchCfg plain{c->stream, false, c->sm_count};
+            LaunchCfg plain{c->stream, false, c->ring_grid};
             if ((e = launch_rmsnorm_plain(c->stream, c->x, L.qkv.rms_w, c->xn, dim)) != cudaSuccess) return e;
             if ((e = launch_matvec_plain_u8(c->stream, L.qkv.seg[0], dim, c->xn, c->y0)) != cudaSuccess) return e;
             if ((e = launch_matvec_plain_u8(c->stream, L.qkv.seg[1], dim, c->xn, c->y1)) != cudaSuccess) return e;
@@ -588,8 +614,16 @@ extern "C" int l2j_create(const l2j_config *cfg, int device, int first_layer, in
     c->chunk_max = (((cfg->seq_len + c->nsplit - 1) / c->nsplit) + 3) & ~3;   // keeps the float4 scratch behind it aligned
     CREATE_CK(dev_alloc(c, &c->attn_part, (int64_t)cfg->n_heads * c->nsplit * (head + 2), true));
     CREATE_CK(dev_alloc(c, &c->attn_counters, cfg->n_heads, true));
-    CREATE_CK(dev_alloc(c, &c->blk_val, c->sm_count + 8, true));
-    CREATE_CK(dev_alloc(c, &c->blk_idx, c->sm_count + 8, true));
+    {   // blocks per ring kernel: two per SM give the streaming kernel the whole shared memory as its ring
+        const char *g = getenv("L2J_BLOCKS_PER_SM");
+        const int per_sm = g ? atoi(g) : 2;
+        c->ring_grid = (per_sm >= 1 && per_sm <= 2 ? per_sm : 1) * c->sm_count;
+    }
+    CREATE_CK(dev_alloc(c, &c->blk_val, c->ring_grid + 8, true));
+    CREATE_CK(dev_alloc(c, &c->blk_idx, c->ring_grid + 8, true));
+    CREATE_CK(dev_alloc(c, &c->work, 2 * (4 * (int64_t)c->nl + 1), true));
+    if (getenv("L2J_TRACE"))
+        CREATE_CK(dev_alloc(c, &c->trace, (4 * (int64_t)c->nl + 1) * c->ring_grid * 16, true));
     CREATE_CK(dev_alloc(c, &c->prompt_dev, cfg->seq_len, true));
     CREATE_CK(dev_alloc(c, &c->out_tokens_dev, cfg->seq_len, true));
     CREATE_CK(dev_alloc(c, &c->state, 1, true));
@@ -763,6 +797,25 @@ extern "C" int l2j_finalize(l2j_ctx *c)
         CK(c, launch_dequant_rms(c->stream, c->qt[L2J_T_RMS_FINAL], 0, dim, c->rms_final));
     CK(c, cudaStreamSynchronize(c->stream));
     build_launch_params(c);
+    {   // largest RMSNorm weight per launch: bounds the normalised vector for the kernels' fixed-point scale
+        std::vector<float> w((size_t)dim * (size_t)(c->nl > 1 ? c->nl : 1));
+        auto vmax = [&](const float *src, int64_t n) {
+            float m = 0.f;
+            for (int64_t i = 0; i < n; ++i)
+                m = std::fmax(m, std::fabs(src[i]));
+            return m;
+        };
+        CK(c, cudaMemcpy(w.data(), c->rms_att, sizeof(float) * (size_t)dim * c->nl, cudaMemcpyDeviceToHost));
+        for (int li = 0; li < c->nl; ++li)
+            c->layers[(size_t)li].qkv.rms_wmax = vmax(w.data() + (int64_t)li * dim, dim);
+        CK(c, cudaMemcpy(w.data(), c->rms_ffn, sizeof(float) * (size_t)dim * c->nl, cudaMemcpyDeviceToHost));
+        for (int li = 0; li < c->nl; ++li)
+            c->layers[(size_t)li].w13.rms_wmax = vmax(w.data() + (int64_t)li * dim, dim);
+        if (c->is_last) {
+            CK(c, cudaMemcpy(w.data(), c->rms_final, sizeof(float) * (size_t)dim, cudaMemcpyDeviceToHost));
+            c->cls.rms_wmax = vmax(w.data(), dim);
+        }
+    }
 
     c->pdl_on = c->use_ring && !(c->flags & L2J_F_NO_PDL);
     if (!(c->flags & L2J_F_NO_GRAPH)) {
@@ -926,6 +979,7 @@ extern "C" int l2j_reset(l2j_ctx *c)
     CK(c, cudaStreamSynchronize(c->stream));
     CK(c, cudaMemset(c->state, 0, sizeof(SeqState)));
     CK(c, cudaMemset(c->attn_counters, 0, sizeof(unsigned int) * (size_t)c->cfg.n_heads));
+    CK(c, cudaMemset(c->work, 0, sizeof(unsigned int) * 2 * (4 * (size_t)c->nl + 1)));
     CK(c, cudaDeviceSynchronize());
     c->forwards = 0;
     c->status_accum = 0;
@@ -961,7 +1015,7 @@ extern "C" int l2j_time_kernels(l2j_ctx *c, int pos, int reps, double *us)
     rc = post_cmd(c, 1, 1, pos);
     if (rc != L2J_OK)
         return rc;
-    LaunchCfg lc{c->stream, false, c->sm_count};
+    LaunchCfg lc{c->stream, false, c->ring_grid};
     CK(c, launch_begin(lc, c->state, c->cmd_dev, c->emb, c->x, c->dim, c->cfg.vocab_size, c->cfg.seq_len, c->is_first ? 1 : 0));
     for (int kind = 0; kind < 6; ++kind) {
         us[kind] = 0.0;
@@ -1001,13 +1055,75 @@ extern "C" int l2j_time_kernels(l2j_ctx *c, int pos, int reps, double *us)
     return L2J_OK;
 }
 
+extern "C" int l2j_read_trace(l2j_ctx *c, uint64_t *out, int64_t max_values)
+{
+    if (!c || !out || max_values <= 0)
+        return L2J_E_INVALID;
+    std::lock_guard<std::mutex> lock(c->mu);
+    if (!c->trace)
+        return fail(c, L2J_E_STATE, "the context was created without L2J_TRACE in the environment");
+    CK(c, cudaSetDevice(c->device));
+    CK(c, cudaStreamSynchronize(c->stream));
+    int64_t n = (4 * (int64_t)c->nl + 1) * c->ring_grid * 16;
+    if (n > max_values)
+        n = max_values;
+    CK(c, cudaMemcpy(out, c->trace, sizeof(uint64_t) * (size_t)n, cudaMemcpyDeviceToHost));
+    return L2J_OK;
+}
+
+extern "C" int l2j_trace_kernel(l2j_ctx *c, int kind, int layer, int pos, uint64_t *out, int max_blocks)
+{
+    if (!c || !out || kind < 0 || kind > 5 || kind == 1 || max_blocks <= 0)
+        return L2J_E_INVALID;
+    std::lock_guard<std::mutex> lock(c->mu);
+    if (!c->finalized || !c->use_ring)
+        return fail(c, L2J_E_STATE, "kernel tracing needs a finalized context on the ring kernels");
+    const int li = layer - c->first_layer;
+    if (li < 0 || li >= c->nl || (kind == 5 && !c->is_last))
+        return fail(c, L2J_E_INVALID, "layer %d is not held by this context", layer);
+    int rc = check_range(c, 1, pos, true);
+    if (rc != L2J_OK)
+        return rc;
+    CK(c, cudaSetDevice(c->device));
+    unsigned long long *dtrace = nullptr;
+    const int nb = c->ring_grid;
+    CK(c, cudaMalloc((void **)&dtrace, sizeof(unsigned long long) * 16 * (size_t)nb));
+    cudaMemset(dtrace, 0, sizeof(unsigned long long) * 16 * (size_t)nb);
+    cudaDeviceSynchronize();
+    rc = post_cmd(c, 1, 1, pos);
+    LaunchCfg lc{c->stream, false, c->ring_grid};
+    cudaError_t e = launch_begin(lc, c->state, c->cmd_dev, c->emb, c->x, c->dim, c->cfg.vocab_size, c->cfg.seq_len, c->is_first ? 1 : 0);
+    LayerLaunch &L = c->layers[(size_t)li];
+    for (int rep = 0; rep < 2 && e == cudaSuccess; ++rep) {   // the second launch is the one recorded
+        MvParams p = kind == 0 ? L.qkv : kind == 2 ? L.wo : kind == 3 ? L.w13 : kind == 4 ? L.w2 : c->cls;
+        const MvPlan &pl = kind == 4 ? c->plan_hidden : kind == 5 ? c->plan_cls : c->plan_dim;
+        p.trace = rep == 1 ? dtrace : nullptr;
+        if (rep == 1 && c->nl > 1 && kind != 5) {   // another layer's weights, so nothing is warm in L2
+            LayerLaunch &L2 = c->layers[(size_t)((li + 1) % c->nl)];
+            MvParams q = kind == 0 ? L2.qkv : kind == 2 ? L2.wo : kind == 3 ? L2.w13 : L2.w2;
+            q.trace = dtrace;
+            p = q;
+        }
+        e = launch_matvec_ring(lc, pl, kind == 5, p);
+    }
+    if (e == cudaSuccess)
+        e = cudaStreamSynchronize(c->stream);
+    const int n = nb < max_blocks ? nb : max_blocks;
+    if (e == cudaSuccess)
+        e = cudaMemcpy(out, dtrace, sizeof(unsigned long long) * 16 * (size_t)n, cudaMemcpyDeviceToHost);
+    cudaFree(dtrace);
+    if (e != cudaSuccess)
+        return fail(c, L2J_E_CUDA, "trace failed: %s", cudaGetErrorString(e));
+    return rc;
+}
+
 // Flags that describe how the per-token work is issued (bit 0: CUDA graph, bit 1: programmatic
 // dependent launch, bit 2: ring kernels), for reports.
 extern "C" int l2j_launch_mode(l2j_ctx *c)
 {
     if (!c)
         return 0;
-    return (c->exec ? 1 : 0) | (c->pdl_on ? 2 : 0) | (c->use_ring ? 4 : 0);
+    return (c->exec ? 1 : 0) | (c->pdl_on ? 2 : 0) | (c->use_ring ? 4 : 0) | (c->ring_grid << 8);
 }
 
 // Reads an internal buffer after a forward (debugging and per-stage parity checks):
@@ -1196,6 +1312,8 @@ extern "C" int l2j_k_matvec_i8(int device, uint32_t flags, const void *groups, i
     KCK(s.alloc(&dx, n));
     KCK(s.alloc(&dy, d, true));
     KCK(s.alloc(&st, 1, true));
+    unsigned int *work = nullptr;
+    KCK(s.alloc(&work, 2, true));
     KCK(cudaMemcpy(raw, groups, (size_t)ng * kGroupBytes, cudaMemcpyHostToDevice));
     KCK(cudaMemcpy(dx, x, (size_t)n * sizeof(float), cudaMemcpyHostToDevice));
     KCK(launch_repack(nullptr, raw, ng, payload, hdr));
@@ -1213,7 +1331,8 @@ extern "C" int l2j_k_matvec_i8(int device, uint32_t flags, const void *groups, i
         p.epilogue = EPI_STORE;
         p.y = dy;
         p.state = st;
-        LaunchCfg lc{nullptr, false, prop.multiProcessorCount};
+        p.work = work;
+        LaunchCfg lc{nullptr, false, 2 * prop.multiProcessorCount};
         KCK(launch_matvec_ring(lc, pl, false, p));
     } else {
         KCK(launch_matvec_plain_u8(nullptr, seg, n, dx, dy));
@@ -1240,8 +1359,10 @@ extern "C" int l2j_k_matvec_f32(int device, uint32_t flags, const float *w, int 
     KCK(s.alloc(&dw, (int64_t)n * d + 64));
     KCK(s.alloc(&dx, n));
     KCK(s.alloc(&dy, d, true));
-    KCK(s.alloc(&bv, prop.multiProcessorCount + 8, true));
-    KCK(s.alloc(&bi, prop.multiProcessorCount + 8, true));
+    KCK(s.alloc(&bv, 2 * prop.multiProcessorCount + 8, true));
+    KCK(s.alloc(&bi, 2 * prop.multiProcessorCount + 8, true));
+    unsigned int *work = nullptr;
+    KCK(s.alloc(&work, 2, true));
     KCK(s.alloc(&outtok, 8, true));
     KCK(s.alloc(&st, 1, true));
     KCK(cudaMemcpy(dw, w, (size_t)n * d * sizeof(float), cudaMemcpyHostToDevice));
@@ -1258,10 +1379,11 @@ extern "C" int l2j_k_matvec_f32(int device, uint32_t flags, const float *w, int 
     p.blk_idx = bi;
     p.out_tokens = outtok;
     p.state = st;
+    p.work = work;
     const MvPlan pl = plan_matvec(n, true, false);
     if (!(flags & L2J_F_SIMPLE) && pl.ok) {
         fill_plan(p, pl);
-        LaunchCfg lc{nullptr, false, prop.multiProcessorCount};
+        LaunchCfg lc{nullptr, false, 2 * prop.multiProcessorCount};
         KCK(launch_matvec_ring(lc, pl, true, p));
     } else {
         float *tmp = nullptr;

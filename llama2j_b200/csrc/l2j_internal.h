@@ -69,9 +69,12 @@ struct MvParams {
     int hdr_off;       // offset of the header area inside a slot
     int half_hdr;      // bytes of one half's header area (paired mode)
     int timeout_us;    // bound of every wait on a copy barrier
+    int seg_stages[3]; // stages per segment
+    int total_stages;
     // prologue
     const float *x_in;       // input vector (n floats)
     const float *rms_w;      // dequantised RMSNorm weights (n floats) or nullptr
+    float rms_wmax;          // max |rms_w| (bounds the normalised vector for the fixed-point scale)
     // epilogue
     int epilogue;
     float *y;                // STORE / RESIDUAL / SWIGLU / LOGITS target
@@ -87,6 +90,10 @@ struct MvParams {
     const int *prompt;       // device prompt tokens
     int *out_tokens;
     SeqState *state;
+    unsigned int *work;  // {next unclaimed stage, blocks that ran out of work}; zero between launches
+    int pdl_mode;        // experiment: 0 trigger dependents at block start, 1 after the main loop, 2 never
+    int producer_wait;   // experiment: producer waits for the previous kernel before its first copy
+    unsigned long long *trace;   // optional per-block timeline (8 slots per block), else nullptr
 };
 
 struct AttnParams {
@@ -103,9 +110,10 @@ struct AttnParams {
 
 struct MvPlan {
     int cpt;       // chunks per thread (template selector)
+    int rt;        // rows per thread and stage (template selector)
     int rpp, wpr;
     int nstage, slot_bytes, hdr_off, half_hdr;
-    int threads;   // block size including the producer warp
+    int threads;   // block size including the producer and the epilogue warp
     int smem_bytes;
     bool ok;
 };

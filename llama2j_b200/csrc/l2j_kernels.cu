@@ -24,6 +24,7 @@
 
 #include <cfloat>
 #include <cmath>
+#include <cstdlib>
 
 #define L2J_DS_WAIT_TIMEOUT 0x1
 #define L2J_DS_BAD_POS 0x2
@@ -38,9 +39,9 @@ namespace l2j {
 // Rows (row, row+1) of segment `seg` of the QKV product: rotate q and k pairs by the position's
 // angle (ApplyRope.java:61-92 arithmetic, no fused multiply-add), write q to its vector and k, v
 // into the cache at [kv_head][pos][d].
-__device__ __forceinline__ void epi_qkv_pair(const MvParams &p, int seg, int row, float v0, float v1, int pos)
+__device__ __forceinline__ void epi_qkv_pair(const MvParams &p, int seg, int row, float v0, float v1, int pos,
+                                             const float *cos_row, const float *sin_row)
 {
-    const int half = p.head >> 1;
     if (seg == 2) {
         const int kvh = row / p.head, d = row - kvh * p.head;
         float *dst = p.v_cache + ((int64_t)kvh * p.seq_len + pos) * p.head + d;
@@ -49,8 +50,8 @@ __device__ __forceinline__ void epi_qkv_pair(const MvParams &p, int seg, int row
         return;
     }
     const int d = row % p.head;
-    const float c = p.rope_cos[(int64_t)pos * half + (d >> 1)];
-    const float s = p.rope_sin[(int64_t)pos * half + (d >> 1)];
+    const float c = cos_row[d >> 1];   // the RoPE table row of this position
+    const float s = sin_row[d >> 1];
     const float r0 = __fsub_rn(__fmul_rn(v0, c), __fmul_rn(v1, s));
     const float r1 = __fadd_rn(__fmul_rn(v0, s), __fmul_rn(v1, c));
     if (seg == 0) {
@@ -114,40 +115,118 @@ __device__ void finish_argmax_warp(const MvParams &p, int nblocks, int lane)
 
 // =============================================================================================
 // matvec_ring_kernel
+//
+// Persistent blocks, two per SM, that pull work (stages of a few matrix rows) from a global counter.
+// Warp roles:
+//   consumer warps 0..nw-1   wpr warps span one row (each lane owns CPT 16-byte chunks of it, with
+//                            the matching slice of x in registers); rpp such groups work on rpp
+//                            rows at once, RT rows each per stage
+//   producer warp nw         one thread claims stages and streams their rows into the shared-memory
+//                            ring with bulk copies, as far ahead as the ring allows.  It does not
+//                            wait for the previous kernel (weights never depend on activations), so
+//                            under programmatic dependent launch the ring fills while the previous
+//                            kernel is still running
+//   epilogue warp nw+1       adds up the per-warp partial sums of a stage and applies the fused
+//                            epilogue, decoupled from the consumers by a ring of reduction buffers
+//
+// Work is claimed dynamically because blocks of consecutive kernels share the SMs: the hardware may
+// place two blocks of one kernel on one SM and none on another, and a static split would then leave
+// the kernel waiting for the doubly loaded SM.
+//
+// u8 weights: x is converted once per block to 32-bit fixed point (one power-of-two scale per
+// vector) and split into four balanced signed byte limbs, so that a 16-byte chunk costs 16 dp4a
+// instructions (u8 weight x s8 limb, exact s32 accumulation) instead of 16 conversions + 16 FMAs.
+// Per chunk the four limb sums are recombined in FP32 and scaled by the group's (min, scale):
+//   sum_j (b_j * s + m) * x_j  =  s * sum_j b_j x_j  +  m * sum_j x_j.
 // =============================================================================================
 
+struct StageDesc {
+    int seg, row0, nrows, e0a, e0b, pad0, pad1, pad2;   // nrows == 0 marks the end of the block's work
+};
+
+// Stage index -> (segment, first row, row count).  The stage counts per segment come from the host.
 __device__ __forceinline__ void decode_stage(const MvParams &p, int rs, int s, int &seg, int &row0, int &nrows)
 {
     seg = 0;
-    if (!p.paired) {
-        int st = (p.seg[0].rows + rs - 1) / rs;
-        while (seg + 1 < p.nseg && s >= st) {
-            s -= st;
-            ++seg;
-            st = (p.seg[seg].rows + rs - 1) / rs;
+    if (!p.paired && p.nseg > 1) {
+        if (s >= p.seg_stages[0]) {
+            s -= p.seg_stages[0];
+            seg = 1;
+            if (s >= p.seg_stages[1]) {
+                s -= p.seg_stages[1];
+                seg = 2;
+            }
         }
     }
     row0 = s * rs;
     nrows = min(rs, p.seg[seg].rows - row0);
 }
 
-__device__ __forceinline__ int total_stages(const MvParams &p, int rs)
-{
-    if (p.paired)
-        return (p.seg[0].rows + rs - 1) / rs;
-    int t = 0;
-    for (int i = 0; i < p.nseg; ++i)
-        t += (p.seg[i].rows + rs - 1) / rs;
-    return t;
-}
-
-constexpr int kSmemHeader = 1024;   // barriers + reduction scratch in front of the ring
-constexpr int kRedOff = 256;        // float red[2][2*rpp*wpr], at most 64 floats
-constexpr int kSsOff = 512;         // float ss[wpr]
-constexpr int kBestOff = 640;       // arg-max scratch: float[32] then int[32]
+constexpr int kRedBufs = 4;
+constexpr int kBarFull = 0;                       // uint64 full[16]
+constexpr int kBarEmpty = 128;                    // uint64 empty[16]
+constexpr int kBarRedFull = 256;                  // uint64 red_full[4]
+constexpr int kBarRedEmpty = 288;                 // uint64 red_empty[4]
+constexpr int kScratchOff = 384;                  // float scratch[64]
+constexpr int kDescOff = 640;                     // StageDesc desc[16]
+constexpr int kRedOff = 1152;                     // 4 x (16-byte header + 64 floats)
+constexpr int kRedStride = 272;
+constexpr int kRopeOff = 2304;                    // float cos[64], sin[64] of the current position
+constexpr int kSmemHeader = 2816;                 // start of the ring (128-byte aligned)
 constexpr uint64_t kShortWaitNs = 2000;
 
-template <bool F32, int CPT, int MAXT>
+__device__ __forceinline__ int dp4a_u8s8(uint32_t a, uint32_t b, int c)
+{
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+// Reduces RT per-lane values over the warp with a halving butterfly (RT - 1 + log2(32 / RT)
+// shuffles instead of 5 * RT); afterwards lane t * (32 / RT) holds the sum of v[t] over all lanes.
+template <int RT, int STEP>
+struct WarpFold {
+    // STEP: lane bit that separates the upper half of the rows from the lower half at this level
+    static __device__ __forceinline__ float run(const float (&v)[RT], int lane)
+    {
+        if constexpr (RT == 1) {
+            float k = v[0];
+#pragma unroll
+            for (int o = STEP; o > 0; o >>= 1)
+                k += __shfl_xor_sync(0xffffffffu, k, o);
+            return k;
+        } else {
+            constexpr int H = RT / 2;
+            const bool up = (lane & STEP) != 0;
+            float k[H];
+#pragma unroll
+            for (int i = 0; i < H; ++i) {
+                const float keep = up ? v[H + i] : v[i];
+                const float send = up ? v[i] : v[H + i];
+                k[i] = keep + __shfl_xor_sync(0xffffffffu, send, STEP);
+            }
+            return WarpFold<H, STEP / 2>::run(k, lane);
+        }
+    }
+};
+
+template <int RT>
+__device__ __forceinline__ float warp_sum_rows(const float (&v)[RT], int lane)
+{
+    static_assert(RT == 2 || RT == 4 || RT == 8, "RT");
+    return WarpFold<RT, 16>::run(v, lane);
+}
+
+// Optional in-kernel timeline (p.trace != nullptr): slot k of the block gets the SM cycle counter.
+// 0 entry, 1 producer's first copy issued, 2 producer's last copy issued, 3 consumer prologue done,
+// 4 first stage landed, 5 consumers done, 6 epilogue warp done, 7 global timer (ns) at entry.
+__device__ __forceinline__ void trace_mark(const MvParams &p, int k)
+{
+    if (p.trace)
+        p.trace[blockIdx.x * 16 + k] = (unsigned long long)clock64();
+}
+
+template <bool F32, int CPT, int RT, int MAXT>
 __global__ void __launch_bounds__(MAXT, 2) matvec_ring_kernel(const __grid_constant__ MvParams p)
 {
     constexpr int EPC = F32 ? 4 : 16;   // elements per 16-byte chunk
@@ -157,61 +236,107 @@ __global__ void __launch_bounds__(MAXT, 2) matvec_ring_kernel(const __grid_const
     const int nw = p.rpp * p.wpr;          // consumer warps
     const int ncons = nw * 32;
     const int nstage = p.nstage;
-    const uint32_t bar_base = smem_u32(smem);
-    const uint32_t ring_base = smem_u32(smem + kSmemHeader);
-    float *red = reinterpret_cast<float *>(smem + kRedOff);
-    float *ssbuf = reinterpret_cast<float *>(smem + kSsOff);
+    const uint32_t sbase = smem_u32(smem);
+    const uint32_t ring_base = sbase + kSmemHeader;
+
+    // The parameter block of every launch is cold in the constant cache; reading one word of each of
+    // its 128-byte lines up front makes the block pay one miss instead of one per line along the
+    // serial set-up below.
+    {
+        const int t0 = p.nseg, t1 = p.epilogue, t2 = p.pdl_mode;
+        asm volatile("" ::"r"(t0), "r"(t1), "r"(t2));
+    }
 
     if (tid == 0) {
-        for (int i = 0; i < nstage; ++i) {
-            mbar_init(bar_base + 8 * i, 1);                 // full: one arrive.expect_tx by the producer
-            mbar_init(bar_base + 8 * (nstage + i), nw);     // empty: one arrive per consumer warp
-        }
-        mbar_fence_init();
+        trace_mark(p, 0);
+        if (p.trace)
+            p.trace[blockIdx.x * 16 + 7] = global_timer_ns();
     }
+    if (tid < nstage) {
+        mbar_init(sbase + kBarFull + 8 * tid, 1);         // one arrive(.expect_tx) by the producer
+        mbar_init(sbase + kBarEmpty + 8 * tid, nw);       // one arrive per consumer warp
+    }
+    if (tid < kRedBufs) {
+        mbar_init(sbase + kBarRedFull + 8 * tid, nw);
+        mbar_init(sbase + kBarRedEmpty + 8 * tid, 1);
+    }
+    if (tid < 32)
+        mbar_fence_init();
     __syncthreads();
-    pdl_launch_dependents();
+    if (tid == 0)
+        trace_mark(p, 9);
+    if (p.pdl_mode == 0)
+        pdl_launch_dependents();
 
-    const int rs = p.paired ? p.rpp : 2 * p.rpp;   // matrix rows (or row pairs) per stage
-    const int S = total_stages(p, rs);
-    const int s_begin = (int)(((int64_t)S * blockIdx.x) / gridDim.x);
-    const int s_end = (int)(((int64_t)S * (blockIdx.x + 1)) / gridDim.x);
+    const int R = RT * p.rpp;                       // rows of a stage in shared memory
+    const int rs = p.paired ? R / 2 : R;            // matrix rows (row pairs) a stage advances
     const int rowbytes = F32 ? p.n * 4 : p.n;
+    const uint64_t wait_ns = (uint64_t)p.timeout_us * 1000ull;
 
     // ------------------------------------------------------------------------------ producer
     if (warp == nw) {
         if (lane == 0) {
+            trace_mark(p, 10);
+            const int S = p.total_stages;
             const uint64_t pol = policy_evict_first();
-            bool lost = false;
-            const uint64_t wait_ns = (uint64_t)p.timeout_us * 1000ull;
-            for (int i = 0, s = s_begin; s < s_end; ++s, ++i) {
-                const int slot = i % nstage;
-                if (i >= nstage) {
-                    const uint32_t parity = (uint32_t)((i / nstage) - 1) & 1u;
-                    if (!mbar_wait_bounded(bar_base + 8 * (nstage + slot), parity, lost ? kShortWaitNs : wait_ns))
+            bool lost = false, first = true;
+            int slot = 0, round = 0;
+            if (p.producer_wait)
+                pdl_wait();
+            // The first `nstatic` stages of a block are fixed (block index + j * grid), so that the blocks
+            // do not all queue up on the counter at kernel start; the rest is claimed from the global
+            // counter, always one claim ahead of the stage being issued.
+            const unsigned int grid = gridDim.x;
+            const unsigned int nstatic = (unsigned int)max(1, S / (2 * (int)grid));
+            unsigned int issued = 0;
+            unsigned int pending = 0xfffffffeu;   // the first claim is made once the first stage is on its way
+            trace_mark(p, 11);
+            for (;;) {
+                if (round > 0) {
+                    if (!mbar_wait_bounded(sbase + kBarEmpty + 8 * slot, (uint32_t)(round - 1) & 1u,
+                                           lost ? kShortWaitNs : wait_ns))
                         lost = true;
                 }
+                const uint32_t full = sbase + kBarFull + 8 * slot;
+                StageDesc *desc = reinterpret_cast<StageDesc *>(smem + kDescOff) + slot;
+                unsigned int cur;
+                if (issued < nstatic) {
+                    cur = blockIdx.x + issued * grid;
+                } else {
+                    cur = pending;
+                    pending = nstatic * grid + atomicAdd(p.work, 1u);
+                }
+                ++issued;
+                if (cur >= (unsigned int)S) {
+                    desc->nrows = 0;            // end marker: a stage without data
+                    mbar_arrive(full);
+                    if (first)                  // nothing was issued: still take part in the counter protocol
+                        pending = nstatic * grid + atomicAdd(p.work, 1u);
+                    break;
+                }
                 int seg, row0, nrows;
-                decode_stage(p, rs, s, seg, row0, nrows);
-                const uint32_t full = bar_base + 8 * slot;
+                decode_stage(p, rs, (int)cur, seg, row0, nrows);
                 const uint32_t dst = ring_base + (uint32_t)slot * (uint32_t)p.slot_bytes;
+                desc->seg = seg;
+                desc->row0 = row0;
+                desc->nrows = nrows;
+                const uint32_t pbytes = (uint32_t)nrows * (uint32_t)rowbytes;
                 if (F32) {
                     const float *src = reinterpret_cast<const float *>(p.seg[seg].payload) + p.seg[seg].flat0 +
                                        (int64_t)row0 * p.n;
-                    const uint32_t bytes = (uint32_t)nrows * (uint32_t)rowbytes;
-                    mbar_arrive_expect_tx(full, bytes);
-                    bulk_g2s(dst, src, bytes, full, pol);
+                    mbar_arrive_expect_tx(full, pbytes);
+                    bulk_g2s(dst, src, pbytes, full, pol);
                 } else if (!p.paired) {
                     const int64_t flat = p.seg[seg].flat0 + (int64_t)row0 * p.n;
-                    const uint32_t pbytes = (uint32_t)nrows * (uint32_t)rowbytes;
                     const int64_t ga = (flat >> 8) & ~(int64_t)1;
                     const int64_t gl = (flat + pbytes - 1) >> 8;
                     const uint32_t hbytes = (uint32_t)(((gl - ga + 2) & ~(int64_t)1) * 8);
+                    desc->e0a = (int)(flat - ga * 256);
+                    desc->e0b = 0;
                     mbar_arrive_expect_tx(full, pbytes + hbytes);
                     bulk_g2s(dst, p.seg[seg].payload + flat, pbytes, full, pol);
                     bulk_g2s(dst + (uint32_t)p.hdr_off, p.seg[seg].hdr + ga, hbytes, full, pol);
                 } else {
-                    const uint32_t pbytes = (uint32_t)nrows * (uint32_t)rowbytes;
                     int64_t flat[2], ga[2];
                     uint32_t hbytes[2];
                     for (int h = 0; h < 2; ++h) {
@@ -220,25 +345,149 @@ __global__ void __launch_bounds__(MAXT, 2) matvec_ring_kernel(const __grid_const
                         const int64_t gl = (flat[h] + pbytes - 1) >> 8;
                         hbytes[h] = (uint32_t)(((gl - ga[h] + 2) & ~(int64_t)1) * 8);
                     }
+                    desc->e0a = (int)(flat[0] - ga[0] * 256);
+                    desc->e0b = (int)(flat[1] - ga[1] * 256);
                     mbar_arrive_expect_tx(full, 2 * pbytes + hbytes[0] + hbytes[1]);
                     for (int h = 0; h < 2; ++h) {
-                        bulk_g2s(dst + (uint32_t)(h * p.rpp) * (uint32_t)rowbytes, p.seg[h].payload + flat[h], pbytes,
+                        bulk_g2s(dst + (uint32_t)(h * (R / 2)) * (uint32_t)rowbytes, p.seg[h].payload + flat[h], pbytes,
                                  full, pol);
                         bulk_g2s(dst + (uint32_t)p.hdr_off + (uint32_t)(h * p.half_hdr), p.seg[h].hdr + ga[h], hbytes[h],
                                  full, pol);
                     }
                 }
+                if (first) {
+                    trace_mark(p, 1);
+                    first = false;
+                    pending = nstatic * grid + atomicAdd(p.work, 1u);
+                }
+                if (++slot == nstage) {
+                    slot = 0;
+                    ++round;
+                }
+            }
+            trace_mark(p, 2);
+            // The block that learns last that the work has run out re-arms the counters for the next launch.
+            __threadfence();
+            if (pending != 0xffffffffu && atomicAdd(p.work + 1, 1u) == gridDim.x - 1) {
+                __threadfence();
+                p.work[0] = 0;
+                p.work[1] = 0;
+                __threadfence();
             }
             if (lost)
                 atomicOr(&p.state->status, L2J_DS_WAIT_TIMEOUT);
         }
         return;
     }
-    if (warp > nw)
+
+    // ------------------------------------------------------------------------------ epilogue warp
+    if (warp == nw + 1) {
+        pdl_wait();
+        const int pos = __ldcg(&p.state->cur_pos);
+        bool lost = (__ldcg(&p.state->status) & L2J_DS_WAIT_TIMEOUT) != 0;
+        const bool lost_before = lost;
+        float *rope_c = reinterpret_cast<float *>(smem + kRopeOff);
+        float *rope_s = rope_c + 64;
+        if (p.epilogue == EPI_QKV_ROPE) {
+            const int half = p.head >> 1;
+            for (int i = lane; i < half; i += 32) {
+                rope_c[i] = __ldg(p.rope_cos + (int64_t)pos * half + i);
+                rope_s[i] = __ldg(p.rope_sin + (int64_t)pos * half + i);
+            }
+            __syncwarp();
+        }
+        float best_v = -FLT_MAX;
+        int best_i = 0x7fffffff;
+        int rb = 0, rround = 0;
+        if (lane == 0)
+            trace_mark(p, 15);
+        for (;;) {
+            if (!mbar_wait_bounded(sbase + kBarRedFull + 8 * rb, (uint32_t)rround & 1u, lost ? kShortWaitNs : wait_ns))
+                lost = true;
+            const int *rh = reinterpret_cast<const int *>(smem + kRedOff + rb * kRedStride);
+            const int seg = rh[0], row0 = rh[1], nrows = rh[2];
+            if (nrows <= 0 || (lost && !lost_before))
+                break;
+            const float *red = reinterpret_cast<const float *>(rh + 4);
+            if (p.epilogue == EPI_QKV_ROPE) {
+                if (lane < (nrows >> 1)) {
+                    float v0 = 0.f, v1 = 0.f;
+                    for (int w = 0; w < p.wpr; ++w) {
+                        v0 += red[(2 * lane) * p.wpr + w];
+                        v1 += red[(2 * lane + 1) * p.wpr + w];
+                    }
+                    epi_qkv_pair(p, seg, row0 + 2 * lane, v0, v1, pos, rope_c, rope_s);
+                }
+            } else if (p.epilogue == EPI_SWIGLU) {
+                if (lane < nrows) {
+                    float v1 = 0.f, v3 = 0.f;
+                    for (int w = 0; w < p.wpr; ++w) {
+                        v1 += red[lane * p.wpr + w];
+                        v3 += red[(R / 2 + lane) * p.wpr + w];
+                    }
+                    p.y[row0 + lane] = epi_swiglu(v1, v3);
+                }
+            } else if (lane < nrows) {
+                float a = 0.f;
+                for (int w = 0; w < p.wpr; ++w)
+                    a += red[lane * p.wpr + w];
+                const int row = row0 + lane;
+                if (p.epilogue == EPI_RESIDUAL) {
+                    atomicAdd(p.y + row, a);   // one add per element and launch: a reduction without a read round trip
+                } else {
+                    p.y[row] = a;
+                    if (p.epilogue == EPI_LOGITS && (a > best_v || (a == best_v && row < best_i))) {
+                        best_v = a;
+                        best_i = row;
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0)
+                mbar_arrive(sbase + kBarRedEmpty + 8 * rb);
+            if (++rb == kRedBufs) {
+                rb = 0;
+                ++rround;
+            }
+        }
+        if (lost && !lost_before && lane == 0)
+            atomicOr(&p.state->status, L2J_DS_WAIT_TIMEOUT);
+        if (lane == 0) {
+            trace_mark(p, 6);
+            if (p.trace)
+                p.trace[blockIdx.x * 16 + 8] = global_timer_ns();
+        }
+        if (p.epilogue == EPI_LOGITS) {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, best_v, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+                if (ov > best_v || (ov == best_v && oi < best_i)) {
+                    best_v = ov;
+                    best_i = oi;
+                }
+            }
+            int last = 0;
+            if (lane == 0) {
+                p.blk_val[blockIdx.x] = best_v;
+                p.blk_idx[blockIdx.x] = best_i;
+                __threadfence();
+                const unsigned int ticket = atomicAdd(&p.state->cls_counter, 1u);
+                last = (ticket == gridDim.x - 1);
+            }
+            last = __shfl_sync(0xffffffffu, last, 0);
+            if (last) {
+                __threadfence();
+                finish_argmax_warp(p, gridDim.x, lane);
+            }
+        }
+        return;
+    }
+    if (warp > nw + 1)
         return;
 
     // ------------------------------------------------------------------------------ consumers
-    const int rsub = warp / p.wpr;   // row of the pass this warp works on
+    const int rsub = warp / p.wpr;   // which of the rpp concurrent rows this warp works on
     const int wi = warp - rsub * p.wpr;
     const int nchunks = p.n / EPC;
     int chunk[CPT];
@@ -249,217 +498,222 @@ __global__ void __launch_bounds__(MAXT, 2) matvec_ring_kernel(const __grid_const
         cvalid[k] = chunk[k] < nchunks;
     }
 
-    pdl_wait();   // the input vector and the position come from the previous kernel
+    pdl_wait();   // the input vector comes from the previous kernel
+    if (tid == 0)
+        trace_mark(p, 12);
 
-    const int pos = __ldcg(&p.state->cur_pos);
+    // ---- prologue: x -> registers with RMSNorm applied (RootMeanSquare.java:25-35,
+    //      WeightNormalizeAndScale.java:71-74), then fixed-point limbs for the u8 path.
+    //      All global loads are issued before the single block-wide reduction.
     float xr[CPT][EPC];
-    float xs[CPT];
+    float wr[CPT][EPC];
+    const bool has_rms = p.rms_w != nullptr;
 #pragma unroll
     for (int k = 0; k < CPT; ++k) {
 #pragma unroll
         for (int e = 0; e < EPC; e += 4) {
             float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (cvalid[k])
+            float4 w = make_float4(1.f, 1.f, 1.f, 1.f);
+            if (cvalid[k]) {
                 v = __ldcg(reinterpret_cast<const float4 *>(p.x_in + (int64_t)chunk[k] * EPC + e));
-            xr[k][e] = v.x;
-            xr[k][e + 1] = v.y;
-            xr[k][e + 2] = v.z;
-            xr[k][e + 3] = v.w;
+                if (has_rms)
+                    w = __ldg(reinterpret_cast<const float4 *>(p.rms_w + (int64_t)chunk[k] * EPC + e));
+            }
+            xr[k][e] = v.x; xr[k][e + 1] = v.y; xr[k][e + 2] = v.z; xr[k][e + 3] = v.w;
+            wr[k][e] = w.x; wr[k][e + 1] = w.y; wr[k][e + 2] = w.z; wr[k][e + 3] = w.w;
         }
     }
-    if (p.rms_w) {
-        // RootMeanSquare.java:25-35 and WeightNormalizeAndScale.java:71-74, on registers
-        float part = 0.f;
-        if (rsub == 0) {
+    bool lost = (__ldcg(&p.state->status) & L2J_DS_WAIT_TIMEOUT) != 0;
+    const bool lost_before = lost;
+    float *scratch = reinterpret_cast<float *>(smem + kScratchOff);
+    float ssq = 0.f, amax = 0.f;
 #pragma unroll
-            for (int k = 0; k < CPT; ++k)
+    for (int k = 0; k < CPT; ++k)
 #pragma unroll
-                for (int e = 0; e < EPC; ++e)
-                    part = fmaf(xr[k][e], xr[k][e], part);
+        for (int e = 0; e < EPC; ++e) {
+            ssq = fmaf(xr[k][e], xr[k][e], ssq);
+            amax = fmaxf(amax, fabsf(xr[k][e]));
         }
-        part = warp_sum(part);
-        if (rsub == 0 && lane == 0)
-            ssbuf[wi] = part;
+    if (tid == 0)
+        trace_mark(p, 13);
+    if (has_rms || !F32) {
+        ssq = warp_sum(ssq);
+        amax = warp_max(amax);
+        if (rsub == 0 && lane == 0) {
+            scratch[wi] = ssq;
+            scratch[32 + wi] = amax;
+        }
         named_barrier_sync(1, ncons);
-        float tot = 0.f;
-        for (int i = 0; i < p.wpr; ++i)
-            tot += ssbuf[i];
-        tot = __fdiv_rn(tot, (float)p.n);
+        ssq = 0.f;
+        amax = 0.f;
+        for (int i = 0; i < p.wpr; ++i) {
+            ssq += scratch[i];
+            amax = fmaxf(amax, scratch[32 + i]);
+        }
+        if (tid == 0)
+            trace_mark(p, 14);
+    }
+    if (has_rms) {
+        float tot = __fdiv_rn(ssq, (float)p.n);
         tot = __fadd_rn(tot, 1e-5f);
         const float ss = __fdiv_rn(1.0f, __fsqrt_rn(tot));
 #pragma unroll
-        for (int k = 0; k < CPT; ++k) {
+        for (int k = 0; k < CPT; ++k)
 #pragma unroll
-            for (int e = 0; e < EPC; e += 4) {
-                float4 w = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (cvalid[k])
-                    w = __ldg(reinterpret_cast<const float4 *>(p.rms_w + (int64_t)chunk[k] * EPC + e));
-                xr[k][e] = __fmul_rn(w.x, __fmul_rn(ss, xr[k][e]));
-                xr[k][e + 1] = __fmul_rn(w.y, __fmul_rn(ss, xr[k][e + 1]));
-                xr[k][e + 2] = __fmul_rn(w.z, __fmul_rn(ss, xr[k][e + 2]));
-                xr[k][e + 3] = __fmul_rn(w.w, __fmul_rn(ss, xr[k][e + 3]));
+            for (int e = 0; e < EPC; ++e)
+                xr[k][e] = __fmul_rn(wr[k][e], __fmul_rn(ss, xr[k][e]));
+        amax = amax * ss * p.rms_wmax * 1.000001f;   // bound of |w * (ss * x)| from max|x| and max|w|
+    }
+
+    uint32_t xl[F32 ? 1 : CPT][4][4];   // [chunk][word of 4 elements][limb]
+    float xs[CPT];                       // sum of the chunk's x (for the group minimum term)
+    float inv = 1.0f;                    // value of one fixed-point unit
+    if constexpr (!F32) {
+        int ex = 0;
+        if (amax > 0.f && amax < 3.0e38f)
+            frexpf(amax, &ex);             // amax < 2^ex
+        ex = max(-90, min(126, ex));
+        const float f = __int_as_float((127 + 30 - ex) << 23);   // 2^(30 - ex)
+        inv = __int_as_float((127 + ex - 30) << 23);             // 2^(ex - 30)
+#pragma unroll
+        for (int k = 0; k < CPT; ++k) {
+            float s = 0.f;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                uint32_t z[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    s += xr[k][4 * q + j];
+                    const int X = __float2int_rn(xr[k][4 * q + j] * f);      // |X| <= 2^30
+                    z[j] = ((uint32_t)X + 0x00808080u) ^ 0x00808080u;        // bytes = balanced signed limbs
+                }
+                // 4x4 byte transpose in 8 permutes: limb l of the four elements ends up in word l
+                const uint32_t t0 = __byte_perm(z[0], z[1], 0x5140);   // z0.b0 z1.b0 z0.b1 z1.b1
+                const uint32_t t1 = __byte_perm(z[0], z[1], 0x7362);   // z0.b2 z1.b2 z0.b3 z1.b3
+                const uint32_t t2 = __byte_perm(z[2], z[3], 0x5140);
+                const uint32_t t3 = __byte_perm(z[2], z[3], 0x7362);
+                xl[k][q][0] = __byte_perm(t0, t2, 0x5410);
+                xl[k][q][1] = __byte_perm(t0, t2, 0x7632);
+                xl[k][q][2] = __byte_perm(t1, t3, 0x5410);
+                xl[k][q][3] = __byte_perm(t1, t3, 0x7632);
             }
+            xs[k] = s;
         }
     }
-#pragma unroll
-    for (int k = 0; k < CPT; ++k) {
-        float s = 0.f;
-#pragma unroll
-        for (int e = 0; e < EPC; ++e)
-            s += xr[k][e];
-        xs[k] = s;
-    }
 
-    // After one wait has run out (here or in an earlier kernel of the stream) later waits give up
-    // almost at once, so a broken copy costs one timeout, not one per stage.
-    bool lost = (__ldcg(&p.state->status) & L2J_DS_WAIT_TIMEOUT) != 0;
-    const bool lost_before = lost;
-    const uint64_t wait_ns = (uint64_t)p.timeout_us * 1000ull;
-    float best_v = -FLT_MAX;   // arg-max candidates of the epilogue threads (EPI_LOGITS)
-    int best_i = 0x7fffffff;
-
-    for (int i = 0, s = s_begin; s < s_end; ++s, ++i) {
-        const int slot = i % nstage;
-        const uint32_t parity = (uint32_t)(i / nstage) & 1u;
-        if (!mbar_wait_bounded(bar_base + 8 * slot, parity, lost ? kShortWaitNs : wait_ns))
+    if (tid == 0)
+        trace_mark(p, 3);
+    int slot = 0, round = 0, rb = 0, rround = 0;
+    bool first = true;
+    for (;;) {
+        if (!mbar_wait_bounded(sbase + kBarFull + 8 * slot, (uint32_t)round & 1u, lost ? kShortWaitNs : wait_ns))
             lost = true;
-        int seg, row0, nrows;
-        decode_stage(p, rs, s, seg, row0, nrows);
+        if (tid == 0 && first) {
+            trace_mark(p, 4);
+            first = false;
+        }
+        const StageDesc d = *(reinterpret_cast<const StageDesc *>(smem + kDescOff) + slot);
+        const bool done = d.nrows <= 0 || (lost && !lost_before);
         const uint8_t *slot_ptr = smem + kSmemHeader + (size_t)slot * p.slot_bytes;
 
-        float acc[2] = {0.f, 0.f};
+        float v[RT];
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            const int r = h * p.rpp + rsub;   // row slot inside the stage
-            const bool rowvalid = p.paired ? (rsub < nrows) : (r < nrows);
-            if (rowvalid) {
+        for (int t = 0; t < RT; ++t) {
+            v[t] = 0.f;
+            const int r = rsub + t * p.rpp;                      // row of the stage in shared memory
+            const int half = (p.paired && t >= RT / 2) ? 1 : 0;  // second half of a paired stage: the partner matrix
+            const int local = r - half * (R / 2);
+            if (!done && local < d.nrows) {
                 const uint8_t *rowp = slot_ptr + (size_t)r * rowbytes;
                 if constexpr (F32) {
+                    float a = 0.f;
 #pragma unroll
                     for (int k = 0; k < CPT; ++k) {
                         if (cvalid[k]) {
                             const float4 w = *reinterpret_cast<const float4 *>(rowp + (size_t)chunk[k] * 16);
-                            float a = acc[h];
                             a = fmaf(w.x, xr[k][0], a);
                             a = fmaf(w.y, xr[k][1], a);
                             a = fmaf(w.z, xr[k][2], a);
                             a = fmaf(w.w, xr[k][3], a);
-                            acc[h] = a;
                         }
                     }
+                    v[t] = a;
                 } else {
-                    int e0;
-                    const float2 *hp;
-                    if (!p.paired) {
-                        const int64_t flat = p.seg[seg].flat0 + (int64_t)row0 * p.n;
-                        const int64_t ga = (flat >> 8) & ~(int64_t)1;
-                        e0 = (int)(flat - ga * 256) + r * p.n;
-                        hp = reinterpret_cast<const float2 *>(slot_ptr + p.hdr_off);
-                    } else {
-                        const int64_t flat = p.seg[h].flat0 + (int64_t)row0 * p.n;
-                        const int64_t ga = (flat >> 8) & ~(int64_t)1;
-                        e0 = (int)(flat - ga * 256) + rsub * p.n;
-                        hp = reinterpret_cast<const float2 *>(slot_ptr + p.hdr_off + h * p.half_hdr);
-                    }
+                    const int e0 = (half ? d.e0b : d.e0a) + local * p.n;
+                    const float2 *hp = reinterpret_cast<const float2 *>(slot_ptr + p.hdr_off + half * p.half_hdr);
+                    float accd = 0.f, accm = 0.f;
 #pragma unroll
                     for (int k = 0; k < CPT; ++k) {
                         if (cvalid[k]) {
                             const uint4 w = *reinterpret_cast<const uint4 *>(rowp + (size_t)chunk[k] * 16);
                             const float2 ms = hp[(e0 + chunk[k] * 16) >> 8];
-                            const float d = dot16_u8(w, xr[k]);
-                            acc[h] = fmaf(ms.y, d, fmaf(ms.x, xs[k], acc[h]));
+                            int a0 = 0, a1 = 0, a2 = 0, a3 = 0;
+                            a0 = dp4a_u8s8(w.x, xl[k][0][0], a0);
+                            a1 = dp4a_u8s8(w.x, xl[k][0][1], a1);
+                            a2 = dp4a_u8s8(w.x, xl[k][0][2], a2);
+                            a3 = dp4a_u8s8(w.x, xl[k][0][3], a3);
+                            a0 = dp4a_u8s8(w.y, xl[k][1][0], a0);
+                            a1 = dp4a_u8s8(w.y, xl[k][1][1], a1);
+                            a2 = dp4a_u8s8(w.y, xl[k][1][2], a2);
+                            a3 = dp4a_u8s8(w.y, xl[k][1][3], a3);
+                            a0 = dp4a_u8s8(w.z, xl[k][2][0], a0);
+                            a1 = dp4a_u8s8(w.z, xl[k][2][1], a1);
+                            a2 = dp4a_u8s8(w.z, xl[k][2][2], a2);
+                            a3 = dp4a_u8s8(w.z, xl[k][2][3], a3);
+                            a0 = dp4a_u8s8(w.w, xl[k][3][0], a0);
+                            a1 = dp4a_u8s8(w.w, xl[k][3][1], a1);
+                            a2 = dp4a_u8s8(w.w, xl[k][3][2], a2);
+                            a3 = dp4a_u8s8(w.w, xl[k][3][3], a3);
+                            float dsum = fmaf((float)a1, 256.0f, (float)a0);
+                            dsum = fmaf((float)a2, 65536.0f, dsum);
+                            dsum = fmaf((float)a3, 16777216.0f, dsum);
+                            accd = fmaf(ms.y, dsum, accd);
+                            accm = fmaf(ms.x, xs[k], accm);
                         }
                     }
+                    v[t] = fmaf(inv, accd, accm);
                 }
             }
         }
-        const float v = warp_sum2(acc[0], acc[1], lane);
+        const float tot = warp_sum_rows<RT>(v, lane);
         __syncwarp();
         if (lane == 0)
-            mbar_arrive(bar_base + 8 * (nstage + slot));   // this warp is done with the slot
-        float *redb = red + (i & 1) * (2 * nw);
-        if (lane == 0)
-            redb[rsub * p.wpr + wi] = v;
-        if (lane == 16)
-            redb[(p.rpp + rsub) * p.wpr + wi] = v;
-        named_barrier_sync(1, ncons);
-
-        // ---- epilogue: a few threads finish the rows of this stage
-        if (p.epilogue == EPI_QKV_ROPE) {
-            if (tid < (nrows >> 1)) {
-                float v0 = 0.f, v1 = 0.f;
-                for (int w = 0; w < p.wpr; ++w) {
-                    v0 += redb[(2 * tid) * p.wpr + w];
-                    v1 += redb[(2 * tid + 1) * p.wpr + w];
-                }
-                epi_qkv_pair(p, seg, row0 + 2 * tid, v0, v1, pos);
-            }
-        } else if (p.epilogue == EPI_SWIGLU) {
-            if (tid < nrows) {
-                float v1 = 0.f, v3 = 0.f;
-                for (int w = 0; w < p.wpr; ++w) {
-                    v1 += redb[tid * p.wpr + w];
-                    v3 += redb[(p.rpp + tid) * p.wpr + w];
-                }
-                p.y[row0 + tid] = epi_swiglu(v1, v3);
-            }
-        } else {
-            if (tid < nrows) {
-                float a = 0.f;
-                for (int w = 0; w < p.wpr; ++w)
-                    a += redb[tid * p.wpr + w];
-                const int row = row0 + tid;
-                if (p.epilogue == EPI_RESIDUAL) {
-                    p.y[row] = __fadd_rn(__ldcg(p.y + row), a);
-                } else {
-                    p.y[row] = a;
-                    if (p.epilogue == EPI_LOGITS && a > best_v) {   // rows ascend: first maximum stays
-                        best_v = a;
-                        best_i = row;
-                    }
-                }
-            }
+            mbar_arrive(sbase + kBarEmpty + 8 * slot);   // this warp is done with the ring slot
+        if (rround > 0) {
+            if (!mbar_wait_bounded(sbase + kBarRedEmpty + 8 * rb, (uint32_t)(rround - 1) & 1u, lost ? kShortWaitNs : wait_ns))
+                lost = true;
         }
-    }
-
-    if (lost && !lost_before) {
-        atomicOr(&p.state->status, L2J_DS_WAIT_TIMEOUT);
-        // give copies that may still be in flight a last bounded chance to land before the block exits
-        const int issued = s_end - s_begin;
-        for (int i = max(0, issued - nstage); i < issued; ++i)
-            mbar_wait_bounded(bar_base + 8 * (i % nstage), (uint32_t)(i / nstage) & 1u, wait_ns);
-    }
-
-    if (p.epilogue == EPI_LOGITS) {
-        float *bvs = reinterpret_cast<float *>(smem + kBestOff);
-        int *bis = reinterpret_cast<int *>(smem + kBestOff + 128);
-        __shared__ int is_last;
-        if (tid < rs) {
-            bvs[tid] = best_v;
-            bis[tid] = best_i;
-        }
-        named_barrier_sync(1, ncons);
+        int *rh = reinterpret_cast<int *>(smem + kRedOff + rb * kRedStride);
+        float *red = reinterpret_cast<float *>(rh + 4);
         if (tid == 0) {
-            float bv = -FLT_MAX;
-            int bi = 0x7fffffff;
-            for (int t = 0; t < rs; ++t) {
-                if (bvs[t] > bv || (bvs[t] == bv && bis[t] < bi)) {
-                    bv = bvs[t];
-                    bi = bis[t];
-                }
-            }
-            p.blk_val[blockIdx.x] = bv;
-            p.blk_idx[blockIdx.x] = bi;
-            __threadfence();
-            const unsigned int ticket = atomicAdd(&p.state->cls_counter, 1u);
-            is_last = (ticket == gridDim.x - 1);
+            rh[0] = d.seg;
+            rh[1] = d.row0;
+            rh[2] = done ? 0 : d.nrows;
         }
-        named_barrier_sync(1, ncons);
-        if (is_last && warp == 0) {
-            __threadfence();
-            finish_argmax_warp(p, gridDim.x, lane);
+        if ((lane & (32 / RT - 1)) == 0) {
+            const int t = lane / (32 / RT);
+            red[(rsub + t * p.rpp) * p.wpr + wi] = tot;
+        }
+        __syncwarp();
+        if (lane == 0)
+            mbar_arrive(sbase + kBarRedFull + 8 * rb);
+        if (done)
+            break;
+        if (++slot == nstage) {
+            slot = 0;
+            ++round;
+        }
+        if (++rb == kRedBufs) {
+            rb = 0;
+            ++rround;
         }
     }
+    if (tid == 0)
+        trace_mark(p, 5);
+    if (p.pdl_mode == 1)
+        pdl_launch_dependents();
+    if (lost && !lost_before)
+        atomicOr(&p.state->status, L2J_DS_WAIT_TIMEOUT);
 }
 
 MvPlan plan_matvec(int n, bool f32, bool paired)
@@ -477,17 +731,27 @@ MvPlan plan_matvec(int n, bool f32, bool paired)
         const int wpr = (nchunks + 32 * cpt - 1) / (32 * cpt);
         if (wpr > maxnw)
             continue;
-        int rpp = maxnw / wpr;
-        if (rpp > 16)
-            rpp = 16;
-        while (rpp > 1 && 2 * rpp * rowbytes > 24 * 1024)
-            --rpp;
+        // One group of wpr warps per block and as many rows per thread as make a stage of about 32 KB;
+        // only short rows get several concurrent row groups.
+        int rt = 8;
+        while (rt > 2 && rt * rowbytes > 36 * 1024)
+            rt /= 2;
+        int rpp = 1;
+        while (2 * rpp * wpr <= maxnw && 2 * rpp * rt <= 32 && 2 * rpp * rt * rowbytes <= 32 * 1024 &&
+               rpp * rt * rowbytes < 16 * 1024)
+            rpp *= 2;
+        if (const char *e = getenv("L2J_WIDE")) {   // experiment: two row groups and half the rows per thread
+            if (atoi(e) && rpp == 1 && rt >= 4 && 2 * wpr <= maxnw) {
+                rpp = 2;
+                rt /= 2;
+            }
+        }
         int half_hdr = 0;
         if (!f32) {
-            half_hdr = (((rpp * n + 255) / 256) + 4) * 8;
+            half_hdr = ((((rt / 2) * rpp * n + 255) / 256) + 4) * 8;
             half_hdr = (half_hdr + 15) & ~15;
         }
-        const int payload = 2 * rpp * rowbytes;
+        const int payload = rt * rpp * rowbytes;
         const int slot = (payload + 2 * half_hdr + 127) & ~127;
         int nstage = kMaxSmemRing / slot;
         if (nstage > 16)
@@ -495,14 +759,15 @@ MvPlan plan_matvec(int n, bool f32, bool paired)
         if (nstage < 2)
             continue;
         pl.cpt = cpt;
+        pl.rt = rt;
         pl.rpp = rpp;
         pl.wpr = wpr;
         pl.nstage = nstage;
         pl.slot_bytes = slot;
         pl.hdr_off = payload;
         pl.half_hdr = half_hdr;
-        pl.threads = (rpp * wpr + 1) * 32;
-        pl.smem_bytes = kSmemHeader + nstage * slot;
+        pl.threads = (rpp * wpr + 2) * 32;
+        pl.smem_bytes = kSmemHeader + nstage * slot;   // header + ring
         pl.ok = true;
         (void)paired;
         return pl;
@@ -510,10 +775,10 @@ MvPlan plan_matvec(int n, bool f32, bool paired)
     return pl;
 }
 
-template <bool F32, int CPT, int MAXT>
+template <bool F32, int CPT, int RT, int MAXT>
 static cudaError_t launch_ring_t(const LaunchCfg &lc, const MvPlan &plan, const MvParams &p)
 {
-    auto kern = matvec_ring_kernel<F32, CPT, MAXT>;
+    auto kern = matvec_ring_kernel<F32, CPT, RT, MAXT>;
     if (plan.threads > MAXT)
         return cudaErrorInvalidConfiguration;
     cudaLaunchConfig_t cfg{};
@@ -529,44 +794,41 @@ static cudaError_t launch_ring_t(const LaunchCfg &lc, const MvPlan &plan, const 
     return cudaLaunchKernelEx(&cfg, kern, p);
 }
 
-template <bool F32, int CPT, int MAXT>
+template <bool F32, int CPT, int RT, int MAXT>
 static cudaError_t prepare_ring_t()
 {
-    auto kern = matvec_ring_kernel<F32, CPT, MAXT>;
+    auto kern = matvec_ring_kernel<F32, CPT, RT, MAXT>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemHeader + kMaxSmemRing);
     if (e != cudaSuccess)
         return e;
     return cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
 }
 
+// Instantiations: (FP32 weights, chunks per thread, rows per thread and stage, largest block).  The
+// block bound sets the register budget so that two blocks fit the register file of an SM.
+#define L2J_RING_VARIANTS(X) \
+    X(true, 1, 2, 576) X(true, 1, 4, 576) X(true, 1, 8, 576) X(true, 2, 2, 576) X(true, 2, 4, 576) X(true, 2, 8, 576) \
+    X(true, 3, 2, 576) X(true, 3, 4, 576) X(true, 3, 8, 576) \
+    X(false, 1, 2, 320) X(false, 1, 4, 320) X(false, 1, 8, 320) X(false, 1, 2, 576) X(false, 1, 4, 576) X(false, 1, 8, 576) \
+    X(false, 2, 2, 384) X(false, 2, 4, 384) X(false, 2, 8, 384) X(false, 3, 2, 352) X(false, 3, 4, 352) X(false, 3, 8, 352)
+
 // Opts the ring kernels of the current device into their dynamic shared memory size.  Call once
 // per device before the first launch (and outside stream capture).
 cudaError_t prepare_kernels()
 {
     cudaError_t e;
-    if ((e = prepare_ring_t<true, 1, 544>()) != cudaSuccess) return e;
-    if ((e = prepare_ring_t<true, 2, 544>()) != cudaSuccess) return e;
-    if ((e = prepare_ring_t<true, 3, 544>()) != cudaSuccess) return e;
-    if ((e = prepare_ring_t<false, 1, 544>()) != cudaSuccess) return e;
-    if ((e = prepare_ring_t<false, 2, 352>()) != cudaSuccess) return e;
-    if ((e = prepare_ring_t<false, 3, 320>()) != cudaSuccess) return e;
+#define X(F, C, R, T) if ((e = prepare_ring_t<F, C, R, T>()) != cudaSuccess) return e;
+    L2J_RING_VARIANTS(X)
+#undef X
     return cudaSuccess;
 }
 
 cudaError_t launch_matvec_ring(const LaunchCfg &lc, const MvPlan &plan, bool f32, const MvParams &p)
 {
-    if (f32) {
-        switch (plan.cpt) {
-        case 1: return launch_ring_t<true, 1, 544>(lc, plan, p);
-        case 2: return launch_ring_t<true, 2, 544>(lc, plan, p);
-        default: return launch_ring_t<true, 3, 544>(lc, plan, p);
-        }
-    }
-    switch (plan.cpt) {
-    case 1: return launch_ring_t<false, 1, 544>(lc, plan, p);
-    case 2: return launch_ring_t<false, 2, 352>(lc, plan, p);
-    default: return launch_ring_t<false, 3, 320>(lc, plan, p);
-    }
+#define X(F, C, R, T) if (f32 == F && plan.cpt == C && plan.rt == R && plan.threads <= T) return launch_ring_t<F, C, R, T>(lc, plan, p);
+    L2J_RING_VARIANTS(X)
+#undef X
+    return cudaErrorInvalidConfiguration;
 }
 
 // =============================================================================================
@@ -630,18 +892,21 @@ cudaError_t launch_begin(const LaunchCfg &lc, SeqState *state, const Cmd *cmd, c
 
 // =============================================================================================
 // attention_kernel: single-query attention for all heads, positions split across blocks
+//
+// One pass with an online softmax: every warp (lane group) streams its share of the positions,
+// loading K and V rows together so that a block pays one memory round trip, not two.  The lane
+// groups of a block are merged through shared memory; if the block covers all positions of its
+// head the result is written directly, otherwise (m, l, o) partials go to scratch and the last
+// block of the head to arrive merges them in a fixed order (bitwise reproducible).
 // =============================================================================================
 
 constexpr int kAttnThreads = 256;
 constexpr int kAttnWarps = kAttnThreads / 32;
+constexpr int kAttnMinChunk = 64;   // positions per block before the work is split further
 
 __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const __grid_constant__ AttnParams p)
 {
-    extern __shared__ __align__(16) float asmem[];
-    float *scores = asmem;                          // [chunk_max]
-    float *vred = asmem + p.chunk_max;              // [kAttnWarps][head]
-    __shared__ float s_red[kAttnWarps];
-    __shared__ float s_bcast;
+    extern __shared__ __align__(16) float asmem[];   // [slots][head + 4]: o, then m, l (16-byte aligned rows)
     __shared__ int s_last;
 
     const int h = blockIdx.x, sp = blockIdx.y;
@@ -651,9 +916,12 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const __grid_co
     int gw = 1;
     while (gw < lpp)
         gw <<= 1;                                   // lane-group width (power of two, <= 32)
-    const int ppw = 32 / gw;                        // positions per warp and step
+    const int ppw = 32 / gw;                        // lane groups (positions in flight) per warp
     const int g = lane / gw, li = lane - g * gw;
     const bool active = li < lpp;
+    const int nslots = kAttnWarps * ppw;
+    const int slot = warp * ppw + g;
+    const int sstride = head + 4;
 
     pdl_launch_dependents();
     pdl_wait();
@@ -661,10 +929,13 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const __grid_co
     const int pos = p.pos_override >= 0 ? p.pos_override : __ldcg(&p.state->cur_pos);
     const int npos = pos + 1;
     int chunk = (npos + p.nsplit - 1) / p.nsplit;
-    if (chunk > p.chunk_max)
-        chunk = p.chunk_max;                        // cannot happen for pos < seq_len
+    if (chunk < kAttnMinChunk)
+        chunk = kAttnMinChunk;
+    const int nact = (npos + chunk - 1) / chunk;    // blocks of this head that have work
+    if (sp >= nact)
+        return;
     const int t0 = sp * chunk;
-    const int cnt = max(0, min(npos, t0 + chunk) - t0);
+    const int cnt = min(npos, t0 + chunk) - t0;
     const int kvh = h / p.kv_mul;
     const float *kb = p.k_cache + ((int64_t)kvh * p.seq_len + t0) * head;
     const float *vb = p.v_cache + ((int64_t)kvh * p.seq_len + t0) * head;
@@ -673,136 +944,117 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const __grid_co
     if (active)
         q4 = __ldcg(reinterpret_cast<const float4 *>(p.q + (int64_t)h * head + 4 * li));
     const float sq = sqrtf((float)head);
-    const int stride = kAttnWarps * ppw;
 
-    // ---- scores: AttentionLoop.java:29-54
-    for (int ib = warp * ppw; ib < cnt; ib += 4 * stride) {
-        float4 kk[4];
+    float m = -INFINITY, l = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int ib = 0; ib < cnt; ib += 4 * nslots) {   // uniform trip count for the whole block
+        float4 kk[4], vv[4];
+        int idx[4];
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
-            const int idx = ib + g + u * stride;
+            idx[u] = ib + u * nslots + slot;
             kk[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (active && idx < cnt)
-                kk[u] = __ldcg(reinterpret_cast<const float4 *>(kb + (int64_t)idx * head + 4 * li));
+            vv[u] = kk[u];
+            if (active && idx[u] < cnt) {
+                kk[u] = __ldcg(reinterpret_cast<const float4 *>(kb + (int64_t)idx[u] * head + 4 * li));
+                vv[u] = __ldcg(reinterpret_cast<const float4 *>(vb + (int64_t)idx[u] * head + 4 * li));
+            }
         }
+        float s[4];
+        float mloc = -INFINITY;
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
-            const int idx = ib + g + u * stride;
             float d = kk[u].x * q4.x;
             d = fmaf(kk[u].y, q4.y, d);
             d = fmaf(kk[u].z, q4.z, d);
             d = fmaf(kk[u].w, q4.w, d);
             for (int o = gw >> 1; o > 0; o >>= 1)
                 d += __shfl_xor_sync(0xffffffffu, d, o);
-            if (li == 0 && idx < cnt)
-                scores[idx] = __fdiv_rn(d, sq);
+            s[u] = idx[u] < cnt ? __fdiv_rn(d, sq) : -INFINITY;   // AttentionLoop.java:48
+            mloc = fmaxf(mloc, s[u]);
+        }
+        if (mloc > -INFINITY) {
+            const float mn = fmaxf(m, mloc);
+            const float sc = expf(m - mn);            // 0 on the first round (m = -inf)
+            l *= sc;
+            acc.x *= sc; acc.y *= sc; acc.z *= sc; acc.w *= sc;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const float pw = expf(s[u] - mn);     // 0 for the padded positions
+                l += pw;
+                acc.x = fmaf(pw, vv[u].x, acc.x);
+                acc.y = fmaf(pw, vv[u].y, acc.y);
+                acc.z = fmaf(pw, vv[u].z, acc.z);
+                acc.w = fmaf(pw, vv[u].w, acc.w);
+            }
+            m = mn;
         }
     }
-    __syncthreads();
-
-    // ---- softmax numerators with the block's own maximum: ExpSumNormalize.java:25-38
-    float m = -INFINITY;
-    for (int i = tid; i < cnt; i += kAttnThreads)
-        m = fmaxf(m, scores[i]);
-    m = warp_max(m);
-    if (lane == 0)
-        s_red[warp] = m;
-    __syncthreads();
-    if (tid == 0) {
-        float mm = s_red[0];
-        for (int w = 1; w < kAttnWarps; ++w)
-            mm = fmaxf(mm, s_red[w]);
-        s_bcast = mm;
+    float *mine = asmem + slot * sstride;
+    if (active)
+        *reinterpret_cast<float4 *>(mine + 4 * li) = acc;
+    if (li == 0) {
+        mine[head] = m;
+        mine[head + 1] = l;
     }
     __syncthreads();
-    m = s_bcast;
-    float l = 0.f;
-    for (int i = tid; i < cnt; i += kAttnThreads) {
-        const float e = expf(scores[i] - m);
-        scores[i] = e;
-        l += e;
-    }
-    l = warp_sum(l);
-    __syncthreads();   // s_red reuse, and the numerators are visible to every warp
-    if (lane == 0)
-        s_red[warp] = l;
-    __syncthreads();
-    l = 0.f;
-    for (int w = 0; w < kAttnWarps; ++w)
-        l += s_red[w];
 
-    // ---- weighted values: AccumWeightedValue.java:40-88
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int ib = warp * ppw; ib < cnt; ib += 4 * stride) {
-        float4 vv[4];
-        float pw[4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const int idx = ib + g + u * stride;
-            vv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-            pw[u] = 0.f;
-            if (active && idx < cnt) {
-                vv[u] = __ldcg(reinterpret_cast<const float4 *>(vb + (int64_t)idx * head + 4 * li));
-                pw[u] = scores[idx];
+    // merge the lane groups of the block in slot order
+    float M = -INFINITY, L = 0.f, O = 0.f;
+    if (tid < head) {
+        for (int s2 = 0; s2 < nslots; ++s2)
+            M = fmaxf(M, asmem[s2 * sstride + head]);
+        for (int s2 = 0; s2 < nslots; ++s2) {
+            const float ms = asmem[s2 * sstride + head];
+            const float ls = asmem[s2 * sstride + head + 1];
+            if (ls > 0.f) {
+                const float w = expf(ms - M);
+                L = fmaf(ls, w, L);
+                O = fmaf(asmem[s2 * sstride + tid], w, O);
             }
         }
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            acc.x = fmaf(pw[u], vv[u].x, acc.x);
-            acc.y = fmaf(pw[u], vv[u].y, acc.y);
-            acc.z = fmaf(pw[u], vv[u].z, acc.z);
-            acc.w = fmaf(pw[u], vv[u].w, acc.w);
-        }
     }
-    for (int o = gw; o < 32; o <<= 1) {   // fold the lane groups of the warp together
-        acc.x += __shfl_xor_sync(0xffffffffu, acc.x, o);
-        acc.y += __shfl_xor_sync(0xffffffffu, acc.y, o);
-        acc.z += __shfl_xor_sync(0xffffffffu, acc.z, o);
-        acc.w += __shfl_xor_sync(0xffffffffu, acc.w, o);
+    if (nact == 1) {
+        if (tid < head)
+            p.out[(int64_t)h * head + tid] = __fdiv_rn(O, L);   // ExpSumNormalize.java:33-37 folded into the sum
+        return;
     }
-    if (g == 0 && active)
-        *reinterpret_cast<float4 *>(vred + warp * head + 4 * li) = acc;
-    __syncthreads();
 
     float *part = p.part + ((int64_t)h * p.nsplit + sp) * (head + 2);
-    if (tid < head) {
-        float o = 0.f;
-        for (int w = 0; w < kAttnWarps; ++w)
-            o += vred[w * head + tid];
-        __stcg(part + 2 + tid, o);
-    }
+    if (tid < head)
+        __stcg(part + 2 + tid, O);
     if (tid == 0) {
-        __stcg(part, m);
-        __stcg(part + 1, l);
+        __stcg(part, M);
+        __stcg(part + 1, L);
     }
     __threadfence();
     __syncthreads();
     if (tid == 0) {
         const unsigned int ticket = atomicAdd(&p.counters[h], 1u);
-        s_last = (ticket == (unsigned)p.nsplit - 1);
+        s_last = (ticket == (unsigned)nact - 1);
     }
     __syncthreads();
     if (!s_last)
         return;
 
-    // ---- the last block of the head merges the splits in a fixed order
+    // ---- the last block of the head merges the partials of the active blocks in a fixed order
     __threadfence();
     if (tid < head) {
         const float *hp = p.part + (int64_t)h * p.nsplit * (head + 2);
         float gm = -INFINITY;
-        for (int s = 0; s < p.nsplit; ++s)
-            gm = fmaxf(gm, __ldcg(hp + (int64_t)s * (head + 2)));
-        float L = 0.f, O = 0.f;
-        for (int s = 0; s < p.nsplit; ++s) {
-            const float ms = __ldcg(hp + (int64_t)s * (head + 2));
-            const float ls = __ldcg(hp + (int64_t)s * (head + 2) + 1);
+        for (int s2 = 0; s2 < nact; ++s2)
+            gm = fmaxf(gm, __ldcg(hp + (int64_t)s2 * (head + 2)));
+        float LL = 0.f, OO = 0.f;
+        for (int s2 = 0; s2 < nact; ++s2) {
+            const float ms = __ldcg(hp + (int64_t)s2 * (head + 2));
+            const float ls = __ldcg(hp + (int64_t)s2 * (head + 2) + 1);
             if (ls > 0.f) {
                 const float w = expf(ms - gm);
-                L = fmaf(ls, w, L);
-                O = fmaf(__ldcg(hp + (int64_t)s * (head + 2) + 2 + tid), w, O);
+                LL = fmaf(ls, w, LL);
+                OO = fmaf(__ldcg(hp + (int64_t)s2 * (head + 2) + 2 + tid), w, OO);
             }
         }
-        p.out[(int64_t)h * head + tid] = __fdiv_rn(O, L);
+        p.out[(int64_t)h * head + tid] = __fdiv_rn(OO, LL);
     }
     if (tid == 0)
         p.counters[h] = 0;
@@ -810,10 +1062,14 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const __grid_co
 
 cudaError_t launch_attention(const LaunchCfg &lc, const AttnParams &p)
 {
+    int gw = 1;
+    while (gw < (p.head >> 2))
+        gw <<= 1;
+    const int nslots = kAttnWarps * (32 / gw);
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3((unsigned)p.n_heads, (unsigned)p.nsplit);
     cfg.blockDim = dim3(kAttnThreads);
-    cfg.dynamicSmemBytes = (size_t)(p.chunk_max + kAttnWarps * p.head) * sizeof(float);
+    cfg.dynamicSmemBytes = (size_t)nslots * (p.head + 4) * sizeof(float);
     cfg.stream = lc.stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -914,7 +1170,8 @@ __global__ void __launch_bounds__(256) epilogue_plain_kernel(MvParams p, const f
         const float *ys[3] = {y0, y1, y2};
         for (int sg = 0; sg < 3; ++sg)
             for (int i = threadIdx.x * 2; i < p.seg[sg].rows; i += 512)
-                epi_qkv_pair(p, sg, i, ys[sg][i], ys[sg][i + 1], pos);
+                epi_qkv_pair(p, sg, i, ys[sg][i], ys[sg][i + 1], pos, p.rope_cos + (int64_t)pos * (p.head >> 1),
+                             p.rope_sin + (int64_t)pos * (p.head >> 1));
     } else if (p.epilogue == EPI_SWIGLU) {
         for (int i = threadIdx.x; i < p.seg[0].rows; i += 256)
             p.y[i] = epi_swiglu(y0[i], y1[i]);

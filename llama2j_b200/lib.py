@@ -64,6 +64,8 @@ _SIGNATURES = {
     "l2j_read_buffer": (C.c_int, [_P, C.c_int, C.c_int, C.c_int, _P, C.c_int]),
     "l2j_last_generate_us": (C.c_int, [_P, C.POINTER(C.c_double)]),
     "l2j_time_kernels": (C.c_int, [_P, C.c_int, C.c_int, C.POINTER(C.c_double)]),
+    "l2j_trace_kernel": (C.c_int, [_P, C.c_int, C.c_int, C.c_int, _P, C.c_int]),
+    "l2j_read_trace": (C.c_int, [_P, _P, C.c_int64]),
     "l2j_quant_encode": (C.c_int, [C.c_int, _P, C.c_int64, _P]),
     "l2j_synth_f32": (C.c_int, [C.c_int, C.c_uint64, C.c_uint32, C.c_int64, C.c_int64, C.c_float, _P]),
     "l2j_synth_quant": (C.c_int, [C.c_int, C.c_uint64, C.c_uint32, C.c_int64, C.c_float, _P]),

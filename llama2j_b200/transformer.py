@@ -141,6 +141,21 @@ class Transformer:
         _lib.check(self._lib.l2j_time_kernels(self._ctx, int(pos), int(reps), arr), self._ctx)
         return dict(zip(("qkv_rope", "attention", "wo_residual", "w13_swiglu", "w2_residual", "classifier_argmax"), arr))
 
+    def trace_kernel(self, kind: int, layer: int = 0, pos: int = 0) -> np.ndarray:
+        """In-kernel timeline of one ring-kernel launch: array (blocks, 8), see l2j_trace_kernel."""
+        nb = self.launch_mode()["ring_blocks"]
+        out = np.zeros((nb, 16), dtype=np.uint64)
+        _lib.check(self._lib.l2j_trace_kernel(self._ctx, kind, layer, pos, out.ctypes.data, nb), self._ctx)
+        return out
+
+    def read_trace(self) -> np.ndarray:
+        """Timelines of every ring-kernel launch of the last forward: (launches, blocks, 16)."""
+        launches = 4 * (self.last_layer - self.first_layer + 1) + 1
+        nb = self.launch_mode()["ring_blocks"]
+        out = np.zeros((launches, nb, 16), dtype=np.uint64)
+        _lib.check(self._lib.l2j_read_trace(self._ctx, out.ctypes.data, out.size), self._ctx)
+        return out
+
     def reset(self) -> None:
         _lib.check(self._lib.l2j_reset(self._ctx), self._ctx)
 
@@ -151,7 +166,7 @@ class Transformer:
 
     def launch_mode(self) -> dict:
         m = self._lib.l2j_launch_mode(self._ctx)
-        return {"graph": bool(m & 1), "pdl": bool(m & 2), "ring": bool(m & 4)}
+        return {"graph": bool(m & 1), "pdl": bool(m & 2), "ring": bool(m & 4), "ring_blocks": m >> 8}
 
     def read_buffer(self, which: int, n: int, layer: int = 0, pos: int = 0) -> np.ndarray:
         out = np.empty(n, dtype=np.float32)
