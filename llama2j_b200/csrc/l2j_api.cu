@@ -51,6 +51,8 @@ struct l2j_ctx {
     int64_t emb_received = 0, wcls_received = 0;
 
     float *x = nullptr, *xb = nullptr, *q = nullptr, *hb = nullptr, *logits = nullptr;
+    int reps = 1;                  // copies of x, xb, hb and the RMSNorm weights
+    int dim_stride = 0, hid_stride = 0;   // distance of the copies in floats
     float *y0 = nullptr, *y1 = nullptr, *y2 = nullptr, *xn = nullptr;
     float *kc = nullptr, *vc = nullptr;
     float *rope_cos = nullptr, *rope_sin = nullptr;
@@ -62,7 +64,8 @@ struct l2j_ctx {
     int *prompt_dev = nullptr, *out_tokens_dev = nullptr;
     unsigned int *work = nullptr;   // two counters per ring-kernel launch of a forward
     unsigned long long *trace = nullptr;   // per-launch timelines, only when L2J_TRACE is set
-    int ring_grid = 0;              // blocks per ring kernel: two per SM
+    int ring_grid = 0;              // blocks per ring kernel
+    int early_fill = 1;             // ring stages a kernel may fetch before its predecessor has finished
     SeqState *state = nullptr;
     Cmd *cmd_dev = nullptr;
     Cmd *cmd_host = nullptr;       // pinned ring
@@ -190,9 +193,18 @@ void fill_plan(MvParams &p, const MvPlan &pl)
     p.slot_bytes = pl.slot_bytes;
     p.hdr_off = pl.hdr_off;
     p.half_hdr = pl.half_hdr;
+    p.xshare_bytes = pl.xshare_bytes;
     p.timeout_us = 50000;
     {   // stage bookkeeping: a stage advances rt*rpp rows (half of that per matrix in paired mode)
         const int rs = p.paired ? (pl.rt * pl.rpp) / 2 : pl.rt * pl.rpp;
+        p.rs = rs;
+        p.rowbytes = p.f32 ? p.n * 4 : p.n;
+        {
+            const char *e = getenv("L2J_PREFETCH_MB");
+            const double mb = e ? atof(e) : 0.0;
+            const int64_t stage_bytes = (int64_t)pl.rt * pl.rpp * p.rowbytes;
+            p.pf_distance = mb > 0 ? (int)((int64_t)(mb * 1048576.0) / stage_bytes) : 0;
+        }
         p.total_stages = 0;
         const int nseg = p.paired ? 1 : p.nseg;
         for (int i = 0; i < 3; ++i) {
@@ -236,8 +248,11 @@ void build_launch_params(l2j_ctx *c)
         a.paired = 0;
         a.n = dim;
         fill_plan(a, c->plan_dim);
+        a.early_fill = c->early_fill;
         a.x_in = c->x;
-        a.rms_w = c->rms_att + (int64_t)li * dim;
+        a.x_reps = c->reps;
+        a.x_stride = c->dim_stride;
+        a.rms_w = c->rms_att + (int64_t)li * c->reps * c->dim_stride;
         a.epilogue = EPI_QKV_ROPE;
         a.q_out = c->q;
         a.k_cache = kc;
@@ -251,6 +266,8 @@ void build_launch_params(l2j_ctx *c)
         t.k_cache = kc;
         t.v_cache = vc;
         t.out = c->xb;
+        t.out_reps = c->reps;
+        t.out_stride = c->dim_stride;
         t.part = c->attn_part;
         t.counters = c->attn_counters;
         t.state = c->state;
@@ -270,9 +287,13 @@ void build_launch_params(l2j_ctx *c)
         o.n = dim;
         fill_plan(o, c->plan_dim);
         o.x_in = c->xb;
+        o.x_reps = c->reps;
+        o.x_stride = c->dim_stride;
         o.rms_w = nullptr;
         o.epilogue = EPI_RESIDUAL;
         o.y = c->x;
+        o.y_reps = c->reps;
+        o.y_stride = c->dim_stride;
         o.work = c->work + 2 * (4 * li + 1);
         o.trace = c->trace ? c->trace + (int64_t)(4 * li + 1) * c->ring_grid * 16 : nullptr;
 
@@ -285,10 +306,15 @@ void build_launch_params(l2j_ctx *c)
         f.paired = 1;
         f.n = dim;
         fill_plan(f, c->plan_dim);
+        f.early_fill = c->early_fill;
         f.x_in = c->x;
-        f.rms_w = c->rms_ffn + (int64_t)li * dim;
+        f.x_reps = c->reps;
+        f.x_stride = c->dim_stride;
+        f.rms_w = c->rms_ffn + (int64_t)li * c->reps * c->dim_stride;
         f.epilogue = EPI_SWIGLU;
         f.y = c->hb;
+        f.y_reps = c->reps;
+        f.y_stride = c->hid_stride;
         f.work = c->work + 2 * (4 * li + 2);
         f.trace = c->trace ? c->trace + (int64_t)(4 * li + 2) * c->ring_grid * 16 : nullptr;
 
@@ -299,10 +325,15 @@ void build_launch_params(l2j_ctx *c)
         w.nseg = 1;
         w.n = hidden;
         fill_plan(w, c->plan_hidden);
+        w.early_fill = c->early_fill;
         w.x_in = c->hb;
+        w.x_reps = c->reps;
+        w.x_stride = c->hid_stride;
         w.rms_w = nullptr;
         w.epilogue = EPI_RESIDUAL;
         w.y = c->x;
+        w.y_reps = c->reps;
+        w.y_stride = c->dim_stride;
         w.work = c->work + 2 * (4 * li + 3);
         w.trace = c->trace ? c->trace + (int64_t)(4 * li + 3) * c->ring_grid * 16 : nullptr;
     }
@@ -321,8 +352,13 @@ void build_launch_params(l2j_ctx *c)
         k.seg[0].rows = c->cfg.vocab_size;
         k.nseg = 1;
         k.n = c->dim;
+        k.f32 = 1;
         fill_plan(k, c->plan_cls);
+        k.early_fill = c->early_fill;
         k.x_in = c->x;
+        k.x_reps = c->reps;
+        k.x_stride = c->dim_stride;
+        k.y_reps = 1;
         k.rms_w = c->rms_final;
         k.epilogue = EPI_LOGITS;
         k.y = c->logits;
@@ -342,7 +378,7 @@ cudaError_t enqueue_forward(l2j_ctx *c, bool pdl, int *n_kernels)
     int nk = 0;
     LaunchCfg lc{c->stream, false, c->ring_grid};
     // The first kernel of a forward follows a memcpy (or the previous graph launch): plain edge.
-    e = launch_begin(lc, c->state, c->cmd_dev, c->emb, c->x, c->dim, c->cfg.vocab_size, c->cfg.seq_len, c->is_first ? 1 : 0);
+    e = launch_begin(lc, c->state, c->cmd_dev, c->emb, c->x, c->dim, c->cfg.vocab_size, c->cfg.seq_len, c->is_first ? 1 : 0, c->reps, c->dim_stride);
     if (e != cudaSuccess)
         return e;
     ++nk;
@@ -351,7 +387,11 @@ cudaError_t enqueue_forward(l2j_ctx *c, bool pdl, int *n_kernels)
     for (int li = 0; li < c->nl; ++li) {
         LayerLaunch &L = c->layers[(size_t)li];
         if (c->use_ring) {
-            if ((e = launch_matvec_ring(lc, c->plan_dim, false, L.qkv)) != cudaSuccess) return e;
+            // The first ring kernel of a forward takes a full dependency on the begin kernel: the attention
+            // kernel behind it reads the position before its own dependency wait.
+            LaunchCfg first = lc;
+            first.pdl = lc.pdl && li > 0;
+            if ((e = launch_matvec_ring(first, c->plan_dim, false, L.qkv)) != cudaSuccess) return e;
             if ((e = launch_attention(lc, L.attn)) != cudaSuccess) return e;
             if ((e = launch_matvec_ring(lc, c->plan_dim, false, L.wo)) != cudaSuccess) return e;
             if ((e = launch_matvec_ring(lc, c->plan_dim, false, L.w13)) != cudaSuccess) return e;
@@ -582,19 +622,22 @@ extern "C" int l2j_create(const l2j_config *cfg, int device, int first_layer, in
             c->needed[L2J_T_WCLS] = true;
         }
     }
-    CREATE_CK(dev_alloc(c, &c->rms_att, (int64_t)c->nl * dim, true));
-    CREATE_CK(dev_alloc(c, &c->rms_ffn, (int64_t)c->nl * dim, true));
-    CREATE_CK(dev_alloc(c, &c->rms_final, dim, true));
+    c->reps = (flags & L2J_F_SIMPLE) ? 1 : kVecReps;
+    c->dim_stride = (int)(((dim + 63) & ~63) + 96);     // odd multiple of 32 floats: copies land on different L2 sets
+    c->hid_stride = (int)(((hid + 63) & ~63) + 96);
+    CREATE_CK(dev_alloc(c, &c->rms_att, (int64_t)c->nl * c->reps * c->dim_stride, true));
+    CREATE_CK(dev_alloc(c, &c->rms_ffn, (int64_t)c->nl * c->reps * c->dim_stride, true));
+    CREATE_CK(dev_alloc(c, &c->rms_final, (int64_t)c->reps * c->dim_stride, true));
 
     // run state, RunState.java:107-166 (q/k/v and att scratch are internal to the fused kernels)
     int64_t ymax = dim > hid ? dim : hid;
     if (cfg->vocab_size > ymax)
         ymax = cfg->vocab_size;
-    CREATE_CK(dev_alloc(c, &c->x, dim, true));
-    CREATE_CK(dev_alloc(c, &c->xb, dim, true));
+    CREATE_CK(dev_alloc(c, &c->x, (int64_t)c->reps * c->dim_stride, true));
+    CREATE_CK(dev_alloc(c, &c->xb, (int64_t)c->reps * c->dim_stride, true));
     CREATE_CK(dev_alloc(c, &c->xn, dim, true));
     CREATE_CK(dev_alloc(c, &c->q, dim, true));
-    CREATE_CK(dev_alloc(c, &c->hb, hid, true));
+    CREATE_CK(dev_alloc(c, &c->hb, (int64_t)c->reps * c->hid_stride, true));
     CREATE_CK(dev_alloc(c, &c->logits, cfg->vocab_size, true));
     CREATE_CK(dev_alloc(c, &c->y0, ymax, true));
     CREATE_CK(dev_alloc(c, &c->y1, ymax, true));
@@ -610,13 +653,15 @@ extern "C" int l2j_create(const l2j_config *cfg, int device, int first_layer, in
     CREATE_CUDA(cudaMemcpy(c->rope_cos, cs.data(), cs.size() * sizeof(float), cudaMemcpyHostToDevice));
     CREATE_CUDA(cudaMemcpy(c->rope_sin, sn.data(), sn.size() * sizeof(float), cudaMemcpyHostToDevice));
 
+    if (const char *e = getenv("L2J_EARLY_FILL"))
+        c->early_fill = atoi(e);
     c->nsplit = choose_nsplit(c->sm_count, cfg->n_heads, cfg->seq_len);
     c->chunk_max = (((cfg->seq_len + c->nsplit - 1) / c->nsplit) + 3) & ~3;   // keeps the float4 scratch behind it aligned
     CREATE_CK(dev_alloc(c, &c->attn_part, (int64_t)cfg->n_heads * c->nsplit * (head + 2), true));
     CREATE_CK(dev_alloc(c, &c->attn_counters, cfg->n_heads, true));
-    {   // blocks per ring kernel: two per SM give the streaming kernel the whole shared memory as its ring
+    {   // blocks per ring kernel: one per SM, holding nearly all of its shared memory as the ring
         const char *g = getenv("L2J_BLOCKS_PER_SM");
-        const int per_sm = g ? atoi(g) : 2;
+        const int per_sm = g ? atoi(g) : 1;
         c->ring_grid = (per_sm >= 1 && per_sm <= 2 ? per_sm : 1) * c->sm_count;
     }
     CREATE_CK(dev_alloc(c, &c->blk_val, c->ring_grid + 8, true));
@@ -630,7 +675,7 @@ extern "C" int l2j_create(const l2j_config *cfg, int device, int first_layer, in
     CREATE_CK(dev_alloc(c, &c->cmd_dev, 1, true));
     CREATE_CUDA(cudaHostAlloc((void **)&c->cmd_host, sizeof(Cmd) * kCmdRing, cudaHostAllocDefault));
     CREATE_CUDA(cudaHostAlloc((void **)&c->logits_host, sizeof(float) * (size_t)cfg->vocab_size, cudaHostAllocDefault));
-    CREATE_CUDA(cudaHostAlloc((void **)&c->x_host, sizeof(float) * (size_t)dim, cudaHostAllocDefault));
+    CREATE_CUDA(cudaHostAlloc((void **)&c->x_host, sizeof(float) * (size_t)c->reps * c->dim_stride, cudaHostAllocDefault));
     CREATE_CUDA(cudaHostAlloc((void **)&c->state_host, sizeof(SeqState), cudaHostAllocDefault));
     memset(c->state_host, 0, sizeof(SeqState));
 
@@ -791,10 +836,16 @@ extern "C" int l2j_finalize(l2j_ctx *c)
         }
     }
     const int64_t dim = c->dim;
-    CK(c, launch_dequant_rms(c->stream, c->qt[L2J_T_RMS_ATT], dim * c->first_layer, dim * c->nl, c->rms_att));
-    CK(c, launch_dequant_rms(c->stream, c->qt[L2J_T_RMS_FFN], dim * c->first_layer, dim * c->nl, c->rms_ffn));
+    for (int li = 0; li < c->nl; ++li) {
+        for (int r = 0; r < c->reps; ++r) {
+            const int64_t off = ((int64_t)li * c->reps + r) * c->dim_stride;
+            CK(c, launch_dequant_rms(c->stream, c->qt[L2J_T_RMS_ATT], dim * (c->first_layer + li), dim, c->rms_att + off));
+            CK(c, launch_dequant_rms(c->stream, c->qt[L2J_T_RMS_FFN], dim * (c->first_layer + li), dim, c->rms_ffn + off));
+        }
+    }
     if (c->is_last)
-        CK(c, launch_dequant_rms(c->stream, c->qt[L2J_T_RMS_FINAL], 0, dim, c->rms_final));
+        for (int r = 0; r < c->reps; ++r)
+            CK(c, launch_dequant_rms(c->stream, c->qt[L2J_T_RMS_FINAL], 0, dim, c->rms_final + (int64_t)r * c->dim_stride));
     CK(c, cudaStreamSynchronize(c->stream));
     build_launch_params(c);
     {   // largest RMSNorm weight per launch: bounds the normalised vector for the kernels' fixed-point scale
@@ -805,18 +856,40 @@ extern "C" int l2j_finalize(l2j_ctx *c)
                 m = std::fmax(m, std::fabs(src[i]));
             return m;
         };
-        CK(c, cudaMemcpy(w.data(), c->rms_att, sizeof(float) * (size_t)dim * c->nl, cudaMemcpyDeviceToHost));
-        for (int li = 0; li < c->nl; ++li)
-            c->layers[(size_t)li].qkv.rms_wmax = vmax(w.data() + (int64_t)li * dim, dim);
-        CK(c, cudaMemcpy(w.data(), c->rms_ffn, sizeof(float) * (size_t)dim * c->nl, cudaMemcpyDeviceToHost));
-        for (int li = 0; li < c->nl; ++li)
-            c->layers[(size_t)li].w13.rms_wmax = vmax(w.data() + (int64_t)li * dim, dim);
+        for (int li = 0; li < c->nl; ++li) {
+            const int64_t off = (int64_t)li * c->reps * c->dim_stride;
+            CK(c, cudaMemcpy(w.data(), c->rms_att + off, sizeof(float) * (size_t)dim, cudaMemcpyDeviceToHost));
+            c->layers[(size_t)li].qkv.rms_wmax = vmax(w.data(), dim);
+            CK(c, cudaMemcpy(w.data(), c->rms_ffn + off, sizeof(float) * (size_t)dim, cudaMemcpyDeviceToHost));
+            c->layers[(size_t)li].w13.rms_wmax = vmax(w.data(), dim);
+        }
         if (c->is_last) {
             CK(c, cudaMemcpy(w.data(), c->rms_final, sizeof(float) * (size_t)dim, cudaMemcpyDeviceToHost));
             c->cls.rms_wmax = vmax(w.data(), dim);
         }
     }
 
+    {   // device copies of the launch parameters, chained in launch order, for the cross-launch L2 prefetch
+        const int count = 4 * c->nl + (c->is_last ? 1 : 0);
+        MvParams *dev = nullptr;
+        int rc2 = dev_alloc(c, &dev, count, true);
+        if (rc2 != L2J_OK)
+            return rc2;
+        std::vector<MvParams *> order;
+        for (int li = 0; li < c->nl; ++li) {
+            LayerLaunch &L = c->layers[(size_t)li];
+            order.push_back(&L.qkv);
+            order.push_back(&L.wo);
+            order.push_back(&L.w13);
+            order.push_back(&L.w2);
+        }
+        if (c->is_last)
+            order.push_back(&c->cls);
+        for (int i = 0; i < count; ++i)
+            order[(size_t)i]->next = dev + (i + 1) % count;   // the last launch of a token prefetches for the next token
+        for (int i = 0; i < count; ++i)
+            CK(c, cudaMemcpy(dev + i, order[(size_t)i], sizeof(MvParams), cudaMemcpyHostToDevice));
+    }
     c->pdl_on = c->use_ring && !(c->flags & L2J_F_NO_PDL);
     if (!(c->flags & L2J_F_NO_GRAPH)) {
         if (!try_capture(c, c->pdl_on)) {
@@ -874,8 +947,10 @@ extern "C" int l2j_forward_stage(l2j_ctx *c, int token, int pos, const float *x_
         return rc;
     CK(c, cudaSetDevice(c->device));
     if (!c->is_first) {
-        memcpy(c->x_host, x_in, sizeof(float) * (size_t)c->dim);
-        CK(c, cudaMemcpyAsync(c->x, c->x_host, sizeof(float) * (size_t)c->dim, cudaMemcpyHostToDevice, c->stream));
+        for (int r = 0; r < c->reps; ++r)
+            memcpy(c->x_host + (size_t)r * c->dim_stride, x_in, sizeof(float) * (size_t)c->dim);
+        CK(c, cudaMemcpyAsync(c->x, c->x_host, sizeof(float) * (size_t)c->reps * c->dim_stride, cudaMemcpyHostToDevice,
+                              c->stream));
     }
     rc = post_cmd(c, 1, c->is_first ? token : 0, pos);
     if (rc != L2J_OK)
@@ -1016,7 +1091,7 @@ extern "C" int l2j_time_kernels(l2j_ctx *c, int pos, int reps, double *us)
     if (rc != L2J_OK)
         return rc;
     LaunchCfg lc{c->stream, false, c->ring_grid};
-    CK(c, launch_begin(lc, c->state, c->cmd_dev, c->emb, c->x, c->dim, c->cfg.vocab_size, c->cfg.seq_len, c->is_first ? 1 : 0));
+    CK(c, launch_begin(lc, c->state, c->cmd_dev, c->emb, c->x, c->dim, c->cfg.vocab_size, c->cfg.seq_len, c->is_first ? 1 : 0, c->reps, c->dim_stride));
     for (int kind = 0; kind < 6; ++kind) {
         us[kind] = 0.0;
         if (kind == 5 && !c->is_last)
@@ -1092,7 +1167,7 @@ extern "C" int l2j_trace_kernel(l2j_ctx *c, int kind, int layer, int pos, uint64
     cudaDeviceSynchronize();
     rc = post_cmd(c, 1, 1, pos);
     LaunchCfg lc{c->stream, false, c->ring_grid};
-    cudaError_t e = launch_begin(lc, c->state, c->cmd_dev, c->emb, c->x, c->dim, c->cfg.vocab_size, c->cfg.seq_len, c->is_first ? 1 : 0);
+    cudaError_t e = launch_begin(lc, c->state, c->cmd_dev, c->emb, c->x, c->dim, c->cfg.vocab_size, c->cfg.seq_len, c->is_first ? 1 : 0, c->reps, c->dim_stride);
     LayerLaunch &L = c->layers[(size_t)li];
     for (int rep = 0; rep < 2 && e == cudaSuccess; ++rep) {   // the second launch is the one recorded
         MvParams p = kind == 0 ? L.qkv : kind == 2 ? L.wo : kind == 3 ? L.w13 : kind == 4 ? L.w2 : c->cls;
@@ -1328,11 +1403,13 @@ extern "C" int l2j_k_matvec_i8(int device, uint32_t flags, const void *groups, i
         p.n = n;
         fill_plan(p, pl);
         p.x_in = dx;
+        p.x_reps = 1;
+        p.y_reps = 1;
         p.epilogue = EPI_STORE;
         p.y = dy;
         p.state = st;
         p.work = work;
-        LaunchCfg lc{nullptr, false, 2 * prop.multiProcessorCount};
+        LaunchCfg lc{nullptr, false, prop.multiProcessorCount};
         KCK(launch_matvec_ring(lc, pl, false, p));
     } else {
         KCK(launch_matvec_plain_u8(nullptr, seg, n, dx, dy));
@@ -1373,6 +1450,8 @@ extern "C" int l2j_k_matvec_f32(int device, uint32_t flags, const float *w, int 
     p.nseg = 1;
     p.n = n;
     p.x_in = dx;
+    p.x_reps = 1;
+    p.y_reps = 1;
     p.epilogue = argmax ? EPI_LOGITS : EPI_STORE;
     p.y = dy;
     p.blk_val = bv;
@@ -1381,9 +1460,10 @@ extern "C" int l2j_k_matvec_f32(int device, uint32_t flags, const float *w, int 
     p.state = st;
     p.work = work;
     const MvPlan pl = plan_matvec(n, true, false);
+    p.f32 = 1;
     if (!(flags & L2J_F_SIMPLE) && pl.ok) {
         fill_plan(p, pl);
-        LaunchCfg lc{nullptr, false, 2 * prop.multiProcessorCount};
+        LaunchCfg lc{nullptr, false, prop.multiProcessorCount};
         KCK(launch_matvec_ring(lc, pl, true, p));
     } else {
         float *tmp = nullptr;
@@ -1506,6 +1586,7 @@ extern "C" int l2j_k_attention(int device, const float *q, const float *key_cach
     p.kv_mul = n_heads / n_kv_heads;
     p.head = head_size;
     p.seq_len = seq_len;
+    p.out_reps = 1;
     p.pos_override = pos;
     LaunchCfg lc{nullptr, false, prop.multiProcessorCount};
     KCK(launch_attention(lc, p));

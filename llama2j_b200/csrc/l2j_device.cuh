@@ -92,6 +92,22 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t
         : "memory");
 }
 
+// 16-byte load through L2 that is only *issued* here: the asm is volatile, so later volatile asm
+// (a barrier arrive, say) stays behind it in program order, and the data is waited for at first use.
+__device__ __forceinline__ float4 ld_cg_f4_issue(const float *p)
+{
+    float4 v;
+    asm volatile("ld.global.cg.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+    return v;
+}
+
+// Asks the memory system to bring [src, src + bytes) into L2 (no destination, no completion signal).
+// src and bytes must be multiples of 16.
+__device__ __forceinline__ void bulk_prefetch_l2(const void *src, uint32_t bytes)
+{
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
+
 // ---------------------------------------------------------------------------------------------
 // programmatic dependent launch
 // ---------------------------------------------------------------------------------------------

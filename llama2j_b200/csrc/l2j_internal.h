@@ -9,7 +9,12 @@ namespace l2j {
 
 constexpr int kGroup = 256;        // elements per quantisation group
 constexpr int kGroupBytes = 264;   // encoded bytes per group in the file format
-constexpr int kMaxSmemRing = 100 * 1024;  // ring budget per CTA; two kernels must fit on one SM
+// Vectors that every block of a kernel reads in full (x, the attention output, the FFN hidden vector,
+// the RMSNorm weights) are kept in several copies: hundreds of blocks asking for the same few L2 lines
+// at the same moment are served one after the other, copies at different addresses are served in parallel.
+constexpr int kVecReps = 1;
+constexpr int kMaxSmemBlock = 208 * 1024;  // dynamic shared memory of a ring-kernel block: one block per SM, with
+                                           // room left for the small blocks of the attention kernel
 
 // Device-resident sequence state, advanced by the kernels themselves so that consecutive tokens
 // can be queued without a host round trip.
@@ -49,6 +54,8 @@ enum MvEpilogue {
     EPI_LOGITS = 4      // logits[i] = v, block argmax, grid argmax by the last block
 };
 
+struct MvParams;
+
 struct MvSeg {
     const uint8_t *payload;   // u8 payload, or the float rows for FP32 weights
     const float2 *hdr;
@@ -68,16 +75,25 @@ struct MvParams {
     int slot_bytes;    // bytes per ring slot
     int hdr_off;       // offset of the header area inside a slot
     int half_hdr;      // bytes of one half's header area (paired mode)
+    int xshare_bytes;  // shared copy of x between the header and the ring
     int timeout_us;    // bound of every wait on a copy barrier
     int seg_stages[3]; // stages per segment
     int total_stages;
+    int rs;            // matrix rows (row pairs in paired mode) a stage advances
+    int rowbytes;      // bytes of one matrix row
+    int f32;           // 1: FP32 weights
+    int pf_distance;   // stages the L2 prefetch runs ahead of the claims (0: off)
+    int early_fill;    // stages the producer may issue before the previous kernel has finished (0: none)
+    const MvParams *next;   // device copy of the next ring launch's parameters (prefetch target) or nullptr
     // prologue
-    const float *x_in;       // input vector (n floats)
+    const float *x_in;       // input vector (n floats), replica 0
+    int x_reps, x_stride;    // copies of the vector (and of rms_w) and their distance in floats; block b reads copy b % x_reps
     const float *rms_w;      // dequantised RMSNorm weights (n floats) or nullptr
     float rms_wmax;          // max |rms_w| (bounds the normalised vector for the fixed-point scale)
     // epilogue
     int epilogue;
-    float *y;                // STORE / RESIDUAL / SWIGLU / LOGITS target
+    float *y;                // STORE / RESIDUAL / SWIGLU / LOGITS target (replica 0)
+    int y_reps, y_stride;    // copies of the target vector that every result is written to
     float *q_out;            // QKV: q (dim)
     float *k_cache;          // QKV: layer base of the K cache [kv_head][seq][head]
     float *v_cache;
@@ -100,7 +116,8 @@ struct AttnParams {
     const float *q;          // (n_heads * head)
     const float *k_cache;    // layer base, [kv_head][seq][head]
     const float *v_cache;
-    float *out;              // (n_heads * head)
+    float *out;              // (n_heads * head), replica 0
+    int out_reps, out_stride;   // copies of the output vector and their distance in floats
     float *part;             // scratch: [n_heads][nsplit][head + 2]
     unsigned int *counters;  // [n_heads], zero between launches
     SeqState *state;
@@ -112,7 +129,7 @@ struct MvPlan {
     int cpt;       // chunks per thread (template selector)
     int rt;        // rows per thread and stage (template selector)
     int rpp, wpr;
-    int nstage, slot_bytes, hdr_off, half_hdr;
+    int nstage, slot_bytes, hdr_off, half_hdr, xshare_bytes;
     int threads;   // block size including the producer and the epilogue warp
     int smem_bytes;
     bool ok;
@@ -133,7 +150,7 @@ cudaError_t prepare_kernels();
 cudaError_t launch_matvec_ring(const LaunchCfg &lc, const MvPlan &plan, bool f32, const MvParams &p);
 cudaError_t launch_attention(const LaunchCfg &lc, const AttnParams &p);
 cudaError_t launch_begin(const LaunchCfg &lc, SeqState *state, const Cmd *cmd, const float *emb, float *x, int dim,
-                         int vocab, int seq_len, int gather);
+                         int vocab, int seq_len, int gather, int x_reps, int x_stride);
 
 // plain (cross-check) kernels
 cudaError_t launch_rmsnorm_plain(cudaStream_t s, const float *x, const float *w, float *out, int n);

@@ -162,17 +162,39 @@ __device__ __forceinline__ void decode_stage(const MvParams &p, int rs, int s, i
     nrows = min(rs, p.seg[seg].rows - row0);
 }
 
+// Brings one stage of launch `q` (this one or the next in the stream) into L2 ahead of its bulk copy.
+__device__ __forceinline__ void prefetch_stage(const MvParams &q, int s)
+{
+    int seg, row0, nrows;
+    decode_stage(q, q.rs, s, seg, row0, nrows);
+    const uint32_t pbytes = (uint32_t)nrows * (uint32_t)q.rowbytes;
+    if (q.f32) {
+        bulk_prefetch_l2(reinterpret_cast<const float *>(q.seg[seg].payload) + q.seg[seg].flat0 + (int64_t)row0 * q.n, pbytes);
+        return;
+    }
+    const int nh = q.paired ? 2 : 1;
+    for (int h = 0; h < nh; ++h) {
+        const MvSeg &sg = q.seg[q.paired ? h : seg];
+        const int64_t flat = sg.flat0 + (int64_t)row0 * q.n;
+        const int64_t ga = (flat >> 8) & ~(int64_t)1;
+        const int64_t gl = (flat + pbytes - 1) >> 8;
+        bulk_prefetch_l2(sg.payload + flat, pbytes);
+        bulk_prefetch_l2(sg.hdr + ga, (uint32_t)(((gl - ga + 2) & ~(int64_t)1) * 8));
+    }
+}
+
 constexpr int kRedBufs = 4;
 constexpr int kBarFull = 0;                       // uint64 full[16]
 constexpr int kBarEmpty = 128;                    // uint64 empty[16]
 constexpr int kBarRedFull = 256;                  // uint64 red_full[4]
 constexpr int kBarRedEmpty = 288;                 // uint64 red_empty[4]
+constexpr int kBarXIssued = 320;                  // uint64: the consumers have issued the loads of x
 constexpr int kScratchOff = 384;                  // float scratch[64]
 constexpr int kDescOff = 640;                     // StageDesc desc[16]
-constexpr int kRedOff = 1152;                     // 4 x (16-byte header + 64 floats)
-constexpr int kRedStride = 272;
-constexpr int kRopeOff = 2304;                    // float cos[64], sin[64] of the current position
-constexpr int kSmemHeader = 2816;                 // start of the ring (128-byte aligned)
+constexpr int kRedOff = 1152;                     // 4 x (16-byte header + 128 floats: up to 8 rows x 16 warps)
+constexpr int kRedStride = 528;
+constexpr int kRopeOff = 3328;                    // float cos[64], sin[64] of the current position
+constexpr int kSmemHeader = 3840;                 // end of the fixed part (128-byte aligned)
 constexpr uint64_t kShortWaitNs = 2000;
 
 __device__ __forceinline__ int dp4a_u8s8(uint32_t a, uint32_t b, int c)
@@ -217,17 +239,17 @@ __device__ __forceinline__ float warp_sum_rows(const float (&v)[RT], int lane)
     return WarpFold<RT, 16>::run(v, lane);
 }
 
-// Optional in-kernel timeline (p.trace != nullptr): slot k of the block gets the SM cycle counter.
+// Optional in-kernel timeline (p.trace != nullptr): slot k of the block gets the global timer (ns).
 // 0 entry, 1 producer's first copy issued, 2 producer's last copy issued, 3 consumer prologue done,
 // 4 first stage landed, 5 consumers done, 6 epilogue warp done, 7 global timer (ns) at entry.
 __device__ __forceinline__ void trace_mark(const MvParams &p, int k)
 {
     if (p.trace)
-        p.trace[blockIdx.x * 16 + k] = (unsigned long long)clock64();
+        p.trace[blockIdx.x * 16 + k] = (unsigned long long)global_timer_ns();
 }
 
 template <bool F32, int CPT, int RT, int MAXT>
-__global__ void __launch_bounds__(MAXT, 2) matvec_ring_kernel(const __grid_constant__ MvParams p)
+__global__ void __launch_bounds__(768, 1) matvec_ring_kernel(const __grid_constant__ MvParams p)
 {
     constexpr int EPC = F32 ? 4 : 16;   // elements per 16-byte chunk
     extern __shared__ __align__(128) uint8_t smem[];
@@ -237,7 +259,7 @@ __global__ void __launch_bounds__(MAXT, 2) matvec_ring_kernel(const __grid_const
     const int ncons = nw * 32;
     const int nstage = p.nstage;
     const uint32_t sbase = smem_u32(smem);
-    const uint32_t ring_base = sbase + kSmemHeader;
+    const uint32_t ring_base = sbase + kSmemHeader + (uint32_t)p.xshare_bytes;   // the ring follows the shared copy of x
 
     // The parameter block of every launch is cold in the constant cache; reading one word of each of
     // its 128-byte lines up front makes the block pay one miss instead of one per line along the
@@ -260,11 +282,11 @@ __global__ void __launch_bounds__(MAXT, 2) matvec_ring_kernel(const __grid_const
         mbar_init(sbase + kBarRedFull + 8 * tid, nw);
         mbar_init(sbase + kBarRedEmpty + 8 * tid, 1);
     }
+    if (tid == 0)
+        mbar_init(sbase + kBarXIssued, p.wpr);
     if (tid < 32)
         mbar_fence_init();
     __syncthreads();
-    if (tid == 0)
-        trace_mark(p, 9);
     if (p.pdl_mode == 0)
         pdl_launch_dependents();
 
@@ -276,7 +298,6 @@ __global__ void __launch_bounds__(MAXT, 2) matvec_ring_kernel(const __grid_const
     // ------------------------------------------------------------------------------ producer
     if (warp == nw) {
         if (lane == 0) {
-            trace_mark(p, 10);
             const int S = p.total_stages;
             const uint64_t pol = policy_evict_first();
             bool lost = false, first = true;
@@ -289,9 +310,25 @@ __global__ void __launch_bounds__(MAXT, 2) matvec_ring_kernel(const __grid_const
             const unsigned int grid = gridDim.x;
             const unsigned int nstatic = (unsigned int)max(1, S / (2 * (int)grid));
             unsigned int issued = 0;
-            unsigned int pending = 0xfffffffeu;   // the first claim is made once the first stage is on its way
-            trace_mark(p, 11);
+            unsigned int pending = 0xfffffffeu, pending2 = 0xfffffffeu;   // two claims in flight once the first stage is on its way
+            // HBM -> L2 for the block's first stages starts at once; the copies into shared memory wait
+            // until the consumers have put their loads of x on the wire.  A ring fill issued earlier
+            // would sit in front of those small, latency-critical loads (and of the attention kernel's,
+            // if that is still running) in the SM's load path.
+            if (!p.early_fill) {
+                for (unsigned int j = 0; j < 3 && j < nstatic; ++j)
+                    if (blockIdx.x + j * grid < (unsigned int)S)
+                        prefetch_stage(p, (int)(blockIdx.x + j * grid));
+            }
+            bool gate_open = false;
             for (;;) {
+                // Only `early_fill` stages are issued before the consumers have put their loads of x on the
+                // wire: a full ring fill in front of those loads would delay them by microseconds.
+                if (!gate_open && issued >= (unsigned int)p.early_fill) {
+                    if (!mbar_wait_bounded(sbase + kBarXIssued, 0u, wait_ns))
+                        lost = true;
+                    gate_open = true;
+                }
                 if (round > 0) {
                     if (!mbar_wait_bounded(sbase + kBarEmpty + 8 * slot, (uint32_t)(round - 1) & 1u,
                                            lost ? kShortWaitNs : wait_ns))
@@ -304,14 +341,17 @@ __global__ void __launch_bounds__(MAXT, 2) matvec_ring_kernel(const __grid_const
                     cur = blockIdx.x + issued * grid;
                 } else {
                     cur = pending;
-                    pending = nstatic * grid + atomicAdd(p.work, 1u);
+                    pending = pending2;
+                    pending2 = nstatic * grid + atomicAdd(p.work, 1u);
                 }
                 ++issued;
                 if (cur >= (unsigned int)S) {
                     desc->nrows = 0;            // end marker: a stage without data
                     mbar_arrive(full);
-                    if (first)                  // nothing was issued: still take part in the counter protocol
+                    if (first) {                // nothing was issued: still take part in the counter protocol
                         pending = nstatic * grid + atomicAdd(p.work, 1u);
+                        pending2 = pending;
+                    }
                     break;
                 }
                 int seg, row0, nrows;
@@ -359,6 +399,20 @@ __global__ void __launch_bounds__(MAXT, 2) matvec_ring_kernel(const __grid_const
                     trace_mark(p, 1);
                     first = false;
                     pending = nstatic * grid + atomicAdd(p.work, 1u);
+                    pending2 = nstatic * grid + atomicAdd(p.work, 1u);
+                }
+                if (p.pf_distance > 0) {
+                    // Keep HBM -> L2 running a fixed distance ahead of the claims, across the boundary to
+                    // the next launch: the ring then fills from L2 and the weight stream does not pause
+                    // while a kernel drains, starts or normalises its input.
+                    const unsigned int pf = cur + (unsigned int)p.pf_distance;
+                    if (pf < (unsigned int)S) {
+                        prefetch_stage(p, (int)pf);
+                    } else if (p.next) {
+                        const int j = (int)(pf - (unsigned int)S);
+                        if (j < p.next->total_stages)
+                            prefetch_stage(*p.next, j);
+                    }
                 }
                 if (++slot == nstage) {
                     slot = 0;
@@ -368,7 +422,7 @@ __global__ void __launch_bounds__(MAXT, 2) matvec_ring_kernel(const __grid_const
             trace_mark(p, 2);
             // The block that learns last that the work has run out re-arms the counters for the next launch.
             __threadfence();
-            if (pending != 0xffffffffu && atomicAdd(p.work + 1, 1u) == gridDim.x - 1) {
+            if (pending != 0xffffffffu && pending2 != 0xffffffffu && atomicAdd(p.work + 1, 1u) == gridDim.x - 1) {
                 __threadfence();
                 p.work[0] = 0;
                 p.work[1] = 0;
@@ -399,8 +453,6 @@ __global__ void __launch_bounds__(MAXT, 2) matvec_ring_kernel(const __grid_const
         float best_v = -FLT_MAX;
         int best_i = 0x7fffffff;
         int rb = 0, rround = 0;
-        if (lane == 0)
-            trace_mark(p, 15);
         for (;;) {
             if (!mbar_wait_bounded(sbase + kBarRedFull + 8 * rb, (uint32_t)rround & 1u, lost ? kShortWaitNs : wait_ns))
                 lost = true;
@@ -425,7 +477,9 @@ __global__ void __launch_bounds__(MAXT, 2) matvec_ring_kernel(const __grid_const
                         v1 += red[lane * p.wpr + w];
                         v3 += red[(R / 2 + lane) * p.wpr + w];
                     }
-                    p.y[row0 + lane] = epi_swiglu(v1, v3);
+                    const float g = epi_swiglu(v1, v3);
+                    for (int r = 0; r < p.y_reps; ++r)
+                        p.y[(int64_t)r * p.y_stride + row0 + lane] = g;
                 }
             } else if (lane < nrows) {
                 float a = 0.f;
@@ -433,7 +487,8 @@ __global__ void __launch_bounds__(MAXT, 2) matvec_ring_kernel(const __grid_const
                     a += red[lane * p.wpr + w];
                 const int row = row0 + lane;
                 if (p.epilogue == EPI_RESIDUAL) {
-                    atomicAdd(p.y + row, a);   // one add per element and launch: a reduction without a read round trip
+                    for (int r = 0; r < p.y_reps; ++r)   // one add per element, copy and launch: no read round trip
+                        atomicAdd(p.y + (int64_t)r * p.y_stride + row, a);
                 } else {
                     p.y[row] = a;
                     if (p.epilogue == EPI_LOGITS && (a > best_v || (a == best_v && row < best_i))) {
@@ -502,104 +557,144 @@ __global__ void __launch_bounds__(MAXT, 2) matvec_ring_kernel(const __grid_const
     if (tid == 0)
         trace_mark(p, 12);
 
-    // ---- prologue: x -> registers with RMSNorm applied (RootMeanSquare.java:25-35,
-    //      WeightNormalizeAndScale.java:71-74), then fixed-point limbs for the u8 path.
-    //      All global loads are issued before the single block-wide reduction.
-    float xr[CPT][EPC];
-    float wr[CPT][EPC];
-    const bool has_rms = p.rms_w != nullptr;
-#pragma unroll
-    for (int k = 0; k < CPT; ++k) {
-#pragma unroll
-        for (int e = 0; e < EPC; e += 4) {
-            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            float4 w = make_float4(1.f, 1.f, 1.f, 1.f);
-            if (cvalid[k]) {
-                v = __ldcg(reinterpret_cast<const float4 *>(p.x_in + (int64_t)chunk[k] * EPC + e));
-                if (has_rms)
-                    w = __ldg(reinterpret_cast<const float4 *>(p.rms_w + (int64_t)chunk[k] * EPC + e));
-            }
-            xr[k][e] = v.x; xr[k][e + 1] = v.y; xr[k][e + 2] = v.z; xr[k][e + 3] = v.w;
-            wr[k][e] = w.x; wr[k][e + 1] = w.y; wr[k][e + 2] = w.z; wr[k][e + 3] = w.w;
-        }
-    }
+    // ---- prologue.  The first row group (wpr warps) loads x, applies RMSNorm (RootMeanSquare.java:25-35,
+    //      WeightNormalizeAndScale.java:71-74), converts to fixed-point limbs for the u8 path and
+    //      publishes the result in shared memory; every group then picks up the chunks it owns.  One
+    //      load of x per block keeps the L2 traffic of a kernel start small.
+    uint8_t *share = smem + kSmemHeader;   // u8: four planes [q][nchunks] of 16 B (limbs of elements 4q..4q+3); FP32: [nchunks] float4
+    float *xs_sh = reinterpret_cast<float *>(share + (size_t)nchunks * (F32 ? 16 : 64));   // [nchunks] chunk sums (u8)
+    float *scratch = reinterpret_cast<float *>(smem + kScratchOff);
     bool lost = (__ldcg(&p.state->status) & L2J_DS_WAIT_TIMEOUT) != 0;
     const bool lost_before = lost;
-    float *scratch = reinterpret_cast<float *>(smem + kScratchOff);
-    float ssq = 0.f, amax = 0.f;
+    if (rsub == 0) {
+        // The producer may start filling the ring now: it needs hundreds of cycles to react, by then
+        // the few loads of x below are on the wire in front of its copies.
+        if (lane == 0)
+            mbar_arrive(sbase + kBarXIssued);
+        float xr[CPT][EPC];
+        float wr[CPT][EPC];
+        const bool has_rms = p.rms_w != nullptr;
+        const int64_t rep_off = (int64_t)(blockIdx.x % (unsigned)p.x_reps) * p.x_stride;
+        const float *xin = p.x_in + rep_off;
+        const float *rmsw = has_rms ? p.rms_w + rep_off : nullptr;
 #pragma unroll
-    for (int k = 0; k < CPT; ++k)
+        for (int k = 0; k < CPT; ++k) {
 #pragma unroll
-        for (int e = 0; e < EPC; ++e) {
-            ssq = fmaf(xr[k][e], xr[k][e], ssq);
-            amax = fmaxf(amax, fabsf(xr[k][e]));
+            for (int e = 0; e < EPC; e += 4) {
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                float4 w = make_float4(1.f, 1.f, 1.f, 1.f);
+                if (cvalid[k]) {
+                    v = ld_cg_f4_issue(xin + (int64_t)chunk[k] * EPC + e);
+                    if (has_rms)
+                        w = ld_cg_f4_issue(rmsw + (int64_t)chunk[k] * EPC + e);
+                }
+                xr[k][e] = v.x; xr[k][e + 1] = v.y; xr[k][e + 2] = v.z; xr[k][e + 3] = v.w;
+                wr[k][e] = w.x; wr[k][e + 1] = w.y; wr[k][e + 2] = w.z; wr[k][e + 3] = w.w;
+            }
         }
-    if (tid == 0)
-        trace_mark(p, 13);
-    if (has_rms || !F32) {
-        ssq = warp_sum(ssq);
-        amax = warp_max(amax);
-        if (rsub == 0 && lane == 0) {
-            scratch[wi] = ssq;
-            scratch[32 + wi] = amax;
-        }
-        named_barrier_sync(1, ncons);
-        ssq = 0.f;
-        amax = 0.f;
-        for (int i = 0; i < p.wpr; ++i) {
-            ssq += scratch[i];
-            amax = fmaxf(amax, scratch[32 + i]);
-        }
-        if (tid == 0)
-            trace_mark(p, 14);
-    }
-    if (has_rms) {
-        float tot = __fdiv_rn(ssq, (float)p.n);
-        tot = __fadd_rn(tot, 1e-5f);
-        const float ss = __fdiv_rn(1.0f, __fsqrt_rn(tot));
+        float ssq = 0.f, amax = 0.f;
 #pragma unroll
         for (int k = 0; k < CPT; ++k)
 #pragma unroll
-            for (int e = 0; e < EPC; ++e)
-                xr[k][e] = __fmul_rn(wr[k][e], __fmul_rn(ss, xr[k][e]));
-        amax = amax * ss * p.rms_wmax * 1.000001f;   // bound of |w * (ss * x)| from max|x| and max|w|
-    }
-
-    uint32_t xl[F32 ? 1 : CPT][4][4];   // [chunk][word of 4 elements][limb]
-    float xs[CPT];                       // sum of the chunk's x (for the group minimum term)
-    float inv = 1.0f;                    // value of one fixed-point unit
-    if constexpr (!F32) {
-        int ex = 0;
-        if (amax > 0.f && amax < 3.0e38f)
-            frexpf(amax, &ex);             // amax < 2^ex
-        ex = max(-90, min(126, ex));
-        const float f = __int_as_float((127 + 30 - ex) << 23);   // 2^(30 - ex)
-        inv = __int_as_float((127 + ex - 30) << 23);             // 2^(ex - 30)
-#pragma unroll
-        for (int k = 0; k < CPT; ++k) {
-            float s = 0.f;
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                uint32_t z[4];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    s += xr[k][4 * q + j];
-                    const int X = __float2int_rn(xr[k][4 * q + j] * f);      // |X| <= 2^30
-                    z[j] = ((uint32_t)X + 0x00808080u) ^ 0x00808080u;        // bytes = balanced signed limbs
-                }
-                // 4x4 byte transpose in 8 permutes: limb l of the four elements ends up in word l
-                const uint32_t t0 = __byte_perm(z[0], z[1], 0x5140);   // z0.b0 z1.b0 z0.b1 z1.b1
-                const uint32_t t1 = __byte_perm(z[0], z[1], 0x7362);   // z0.b2 z1.b2 z0.b3 z1.b3
-                const uint32_t t2 = __byte_perm(z[2], z[3], 0x5140);
-                const uint32_t t3 = __byte_perm(z[2], z[3], 0x7362);
-                xl[k][q][0] = __byte_perm(t0, t2, 0x5410);
-                xl[k][q][1] = __byte_perm(t0, t2, 0x7632);
-                xl[k][q][2] = __byte_perm(t1, t3, 0x5410);
-                xl[k][q][3] = __byte_perm(t1, t3, 0x7632);
+            for (int e = 0; e < EPC; ++e) {
+                ssq = fmaf(xr[k][e], xr[k][e], ssq);
+                amax = fmaxf(amax, fabsf(xr[k][e]));
             }
-            xs[k] = s;
+        if (tid == 0)
+            trace_mark(p, 13);
+        if (has_rms || !F32) {
+            ssq = warp_sum(ssq);
+            amax = warp_max(amax);
+            if (lane == 0) {
+                scratch[wi] = ssq;
+                scratch[32 + wi] = amax;
+            }
+            named_barrier_sync(2, p.wpr * 32);
+            ssq = 0.f;
+            amax = 0.f;
+            for (int i = 0; i < p.wpr; ++i) {
+                ssq += scratch[i];
+                amax = fmaxf(amax, scratch[32 + i]);
+            }
+        }
+        if (has_rms) {
+            float tot = __fdiv_rn(ssq, (float)p.n);
+            tot = __fadd_rn(tot, 1e-5f);
+            const float ss = __fdiv_rn(1.0f, __fsqrt_rn(tot));
+#pragma unroll
+            for (int k = 0; k < CPT; ++k)
+#pragma unroll
+                for (int e = 0; e < EPC; ++e)
+                    xr[k][e] = __fmul_rn(wr[k][e], __fmul_rn(ss, xr[k][e]));
+            amax = amax * ss * p.rms_wmax * 1.000001f;   // bound of |w * (ss * x)| from max|x| and max|w|
+        }
+        if constexpr (F32) {
+#pragma unroll
+            for (int k = 0; k < CPT; ++k)
+                if (cvalid[k])
+                    *reinterpret_cast<float4 *>(share + (size_t)chunk[k] * 16) = make_float4(xr[k][0], xr[k][1], xr[k][2], xr[k][3]);
+        } else {
+            int ex = 0;
+            if (amax > 0.f && amax < 3.0e38f)
+                frexpf(amax, &ex);             // amax < 2^ex
+            ex = max(-90, min(126, ex));
+            const float f = __int_as_float((127 + 30 - ex) << 23);   // 2^(30 - ex)
+            if (tid == 0)
+                scratch[63] = __int_as_float((127 + ex - 30) << 23); // 2^(ex - 30): value of one fixed-point unit
+#pragma unroll
+            for (int k = 0; k < CPT; ++k) {
+                float sum = 0.f;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    uint32_t z[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        sum += xr[k][4 * q + j];
+                        const int X = __float2int_rn(xr[k][4 * q + j] * f);      // |X| <= 2^30
+                        z[j] = ((uint32_t)X + 0x00808080u) ^ 0x00808080u;        // bytes = balanced signed limbs
+                    }
+                    // 4x4 byte transpose in 8 permutes: limb l of the four elements ends up in word l
+                    const uint32_t t0 = __byte_perm(z[0], z[1], 0x5140);   // z0.b0 z1.b0 z0.b1 z1.b1
+                    const uint32_t t1 = __byte_perm(z[0], z[1], 0x7362);   // z0.b2 z1.b2 z0.b3 z1.b3
+                    const uint32_t t2 = __byte_perm(z[2], z[3], 0x5140);
+                    const uint32_t t3 = __byte_perm(z[2], z[3], 0x7362);
+                    if (cvalid[k])
+                        *reinterpret_cast<uint4 *>(share + ((size_t)q * nchunks + chunk[k]) * 16) =
+                            make_uint4(__byte_perm(t0, t2, 0x5410), __byte_perm(t0, t2, 0x7632), __byte_perm(t1, t3, 0x5410),
+                                       __byte_perm(t1, t3, 0x7632));
+                }
+                if (cvalid[k])
+                    xs_sh[chunk[k]] = sum;
+            }
         }
     }
+    named_barrier_sync(1, ncons);
+
+    float xv[F32 ? CPT : 1][4];           // FP32 path: the chunk's four x values
+    uint32_t xl[F32 ? 1 : CPT][4][4];     // u8 path: [chunk][word of 4 elements][limb]
+    float xs[CPT];                         // u8 path: sum of the chunk's x (for the group minimum term)
+    float inv = 1.0f;                      // u8 path: value of one fixed-point unit
+#pragma unroll
+    for (int k = 0; k < CPT; ++k) {
+        if constexpr (F32) {
+            float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (cvalid[k])
+                t = *reinterpret_cast<const float4 *>(share + (size_t)chunk[k] * 16);
+            xv[k][0] = t.x; xv[k][1] = t.y; xv[k][2] = t.z; xv[k][3] = t.w;
+            xs[k] = 0.f;
+        } else {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                uint4 t = make_uint4(0u, 0u, 0u, 0u);
+                if (cvalid[k])
+                    t = *reinterpret_cast<const uint4 *>(share + ((size_t)q * nchunks + chunk[k]) * 16);
+                xl[k][q][0] = t.x; xl[k][q][1] = t.y; xl[k][q][2] = t.z; xl[k][q][3] = t.w;
+            }
+            xs[k] = cvalid[k] ? xs_sh[chunk[k]] : 0.f;
+        }
+    }
+    if constexpr (!F32)
+        inv = scratch[63];
 
     if (tid == 0)
         trace_mark(p, 3);
@@ -614,7 +709,7 @@ __global__ void __launch_bounds__(MAXT, 2) matvec_ring_kernel(const __grid_const
         }
         const StageDesc d = *(reinterpret_cast<const StageDesc *>(smem + kDescOff) + slot);
         const bool done = d.nrows <= 0 || (lost && !lost_before);
-        const uint8_t *slot_ptr = smem + kSmemHeader + (size_t)slot * p.slot_bytes;
+        const uint8_t *slot_ptr = smem + kSmemHeader + p.xshare_bytes + (size_t)slot * p.slot_bytes;
 
         float v[RT];
 #pragma unroll
@@ -631,10 +726,10 @@ __global__ void __launch_bounds__(MAXT, 2) matvec_ring_kernel(const __grid_const
                     for (int k = 0; k < CPT; ++k) {
                         if (cvalid[k]) {
                             const float4 w = *reinterpret_cast<const float4 *>(rowp + (size_t)chunk[k] * 16);
-                            a = fmaf(w.x, xr[k][0], a);
-                            a = fmaf(w.y, xr[k][1], a);
-                            a = fmaf(w.z, xr[k][2], a);
-                            a = fmaf(w.w, xr[k][3], a);
+                            a = fmaf(w.x, xv[k][0], a);
+                            a = fmaf(w.y, xv[k][1], a);
+                            a = fmaf(w.z, xv[k][2], a);
+                            a = fmaf(w.w, xv[k][3], a);
                         }
                     }
                     v[t] = a;
@@ -725,26 +820,25 @@ MvPlan plan_matvec(int n, bool f32, bool paired)
         return pl;
     const int nchunks = n / epc;
     const int rowbytes = f32 ? n * 4 : n;
-    const int max_nw_u8[3] = {16, 10, 9};
-    for (int cpt = 1; cpt <= 3; ++cpt) {
-        const int maxnw = f32 ? 16 : max_nw_u8[cpt - 1];
+    // shared copy of x in front of the ring: 16 B (FP32) or 64 B of limbs + 4 B of sum (u8) per chunk
+    const int xshare = ((f32 ? nchunks * 16 : nchunks * 68) + 127) & ~127;
+    for (int cpt = 1; cpt <= 4; ++cpt) {
         const int wpr = (nchunks + 32 * cpt - 1) / (32 * cpt);
-        if (wpr > maxnw)
-            continue;
-        // One group of wpr warps per block and as many rows per thread as make a stage of about 32 KB;
-        // only short rows get several concurrent row groups.
-        int rt = 8;
-        while (rt > 2 && rt * rowbytes > 36 * 1024)
-            rt /= 2;
-        int rpp = 1;
-        while (2 * rpp * wpr <= maxnw && 2 * rpp * rt <= 32 && 2 * rpp * rt * rowbytes <= 32 * 1024 &&
-               rpp * rt * rowbytes < 16 * 1024)
+        if (wpr > 8)
+            continue;   // two row groups must fit 16 consumer warps
+        int rpp = 2;
+        while (2 * rpp * wpr <= 16 && rpp < 8)
             rpp *= 2;
-        if (const char *e = getenv("L2J_WIDE")) {   // experiment: two row groups and half the rows per thread
-            if (atoi(e) && rpp == 1 && rt >= 4 && 2 * wpr <= maxnw) {
-                rpp = 2;
+        // rows per thread and stage: aim at stages of 32-48 KB, at most 32 rows
+        int rt = 8;
+        while (rt > 2 && (rt * rpp > 32 || rt * rpp * rowbytes > 64 * 1024))
+            rt /= 2;
+        while (rpp > 1 && rt * rpp * rowbytes > 64 * 1024)
+            rpp /= 2;
+        if (const char *e = getenv("L2J_RT")) {   // experiment: cap the rows per thread and stage
+            const int cap = atoi(e);
+            while (rt > 2 && rt > cap)
                 rt /= 2;
-            }
         }
         int half_hdr = 0;
         if (!f32) {
@@ -753,7 +847,7 @@ MvPlan plan_matvec(int n, bool f32, bool paired)
         }
         const int payload = rt * rpp * rowbytes;
         const int slot = (payload + 2 * half_hdr + 127) & ~127;
-        int nstage = kMaxSmemRing / slot;
+        int nstage = (kMaxSmemBlock - kSmemHeader - xshare) / slot;
         if (nstage > 16)
             nstage = 16;
         if (nstage < 2)
@@ -766,8 +860,9 @@ MvPlan plan_matvec(int n, bool f32, bool paired)
         pl.slot_bytes = slot;
         pl.hdr_off = payload;
         pl.half_hdr = half_hdr;
+        pl.xshare_bytes = xshare;
         pl.threads = (rpp * wpr + 2) * 32;
-        pl.smem_bytes = kSmemHeader + nstage * slot;   // header + ring
+        pl.smem_bytes = kSmemHeader + xshare + nstage * slot;   // header + shared x + ring
         pl.ok = true;
         (void)paired;
         return pl;
@@ -798,19 +893,18 @@ template <bool F32, int CPT, int RT, int MAXT>
 static cudaError_t prepare_ring_t()
 {
     auto kern = matvec_ring_kernel<F32, CPT, RT, MAXT>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemHeader + kMaxSmemRing);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmemBlock);
     if (e != cudaSuccess)
         return e;
     return cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
 }
 
-// Instantiations: (FP32 weights, chunks per thread, rows per thread and stage, largest block).  The
-// block bound sets the register budget so that two blocks fit the register file of an SM.
+// Instantiations: (FP32 weights, chunks per thread, rows per thread and stage, largest block).
 #define L2J_RING_VARIANTS(X) \
     X(true, 1, 2, 576) X(true, 1, 4, 576) X(true, 1, 8, 576) X(true, 2, 2, 576) X(true, 2, 4, 576) X(true, 2, 8, 576) \
-    X(true, 3, 2, 576) X(true, 3, 4, 576) X(true, 3, 8, 576) \
-    X(false, 1, 2, 320) X(false, 1, 4, 320) X(false, 1, 8, 320) X(false, 1, 2, 576) X(false, 1, 4, 576) X(false, 1, 8, 576) \
-    X(false, 2, 2, 384) X(false, 2, 4, 384) X(false, 2, 8, 384) X(false, 3, 2, 352) X(false, 3, 4, 352) X(false, 3, 8, 352)
+    X(true, 3, 2, 576) X(true, 3, 4, 576) X(true, 3, 8, 576) X(true, 4, 2, 576) X(true, 4, 4, 576) X(true, 4, 8, 576) \
+    X(false, 1, 2, 576) X(false, 1, 4, 576) X(false, 1, 8, 576) X(false, 2, 2, 576) X(false, 2, 4, 576) X(false, 2, 8, 576) \
+    X(false, 3, 2, 576) X(false, 3, 4, 576) X(false, 3, 8, 576) X(false, 4, 2, 576) X(false, 4, 4, 576) X(false, 4, 8, 576)
 
 // Opts the ring kernels of the current device into their dynamic shared memory size.  Call once
 // per device before the first launch (and outside stream capture).
@@ -836,7 +930,7 @@ cudaError_t launch_matvec_ring(const LaunchCfg &lc, const MvPlan &plan, bool f32
 // =============================================================================================
 
 __global__ void __launch_bounds__(256) begin_kernel(SeqState *state, const Cmd *cmd, const float *emb, float *x, int dim,
-                                                    int vocab, int seq_len, int gather)
+                                                    int vocab, int seq_len, int gather, int x_reps, int x_stride)
 {
     __shared__ int s_tok;
     pdl_launch_dependents();
@@ -868,14 +962,23 @@ __global__ void __launch_bounds__(256) begin_kernel(SeqState *state, const Cmd *
     __syncthreads();
     if (gather) {
         const float4 *src = reinterpret_cast<const float4 *>(emb + (int64_t)s_tok * dim);
-        float4 *dst = reinterpret_cast<float4 *>(x);
-        for (int i = threadIdx.x; i < dim / 4; i += blockDim.x)
-            dst[i] = __ldg(src + i);
+        for (int i = threadIdx.x; i < dim / 4; i += blockDim.x) {
+            const float4 v = __ldg(src + i);
+            for (int r = 0; r < x_reps; ++r)
+                reinterpret_cast<float4 *>(x + (int64_t)r * x_stride)[i] = v;
+        }
+    } else {
+        // a later pipeline stage: the caller put x into copy 0, spread it to the other copies
+        for (int i = threadIdx.x; i < dim / 4; i += blockDim.x) {
+            const float4 v = __ldcg(reinterpret_cast<const float4 *>(x) + i);
+            for (int r = 1; r < x_reps; ++r)
+                reinterpret_cast<float4 *>(x + (int64_t)r * x_stride)[i] = v;
+        }
     }
 }
 
 cudaError_t launch_begin(const LaunchCfg &lc, SeqState *state, const Cmd *cmd, const float *emb, float *x, int dim,
-                         int vocab, int seq_len, int gather)
+                         int vocab, int seq_len, int gather, int x_reps, int x_stride)
 {
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(1);
@@ -887,7 +990,7 @@ cudaError_t launch_begin(const LaunchCfg &lc, SeqState *state, const Cmd *cmd, c
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = lc.pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, begin_kernel, state, cmd, emb, x, dim, vocab, seq_len, gather);
+    return cudaLaunchKernelEx(&cfg, begin_kernel, state, cmd, emb, x, dim, vocab, seq_len, gather, x_reps, x_stride);
 }
 
 // =============================================================================================
@@ -924,40 +1027,60 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const __grid_co
     const int sstride = head + 4;
 
     pdl_launch_dependents();
-    pdl_wait();
 
+    // The position was fixed when the token started and every cached row but the newest is older than
+    // that, so both can be read before the QKV kernel in front of this one has finished: the block
+    // becomes resident early and hides its first memory round trip behind that kernel.
     const int pos = p.pos_override >= 0 ? p.pos_override : __ldcg(&p.state->cur_pos);
     const int npos = pos + 1;
     int chunk = (npos + p.nsplit - 1) / p.nsplit;
     if (chunk < kAttnMinChunk)
         chunk = kAttnMinChunk;
     const int nact = (npos + chunk - 1) / chunk;    // blocks of this head that have work
-    if (sp >= nact)
+    if (sp >= nact) {
+        pdl_wait();
         return;
+    }
     const int t0 = sp * chunk;
     const int cnt = min(npos, t0 + chunk) - t0;
     const int kvh = h / p.kv_mul;
     const float *kb = p.k_cache + ((int64_t)kvh * p.seq_len + t0) * head;
     const float *vb = p.v_cache + ((int64_t)kvh * p.seq_len + t0) * head;
+    const float sq = sqrtf((float)head);
+
+    float4 kk[4], vv[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const int idx = u * nslots + slot;
+        kk[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        vv[u] = kk[u];
+        if (active && idx < cnt && t0 + idx < pos) {
+            kk[u] = __ldcg(reinterpret_cast<const float4 *>(kb + (int64_t)idx * head + 4 * li));
+            vv[u] = __ldcg(reinterpret_cast<const float4 *>(vb + (int64_t)idx * head + 4 * li));
+        }
+    }
+
+    pdl_wait();   // q and the newest K/V row come from the kernel in front
 
     float4 q4 = make_float4(0.f, 0.f, 0.f, 0.f);
     if (active)
         q4 = __ldcg(reinterpret_cast<const float4 *>(p.q + (int64_t)h * head + 4 * li));
-    const float sq = sqrtf((float)head);
 
     float m = -INFINITY, l = 0.f;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int ib = 0; ib < cnt; ib += 4 * nslots) {   // uniform trip count for the whole block
-        float4 kk[4], vv[4];
         int idx[4];
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
             idx[u] = ib + u * nslots + slot;
-            kk[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-            vv[u] = kk[u];
-            if (active && idx[u] < cnt) {
-                kk[u] = __ldcg(reinterpret_cast<const float4 *>(kb + (int64_t)idx[u] * head + 4 * li));
-                vv[u] = __ldcg(reinterpret_cast<const float4 *>(vb + (int64_t)idx[u] * head + 4 * li));
+            const bool preloaded = ib == 0 && t0 + idx[u] < pos;
+            if (!preloaded) {
+                kk[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                vv[u] = kk[u];
+                if (active && idx[u] < cnt) {
+                    kk[u] = __ldcg(reinterpret_cast<const float4 *>(kb + (int64_t)idx[u] * head + 4 * li));
+                    vv[u] = __ldcg(reinterpret_cast<const float4 *>(vb + (int64_t)idx[u] * head + 4 * li));
+                }
             }
         }
         float s[4];
@@ -1015,8 +1138,12 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const __grid_co
         }
     }
     if (nact == 1) {
-        if (tid < head)
-            p.out[(int64_t)h * head + tid] = __fdiv_rn(O, L);   // ExpSumNormalize.java:33-37 folded into the sum
+        {
+            const float o = __fdiv_rn(O, L);   // ExpSumNormalize.java:33-37 folded into the sum
+            if (tid < head)
+                for (int r = 0; r < p.out_reps; ++r)
+                    p.out[(int64_t)r * p.out_stride + (int64_t)h * head + tid] = o;
+        }
         return;
     }
 
@@ -1054,7 +1181,9 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const __grid_co
                 OO = fmaf(__ldcg(hp + (int64_t)s2 * (head + 2) + 2 + tid), w, OO);
             }
         }
-        p.out[(int64_t)h * head + tid] = __fdiv_rn(OO, LL);
+        const float o = __fdiv_rn(OO, LL);
+        for (int r = 0; r < p.out_reps; ++r)
+            p.out[(int64_t)r * p.out_stride + (int64_t)h * head + tid] = o;
     }
     if (tid == 0)
         p.counters[h] = 0;
@@ -1174,10 +1303,12 @@ __global__ void __launch_bounds__(256) epilogue_plain_kernel(MvParams p, const f
                              p.rope_sin + (int64_t)pos * (p.head >> 1));
     } else if (p.epilogue == EPI_SWIGLU) {
         for (int i = threadIdx.x; i < p.seg[0].rows; i += 256)
-            p.y[i] = epi_swiglu(y0[i], y1[i]);
+            for (int r = 0; r < p.y_reps; ++r)
+                p.y[(int64_t)r * p.y_stride + i] = epi_swiglu(y0[i], y1[i]);
     } else if (p.epilogue == EPI_RESIDUAL) {
         for (int i = threadIdx.x; i < p.seg[0].rows; i += 256)
-            p.y[i] = __fadd_rn(p.y[i], y0[i]);
+            for (int r = 0; r < p.y_reps; ++r)
+                p.y[(int64_t)r * p.y_stride + i] = __fadd_rn(p.y[(int64_t)r * p.y_stride + i], y0[i]);
     } else if (p.epilogue == EPI_LOGITS) {
         __shared__ float sv[256];
         __shared__ int si[256];
