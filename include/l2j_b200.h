@@ -245,6 +245,24 @@ L2J_API int l2j_k_attention(int device, const float *q, const float *key_cache, 
 /* Silu.call (kernel/Silu.java:97-135): hb = hb * sigmoid(hb) * hb2. */
 L2J_API int l2j_k_swiglu(int device, float *hb, const float *hb2, int n);
 
+/* No counterpart in the reference.  The attention step for hosts that must not allocate device memory
+ * while they run (a process whose memory pool belongs to another allocator, a latency-bound loop that
+ * cannot afford cudaMalloc's implicit synchronisation): the same kernel as l2j_k_attention, but all
+ * pointers are device pointers supplied by the caller, the caches are in the library's own layout
+ * (kv_head, position, head_size) with row stride seq_len, and the split-merge scratch is a fixed
+ * ~2.1 MB array inside the library that every GPU loading it holds until exit.  Limits: at most 128
+ * heads of at most 128 floats; larger problems are rejected with L2J_E_INVALID.  The call only enqueues
+ * work on `stream` (a cudaStream_t, NULL for the default stream) and does not synchronise; it calls no
+ * cudaMalloc / cudaFree.  The first call on a device looks up the scratch array's device address, so
+ * make it before any stream capture.  All calls share the one array: two calls whose kernels overlap
+ * on the GPU race on it, keep them on one stream or order them yourself. */
+L2J_API int l2j_k_attention_noalloc(int device, const float *q_dev, const float *k_cache_dev, const float *v_cache_dev,
+                                    int pos, int n_heads, int n_kv_heads, int head_size, int seq_len, float *out_dev,
+                                    void *stream);
+
+/* Message of the calling thread's most recent l2j_k_attention_noalloc failure ("" if none). */
+L2J_API const char *l2j_noalloc_last_error(void);
+
 /* Copies n bytes device-to-device repeatedly and returns the best time; the denominator check of
  * the roofline (no counterpart in the reference). */
 L2J_API int l2j_k_copy_bandwidth(int device, int64_t bytes, int iters, double *best_gbs);
