@@ -13,7 +13,7 @@ constexpr int kGroupBytes = 264;   // encoded bytes per group in the file format
 // the RMSNorm weights) are kept in several copies: hundreds of blocks asking for the same few L2 lines
 // at the same moment are served one after the other, copies at different addresses are served in parallel.
 constexpr int kVecReps = 1;
-constexpr int kMaxSmemBlock = 208 * 1024;  // dynamic shared memory of a ring-kernel block: one block per SM, with
+constexpr int kMaxSmemBlock = 221 * 1024;  // dynamic shared memory of a ring-kernel block: one block per SM, with
                                            // room left for the small blocks of the attention kernel
 
 // Device-resident sequence state, advanced by the kernels themselves so that consecutive tokens
