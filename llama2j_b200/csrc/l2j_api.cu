@@ -205,6 +205,10 @@ void fill_plan(MvParams &p, const MvPlan &pl)
             const int64_t stage_bytes = (int64_t)pl.rt * pl.rpp * p.rowbytes;
             p.pf_distance = mb > 0 ? (int)((int64_t)(mb * 1048576.0) / stage_bytes) : 0;
         }
+        {
+            const char *e = getenv("L2J_TAIL_PREFETCH");
+            p.tail_prefetch = e ? atoi(e) : 3;
+        }
         p.total_stages = 0;
         const int nseg = p.paired ? 1 : p.nseg;
         for (int i = 0; i < 3; ++i) {

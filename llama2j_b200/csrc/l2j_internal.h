@@ -83,6 +83,7 @@ struct MvParams {
     int rowbytes;      // bytes of one matrix row
     int f32;           // 1: FP32 weights
     int pf_distance;   // stages the L2 prefetch runs ahead of the claims (0: off)
+    int tail_prefetch; // stages of the next launch each block prefetches into L2 when it runs out of work
     int early_fill;    // stages the producer may issue before the previous kernel has finished (0: none)
     const MvParams *next;   // device copy of the next ring launch's parameters (prefetch target) or nullptr
     // prologue

@@ -287,7 +287,7 @@ __global__ void __launch_bounds__(768, 1) matvec_ring_kernel(const __grid_consta
     if (tid < 32)
         mbar_fence_init();
     __syncthreads();
-    if (p.pdl_mode == 0)
+    if ((p.pdl_mode & 3) == 0)
         pdl_launch_dependents();
 
     const int R = RT * p.rpp;                       // rows of a stage in shared memory
@@ -373,9 +373,14 @@ __global__ void __launch_bounds__(768, 1) matvec_ring_kernel(const __grid_consta
                     const uint32_t hbytes = (uint32_t)(((gl - ga + 2) & ~(int64_t)1) * 8);
                     desc->e0a = (int)(flat - ga * 256);
                     desc->e0b = 0;
+                    if (p.pdl_mode & 16) {
+                        mbar_arrive_expect_tx(full, pbytes);
+                        bulk_g2s(dst, p.seg[seg].payload + flat, pbytes, full, pol);
+                    } else {
                     mbar_arrive_expect_tx(full, pbytes + hbytes);
                     bulk_g2s(dst, p.seg[seg].payload + flat, pbytes, full, pol);
                     bulk_g2s(dst + (uint32_t)p.hdr_off, p.seg[seg].hdr + ga, hbytes, full, pol);
+                    }
                 } else {
                     int64_t flat[2], ga[2];
                     uint32_t hbytes[2];
@@ -387,12 +392,19 @@ __global__ void __launch_bounds__(768, 1) matvec_ring_kernel(const __grid_consta
                     }
                     desc->e0a = (int)(flat[0] - ga[0] * 256);
                     desc->e0b = (int)(flat[1] - ga[1] * 256);
+                    if (p.pdl_mode & 16) {
+                        mbar_arrive_expect_tx(full, 2 * pbytes);
+                        for (int h = 0; h < 2; ++h)
+                            bulk_g2s(dst + (uint32_t)(h * (R / 2)) * (uint32_t)rowbytes, p.seg[h].payload + flat[h], pbytes,
+                                     full, pol);
+                    } else {
                     mbar_arrive_expect_tx(full, 2 * pbytes + hbytes[0] + hbytes[1]);
                     for (int h = 0; h < 2; ++h) {
                         bulk_g2s(dst + (uint32_t)(h * (R / 2)) * (uint32_t)rowbytes, p.seg[h].payload + flat[h], pbytes,
                                  full, pol);
                         bulk_g2s(dst + (uint32_t)p.hdr_off + (uint32_t)(h * p.half_hdr), p.seg[h].hdr + ga[h], hbytes[h],
                                  full, pol);
+                    }
                     }
                 }
                 if (first) {
@@ -420,6 +432,16 @@ __global__ void __launch_bounds__(768, 1) matvec_ring_kernel(const __grid_consta
                 }
             }
             trace_mark(p, 2);
+            // Out of work: while the consumers drain the ring, start HBM -> L2 for the stages the next launch
+            // will ask for first, so that the memory system does not run dry between the two kernels.
+            if (p.next && p.tail_prefetch > 0) {
+                const int ns = p.next->total_stages;
+                for (int j = 0; j < p.tail_prefetch; ++j) {
+                    const int st = (int)blockIdx.x + j * (int)gridDim.x;
+                    if (st < ns)
+                        prefetch_stage(*p.next, st);
+                }
+            }
             // The block that learns last that the work has run out re-arms the counters for the next launch.
             __threadfence();
             if (pending != 0xffffffffu && pending2 != 0xffffffffu && atomicAdd(p.work + 1, 1u) == gridDim.x - 1) {
@@ -718,7 +740,7 @@ __global__ void __launch_bounds__(768, 1) matvec_ring_kernel(const __grid_consta
             const int r = rsub + t * p.rpp;                      // row of the stage in shared memory
             const int half = (p.paired && t >= RT / 2) ? 1 : 0;  // second half of a paired stage: the partner matrix
             const int local = r - half * (R / 2);
-            if (!done && local < d.nrows) {
+            if (!done && local < d.nrows && !(p.pdl_mode & 32)) {
                 const uint8_t *rowp = slot_ptr + (size_t)r * rowbytes;
                 if constexpr (F32) {
                     float a = 0.f;
@@ -805,7 +827,7 @@ __global__ void __launch_bounds__(768, 1) matvec_ring_kernel(const __grid_consta
     }
     if (tid == 0)
         trace_mark(p, 5);
-    if (p.pdl_mode == 1)
+    if ((p.pdl_mode & 3) == 1)
         pdl_launch_dependents();
     if (lost && !lost_before)
         atomicOr(&p.state->status, L2J_DS_WAIT_TIMEOUT);

@@ -1,0 +1,107 @@
+"""Command-line run loop with the reference's flags, CUDA mode only.
+
+Mirror of Run.main (Run.java:528-707) and CommandLine (CommandLine.java:12-133) for the decode path:
+`--checkpoint X --mode CUDA --gpuMem a,b --temp 0.0 --steps N`, checkpoint resolved under `models/`,
+quant cache files beside it (TransformerWeights.java:191-232).  The tokenizer stays outside this
+repository, so prompts are token ids (`--promptTokens 5,17,...`, an addition) and the output is ids.
+There is no CPU mode here: `--mode CPU` is refused.
+
+  python -m llama2j_b200.run --checkpoint stories15M.bin --temp 0.0 --steps 64 --promptTokens 5,9
+"""
+from __future__ import annotations
+
+import os
+import sys
+import time
+
+import numpy as np
+
+from . import lib as _lib
+from . import model_files as mf
+from . import synthetic as syn
+from .layer_allocation import LayerAllocation, parse_gpu_mem
+from .transformer import Transformer, argmax
+
+MODELS_DIRECTORY = "models"   # Run.java:34
+
+FLAGS = ("--checkpoint", "--mode", "--temp", "--topp", "--seed", "--steps", "--gpuMem", "--prompt", "--tokenizer",
+         "--promptTokens")
+
+
+def parse_args(argv):
+    """`--flag value` pairs (CommandLine.java:35-39) with the reference's defaults (CommandLine.java:22-29)."""
+    args = {"--mode": "CUDA", "--temp": "0.9", "--topp": "0.9", "--steps": "256", "--gpuMem": None,
+            "--promptTokens": ""}
+    for i in range(0, len(argv) - 1, 2):
+        args[argv[i]] = argv[i + 1]
+    if "--checkpoint" not in args:
+        raise SystemExit("Usage: --checkpoint <file> [--mode CUDA] [--temp 0.0] [--steps N] [--gpuMem a,b,...] "
+                         "[--promptTokens id,id,...]")
+    return args
+
+
+def load_quant_tensor(path: str, cfg: mf.ModelConfig, tensor: int, device: int) -> np.ndarray:
+    """readAsQuant (TransformerWeights.java:191-232): use the cache file if present, otherwise quantise the
+    checkpoint tensor (on the GPU, bit-exact Quant.encode) and write the cache."""
+    cache = mf.quant_cache_path(path, tensor)
+    n = cfg.tensor_floats(tensor)
+    if os.path.exists(cache):
+        return mf.read_quant_cache(cache, n)
+    groups = syn.quant_encode(np.asarray(mf.read_checkpoint_tensor(path, cfg, tensor)), device)
+    mf.write_quant_cache(cache, groups)
+    return groups
+
+
+def main(argv=None) -> int:
+    args = parse_args(sys.argv[1:] if argv is None else argv)
+    if args["--mode"].upper() != "CUDA":
+        raise SystemExit("only --mode CUDA exists in this implementation (no CPU path)")
+    if float(args["--temp"]) != 0.0:
+        raise SystemExit("temperature sampling stays in the Java host; run with --temp 0.0")
+    path = os.path.join(MODELS_DIRECTORY, args["--checkpoint"])
+    cfg = mf.read_checkpoint_header(path)
+    gpu_mem = parse_gpu_mem(args["--gpuMem"]) if args["--gpuMem"] else [180 * 1024 ** 3]
+    alloc = LayerAllocation.from_gpu_mem(gpu_mem, cfg)
+    t0 = time.time()
+    stages = [Transformer(cfg, dev, alloc.first_layer[dev], alloc.last_layer[dev]) for dev in range(alloc.device_count)]
+    for t in _lib.QUANT_TENSORS:
+        groups = load_quant_tensor(path, cfg, t, 0)
+        for st in stages:
+            st.upload_quant(t, groups)
+    emb = np.asarray(mf.read_checkpoint_tensor(path, cfg, _lib.T_TOKEN_EMBEDDING))
+    for st in stages:
+        st.upload_f32(_lib.T_TOKEN_EMBEDDING, emb)
+    if not cfg.shared_classifier:
+        stages[-1].upload_f32(_lib.T_WCLS, np.asarray(mf.read_checkpoint_tensor(path, cfg, _lib.T_WCLS)))
+    for st in stages:
+        st.finalize()
+    print(f"INFO: Initialized transformer in {time.time() - t0:.2f} s")
+    steps = int(args["--steps"])
+    if steps <= 0 or steps > cfg.seq_len:
+        steps = cfg.seq_len                                  # Run.java:599-602
+    prompt = [int(t) for t in args["--promptTokens"].split(",") if t.strip()]
+    token, pos, start, out = 1, 0, 0.0, []
+    while pos < steps:                                       # Run.java:623-685
+        x = None
+        for st in stages[:-1]:
+            x = st.forward_stage(token, pos, x)
+        logits, _ = stages[-1].forward_stage(token, pos, x) if len(stages) > 1 else stages[0].forward(token, pos)
+        nxt = prompt[pos] if pos < len(prompt) else argmax(logits)
+        pos += 1
+        if nxt == 1:
+            break
+        out.append(nxt)
+        token = nxt
+        if start == 0.0:
+            start = time.time()
+    end = time.time()
+    print(" ".join(str(t) for t in out))
+    if pos > 1:
+        print(f"DEBUG: achieved tok/s: {(pos - 1) / max(end - start, 1e-9):.2f}")   # Run.java:703-706
+    for st in stages:
+        st.close()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -5,6 +5,8 @@ token sequence.  The oracle runs in its CUDA-faithful arithmetic (exact sigmoid)
 its CPU-faithful lookup-table SiLU is measured and bounded separately, as the reference's two paths
 differ from each other by that much.  The oracle is teacher-forced with the GPU's tokens so that every
 position is compared even if a near-tie flips an arg-max."""
+import os
+
 import numpy as np
 import pytest
 
@@ -228,3 +230,42 @@ def test_llama2_7b_shape_first_positions(oracle):
     assert np.array_equal(host, a[:48])                                # host-driven loop = device loop
     assert m.stats().device_status == 0
     m.close()
+
+
+def test_cli_run_loop_with_checkpoint_and_quant_cache(oracle, tmp_path, monkeypatch, capsys):
+    """The reference's flow end to end: llama2.c checkpoint under models/, quant cache files written beside
+    it on the first run (bit-identical to the oracle's Quant.encode) and read back on the second, greedy
+    tokens equal to the oracle's run loop."""
+    from llama2j_b200 import model_files as mf
+    from llama2j_b200 import run as cli
+    cfg = ModelConfig(dim=128, hidden_dim=352, n_layers=2, n_heads=4, n_kv_heads=4, vocab_size=300, seq_len=48,
+                      shared_classifier=True)
+    rng = np.random.default_rng(12)
+    fp32 = {t: rng.normal(0, 0.05, cfg.tensor_floats(t)).astype(np.float32) for t in range(11)}
+    for t in (L.T_RMS_ATT, L.T_RMS_FFN, L.T_RMS_FINAL):
+        fp32[t] = rng.uniform(0.5, 1.5, cfg.tensor_floats(t)).astype(np.float32)
+    (tmp_path / "models").mkdir()
+    path = str(tmp_path / "models" / "tiny.bin")
+    mf.write_checkpoint(path, cfg, fp32)
+    monkeypatch.chdir(tmp_path)
+    argv = ["--checkpoint", "tiny.bin", "--mode", "CUDA", "--temp", "0.0", "--steps", "40", "--promptTokens", "5,17,200,3"]
+    assert cli.main(argv) == 0
+    first = capsys.readouterr().out.strip().splitlines()
+    tensors = {L.T_TOKEN_EMBEDDING: fp32[L.T_TOKEN_EMBEDDING]}
+    for t in L.QUANT_TENSORS:
+        cache = mf.quant_cache_path(path, t)
+        assert os.path.exists(cache)
+        tensors[t] = oracle.quant_encode(fp32[t])
+        assert np.array_equal(mf.read_quant_cache(cache, cfg.tensor_floats(t)), tensors[t])
+    om = oracle.OracleModel(cfg, tensors, oracle.SILU_EXACT, oracle.SOFTMAX_REFERENCE)
+    ref, _ = oracle.greedy_run(om, [5, 17, 200, 3], 40)
+    ref = ref.tolist()
+    if 1 in ref:
+        ref = ref[:ref.index(1)]                                      # the loop stops on a sampled BOS
+    got = [int(t) for t in first[1].split()]
+    assert got == ref
+    assert cli.main(argv) == 0                                         # second run: from the cache files
+    second = capsys.readouterr().out.strip().splitlines()
+    assert second[1] == first[1]
+    with pytest.raises(SystemExit):
+        cli.main(["--checkpoint", "tiny.bin", "--mode", "CPU"])
