@@ -182,6 +182,48 @@ def run_reference(args, cfg, rank: int, world: int) -> None:
     print(json.dumps(line), flush=True)
 
 
+def run_long_context(args, cfg, model, rank, world, max_over_ranks, barrier) -> None:
+    """Long-context attention stress: a 3840-token seeded prompt pushed through the decode path (the
+    reference has no batched prefill), then greedy decode of positions 3840..seq_len-1.  The decode span is
+    timed as the difference of two device-timed runs (to seq_len and to 3840 positions)."""
+    from llama2j_b200 import synthetic as syn
+    n_prompt = min(3840, cfg.seq_len - 2)
+    prompt = syn.synthetic_prompt(n_prompt, 1, cfg.vocab_size)
+    full, head = cfg.seq_len, n_prompt
+    model.generate_greedy(prompt, full)                     # warm-up, fills the KV cache
+    t_full, t_head = [], []
+    for _ in range(max(1, args.steps)):
+        barrier()
+        model.generate_greedy(prompt, full)
+        t_full.append(model.last_generate_us())
+        model.generate_greedy(prompt, head)
+        t_head.append(model.last_generate_us())
+    span_us = max_over_ranks(float(np.median(t_full) - np.median(t_head)))
+    n_dec = full - head
+    pos_mid = head + n_dec // 2
+    kt = model.time_kernels(pos_mid, reps=2)
+    model.reset()
+    peak, peak_kind = peak_hbm_gbs()
+    attn_bytes = 2 * cfg.kv_dim * 4 * (pos_mid + 1)
+    tok_bytes = float(np.mean([bytes_per_token(cfg, p)["total"] for p in range(head, full)]))
+    value = world * n_dec / (span_us * 1e-6)
+    line = {
+        "metric": "batch-1 decode tok/s at positions %d-%d" % (head, full - 1), "value": value, "unit": "tok/s",
+        "n_gpus": world, "steps": args.steps, "warmup": 1, "ms_per_step": span_us * 1e-3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32 activations x u8 group-quantised weights", "data": "synthetic",
+        "config": {"workload": f"{args.shape}-shaped, KV cache prefilled by a {n_prompt}-token seeded prompt, greedy decode of "
+                               f"positions {head}-{full - 1}", "parallelism": f"replicas x{world}"},
+        "attention_kernel": {"pos": pos_mid, "us_per_layer": kt["attention"], "bytes_per_layer": attn_bytes,
+                             "gbs": attn_bytes / (kt["attention"] * 1e3), "frac": attn_bytes / (kt["attention"] * 1e3) / peak},
+        "roofline": {"bound": "hbm", "achieved": tok_bytes / (span_us / n_dec * 1e3), "peak": peak, "unit": "GB/s",
+                     "frac": tok_bytes / (span_us / n_dec * 1e3) / peak, "peak_kind": f"of {peak_kind}", "traffic": None,
+                     "bytes_per_token": tok_bytes},
+        "gpu_launches": int(model.stats().kernels_per_forward) * (full + head) * max(1, args.steps),
+    }
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+
+
 def workload_name(shape: str) -> str:
     return (f"{shape}-shaped W8A32 batch-1 decode: BOS + {PROMPT_LEN} forced prompt tokens + greedy to "
             f"{FORWARDS_PER_STEP} forwards per step; N(0,0.02) weights seed 0, prompt seed 1")
@@ -195,6 +237,8 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--shape", default="llama2-7b")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="decode", choices=["decode", "long"],
+                    help="decode: the headline 288-forward workload; long: positions 3840-4095 after a 3840-token prompt")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -239,6 +283,13 @@ def main() -> None:
     mode = model.launch_mode()
     if not mode["ring"]:
         raise SystemExit("the sm_100a ring kernels are not active; refusing to time a fallback")
+
+    if args.workload == "long":
+        run_long_context(args, cfg, model, rank, world, max_over_ranks, barrier)
+        model.close()
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     # ---- device-resident arm: inputs in HBM, the whole greedy loop queued on the device -----------
     for _ in range(args.warmup):

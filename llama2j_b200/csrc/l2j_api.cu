@@ -73,7 +73,7 @@ struct l2j_ctx {
     float *x_host = nullptr;       // pinned
     SeqState *state_host = nullptr;
 
-    MvPlan plan_dim{}, plan_hidden{}, plan_cls{};
+    MvPlan plan_dim{}, plan_wo{}, plan_hidden{}, plan_cls{};
     bool use_ring = false;
     std::vector<LayerLaunch> layers;
     MvParams cls{};
@@ -208,6 +208,10 @@ void fill_plan(MvParams &p, const MvPlan &pl)
         {
             const char *e = getenv("L2J_TAIL_PREFETCH");
             p.tail_prefetch = e ? atoi(e) : 3;
+            const char *e2 = getenv("L2J_HEAD_PREFETCH");
+            p.head_prefetch = e2 ? atoi(e2) : 0;
+            const char *e3 = getenv("L2J_STATIC_SHARE");
+            p.static_share = e3 ? atoi(e3) : 0;
         }
         p.total_stages = 0;
         const int nseg = p.paired ? 1 : p.nseg;
@@ -289,7 +293,7 @@ void build_launch_params(l2j_ctx *c)
         o.seg[0] = make_seg(c->qt[L2J_T_WO], l * dim * dim, dim);
         o.nseg = 1;
         o.n = dim;
-        fill_plan(o, c->plan_dim);
+        fill_plan(o, c->plan_wo);
         o.x_in = c->xb;
         o.x_reps = c->reps;
         o.x_stride = c->dim_stride;
@@ -397,7 +401,7 @@ cudaError_t enqueue_forward(l2j_ctx *c, bool pdl, int *n_kernels)
             first.pdl = lc.pdl && li > 0;
             if ((e = launch_matvec_ring(first, c->plan_dim, false, L.qkv)) != cudaSuccess) return e;
             if ((e = launch_attention(lc, L.attn)) != cudaSuccess) return e;
-            if ((e = launch_matvec_ring(lc, c->plan_dim, false, L.wo)) != cudaSuccess) return e;
+            if ((e = launch_matvec_ring(lc, c->plan_wo, false, L.wo)) != cudaSuccess) return e;
             if ((e = launch_matvec_ring(lc, c->plan_dim, false, L.w13)) != cudaSuccess) return e;
             if ((e = launch_matvec_ring(lc, c->plan_hidden, false, L.w2)) != cudaSuccess) return e;
             nk += 5;
@@ -684,6 +688,7 @@ extern "C" int l2j_create(const l2j_config *cfg, int device, int first_layer, in
     memset(c->state_host, 0, sizeof(SeqState));
 
     c->plan_dim = plan_matvec(c->dim, false, false);
+    c->plan_wo = plan_matvec(c->dim, false, false, c->dim, c->ring_grid);
     c->plan_hidden = plan_matvec(c->hidden, false, false);
     c->plan_cls = plan_matvec(c->dim, true, false);
     c->use_ring = !(flags & L2J_F_SIMPLE) && c->plan_dim.ok && c->plan_hidden.ok && c->plan_cls.ok && (head % 2 == 0);
@@ -1113,7 +1118,7 @@ extern "C" int l2j_time_kernels(l2j_ctx *c, int pos, int reps, double *us)
                     switch (kind) {
                     case 0: e = launch_matvec_ring(lc, c->plan_dim, false, L.qkv); break;
                     case 1: e = launch_attention(lc, L.attn); break;
-                    case 2: e = launch_matvec_ring(lc, c->plan_dim, false, L.wo); break;
+                    case 2: e = launch_matvec_ring(lc, c->plan_wo, false, L.wo); break;
                     case 3: e = launch_matvec_ring(lc, c->plan_dim, false, L.w13); break;
                     case 4: e = launch_matvec_ring(lc, c->plan_hidden, false, L.w2); break;
                     default: e = launch_matvec_ring(lc, c->plan_cls, true, c->cls); break;
@@ -1175,7 +1180,7 @@ extern "C" int l2j_trace_kernel(l2j_ctx *c, int kind, int layer, int pos, uint64
     LayerLaunch &L = c->layers[(size_t)li];
     for (int rep = 0; rep < 2 && e == cudaSuccess; ++rep) {   // the second launch is the one recorded
         MvParams p = kind == 0 ? L.qkv : kind == 2 ? L.wo : kind == 3 ? L.w13 : kind == 4 ? L.w2 : c->cls;
-        const MvPlan &pl = kind == 4 ? c->plan_hidden : kind == 5 ? c->plan_cls : c->plan_dim;
+        const MvPlan &pl = kind == 4 ? c->plan_hidden : kind == 5 ? c->plan_cls : kind == 2 ? c->plan_wo : c->plan_dim;
         p.trace = rep == 1 ? dtrace : nullptr;
         if (rep == 1 && c->nl > 1 && kind != 5) {   // another layer's weights, so nothing is warm in L2
             LayerLaunch &L2 = c->layers[(size_t)((li + 1) % c->nl)];

@@ -83,6 +83,8 @@ struct MvParams {
     int rowbytes;      // bytes of one matrix row
     int f32;           // 1: FP32 weights
     int pf_distance;   // stages the L2 prefetch runs ahead of the claims (0: off)
+    int head_prefetch; // fixed stages each block prefetches into L2 at its start, beyond the early ring fill
+    int static_share;  // > 0: all but this many stages per block are fixed, the rest is claimed dynamically
     int tail_prefetch; // stages of the next launch each block prefetches into L2 when it runs out of work
     int early_fill;    // stages the producer may issue before the previous kernel has finished (0: none)
     const MvParams *next;   // device copy of the next ring launch's parameters (prefetch target) or nullptr
@@ -138,7 +140,7 @@ struct MvPlan {
 
 // Chooses the thread mapping and ring geometry for a row length; ok=false if the ring kernel
 // cannot take the shape (the caller then uses the plain kernels).
-MvPlan plan_matvec(int n, bool f32, bool paired);
+MvPlan plan_matvec(int n, bool f32, bool paired, int rows = 0, int blocks = 0);
 
 // ---- launch wrappers (all asynchronous on `stream`) ---------------------------------------
 struct LaunchCfg {

@@ -308,18 +308,18 @@ __global__ void __launch_bounds__(768, 1) matvec_ring_kernel(const __grid_consta
             // do not all queue up on the counter at kernel start; the rest is claimed from the global
             // counter, always one claim ahead of the stage being issued.
             const unsigned int grid = gridDim.x;
-            const unsigned int nstatic = (unsigned int)max(1, S / (2 * (int)grid));
+            const unsigned int nstatic = p.static_share < 0 ? 0x3fffffffu / grid : (unsigned int)max(1, p.static_share > 0 ? S / (int)grid - p.static_share : S / (2 * (int)grid));
             unsigned int issued = 0;
             unsigned int pending = 0xfffffffeu, pending2 = 0xfffffffeu;   // two claims in flight once the first stage is on its way
             // HBM -> L2 for the block's first stages starts at once; the copies into shared memory wait
             // until the consumers have put their loads of x on the wire.  A ring fill issued earlier
             // would sit in front of those small, latency-critical loads (and of the attention kernel's,
             // if that is still running) in the SM's load path.
-            if (!p.early_fill) {
-                for (unsigned int j = 0; j < 3 && j < nstatic; ++j)
-                    if (blockIdx.x + j * grid < (unsigned int)S)
-                        prefetch_stage(p, (int)(blockIdx.x + j * grid));
-            }
+            // HBM -> L2 for the block's fixed stages that are not fetched into the ring right away: the ring
+            // then fills from L2 once the gate opens, and HBM keeps working while the block sets up.
+            for (unsigned int j = (unsigned int)p.early_fill; j < (unsigned int)(p.early_fill + p.head_prefetch) && j < nstatic; ++j)
+                if (blockIdx.x + j * grid < (unsigned int)S)
+                    prefetch_stage(p, (int)(blockIdx.x + j * grid));
             bool gate_open = false;
             for (;;) {
                 // Only `early_fill` stages are issued before the consumers have put their loads of x on the
@@ -833,7 +833,7 @@ __global__ void __launch_bounds__(768, 1) matvec_ring_kernel(const __grid_consta
         atomicOr(&p.state->status, L2J_DS_WAIT_TIMEOUT);
 }
 
-MvPlan plan_matvec(int n, bool f32, bool paired)
+MvPlan plan_matvec(int n, bool f32, bool paired, int rows, int blocks)
 {
     MvPlan pl{};
     pl.ok = false;
@@ -857,6 +857,10 @@ MvPlan plan_matvec(int n, bool f32, bool paired)
             rt /= 2;
         while (rpp > 1 && rt * rpp * rowbytes > 64 * 1024)
             rpp /= 2;
+        // a matrix with few rows gets smaller stages, so that every block still has several of them to balance
+        if (rows > 0 && blocks > 0)
+            while (rt > 2 && rows / (rt * rpp * (paired ? 1 : 1)) < 3 * blocks && rt * rpp * rowbytes > 32 * 1024)
+                rt /= 2;
         if (const char *e = getenv("L2J_RT")) {   // experiment: cap the rows per thread and stage
             const int cap = atoi(e);
             while (rt > 2 && rt > cap)
