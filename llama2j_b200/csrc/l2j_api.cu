@@ -73,7 +73,7 @@ struct l2j_ctx {
     float *x_host = nullptr;       // pinned
     SeqState *state_host = nullptr;
 
-    MvPlan plan_dim{}, plan_wo{}, plan_hidden{}, plan_cls{};
+    MvPlan plan_qkv{}, plan_wo{}, plan_w13{}, plan_hidden{}, plan_cls{};
     bool use_ring = false;
     std::vector<LayerLaunch> layers;
     MvParams cls{};
@@ -255,7 +255,7 @@ void build_launch_params(l2j_ctx *c)
         a.nseg = 3;
         a.paired = 0;
         a.n = dim;
-        fill_plan(a, c->plan_dim);
+        fill_plan(a, c->plan_qkv);
         a.early_fill = c->early_fill;
         a.x_in = c->x;
         a.x_reps = c->reps;
@@ -313,7 +313,7 @@ void build_launch_params(l2j_ctx *c)
         f.nseg = 1;
         f.paired = 1;
         f.n = dim;
-        fill_plan(f, c->plan_dim);
+        fill_plan(f, c->plan_w13);
         f.early_fill = c->early_fill;
         f.x_in = c->x;
         f.x_reps = c->reps;
@@ -399,10 +399,10 @@ cudaError_t enqueue_forward(l2j_ctx *c, bool pdl, int *n_kernels)
             // kernel behind it reads the position before its own dependency wait.
             LaunchCfg first = lc;
             first.pdl = lc.pdl && li > 0;
-            if ((e = launch_matvec_ring(first, c->plan_dim, false, L.qkv)) != cudaSuccess) return e;
+            if ((e = launch_matvec_ring(first, c->plan_qkv, false, L.qkv)) != cudaSuccess) return e;
             if ((e = launch_attention(lc, L.attn)) != cudaSuccess) return e;
             if ((e = launch_matvec_ring(lc, c->plan_wo, false, L.wo)) != cudaSuccess) return e;
-            if ((e = launch_matvec_ring(lc, c->plan_dim, false, L.w13)) != cudaSuccess) return e;
+            if ((e = launch_matvec_ring(lc, c->plan_w13, false, L.w13)) != cudaSuccess) return e;
             if ((e = launch_matvec_ring(lc, c->plan_hidden, false, L.w2)) != cudaSuccess) return e;
             nk += 5;
         } else {
@@ -687,11 +687,13 @@ extern "C" int l2j_create(const l2j_config *cfg, int device, int first_layer, in
     CREATE_CUDA(cudaHostAlloc((void **)&c->state_host, sizeof(SeqState), cudaHostAllocDefault));
     memset(c->state_host, 0, sizeof(SeqState));
 
-    c->plan_dim = plan_matvec(c->dim, false, false);
+    c->plan_qkv = plan_matvec(c->dim, false, false, 0, 0, 2);   // RoPE works on row pairs: stages of an even number of rows
     c->plan_wo = plan_matvec(c->dim, false, false, c->dim, c->ring_grid);
+    c->plan_w13 = plan_matvec(c->dim, false, true);
     c->plan_hidden = plan_matvec(c->hidden, false, false);
     c->plan_cls = plan_matvec(c->dim, true, false);
-    c->use_ring = !(flags & L2J_F_SIMPLE) && c->plan_dim.ok && c->plan_hidden.ok && c->plan_cls.ok && (head % 2 == 0);
+    c->use_ring = !(flags & L2J_F_SIMPLE) && c->plan_qkv.ok && c->plan_wo.ok && c->plan_w13.ok && c->plan_hidden.ok &&
+                  c->plan_cls.ok && (head % 2 == 0);
     CREATE_CUDA(cudaStreamSynchronize(c->stream));
     CREATE_CUDA(cudaDeviceSynchronize());
 #undef CREATE_CK
@@ -1116,10 +1118,10 @@ extern "C" int l2j_time_kernels(l2j_ctx *c, int pos, int reps, double *us)
                     LayerLaunch &L = c->layers[(size_t)(kind == 5 ? 0 : li)];
                     cudaError_t e = cudaSuccess;
                     switch (kind) {
-                    case 0: e = launch_matvec_ring(lc, c->plan_dim, false, L.qkv); break;
+                    case 0: e = launch_matvec_ring(lc, c->plan_qkv, false, L.qkv); break;
                     case 1: e = launch_attention(lc, L.attn); break;
                     case 2: e = launch_matvec_ring(lc, c->plan_wo, false, L.wo); break;
-                    case 3: e = launch_matvec_ring(lc, c->plan_dim, false, L.w13); break;
+                    case 3: e = launch_matvec_ring(lc, c->plan_w13, false, L.w13); break;
                     case 4: e = launch_matvec_ring(lc, c->plan_hidden, false, L.w2); break;
                     default: e = launch_matvec_ring(lc, c->plan_cls, true, c->cls); break;
                     }
@@ -1180,7 +1182,7 @@ extern "C" int l2j_trace_kernel(l2j_ctx *c, int kind, int layer, int pos, uint64
     LayerLaunch &L = c->layers[(size_t)li];
     for (int rep = 0; rep < 2 && e == cudaSuccess; ++rep) {   // the second launch is the one recorded
         MvParams p = kind == 0 ? L.qkv : kind == 2 ? L.wo : kind == 3 ? L.w13 : kind == 4 ? L.w2 : c->cls;
-        const MvPlan &pl = kind == 4 ? c->plan_hidden : kind == 5 ? c->plan_cls : kind == 2 ? c->plan_wo : c->plan_dim;
+        const MvPlan &pl = kind == 4 ? c->plan_hidden : kind == 5 ? c->plan_cls : kind == 2 ? c->plan_wo : kind == 3 ? c->plan_w13 : c->plan_qkv;
         p.trace = rep == 1 ? dtrace : nullptr;
         if (rep == 1 && c->nl > 1 && kind != 5) {   // another layer's weights, so nothing is warm in L2
             LayerLaunch &L2 = c->layers[(size_t)((li + 1) % c->nl)];
@@ -1402,7 +1404,8 @@ extern "C" int l2j_k_matvec_i8(int device, uint32_t flags, const void *groups, i
     KCK(cudaMemcpy(dx, x, (size_t)n * sizeof(float), cudaMemcpyHostToDevice));
     KCK(launch_repack(nullptr, raw, ng, payload, hdr));
     MvSeg seg{payload, hdr, weight_index, d};
-    const MvPlan pl = plan_matvec(n, false, false);
+    // the grouped thread mapping needs rows that start on a group boundary
+    const MvPlan pl = plan_matvec(n, false, false, 0, 0, 1, weight_index % kGroup == 0);
     if (!(flags & L2J_F_SIMPLE) && pl.ok) {
         cudaDeviceProp prop{};
         KCK(cudaGetDeviceProperties(&prop, device));

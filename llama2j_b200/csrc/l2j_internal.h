@@ -129,6 +129,7 @@ struct AttnParams {
 };
 
 struct MvPlan {
+    bool grouped;  // u8 rows of whole groups: four lanes share a group (template selector)
     int cpt;       // chunks per thread (template selector)
     int rt;        // rows per thread and stage (template selector)
     int rpp, wpr;
@@ -139,8 +140,11 @@ struct MvPlan {
 };
 
 // Chooses the thread mapping and ring geometry for a row length; ok=false if the ring kernel
-// cannot take the shape (the caller then uses the plain kernels).
-MvPlan plan_matvec(int n, bool f32, bool paired, int rows = 0, int blocks = 0);
+// cannot take the shape (the caller then uses the plain kernels).  rows/blocks (optional) let a matrix
+// with few rows get smaller stages; row_align is the multiple of rows every stage must hold; group_aligned
+// says that every row starts on a quantisation-group boundary whenever n is a multiple of the group size.
+MvPlan plan_matvec(int n, bool f32, bool paired, int rows = 0, int blocks = 0, int row_align = 1,
+                   bool group_aligned = true);
 
 // ---- launch wrappers (all asynchronous on `stream`) ---------------------------------------
 struct LaunchCfg {

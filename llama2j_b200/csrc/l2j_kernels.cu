@@ -196,6 +196,8 @@ constexpr int kRedStride = 528;
 constexpr int kRopeOff = 3328;                    // float cos[64], sin[64] of the current position
 constexpr int kSmemHeader = 3840;                 // end of the fixed part (128-byte aligned)
 constexpr uint64_t kShortWaitNs = 2000;
+constexpr int kRingMaxThreads = 640;              // 18 consumer warps + producer + epilogue warp: 102 registers per thread
+constexpr int kPrologueRounds = 8;                // 16-byte loads of x per consumer thread in the prologue
 
 __device__ __forceinline__ int dp4a_u8s8(uint32_t a, uint32_t b, int c)
 {
@@ -235,7 +237,7 @@ struct WarpFold {
 template <int RT>
 __device__ __forceinline__ float warp_sum_rows(const float (&v)[RT], int lane)
 {
-    static_assert(RT == 2 || RT == 4 || RT == 8, "RT");
+    static_assert(RT == 1 || RT == 2 || RT == 4 || RT == 8, "RT");
     return WarpFold<RT, 16>::run(v, lane);
 }
 
@@ -248,8 +250,8 @@ __device__ __forceinline__ void trace_mark(const MvParams &p, int k)
         p.trace[blockIdx.x * 16 + k] = (unsigned long long)global_timer_ns();
 }
 
-template <bool F32, int CPT, int RT, int MAXT>
-__global__ void __launch_bounds__(768, 1) matvec_ring_kernel(const __grid_constant__ MvParams p)
+template <bool F32, bool GRP, int CPT, int RT>
+__global__ void __launch_bounds__(kRingMaxThreads, 1) matvec_ring_kernel(const __grid_constant__ MvParams p)
 {
     constexpr int EPC = F32 ? 4 : 16;   // elements per 16-byte chunk
     extern __shared__ __align__(128) uint8_t smem[];
@@ -283,7 +285,7 @@ __global__ void __launch_bounds__(768, 1) matvec_ring_kernel(const __grid_consta
         mbar_init(sbase + kBarRedEmpty + 8 * tid, 1);
     }
     if (tid == 0)
-        mbar_init(sbase + kBarXIssued, p.wpr);
+        mbar_init(sbase + kBarXIssued, nw);
     if (tid < 32)
         mbar_fence_init();
     __syncthreads();
@@ -567,156 +569,171 @@ __global__ void __launch_bounds__(768, 1) matvec_ring_kernel(const __grid_consta
     const int rsub = warp / p.wpr;   // which of the rpp concurrent rows this warp works on
     const int wi = warp - rsub * p.wpr;
     const int nchunks = p.n / EPC;
-    int chunk[CPT];
-    bool cvalid[CPT];
+    constexpr int NCH = GRP ? 4 : CPT;   // 16-byte chunks of a row that a thread owns
+    int chunk[NCH];
+    bool cvalid[NCH];
+    if constexpr (GRP) {
+        // Four lanes share one quantisation group (16 chunks): lane s of them owns chunks 4k + s, k = 0..3,
+        // so a thread needs one group header and one integer -> float conversion per row.  k is swizzled
+        // with the group's parity: the 16-byte loads of a quarter-warp then fall into eight different
+        // bank groups.
+        const int g = wi * 8 + (lane >> 2);
 #pragma unroll
-    for (int k = 0; k < CPT; ++k) {
-        chunk[k] = (wi * CPT + k) * 32 + lane;
-        cvalid[k] = chunk[k] < nchunks;
+        for (int k = 0; k < NCH; ++k) {
+            chunk[k] = g * 16 + 4 * (k ^ ((lane >> 2) & 1)) + (lane & 3);
+            cvalid[k] = g < (p.n >> 8);
+        }
+    } else {
+#pragma unroll
+        for (int k = 0; k < NCH; ++k) {
+            chunk[k] = (wi * CPT + k) * 32 + lane;
+            cvalid[k] = chunk[k] < nchunks;
+        }
     }
 
     pdl_wait();   // the input vector comes from the previous kernel
     if (tid == 0)
         trace_mark(p, 12);
 
-    // ---- prologue.  The first row group (wpr warps) loads x, applies RMSNorm (RootMeanSquare.java:25-35,
-    //      WeightNormalizeAndScale.java:71-74), converts to fixed-point limbs for the u8 path and
-    //      publishes the result in shared memory; every group then picks up the chunks it owns.  One
-    //      load of x per block keeps the L2 traffic of a kernel start small.
-    uint8_t *share = smem + kSmemHeader;   // u8: four planes [q][nchunks] of 16 B (limbs of elements 4q..4q+3); FP32: [nchunks] float4
-    float *xs_sh = reinterpret_cast<float *>(share + (size_t)nchunks * (F32 ? 16 : 64));   // [nchunks] chunk sums (u8)
+    // ---- prologue.  All consumer threads load x (coalesced, 16 bytes per thread and round), apply
+    //      RMSNorm (RootMeanSquare.java:25-35, WeightNormalizeAndScale.java:71-74), convert to
+    //      fixed-point limbs for the u8 path and publish the result in shared memory; every thread
+    //      then picks up the chunks it owns.
+    uint8_t *share = smem + kSmemHeader;   // u8: three planes [limb][nchunks] of 16 B (4 bytes per 4 elements); FP32: [nchunks] float4
     float *scratch = reinterpret_cast<float *>(smem + kScratchOff);
     bool lost = (__ldcg(&p.state->status) & L2J_DS_WAIT_TIMEOUT) != 0;
     const bool lost_before = lost;
-    if (rsub == 0) {
-        // The producer may start filling the ring now: it needs hundreds of cycles to react, by then
+    float inv = 1.0f;                      // u8 path: value of one fixed-point unit
+    {
+        // The producer may fill the ring from now on: it needs hundreds of cycles to react, by then
         // the few loads of x below are on the wire in front of its copies.
         if (lane == 0)
             mbar_arrive(sbase + kBarXIssued);
-        float xr[CPT][EPC];
-        float wr[CPT][EPC];
+        const int n4 = p.n >> 2;
+        float4 xr[kPrologueRounds], wr[kPrologueRounds];
         const bool has_rms = p.rms_w != nullptr;
         const int64_t rep_off = (int64_t)(blockIdx.x % (unsigned)p.x_reps) * p.x_stride;
         const float *xin = p.x_in + rep_off;
         const float *rmsw = has_rms ? p.rms_w + rep_off : nullptr;
 #pragma unroll
-        for (int k = 0; k < CPT; ++k) {
-#pragma unroll
-            for (int e = 0; e < EPC; e += 4) {
-                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                float4 w = make_float4(1.f, 1.f, 1.f, 1.f);
-                if (cvalid[k]) {
-                    v = ld_cg_f4_issue(xin + (int64_t)chunk[k] * EPC + e);
-                    if (has_rms)
-                        w = ld_cg_f4_issue(rmsw + (int64_t)chunk[k] * EPC + e);
-                }
-                xr[k][e] = v.x; xr[k][e + 1] = v.y; xr[k][e + 2] = v.z; xr[k][e + 3] = v.w;
-                wr[k][e] = w.x; wr[k][e + 1] = w.y; wr[k][e + 2] = w.z; wr[k][e + 3] = w.w;
+        for (int j = 0; j < kPrologueRounds; ++j) {
+            const int idx = tid + j * ncons;
+            xr[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+            wr[j] = make_float4(1.f, 1.f, 1.f, 1.f);
+            if (idx < n4) {
+                xr[j] = ld_cg_f4_issue(xin + (int64_t)idx * 4);
+                if (has_rms)
+                    wr[j] = ld_cg_f4_issue(rmsw + (int64_t)idx * 4);
             }
         }
         float ssq = 0.f, amax = 0.f;
 #pragma unroll
-        for (int k = 0; k < CPT; ++k)
-#pragma unroll
-            for (int e = 0; e < EPC; ++e) {
-                ssq = fmaf(xr[k][e], xr[k][e], ssq);
-                amax = fmaxf(amax, fabsf(xr[k][e]));
-            }
+        for (int j = 0; j < kPrologueRounds; ++j) {
+            ssq = fmaf(xr[j].x, xr[j].x, ssq);
+            ssq = fmaf(xr[j].y, xr[j].y, ssq);
+            ssq = fmaf(xr[j].z, xr[j].z, ssq);
+            ssq = fmaf(xr[j].w, xr[j].w, ssq);
+            amax = fmaxf(fmaxf(amax, fmaxf(fabsf(xr[j].x), fabsf(xr[j].y))), fmaxf(fabsf(xr[j].z), fabsf(xr[j].w)));
+        }
         if (tid == 0)
             trace_mark(p, 13);
         if (has_rms || !F32) {
             ssq = warp_sum(ssq);
             amax = warp_max(amax);
             if (lane == 0) {
-                scratch[wi] = ssq;
-                scratch[32 + wi] = amax;
+                scratch[warp] = ssq;
+                scratch[32 + warp] = amax;
             }
-            named_barrier_sync(2, p.wpr * 32);
-            ssq = 0.f;
-            amax = 0.f;
-            for (int i = 0; i < p.wpr; ++i) {
-                ssq += scratch[i];
-                amax = fmaxf(amax, scratch[32 + i]);
-            }
+            named_barrier_sync(2, ncons);
+            ssq = warp_sum(lane < nw ? scratch[lane] : 0.f);          // same order in every warp and block
+            amax = warp_max(lane < nw ? scratch[32 + lane] : 0.f);
         }
         if (has_rms) {
             float tot = __fdiv_rn(ssq, (float)p.n);
             tot = __fadd_rn(tot, 1e-5f);
             const float ss = __fdiv_rn(1.0f, __fsqrt_rn(tot));
 #pragma unroll
-            for (int k = 0; k < CPT; ++k)
-#pragma unroll
-                for (int e = 0; e < EPC; ++e)
-                    xr[k][e] = __fmul_rn(wr[k][e], __fmul_rn(ss, xr[k][e]));
+            for (int j = 0; j < kPrologueRounds; ++j) {
+                xr[j].x = __fmul_rn(wr[j].x, __fmul_rn(ss, xr[j].x));
+                xr[j].y = __fmul_rn(wr[j].y, __fmul_rn(ss, xr[j].y));
+                xr[j].z = __fmul_rn(wr[j].z, __fmul_rn(ss, xr[j].z));
+                xr[j].w = __fmul_rn(wr[j].w, __fmul_rn(ss, xr[j].w));
+            }
             amax = amax * ss * p.rms_wmax * 1.000001f;   // bound of |w * (ss * x)| from max|x| and max|w|
         }
         if constexpr (F32) {
 #pragma unroll
-            for (int k = 0; k < CPT; ++k)
-                if (cvalid[k])
-                    *reinterpret_cast<float4 *>(share + (size_t)chunk[k] * 16) = make_float4(xr[k][0], xr[k][1], xr[k][2], xr[k][3]);
+            for (int j = 0; j < kPrologueRounds; ++j) {
+                const int idx = tid + j * ncons;
+                if (idx < n4)
+                    *reinterpret_cast<float4 *>(share + (size_t)idx * 16) = xr[j];
+            }
         } else {
             int ex = 0;
             if (amax > 0.f && amax < 3.0e38f)
                 frexpf(amax, &ex);             // amax < 2^ex
             ex = max(-90, min(126, ex));
-            const float f = __int_as_float((127 + 30 - ex) << 23);   // 2^(30 - ex)
-            if (tid == 0)
-                scratch[63] = __int_as_float((127 + ex - 30) << 23); // 2^(ex - 30): value of one fixed-point unit
+            const float f = __int_as_float((127 + 22 - ex) << 23);   // 2^(22 - ex): |x * f| <= 2^22
+            inv = __int_as_float((127 + ex - 22) << 23);             // 2^(ex - 22): value of one fixed-point unit
 #pragma unroll
-            for (int k = 0; k < CPT; ++k) {
-                float sum = 0.f;
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    uint32_t z[4];
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        sum += xr[k][4 * q + j];
-                        const int X = __float2int_rn(xr[k][4 * q + j] * f);      // |X| <= 2^30
-                        z[j] = ((uint32_t)X + 0x00808080u) ^ 0x00808080u;        // bytes = balanced signed limbs
-                    }
-                    // 4x4 byte transpose in 8 permutes: limb l of the four elements ends up in word l
-                    const uint32_t t0 = __byte_perm(z[0], z[1], 0x5140);   // z0.b0 z1.b0 z0.b1 z1.b1
-                    const uint32_t t1 = __byte_perm(z[0], z[1], 0x7362);   // z0.b2 z1.b2 z0.b3 z1.b3
-                    const uint32_t t2 = __byte_perm(z[2], z[3], 0x5140);
-                    const uint32_t t3 = __byte_perm(z[2], z[3], 0x7362);
-                    if (cvalid[k])
-                        *reinterpret_cast<uint4 *>(share + ((size_t)q * nchunks + chunk[k]) * 16) =
-                            make_uint4(__byte_perm(t0, t2, 0x5410), __byte_perm(t0, t2, 0x7632), __byte_perm(t1, t3, 0x5410),
-                                       __byte_perm(t1, t3, 0x7632));
+            for (int j = 0; j < kPrologueRounds; ++j) {
+                const int idx = tid + j * ncons;
+                if (idx < n4) {
+                    // 24-bit fixed point as three balanced signed byte limbs: after the add-and-flip, bytes
+                    // 0..2 of z are l0, l1, l2 in [-128, 127] with X = l0 + 256 l1 + 65536 l2
+                    const uint32_t z0 = ((uint32_t)__float2int_rn(xr[j].x * f) + 0x00008080u) ^ 0x00008080u;
+                    const uint32_t z1 = ((uint32_t)__float2int_rn(xr[j].y * f) + 0x00008080u) ^ 0x00008080u;
+                    const uint32_t z2 = ((uint32_t)__float2int_rn(xr[j].z * f) + 0x00008080u) ^ 0x00008080u;
+                    const uint32_t z3 = ((uint32_t)__float2int_rn(xr[j].w * f) + 0x00008080u) ^ 0x00008080u;
+                    // byte transpose: limb l of the four elements ends up in word l
+                    const uint32_t t0 = __byte_perm(z0, z1, 0x5140);   // z0.b0 z1.b0 z0.b1 z1.b1
+                    const uint32_t t2 = __byte_perm(z2, z3, 0x5140);
+                    const uint32_t t1 = __byte_perm(z0, z1, 0x0062);   // z0.b2 z1.b2 . .
+                    const uint32_t t3 = __byte_perm(z2, z3, 0x0062);
+                    uint32_t *dst = reinterpret_cast<uint32_t *>(share) + idx;
+                    dst[0] = __byte_perm(t0, t2, 0x5410);
+                    dst[p.n >> 2] = __byte_perm(t0, t2, 0x7632);
+                    dst[p.n >> 1] = __byte_perm(t1, t3, 0x5410);
                 }
-                if (cvalid[k])
-                    xs_sh[chunk[k]] = sum;
             }
         }
     }
     named_barrier_sync(1, ncons);
 
     float xv[F32 ? CPT : 1][4];           // FP32 path: the chunk's four x values
-    uint32_t xl[F32 ? 1 : CPT][4][4];     // u8 path: [chunk][word of 4 elements][limb]
-    float xs[CPT];                         // u8 path: sum of the chunk's x (for the group minimum term)
-    float inv = 1.0f;                      // u8 path: value of one fixed-point unit
+    uint32_t xl[F32 ? 1 : NCH][4][3];     // u8 path: [chunk][word of 4 elements][limb]
+    float xs[F32 ? 1 : (GRP ? 1 : NCH)];  // u8 path: sum of the owned x in fixed-point units (for the group minimum term)
+    if constexpr (F32) {
 #pragma unroll
-    for (int k = 0; k < CPT; ++k) {
-        if constexpr (F32) {
+        for (int k = 0; k < CPT; ++k) {
             float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
             if (cvalid[k])
                 t = *reinterpret_cast<const float4 *>(share + (size_t)chunk[k] * 16);
             xv[k][0] = t.x; xv[k][1] = t.y; xv[k][2] = t.z; xv[k][3] = t.w;
-            xs[k] = 0.f;
-        } else {
+        }
+    } else {
+        int s0 = 0, s1 = 0, s2 = 0;
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
+        for (int k = 0; k < NCH; ++k) {
+#pragma unroll
+            for (int l = 0; l < 3; ++l) {
                 uint4 t = make_uint4(0u, 0u, 0u, 0u);
                 if (cvalid[k])
-                    t = *reinterpret_cast<const uint4 *>(share + ((size_t)q * nchunks + chunk[k]) * 16);
-                xl[k][q][0] = t.x; xl[k][q][1] = t.y; xl[k][q][2] = t.z; xl[k][q][3] = t.w;
+                    t = *reinterpret_cast<const uint4 *>(share + (size_t)l * p.n + (size_t)chunk[k] * 16);
+                xl[k][0][l] = t.x; xl[k][1][l] = t.y; xl[k][2][l] = t.z; xl[k][3][l] = t.w;
             }
-            xs[k] = cvalid[k] ? xs_sh[chunk[k]] : 0.f;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                s0 = dp4a_u8s8(0x01010101u, xl[k][q][0], s0);
+                s1 = dp4a_u8s8(0x01010101u, xl[k][q][1], s1);
+                s2 = dp4a_u8s8(0x01010101u, xl[k][q][2], s2);
+            }
+            if (!GRP || k == NCH - 1) {
+                xs[GRP ? 0 : k] = fmaf((float)s2, 65536.0f, fmaf((float)s1, 256.0f, (float)s0));
+                s0 = s1 = s2 = 0;
+            }
         }
     }
-    if constexpr (!F32)
-        inv = scratch[63];
 
     if (tid == 0)
         trace_mark(p, 3);
@@ -755,44 +772,64 @@ __global__ void __launch_bounds__(768, 1) matvec_ring_kernel(const __grid_consta
                         }
                     }
                     v[t] = a;
-                } else {
-                    const int e0 = (half ? d.e0b : d.e0a) + local * p.n;
-                    const float2 *hp = reinterpret_cast<const float2 *>(slot_ptr + p.hdr_off + half * p.half_hdr);
-                    float accd = 0.f, accm = 0.f;
+                } else if constexpr (GRP) {
+                    if (cvalid[0]) {
+                        const int e0 = (half ? d.e0b : d.e0a) + local * p.n;
+                        const float2 *hp = reinterpret_cast<const float2 *>(slot_ptr + p.hdr_off + half * p.half_hdr);
+                        const float2 ms = hp[(e0 + chunk[0] * 16) >> 8];
+                        int a0 = 0, a1 = 0, a2 = 0;
 #pragma unroll
-                    for (int k = 0; k < CPT; ++k) {
-                        if (cvalid[k]) {
+                        for (int k = 0; k < NCH; ++k) {
                             const uint4 w = *reinterpret_cast<const uint4 *>(rowp + (size_t)chunk[k] * 16);
-                            const float2 ms = hp[(e0 + chunk[k] * 16) >> 8];
-                            int a0 = 0, a1 = 0, a2 = 0, a3 = 0;
                             a0 = dp4a_u8s8(w.x, xl[k][0][0], a0);
                             a1 = dp4a_u8s8(w.x, xl[k][0][1], a1);
                             a2 = dp4a_u8s8(w.x, xl[k][0][2], a2);
-                            a3 = dp4a_u8s8(w.x, xl[k][0][3], a3);
                             a0 = dp4a_u8s8(w.y, xl[k][1][0], a0);
                             a1 = dp4a_u8s8(w.y, xl[k][1][1], a1);
                             a2 = dp4a_u8s8(w.y, xl[k][1][2], a2);
-                            a3 = dp4a_u8s8(w.y, xl[k][1][3], a3);
                             a0 = dp4a_u8s8(w.z, xl[k][2][0], a0);
                             a1 = dp4a_u8s8(w.z, xl[k][2][1], a1);
                             a2 = dp4a_u8s8(w.z, xl[k][2][2], a2);
-                            a3 = dp4a_u8s8(w.z, xl[k][2][3], a3);
                             a0 = dp4a_u8s8(w.w, xl[k][3][0], a0);
                             a1 = dp4a_u8s8(w.w, xl[k][3][1], a1);
                             a2 = dp4a_u8s8(w.w, xl[k][3][2], a2);
-                            a3 = dp4a_u8s8(w.w, xl[k][3][3], a3);
-                            float dsum = fmaf((float)a1, 256.0f, (float)a0);
-                            dsum = fmaf((float)a2, 65536.0f, dsum);
-                            dsum = fmaf((float)a3, 16777216.0f, dsum);
-                            accd = fmaf(ms.y, dsum, accd);
-                            accm = fmaf(ms.x, xs[k], accm);
+                        }
+                        // |a_l| <= 64 * 255 * 128 < 2^24: the conversions are exact
+                        const float dsum = fmaf((float)a2, 65536.0f, fmaf((float)a1, 256.0f, (float)a0));
+                        v[t] = fmaf(ms.y, dsum, ms.x * xs[0]);
+                    }
+                } else {
+                    const int e0 = (half ? d.e0b : d.e0a) + local * p.n;
+                    const float2 *hp = reinterpret_cast<const float2 *>(slot_ptr + p.hdr_off + half * p.half_hdr);
+                    float acc = 0.f;
+#pragma unroll
+                    for (int k = 0; k < NCH; ++k) {
+                        if (cvalid[k]) {
+                            const uint4 w = *reinterpret_cast<const uint4 *>(rowp + (size_t)chunk[k] * 16);
+                            const float2 ms = hp[(e0 + chunk[k] * 16) >> 8];
+                            int a0 = 0, a1 = 0, a2 = 0;
+                            a0 = dp4a_u8s8(w.x, xl[k][0][0], a0);
+                            a1 = dp4a_u8s8(w.x, xl[k][0][1], a1);
+                            a2 = dp4a_u8s8(w.x, xl[k][0][2], a2);
+                            a0 = dp4a_u8s8(w.y, xl[k][1][0], a0);
+                            a1 = dp4a_u8s8(w.y, xl[k][1][1], a1);
+                            a2 = dp4a_u8s8(w.y, xl[k][1][2], a2);
+                            a0 = dp4a_u8s8(w.z, xl[k][2][0], a0);
+                            a1 = dp4a_u8s8(w.z, xl[k][2][1], a1);
+                            a2 = dp4a_u8s8(w.z, xl[k][2][2], a2);
+                            a0 = dp4a_u8s8(w.w, xl[k][3][0], a0);
+                            a1 = dp4a_u8s8(w.w, xl[k][3][1], a1);
+                            a2 = dp4a_u8s8(w.w, xl[k][3][2], a2);
+                            const float dsum = fmaf((float)a2, 65536.0f, fmaf((float)a1, 256.0f, (float)a0));
+                            acc = fmaf(ms.y, dsum, acc);
+                            acc = fmaf(ms.x, xs[k], acc);
                         }
                     }
-                    v[t] = fmaf(inv, accd, accm);
+                    v[t] = acc;
                 }
             }
         }
-        const float tot = warp_sum_rows<RT>(v, lane);
+        const float tot = warp_sum_rows<RT>(v, lane) * inv;
         __syncwarp();
         if (lane == 0)
             mbar_arrive(sbase + kBarEmpty + 8 * slot);   // this warp is done with the ring slot
@@ -833,7 +870,7 @@ __global__ void __launch_bounds__(768, 1) matvec_ring_kernel(const __grid_consta
         atomicOr(&p.state->status, L2J_DS_WAIT_TIMEOUT);
 }
 
-MvPlan plan_matvec(int n, bool f32, bool paired, int rows, int blocks)
+MvPlan plan_matvec(int n, bool f32, bool paired, int rows, int blocks, int row_align, bool group_aligned)
 {
     MvPlan pl{};
     pl.ok = false;
@@ -842,33 +879,51 @@ MvPlan plan_matvec(int n, bool f32, bool paired, int rows, int blocks)
         return pl;
     const int nchunks = n / epc;
     const int rowbytes = f32 ? n * 4 : n;
-    // shared copy of x in front of the ring: 16 B (FP32) or 64 B of limbs + 4 B of sum (u8) per chunk
-    const int xshare = ((f32 ? nchunks * 16 : nchunks * 68) + 127) & ~127;
-    for (int cpt = 1; cpt <= 4; ++cpt) {
-        const int wpr = (nchunks + 32 * cpt - 1) / (32 * cpt);
-        if (wpr > 8)
-            continue;   // two row groups must fit 16 consumer warps
-        int rpp = 2;
-        while (2 * rpp * wpr <= 16 && rpp < 8)
-            rpp *= 2;
-        // rows per thread and stage: aim at stages of 32-48 KB, at most 32 rows
-        int rt = 8;
-        while (rt > 2 && (rt * rpp > 32 || rt * rpp * rowbytes > 64 * 1024))
+    const int max_cons = kRingMaxThreads / 32 - 2;   // consumer warps beside the producer and the epilogue warp
+    // shared copy of x in front of the ring: FP32 values, or three byte planes of fixed-point limbs
+    const int xshare = ((f32 ? n * 4 : n * 3) + 127) & ~127;
+    const bool grouped = !f32 && group_aligned && (n % kGroup) == 0;
+    const int rt_min = paired ? 2 : 1;
+    for (int cpt = grouped ? 4 : 1; cpt <= 4; ++cpt) {
+        int wpr, rpp, rt;
+        if (grouped) {
+            wpr = (n / kGroup + 7) / 8;   // a warp spans eight groups
+            if (wpr > max_cons)
+                return pl;
+            rpp = max_cons / wpr;
+            if (rpp > 8)
+                rpp = 8;
+            rt = 4;
+        } else {
+            wpr = (nchunks + 32 * cpt - 1) / (32 * cpt);
+            if (wpr > max_cons)
+                continue;
+            rpp = 1;
+            while (2 * rpp * wpr <= 16 && rpp < 8)
+                rpp *= 2;
+            rt = 8;
+        }
+        // rows per thread and stage: stages of at most 64 KB and 32 rows
+        const int rt_floor = grouped ? rt_min : 2;
+        while (rt > rt_floor && (rt * rpp > 32 || rt * rpp * rowbytes > 64 * 1024))
             rt /= 2;
         while (rpp > 1 && rt * rpp * rowbytes > 64 * 1024)
-            rpp /= 2;
+            rpp = grouped ? rpp - 1 : rpp / 2;
         // a matrix with few rows gets smaller stages, so that every block still has several of them to balance
         if (rows > 0 && blocks > 0)
-            while (rt > 2 && rows / (rt * rpp * (paired ? 1 : 1)) < 3 * blocks && rt * rpp * rowbytes > 32 * 1024)
+            while (rt > rt_floor && rows / (rt * rpp) < 3 * blocks && rt * rpp * rowbytes > 32 * 1024)
                 rt /= 2;
-        if (const char *e = getenv("L2J_RT")) {   // experiment: cap the rows per thread and stage
-            const int cap = atoi(e);
-            while (rt > 2 && rt > cap)
-                rt /= 2;
+        if (row_align > 1 && (rt * rpp) % row_align != 0) {
+            if (rpp > 1 && ((rpp - 1) * rt) % row_align == 0)
+                --rpp;
+            else
+                continue;
         }
+        if (n / 4 > kPrologueRounds * rpp * wpr * 32)
+            continue;   // the prologue could not hold x in registers
         int half_hdr = 0;
         if (!f32) {
-            half_hdr = ((((rt / 2) * rpp * n + 255) / 256) + 4) * 8;
+            half_hdr = (((rt * rpp * n / 2 + 255) / 256) + 4) * 8;
             half_hdr = (half_hdr + 15) & ~15;
         }
         const int payload = rt * rpp * rowbytes;
@@ -878,6 +933,7 @@ MvPlan plan_matvec(int n, bool f32, bool paired, int rows, int blocks)
             nstage = 16;
         if (nstage < 2)
             continue;
+        pl.grouped = grouped;
         pl.cpt = cpt;
         pl.rt = rt;
         pl.rpp = rpp;
@@ -890,17 +946,16 @@ MvPlan plan_matvec(int n, bool f32, bool paired, int rows, int blocks)
         pl.threads = (rpp * wpr + 2) * 32;
         pl.smem_bytes = kSmemHeader + xshare + nstage * slot;   // header + shared x + ring
         pl.ok = true;
-        (void)paired;
         return pl;
     }
     return pl;
 }
 
-template <bool F32, int CPT, int RT, int MAXT>
+template <bool F32, bool GRP, int CPT, int RT>
 static cudaError_t launch_ring_t(const LaunchCfg &lc, const MvPlan &plan, const MvParams &p)
 {
-    auto kern = matvec_ring_kernel<F32, CPT, RT, MAXT>;
-    if (plan.threads > MAXT)
+    auto kern = matvec_ring_kernel<F32, GRP, CPT, RT>;
+    if (plan.threads > kRingMaxThreads)
         return cudaErrorInvalidConfiguration;
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3((unsigned)lc.grid);
@@ -915,29 +970,30 @@ static cudaError_t launch_ring_t(const LaunchCfg &lc, const MvPlan &plan, const 
     return cudaLaunchKernelEx(&cfg, kern, p);
 }
 
-template <bool F32, int CPT, int RT, int MAXT>
+template <bool F32, bool GRP, int CPT, int RT>
 static cudaError_t prepare_ring_t()
 {
-    auto kern = matvec_ring_kernel<F32, CPT, RT, MAXT>;
+    auto kern = matvec_ring_kernel<F32, GRP, CPT, RT>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmemBlock);
     if (e != cudaSuccess)
         return e;
     return cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
 }
 
-// Instantiations: (FP32 weights, chunks per thread, rows per thread and stage, largest block).
+// Instantiations: (FP32 weights, grouped thread mapping, chunks per thread, rows per thread and stage).
 #define L2J_RING_VARIANTS(X) \
-    X(true, 1, 2, 576) X(true, 1, 4, 576) X(true, 1, 8, 576) X(true, 2, 2, 576) X(true, 2, 4, 576) X(true, 2, 8, 576) \
-    X(true, 3, 2, 576) X(true, 3, 4, 576) X(true, 3, 8, 576) X(true, 4, 2, 576) X(true, 4, 4, 576) X(true, 4, 8, 576) \
-    X(false, 1, 2, 576) X(false, 1, 4, 576) X(false, 1, 8, 576) X(false, 2, 2, 576) X(false, 2, 4, 576) X(false, 2, 8, 576) \
-    X(false, 3, 2, 576) X(false, 3, 4, 576) X(false, 3, 8, 576) X(false, 4, 2, 576) X(false, 4, 4, 576) X(false, 4, 8, 576)
+    X(true, false, 1, 2) X(true, false, 1, 4) X(true, false, 1, 8) X(true, false, 2, 2) X(true, false, 2, 4) X(true, false, 2, 8) \
+    X(true, false, 3, 2) X(true, false, 3, 4) X(true, false, 3, 8) X(true, false, 4, 2) X(true, false, 4, 4) X(true, false, 4, 8) \
+    X(false, false, 1, 2) X(false, false, 1, 4) X(false, false, 1, 8) X(false, false, 2, 2) X(false, false, 2, 4) X(false, false, 2, 8) \
+    X(false, false, 3, 2) X(false, false, 3, 4) X(false, false, 3, 8) X(false, false, 4, 2) X(false, false, 4, 4) X(false, false, 4, 8) \
+    X(false, true, 4, 1) X(false, true, 4, 2) X(false, true, 4, 4)
 
 // Opts the ring kernels of the current device into their dynamic shared memory size.  Call once
 // per device before the first launch (and outside stream capture).
 cudaError_t prepare_kernels()
 {
     cudaError_t e;
-#define X(F, C, R, T) if ((e = prepare_ring_t<F, C, R, T>()) != cudaSuccess) return e;
+#define X(F, G, C, R) if ((e = prepare_ring_t<F, G, C, R>()) != cudaSuccess) return e;
     L2J_RING_VARIANTS(X)
 #undef X
     return cudaSuccess;
@@ -945,7 +1001,7 @@ cudaError_t prepare_kernels()
 
 cudaError_t launch_matvec_ring(const LaunchCfg &lc, const MvPlan &plan, bool f32, const MvParams &p)
 {
-#define X(F, C, R, T) if (f32 == F && plan.cpt == C && plan.rt == R && plan.threads <= T) return launch_ring_t<F, C, R, T>(lc, plan, p);
+#define X(F, G, C, R) if (f32 == F && plan.grouped == G && plan.cpt == C && plan.rt == R) return launch_ring_t<F, G, C, R>(lc, plan, p);
     L2J_RING_VARIANTS(X)
 #undef X
     return cudaErrorInvalidConfiguration;
