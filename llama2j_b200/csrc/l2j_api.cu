@@ -63,6 +63,9 @@ struct l2j_ctx {
     int *blk_idx = nullptr;
     int *prompt_dev = nullptr, *out_tokens_dev = nullptr;
     unsigned int *work = nullptr;   // two counters per ring-kernel launch of a forward
+    unsigned int *chain = nullptr;  // hand-over counters, one per kernel of a forward, each on its own 128-byte line
+    bool chain_on = true;
+    bool attn_cluster = true;       // one thread-block cluster per head in the attention kernel
     unsigned long long *trace = nullptr;   // per-launch timelines, only when L2J_TRACE is set
     int ring_grid = 0;              // blocks per ring kernel
     int early_fill = 1;             // ring stages a kernel may fetch before its predecessor has finished
@@ -226,6 +229,39 @@ void fill_plan(MvParams &p, const MvPlan &pl)
     p.producer_wait = pw ? atoi(pw) : 0;
 }
 
+constexpr int kChainStride = 32;   // unsigned ints between two hand-over counters (128 bytes)
+
+// Links the kernels of a forward through hand-over counters: kernel i waits on the counter of kernel
+// i - 1.  The first ring kernel follows the begin kernel with a full dependency and needs none.
+void link_chain(l2j_ctx *c)
+{
+    if (!c->use_ring || !c->chain_on)
+        return;
+    const unsigned int ring_blocks = (unsigned int)c->ring_grid;
+    const unsigned int attn_blocks = (unsigned int)(c->cfg.n_heads * c->nsplit);
+    const unsigned int *prev = nullptr;
+    unsigned int prev_blocks = 0;
+    int idx = 0;
+    auto link = [&](ChainLink &ch, unsigned int blocks) {
+        ch.wait_counter = prev;
+        ch.wait_blocks = prev_blocks;
+        ch.done_counter = c->chain + (int64_t)kChainStride * idx++;
+        ch.epoch = c->chain + (int64_t)kChainStride * (5 * c->nl + 1);
+        prev = ch.done_counter;
+        prev_blocks = blocks;
+    };
+    for (int li = 0; li < c->nl; ++li) {
+        LayerLaunch &L = c->layers[(size_t)li];
+        link(L.qkv.chain, ring_blocks);
+        link(L.attn.chain, attn_blocks);
+        link(L.wo.chain, ring_blocks);
+        link(L.w13.chain, ring_blocks);
+        link(L.w2.chain, ring_blocks);
+    }
+    if (c->is_last)
+        link(c->cls.chain, ring_blocks);
+}
+
 // Builds the static kernel parameter blocks of every layer this context owns.
 void build_launch_params(l2j_ctx *c)
 {
@@ -286,6 +322,10 @@ void build_launch_params(l2j_ctx *c)
         t.nsplit = c->nsplit;
         t.chunk_max = c->chunk_max;
         t.pos_override = -1;
+        t.cluster = c->attn_cluster ? 1 : 0;
+        t.timeout_us = 50000;
+        t.trace = c->trace ? c->trace + (int64_t)(4 * c->nl + 1 + li) * c->ring_grid * 16 : nullptr;
+        t.trace_blocks = c->ring_grid;
 
         // x += Wo att                                          (Run.java:483-485)
         MvParams &o = L.wo;
@@ -377,6 +417,15 @@ void build_launch_params(l2j_ctx *c)
         k.work = c->work + 2 * (4 * c->nl);
         k.trace = c->trace ? c->trace + (int64_t)(4 * c->nl) * c->ring_grid * 16 : nullptr;
     }
+    link_chain(c);
+}
+
+// A kernel launched on its own (timing, tracing) must neither wait on nor bump the hand-over counters.
+template <typename P>
+P unchained(P p)
+{
+    p.chain = ChainLink{};
+    return p;
 }
 
 // Enqueues the kernels of one forward of this context's layer range on its stream.
@@ -386,7 +435,8 @@ cudaError_t enqueue_forward(l2j_ctx *c, bool pdl, int *n_kernels)
     int nk = 0;
     LaunchCfg lc{c->stream, false, c->ring_grid};
     // The first kernel of a forward follows a memcpy (or the previous graph launch): plain edge.
-    e = launch_begin(lc, c->state, c->cmd_dev, c->emb, c->x, c->dim, c->cfg.vocab_size, c->cfg.seq_len, c->is_first ? 1 : 0, c->reps, c->dim_stride);
+    e = launch_begin(lc, c->state, c->cmd_dev, c->emb, c->x, c->dim, c->cfg.vocab_size, c->cfg.seq_len, c->is_first ? 1 : 0, c->reps, c->dim_stride,
+                     c->use_ring && c->chain_on ? c->chain + (int64_t)kChainStride * (5 * c->nl + 1) : nullptr);
     if (e != cudaSuccess)
         return e;
     ++nk;
@@ -664,6 +714,10 @@ extern "C" int l2j_create(const l2j_config *cfg, int device, int first_layer, in
     if (const char *e = getenv("L2J_EARLY_FILL"))
         c->early_fill = atoi(e);
     c->nsplit = choose_nsplit(c->sm_count, cfg->n_heads, cfg->seq_len);
+    if (const char *e = getenv("L2J_ATTN_CLUSTER"))
+        c->attn_cluster = atoi(e) != 0;
+    if (c->attn_cluster && c->nsplit > 8)
+        c->nsplit = 8;   // portable cluster size
     c->chunk_max = (((cfg->seq_len + c->nsplit - 1) / c->nsplit) + 3) & ~3;   // keeps the float4 scratch behind it aligned
     CREATE_CK(dev_alloc(c, &c->attn_part, (int64_t)cfg->n_heads * c->nsplit * (head + 2), true));
     CREATE_CK(dev_alloc(c, &c->attn_counters, cfg->n_heads, true));
@@ -675,8 +729,11 @@ extern "C" int l2j_create(const l2j_config *cfg, int device, int first_layer, in
     CREATE_CK(dev_alloc(c, &c->blk_val, c->ring_grid + 8, true));
     CREATE_CK(dev_alloc(c, &c->blk_idx, c->ring_grid + 8, true));
     CREATE_CK(dev_alloc(c, &c->work, 2 * (4 * (int64_t)c->nl + 1), true));
+    CREATE_CK(dev_alloc(c, &c->chain, kChainStride * (5 * (int64_t)c->nl + 2), true));   // + the epoch word
+    if (const char *e = getenv("L2J_CHAIN"))
+        c->chain_on = atoi(e) != 0;
     if (getenv("L2J_TRACE"))
-        CREATE_CK(dev_alloc(c, &c->trace, (4 * (int64_t)c->nl + 1) * c->ring_grid * 16, true));
+        CREATE_CK(dev_alloc(c, &c->trace, (5 * (int64_t)c->nl + 1) * c->ring_grid * 16, true));
     CREATE_CK(dev_alloc(c, &c->prompt_dev, cfg->seq_len, true));
     CREATE_CK(dev_alloc(c, &c->out_tokens_dev, cfg->seq_len, true));
     CREATE_CK(dev_alloc(c, &c->state, 1, true));
@@ -1066,6 +1123,7 @@ extern "C" int l2j_reset(l2j_ctx *c)
     CK(c, cudaMemset(c->state, 0, sizeof(SeqState)));
     CK(c, cudaMemset(c->attn_counters, 0, sizeof(unsigned int) * (size_t)c->cfg.n_heads));
     CK(c, cudaMemset(c->work, 0, sizeof(unsigned int) * 2 * (4 * (size_t)c->nl + 1)));
+    CK(c, cudaMemset(c->chain, 0, sizeof(unsigned int) * kChainStride * (5 * (size_t)c->nl + 2)));   // the epoch word too
     CK(c, cudaDeviceSynchronize());
     c->forwards = 0;
     c->status_accum = 0;
@@ -1102,7 +1160,7 @@ extern "C" int l2j_time_kernels(l2j_ctx *c, int pos, int reps, double *us)
     if (rc != L2J_OK)
         return rc;
     LaunchCfg lc{c->stream, false, c->ring_grid};
-    CK(c, launch_begin(lc, c->state, c->cmd_dev, c->emb, c->x, c->dim, c->cfg.vocab_size, c->cfg.seq_len, c->is_first ? 1 : 0, c->reps, c->dim_stride));
+    CK(c, launch_begin(lc, c->state, c->cmd_dev, c->emb, c->x, c->dim, c->cfg.vocab_size, c->cfg.seq_len, c->is_first ? 1 : 0, c->reps, c->dim_stride, nullptr));
     for (int kind = 0; kind < 6; ++kind) {
         us[kind] = 0.0;
         if (kind == 5 && !c->is_last)
@@ -1118,12 +1176,12 @@ extern "C" int l2j_time_kernels(l2j_ctx *c, int pos, int reps, double *us)
                     LayerLaunch &L = c->layers[(size_t)(kind == 5 ? 0 : li)];
                     cudaError_t e = cudaSuccess;
                     switch (kind) {
-                    case 0: e = launch_matvec_ring(lc, c->plan_qkv, false, L.qkv); break;
-                    case 1: e = launch_attention(lc, L.attn); break;
-                    case 2: e = launch_matvec_ring(lc, c->plan_wo, false, L.wo); break;
-                    case 3: e = launch_matvec_ring(lc, c->plan_w13, false, L.w13); break;
-                    case 4: e = launch_matvec_ring(lc, c->plan_hidden, false, L.w2); break;
-                    default: e = launch_matvec_ring(lc, c->plan_cls, true, c->cls); break;
+                    case 0: e = launch_matvec_ring(lc, c->plan_qkv, false, unchained(L.qkv)); break;
+                    case 1: e = launch_attention(lc, unchained(L.attn)); break;
+                    case 2: e = launch_matvec_ring(lc, c->plan_wo, false, unchained(L.wo)); break;
+                    case 3: e = launch_matvec_ring(lc, c->plan_w13, false, unchained(L.w13)); break;
+                    case 4: e = launch_matvec_ring(lc, c->plan_hidden, false, unchained(L.w2)); break;
+                    default: e = launch_matvec_ring(lc, c->plan_cls, true, unchained(c->cls)); break;
                     }
                     CK(c, e);
                     if (phase == 1)
@@ -1150,7 +1208,7 @@ extern "C" int l2j_read_trace(l2j_ctx *c, uint64_t *out, int64_t max_values)
         return fail(c, L2J_E_STATE, "the context was created without L2J_TRACE in the environment");
     CK(c, cudaSetDevice(c->device));
     CK(c, cudaStreamSynchronize(c->stream));
-    int64_t n = (4 * (int64_t)c->nl + 1) * c->ring_grid * 16;
+    int64_t n = (5 * (int64_t)c->nl + 1) * c->ring_grid * 16;
     if (n > max_values)
         n = max_values;
     CK(c, cudaMemcpy(out, c->trace, sizeof(uint64_t) * (size_t)n, cudaMemcpyDeviceToHost));
@@ -1178,7 +1236,7 @@ extern "C" int l2j_trace_kernel(l2j_ctx *c, int kind, int layer, int pos, uint64
     cudaDeviceSynchronize();
     rc = post_cmd(c, 1, 1, pos);
     LaunchCfg lc{c->stream, false, c->ring_grid};
-    cudaError_t e = launch_begin(lc, c->state, c->cmd_dev, c->emb, c->x, c->dim, c->cfg.vocab_size, c->cfg.seq_len, c->is_first ? 1 : 0, c->reps, c->dim_stride);
+    cudaError_t e = launch_begin(lc, c->state, c->cmd_dev, c->emb, c->x, c->dim, c->cfg.vocab_size, c->cfg.seq_len, c->is_first ? 1 : 0, c->reps, c->dim_stride, nullptr);
     LayerLaunch &L = c->layers[(size_t)li];
     for (int rep = 0; rep < 2 && e == cudaSuccess; ++rep) {   // the second launch is the one recorded
         MvParams p = kind == 0 ? L.qkv : kind == 2 ? L.wo : kind == 3 ? L.w13 : kind == 4 ? L.w2 : c->cls;
@@ -1190,7 +1248,7 @@ extern "C" int l2j_trace_kernel(l2j_ctx *c, int kind, int layer, int pos, uint64
             q.trace = dtrace;
             p = q;
         }
-        e = launch_matvec_ring(lc, pl, kind == 5, p);
+        e = launch_matvec_ring(lc, pl, kind == 5, unchained(p));
     }
     if (e == cudaSuccess)
         e = cudaStreamSynchronize(c->stream);

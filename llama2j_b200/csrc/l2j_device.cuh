@@ -124,6 +124,38 @@ __device__ __forceinline__ void pdl_wait()
     asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
+// ---------------------------------------------------------------------------------------------
+// hand-over counters between consecutive kernels
+// ---------------------------------------------------------------------------------------------
+
+__device__ __forceinline__ unsigned int ld_acquire_u32(const unsigned int *p)
+{
+    unsigned int v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// Publishes everything this thread (and, after a barrier, its block) wrote before: release + add.
+__device__ __forceinline__ void red_release_add_u32(unsigned int *p, unsigned int v)
+{
+    asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Polls until the counter has reached `target` (wrap-around safe); gives up after timeout_ns and
+// returns false, so a lost predecessor can never hang the GPU.
+__device__ __forceinline__ bool counter_wait_bounded(const unsigned int *ctr, unsigned int target, uint64_t timeout_ns)
+{
+    if ((int)(ld_acquire_u32(ctr) - target) >= 0)
+        return true;
+    const uint64_t t0 = global_timer_ns();
+    for (;;) {
+        if ((int)(ld_acquire_u32(ctr) - target) >= 0)
+            return true;
+        if (global_timer_ns() - t0 > timeout_ns)
+            return false;
+    }
+}
+
 __device__ __forceinline__ void named_barrier_sync(int id, int nthreads)
 {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");

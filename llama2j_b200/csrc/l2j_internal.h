@@ -29,6 +29,18 @@ struct SeqState {
     unsigned int cls_counter;   // arrival counter of the classifier's argmax reduction
 };
 
+// Hand-over between consecutive kernels of a forward.  Waiting for the grid in front to complete costs
+// microseconds after its last block has finished; instead every block bumps a counter once its results
+// are visible, and the blocks of the next kernel (already resident under programmatic dependent launch)
+// poll that counter.  Counters only grow: after forward number e (the epoch word, bumped by the begin
+// kernel) every block has bumped e times.
+struct ChainLink {
+    const unsigned int *wait_counter;   // counter of the kernel in front, or nullptr: wait for grid completion
+    unsigned int wait_blocks;           // bumps per forward on that counter
+    unsigned int *done_counter;         // counter this launch bumps once per block, or nullptr
+    const unsigned int *epoch;          // forwards started on this context
+};
+
 struct Cmd {
     int mode;    // 1: feed (token, pos) from the host; 0: continue the device-side greedy loop
     int token;
@@ -109,6 +121,7 @@ struct MvParams {
     const int *prompt;       // device prompt tokens
     int *out_tokens;
     SeqState *state;
+    ChainLink chain;
     unsigned int *work;  // {next unclaimed stage, blocks that ran out of work}; zero between launches
     int pdl_mode;        // experiment: 0 trigger dependents at block start, 1 after the main loop, 2 never
     int producer_wait;   // experiment: producer waits for the previous kernel before its first copy
@@ -126,6 +139,12 @@ struct AttnParams {
     SeqState *state;
     int n_heads, kv_mul, head, seq_len, nsplit, chunk_max;
     int pos_override;        // >= 0: use this position instead of state->cur_pos (tests)
+    int cluster;             // 1: the nsplit (<= 8) blocks of a head are launched as one thread-block cluster and merge
+                             // their partial results through distributed shared memory instead of `part`
+    ChainLink chain;
+    int timeout_us;          // bound of the wait on the hand-over counter
+    unsigned long long *trace;   // optional timeline of the first trace_blocks blocks (16 slots each), else nullptr
+    int trace_blocks;
 };
 
 struct MvPlan {
@@ -157,7 +176,7 @@ cudaError_t prepare_kernels();
 cudaError_t launch_matvec_ring(const LaunchCfg &lc, const MvPlan &plan, bool f32, const MvParams &p);
 cudaError_t launch_attention(const LaunchCfg &lc, const AttnParams &p);
 cudaError_t launch_begin(const LaunchCfg &lc, SeqState *state, const Cmd *cmd, const float *emb, float *x, int dim,
-                         int vocab, int seq_len, int gather, int x_reps, int x_stride);
+                         int vocab, int seq_len, int gather, int x_reps, int x_stride, unsigned int *epoch);
 
 // plain (cross-check) kernels
 cudaError_t launch_rmsnorm_plain(cudaStream_t s, const float *x, const float *w, float *out, int n);

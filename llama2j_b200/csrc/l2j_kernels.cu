@@ -24,6 +24,7 @@
 
 #include <cfloat>
 #include <cmath>
+#include <cooperative_groups.h>
 #include <cstdlib>
 
 #define L2J_DS_WAIT_TIMEOUT 0x1
@@ -181,6 +182,23 @@ __device__ __forceinline__ void prefetch_stage(const MvParams &q, int s)
         bulk_prefetch_l2(sg.payload + flat, pbytes);
         bulk_prefetch_l2(sg.hdr + ga, (uint32_t)(((gl - ga + 2) & ~(int64_t)1) * 8));
     }
+}
+
+// Waits for the kernel in front: on its hand-over counter if the launch has one, else for the grid to
+// complete.  Called by all `nthreads` threads that share barrier `bar_id`; `flag` is a shared-memory word
+// of theirs.  Returns false if the bounded wait ran out.
+__device__ __forceinline__ bool chain_wait_group(const ChainLink &c, bool poller, int bar_id, int nthreads, uint64_t timeout_ns,
+                                                 volatile int *flag)
+{
+    if (c.wait_counter == nullptr) {
+        pdl_wait();
+        return true;
+    }
+    // One thread polls: thousands of pollers on one line would stand in the way of the bumps themselves.
+    if (poller)
+        *flag = counter_wait_bounded(c.wait_counter, __ldcg(c.epoch) * c.wait_blocks, timeout_ns) ? 1 : 0;
+    named_barrier_sync(bar_id, nthreads);   // orders the other threads' loads behind the poller's acquire
+    return *flag != 0;
 }
 
 constexpr int kRedBufs = 4;
@@ -460,7 +478,10 @@ __global__ void __launch_bounds__(kRingMaxThreads, 1) matvec_ring_kernel(const _
 
     // ------------------------------------------------------------------------------ epilogue warp
     if (warp == nw + 1) {
-        pdl_wait();
+        // With a hand-over counter nothing is needed here: the position was fixed when the forward began and
+        // every result this warp writes is computed from data the consumers have waited for.
+        if (p.chain.wait_counter == nullptr)
+            pdl_wait();
         const int pos = __ldcg(&p.state->cur_pos);
         bool lost = (__ldcg(&p.state->status) & L2J_DS_WAIT_TIMEOUT) != 0;
         const bool lost_before = lost;
@@ -531,6 +552,11 @@ __global__ void __launch_bounds__(kRingMaxThreads, 1) matvec_ring_kernel(const _
         }
         if (lost && !lost_before && lane == 0)
             atomicOr(&p.state->status, L2J_DS_WAIT_TIMEOUT);
+        if (p.chain.done_counter) {   // all results of the block were written by this warp; the release is cumulative
+            __syncwarp();
+            if (lane == 0)
+                red_release_add_u32(p.chain.done_counter, 1u);
+        }
         if (lane == 0) {
             trace_mark(p, 6);
             if (p.trace)
@@ -591,7 +617,10 @@ __global__ void __launch_bounds__(kRingMaxThreads, 1) matvec_ring_kernel(const _
         }
     }
 
-    pdl_wait();   // the input vector comes from the previous kernel
+    bool lost = false;
+    // the input vector comes from the previous kernel
+    if (!chain_wait_group(p.chain, tid == 0, 1, ncons, wait_ns, reinterpret_cast<volatile int *>(smem + kScratchOff + 252)))
+        lost = true;
     if (tid == 0)
         trace_mark(p, 12);
 
@@ -601,8 +630,8 @@ __global__ void __launch_bounds__(kRingMaxThreads, 1) matvec_ring_kernel(const _
     //      then picks up the chunks it owns.
     uint8_t *share = smem + kSmemHeader;   // u8: three planes [limb][nchunks] of 16 B (4 bytes per 4 elements); FP32: [nchunks] float4
     float *scratch = reinterpret_cast<float *>(smem + kScratchOff);
-    bool lost = (__ldcg(&p.state->status) & L2J_DS_WAIT_TIMEOUT) != 0;
-    const bool lost_before = lost;
+    const bool lost_before = (__ldcg(&p.state->status) & L2J_DS_WAIT_TIMEOUT) != 0;
+    lost = lost || lost_before;
     float inv = 1.0f;                      // u8 path: value of one fixed-point unit
     {
         // The producer may fill the ring from now on: it needs hundreds of cycles to react, by then
@@ -648,6 +677,8 @@ __global__ void __launch_bounds__(kRingMaxThreads, 1) matvec_ring_kernel(const _
             ssq = warp_sum(lane < nw ? scratch[lane] : 0.f);          // same order in every warp and block
             amax = warp_max(lane < nw ? scratch[32 + lane] : 0.f);
         }
+        if (tid == 0)
+            trace_mark(p, 9);
         if (has_rms) {
             float tot = __fdiv_rn(ssq, (float)p.n);
             tot = __fadd_rn(tot, 1e-5f);
@@ -697,8 +728,12 @@ __global__ void __launch_bounds__(kRingMaxThreads, 1) matvec_ring_kernel(const _
                 }
             }
         }
+        if (tid == 0)
+            trace_mark(p, 10);
     }
     named_barrier_sync(1, ncons);
+    if (tid == 0)
+        trace_mark(p, 11);
 
     float xv[F32 ? CPT : 1][4];           // FP32 path: the chunk's four x values
     uint32_t xl[F32 ? 1 : NCH][4][3];     // u8 path: [chunk][word of 4 elements][limb]
@@ -1012,7 +1047,7 @@ cudaError_t launch_matvec_ring(const LaunchCfg &lc, const MvPlan &plan, bool f32
 // =============================================================================================
 
 __global__ void __launch_bounds__(256) begin_kernel(SeqState *state, const Cmd *cmd, const float *emb, float *x, int dim,
-                                                    int vocab, int seq_len, int gather, int x_reps, int x_stride)
+                                                    int vocab, int seq_len, int gather, int x_reps, int x_stride, unsigned int *epoch)
 {
     __shared__ int s_tok;
     pdl_launch_dependents();
@@ -1039,6 +1074,8 @@ __global__ void __launch_bounds__(256) begin_kernel(SeqState *state, const Cmd *
             atomicOr(&state->status, st);
         state->cur_token = tok;
         state->cur_pos = pos;
+        if (epoch)   // a whole forward follows: its kernels hand over through the counters
+            *epoch = __ldcg(epoch) + 1u;
         s_tok = tok;
     }
     __syncthreads();
@@ -1060,7 +1097,7 @@ __global__ void __launch_bounds__(256) begin_kernel(SeqState *state, const Cmd *
 }
 
 cudaError_t launch_begin(const LaunchCfg &lc, SeqState *state, const Cmd *cmd, const float *emb, float *x, int dim,
-                         int vocab, int seq_len, int gather, int x_reps, int x_stride)
+                         int vocab, int seq_len, int gather, int x_reps, int x_stride, unsigned int *epoch)
 {
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(1);
@@ -1072,7 +1109,7 @@ cudaError_t launch_begin(const LaunchCfg &lc, SeqState *state, const Cmd *cmd, c
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = lc.pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, begin_kernel, state, cmd, emb, x, dim, vocab, seq_len, gather, x_reps, x_stride);
+    return cudaLaunchKernelEx(&cfg, begin_kernel, state, cmd, emb, x, dim, vocab, seq_len, gather, x_reps, x_stride, epoch);
 }
 
 // =============================================================================================
@@ -1087,14 +1124,13 @@ cudaError_t launch_begin(const LaunchCfg &lc, SeqState *state, const Cmd *cmd, c
 
 constexpr int kAttnThreads = 256;
 constexpr int kAttnWarps = kAttnThreads / 32;
-constexpr int kAttnMinChunk = 64;   // positions per block before the work is split further
+constexpr int kAttnMinChunk = 32;   // positions per block before the work is split further: one round of loads
 
-__global__ void __launch_bounds__(kAttnThreads) attention_kernel(const __grid_constant__ AttnParams p)
+// Streams positions [t0, t0 + cnt) of head h and merges the block's lane groups: afterwards thread
+// tid < head holds (M, L, O[tid]) of those positions.  Called by the whole block.
+__device__ __forceinline__ void attention_block(const AttnParams &p, int h, int t0, int cnt, int pos, float *asmem, int *s_flag,
+                                                unsigned long long *tr, float &M, float &L, float &O)
 {
-    extern __shared__ __align__(16) float asmem[];   // [slots][head + 4]: o, then m, l (16-byte aligned rows)
-    __shared__ int s_last;
-
-    const int h = blockIdx.x, sp = blockIdx.y;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int head = p.head;
     const int lpp = head >> 2;                      // lanes per position (float4 each)
@@ -1107,29 +1143,13 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const __grid_co
     const int nslots = kAttnWarps * ppw;
     const int slot = warp * ppw + g;
     const int sstride = head + 4;
-
-    pdl_launch_dependents();
-
-    // The position was fixed when the token started and every cached row but the newest is older than
-    // that, so both can be read before the QKV kernel in front of this one has finished: the block
-    // becomes resident early and hides its first memory round trip behind that kernel.
-    const int pos = p.pos_override >= 0 ? p.pos_override : __ldcg(&p.state->cur_pos);
-    const int npos = pos + 1;
-    int chunk = (npos + p.nsplit - 1) / p.nsplit;
-    if (chunk < kAttnMinChunk)
-        chunk = kAttnMinChunk;
-    const int nact = (npos + chunk - 1) / chunk;    // blocks of this head that have work
-    if (sp >= nact) {
-        pdl_wait();
-        return;
-    }
-    const int t0 = sp * chunk;
-    const int cnt = min(npos, t0 + chunk) - t0;
     const int kvh = h / p.kv_mul;
     const float *kb = p.k_cache + ((int64_t)kvh * p.seq_len + t0) * head;
     const float *vb = p.v_cache + ((int64_t)kvh * p.seq_len + t0) * head;
     const float sq = sqrtf((float)head);
 
+    // Every cached row but the newest is older than this forward, so the first round of rows can be on
+    // its way before the QKV kernel in front has finished.
     float4 kk[4], vv[4];
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
@@ -1142,7 +1162,11 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const __grid_co
         }
     }
 
-    pdl_wait();   // q and the newest K/V row come from the kernel in front
+    // q and the newest K/V row come from the kernel in front
+    if (!chain_wait_group(p.chain, tid == 0, 1, kAttnThreads, (uint64_t)p.timeout_us * 1000ull, s_flag) && tid == 0)
+        atomicOr(&p.state->status, L2J_DS_WAIT_TIMEOUT);
+    if (tr)
+        tr[1] = global_timer_ns();
 
     float4 q4 = make_float4(0.f, 0.f, 0.f, 0.f);
     if (active)
@@ -1195,6 +1219,8 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const __grid_co
             m = mn;
         }
     }
+    if (tr)
+        tr[2] = global_timer_ns();
     float *mine = asmem + slot * sstride;
     if (active)
         *reinterpret_cast<float4 *>(mine + 4 * li) = acc;
@@ -1205,7 +1231,9 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const __grid_co
     __syncthreads();
 
     // merge the lane groups of the block in slot order
-    float M = -INFINITY, L = 0.f, O = 0.f;
+    M = -INFINITY;
+    L = 0.f;
+    O = 0.f;
     if (tid < head) {
         for (int s2 = 0; s2 < nslots; ++s2)
             M = fmaxf(M, asmem[s2 * sstride + head]);
@@ -1219,13 +1247,110 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const __grid_co
             }
         }
     }
-    if (nact == 1) {
-        {
-            const float o = __fdiv_rn(O, L);   // ExpSumNormalize.java:33-37 folded into the sum
-            if (tid < head)
-                for (int r = 0; r < p.out_reps; ++r)
-                    p.out[(int64_t)r * p.out_stride + (int64_t)h * head + tid] = o;
+    if (tr)
+        tr[3] = global_timer_ns();
+}
+
+// Tells the kernel behind that this block's results are visible (after a block-wide barrier the release
+// by one thread covers what the others wrote).
+__device__ __forceinline__ void attention_signal(const AttnParams &p)
+{
+    if (p.chain.done_counter) {
+        __syncthreads();
+        if (threadIdx.x == 0)
+            red_release_add_u32(p.chain.done_counter, 1u);
+    }
+}
+
+__global__ void __launch_bounds__(kAttnThreads) attention_kernel(const __grid_constant__ AttnParams p)
+{
+    extern __shared__ __align__(16) float asmem[];   // [slots][head + 4]: o, then m, l (16-byte aligned rows); [head + 4] block result
+    __shared__ int s_last;
+
+    const int h = blockIdx.x, sp = blockIdx.y;
+    const int tid = threadIdx.x;
+    const int head = p.head;
+
+    pdl_launch_dependents();
+    const int bl = sp * (int)gridDim.x + h;
+    unsigned long long *tr = (p.trace && bl < p.trace_blocks && tid == 0) ? p.trace + bl * 16 : nullptr;
+    if (tr)
+        tr[0] = global_timer_ns();
+
+    // The position was fixed when the token started, so it can be read before the kernel in front has
+    // finished: the block becomes resident early and hides its first memory round trip behind that kernel.
+    const int pos = p.pos_override >= 0 ? p.pos_override : __ldcg(&p.state->cur_pos);
+    const int npos = pos + 1;
+    int chunk = (npos + p.nsplit - 1) / p.nsplit;
+    if (chunk < kAttnMinChunk)
+        chunk = kAttnMinChunk;
+    const int nact = (npos + chunk - 1) / chunk;    // blocks of this head that have work
+    const bool cluster_merge = p.cluster && nact > 1;
+    if (sp >= nact && !cluster_merge) {   // no work, no results, nobody to meet: report at once
+        if (p.chain.done_counter) {
+            if (tid == 0)
+                red_release_add_u32(p.chain.done_counter, 1u);
+        } else {
+            pdl_wait();
         }
+        return;
+    }
+
+    float M = -INFINITY, L = 0.f, O = 0.f;
+    if (sp < nact) {
+        const int t0 = sp * chunk;
+        const int cnt = min(npos, t0 + chunk) - t0;
+        attention_block(p, h, t0, cnt, pos, asmem, &s_last, tr, M, L, O);
+    }
+
+    if (nact == 1) {
+        const float o = __fdiv_rn(O, L);   // ExpSumNormalize.java:33-37 folded into the sum
+        if (tid < head)
+            for (int r = 0; r < p.out_reps; ++r)
+                p.out[(int64_t)r * p.out_stride + (int64_t)h * head + tid] = o;
+        attention_signal(p);
+        return;
+    }
+
+    if (cluster_merge) {
+        // The blocks of a head form one thread-block cluster: the partial results stay in shared memory and
+        // block 0 of the cluster reads them from its neighbours, in block order (bitwise reproducible).
+        namespace cg = cooperative_groups;
+        cg::cluster_group cl = cg::this_cluster();
+        int gw = 1;
+        while (gw < (head >> 2))
+            gw <<= 1;
+        float *res = asmem + kAttnWarps * (32 / gw) * (head + 4);
+        if (tid < head)
+            res[tid] = O;
+        if (tid == 0) {
+            res[head] = M;
+            res[head + 1] = L;
+        }
+        cl.sync();
+        if (sp == 0 && tid < head) {
+            float gm = -INFINITY;
+            for (int s2 = 0; s2 < nact; ++s2)
+                gm = fmaxf(gm, cl.map_shared_rank(res, s2)[head]);
+            float LL = 0.f, OO = 0.f;
+            for (int s2 = 0; s2 < nact; ++s2) {
+                const float *rs = cl.map_shared_rank(res, s2);
+                const float ms = rs[head];
+                const float ls = rs[head + 1];
+                if (ls > 0.f) {
+                    const float w = expf(ms - gm);
+                    LL = fmaf(ls, w, LL);
+                    OO = fmaf(rs[tid], w, OO);
+                }
+            }
+            const float o = __fdiv_rn(OO, LL);
+            for (int r = 0; r < p.out_reps; ++r)
+                p.out[(int64_t)r * p.out_stride + (int64_t)h * head + tid] = o;
+        }
+        if (tr)
+            tr[5] = global_timer_ns();
+        cl.sync();   // a block's shared memory must outlive the reads of block 0
+        attention_signal(p);
         return;
     }
 
@@ -1243,8 +1368,13 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const __grid_co
         s_last = (ticket == (unsigned)nact - 1);
     }
     __syncthreads();
-    if (!s_last)
+    if (tr)
+        tr[4] = global_timer_ns();
+    if (!s_last) {
+        if (tid == 0 && p.chain.done_counter)   // the partials were fenced before the ticket
+            red_release_add_u32(p.chain.done_counter, 1u);
         return;
+    }
 
     // ---- the last block of the head merges the partials of the active blocks in a fixed order
     __threadfence();
@@ -1269,6 +1399,9 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const __grid_co
     }
     if (tid == 0)
         p.counters[h] = 0;
+    if (tr)
+        tr[5] = global_timer_ns();
+    attention_signal(p);
 }
 
 cudaError_t launch_attention(const LaunchCfg &lc, const AttnParams &p)
@@ -1277,16 +1410,29 @@ cudaError_t launch_attention(const LaunchCfg &lc, const AttnParams &p)
     while (gw < (p.head >> 2))
         gw <<= 1;
     const int nslots = kAttnWarps * (32 / gw);
+    if (p.cluster && (p.nsplit < 1 || p.nsplit > 8))
+        return cudaErrorInvalidConfiguration;
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3((unsigned)p.n_heads, (unsigned)p.nsplit);
     cfg.blockDim = dim3(kAttnThreads);
-    cfg.dynamicSmemBytes = (size_t)nslots * (p.head + 4) * sizeof(float);
+    cfg.dynamicSmemBytes = (size_t)(nslots + 1) * (p.head + 4) * sizeof(float);
     cfg.stream = lc.stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    if (lc.pdl) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    if (p.cluster && p.nsplit > 1) {   // the blocks of a head are one cluster
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = 1;
+        attr[na].val.clusterDim.y = (unsigned)p.nsplit;
+        attr[na].val.clusterDim.z = 1;
+        ++na;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = lc.pdl ? 1 : 0;
+    cfg.numAttrs = na;
     return cudaLaunchKernelEx(&cfg, attention_kernel, p);
 }
 

@@ -149,8 +149,9 @@ class Transformer:
         return out
 
     def read_trace(self) -> np.ndarray:
-        """Timelines of every ring-kernel launch of the last forward: (launches, blocks, 16)."""
-        launches = 4 * (self.last_layer - self.first_layer + 1) + 1
+        """Timelines of every launch of the last forward: (launches, blocks, 16); the ring kernels of the
+        layers first (4 per layer), the classifier, then the attention kernels (one per layer)."""
+        launches = 5 * (self.last_layer - self.first_layer + 1) + 1
         nb = self.launch_mode()["ring_blocks"]
         out = np.zeros((launches, nb, 16), dtype=np.uint64)
         _lib.check(self._lib.l2j_read_trace(self._ctx, out.ctypes.data, out.size), self._ctx)
