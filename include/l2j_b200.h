@@ -161,6 +161,25 @@ L2J_API int l2j_sync(l2j_ctx *ctx);
  * sampled BOS (Run.java:670-672) is left to the caller, who truncates. */
 L2J_API int l2j_generate_greedy(l2j_ctx *ctx, const int32_t *prompt, int n_prompt, int steps, int32_t *out_tokens);
 
+/* ---- layer split over several devices, one host thread (Run.java:368-413) ------------------- */
+
+/* Connects contexts that tile the layers in order (stage 0 from layer 0, the last stage with the
+ * classifier), one per device as `--gpuMem a,b,...` creates them (LayerAllocation.java:54-95,
+ * Context.java:16-23).  Afterwards a stage reads the activation vector x straight from the previous
+ * stage's device memory over the peer link, where the reference copies it through a host array
+ * with two blocking synchronisations (ContextCUDA.java:269-280).  Needs peer access between the
+ * devices of neighbouring stages; returns L2J_E_STATE without it (l2j_forward_stage still works). */
+L2J_API int l2j_pipeline_link(l2j_ctx *const *stages, int n_stages);
+
+/* One decode step over linked stages: the loop over devices of Run.transformerCUDA.  Each stage's
+ * stream waits for the stage in front through an event; the host blocks only at the end. */
+L2J_API int l2j_pipeline_forward(l2j_ctx *const *stages, int n_stages, int token, int pos, float *logits, int *argmax);
+
+/* l2j_generate_greedy over linked stages: the chosen token stays on the last stage's device and the
+ * first stage reads it from there.  l2j_last_generate_us(stages[0]) gives the device time. */
+L2J_API int l2j_pipeline_generate_greedy(l2j_ctx *const *stages, int n_stages, const int32_t *prompt, int n_prompt, int steps,
+                                         int32_t *out_tokens);
+
 /* Clears the KV cache position bookkeeping and the statistics (a new sequence). */
 L2J_API int l2j_reset(l2j_ctx *ctx);
 

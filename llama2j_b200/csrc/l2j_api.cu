@@ -72,6 +72,8 @@ struct l2j_ctx {
     SeqState *state = nullptr;
     Cmd *cmd_dev = nullptr;
     Cmd *cmd_host = nullptr;       // pinned ring
+    StageLink *link_dev = nullptr; // peer pointers of a linked layer split (zero until linked)
+    cudaEvent_t ev_stage = nullptr;   // "this stage's step is done", waited for by the next stage's stream
     float *logits_host = nullptr;  // pinned
     float *x_host = nullptr;       // pinned
     SeqState *state_host = nullptr;
@@ -436,7 +438,7 @@ cudaError_t enqueue_forward(l2j_ctx *c, bool pdl, int *n_kernels)
     LaunchCfg lc{c->stream, false, c->ring_grid};
     // The first kernel of a forward follows a memcpy (or the previous graph launch): plain edge.
     e = launch_begin(lc, c->state, c->cmd_dev, c->emb, c->x, c->dim, c->cfg.vocab_size, c->cfg.seq_len, c->is_first ? 1 : 0, c->reps, c->dim_stride,
-                     c->use_ring && c->chain_on ? c->chain + (int64_t)kChainStride * (5 * c->nl + 1) : nullptr);
+                     c->use_ring && c->chain_on ? c->chain + (int64_t)kChainStride * (5 * c->nl + 1) : nullptr, c->link_dev);
     if (e != cudaSuccess)
         return e;
     ++nk;
@@ -540,13 +542,13 @@ int check_range(l2j_ctx *c, int token, int pos, bool need_token)
     return L2J_OK;
 }
 
-int post_cmd(l2j_ctx *c, int mode, int token, int pos)
+int post_cmd(l2j_ctx *c, int mode, int token, int pos, int flags = 0)
 {
     Cmd *slot = c->cmd_host + (c->forwards % kCmdRing);
     slot->mode = mode;
     slot->token = token;
     slot->pos = pos;
-    slot->pad = 0;
+    slot->flags = flags;
     CK(c, cudaMemcpyAsync(c->cmd_dev, slot, sizeof(Cmd), cudaMemcpyHostToDevice, c->stream));
     return L2J_OK;
 }
@@ -739,6 +741,8 @@ extern "C" int l2j_create(const l2j_config *cfg, int device, int first_layer, in
     CREATE_CK(dev_alloc(c, &c->state, 1, true));
     CREATE_CK(dev_alloc(c, &c->cmd_dev, 1, true));
     CREATE_CUDA(cudaHostAlloc((void **)&c->cmd_host, sizeof(Cmd) * kCmdRing, cudaHostAllocDefault));
+    CREATE_CK(dev_alloc(c, &c->link_dev, 1, true));
+    CREATE_CUDA(cudaEventCreateWithFlags(&c->ev_stage, cudaEventDisableTiming));
     CREATE_CUDA(cudaHostAlloc((void **)&c->logits_host, sizeof(float) * (size_t)cfg->vocab_size, cudaHostAllocDefault));
     CREATE_CUDA(cudaHostAlloc((void **)&c->x_host, sizeof(float) * (size_t)c->reps * c->dim_stride, cudaHostAllocDefault));
     CREATE_CUDA(cudaHostAlloc((void **)&c->state_host, sizeof(SeqState), cudaHostAllocDefault));
@@ -774,6 +778,8 @@ extern "C" void l2j_destroy(l2j_ctx *c)
         cudaFree(p);
     if (c->cmd_host)
         cudaFreeHost(c->cmd_host);
+    if (c->ev_stage)
+        cudaEventDestroy(c->ev_stage);
     if (c->logits_host)
         cudaFreeHost(c->logits_host);
     if (c->x_host)
@@ -1105,6 +1111,196 @@ extern "C" int l2j_generate_greedy(l2j_ctx *c, const int32_t *prompt, int n_prom
     return finish_status(c);
 }
 
+// ===============================================================================================
+// layer split over several devices driven by one host thread (Run.java:368-413)
+// ===============================================================================================
+
+namespace {
+
+int check_stages(l2j_ctx *const *stages, int n)
+{
+    if (!stages || n <= 0)
+        return L2J_E_INVALID;
+    for (int i = 0; i < n; ++i)
+        if (!stages[i])
+            return L2J_E_INVALID;
+    l2j_ctx *c0 = stages[0];
+    for (int i = 0; i < n; ++i) {
+        l2j_ctx *c = stages[i];
+        if (!c->finalized)
+            return fail(c0, L2J_E_STATE, "stage %d is not finalized", i);
+        if (memcmp(&c->cfg, &c0->cfg, sizeof(l2j_config)) != 0)
+            return fail(c0, L2J_E_INVALID, "stage %d was created for another model", i);
+        if ((i == 0) != c->is_first || (i == n - 1) != c->is_last || (i > 0 && c->first_layer != stages[i - 1]->last_layer + 1))
+            return fail(c0, L2J_E_INVALID, "the stages do not tile the layers in order (stage %d holds %d..%d)", i,
+                        c->first_layer, c->last_layer);
+    }
+    return L2J_OK;
+}
+
+// Stage i's stream waits for stage i-1's step, then runs its own; the hand-off itself is the peer read
+// in the stage's begin kernel.
+int enqueue_stage(l2j_ctx *const *stages, int n, int i)
+{
+    l2j_ctx *c = stages[i];
+    CK(c, cudaSetDevice(c->device));
+    if (n > 1)
+        CK(c, cudaStreamWaitEvent(c->stream, stages[(i + n - 1) % n]->ev_stage, 0));
+    int rc = launch_forward(c);
+    if (rc != L2J_OK)
+        return rc;
+    CK(c, cudaEventRecord(c->ev_stage, c->stream));
+    return L2J_OK;
+}
+
+}  // namespace
+
+extern "C" int l2j_pipeline_link(l2j_ctx *const *stages, int n_stages)
+{
+    int rc = check_stages(stages, n_stages);
+    if (rc != L2J_OK)
+        return rc;
+    for (int i = 0; i < n_stages; ++i) {
+        l2j_ctx *c = stages[i];
+        std::lock_guard<std::mutex> lock(c->mu);
+        l2j_ctx *prev = stages[(i + n_stages - 1) % n_stages];   // stage 0 reads the token from the last stage
+        CK(c, cudaSetDevice(c->device));
+        if (prev->device != c->device) {
+            int can = 0;
+            CK(c, cudaDeviceCanAccessPeer(&can, c->device, prev->device));
+            if (!can)
+                return fail(stages[0], L2J_E_STATE, "device %d cannot read the memory of device %d", c->device, prev->device);
+            cudaError_t e = cudaDeviceEnablePeerAccess(prev->device, 0);
+            if (e == cudaErrorPeerAccessAlreadyEnabled)
+                cudaGetLastError();
+            else
+                CK(c, e);
+        }
+        StageLink link{};
+        link.x_src = i > 0 ? prev->x : nullptr;
+        link.token_src = i == 0 && n_stages > 1 ? &prev->state->token : nullptr;
+        CK(c, cudaMemcpy(c->link_dev, &link, sizeof(StageLink), cudaMemcpyHostToDevice));
+        // an event recorded once, so that the first wait of the ring of stages finds it complete
+        CK(c, cudaEventRecord(c->ev_stage, c->stream));
+        CK(c, cudaStreamSynchronize(c->stream));
+    }
+    return L2J_OK;
+}
+
+extern "C" int l2j_pipeline_forward(l2j_ctx *const *stages, int n_stages, int token, int pos, float *logits, int *argmax)
+{
+    int rc = check_stages(stages, n_stages);
+    if (rc != L2J_OK)
+        return rc;
+    rc = check_range(stages[0], token, pos, true);
+    if (rc != L2J_OK)
+        return rc;
+    for (int i = 0; i < n_stages; ++i) {
+        l2j_ctx *c = stages[i];
+        std::lock_guard<std::mutex> lock(c->mu);
+        CK(c, cudaSetDevice(c->device));
+        rc = post_cmd(c, 1, i == 0 ? token : 0, pos, i > 0 ? kCmdXFromPeer : 0);
+        if (rc != L2J_OK)
+            return rc;
+        if (i > 0)
+            CK(c, cudaStreamWaitEvent(c->stream, stages[i - 1]->ev_stage, 0));
+        rc = launch_forward(c);
+        if (rc != L2J_OK)
+            return rc;
+        CK(c, cudaEventRecord(c->ev_stage, c->stream));
+    }
+    int status = L2J_OK;
+    for (int i = 0; i < n_stages; ++i) {   // every stage's status word is checked
+        l2j_ctx *c = stages[i];
+        std::lock_guard<std::mutex> lock(c->mu);
+        CK(c, cudaSetDevice(c->device));
+        if (c->is_last && logits)
+            CK(c, cudaMemcpyAsync(c->logits_host, c->logits, sizeof(float) * (size_t)c->cfg.vocab_size, cudaMemcpyDeviceToHost,
+                                  c->stream));
+        CK(c, cudaMemcpyAsync(c->state_host, c->state, sizeof(SeqState), cudaMemcpyDeviceToHost, c->stream));
+        CK(c, cudaStreamSynchronize(c->stream));
+        if (c->is_last && logits)
+            memcpy(logits, c->logits_host, sizeof(float) * (size_t)c->cfg.vocab_size);
+        if (c->is_last && argmax)
+            *argmax = c->state_host->argmax;
+        const int r = finish_status(c);
+        if (r != L2J_OK && status == L2J_OK) {
+            status = r;
+            if (c != stages[0])
+                fail(stages[0], r, "stage %d: %s", i, c->err.c_str());
+        }
+    }
+    return status;
+}
+
+extern "C" int l2j_pipeline_generate_greedy(l2j_ctx *const *stages, int n_stages, const int32_t *prompt, int n_prompt, int steps,
+                                            int32_t *out_tokens)
+{
+    int rc = check_stages(stages, n_stages);
+    if (rc != L2J_OK)
+        return rc;
+    l2j_ctx *c0 = stages[0], *cl = stages[n_stages - 1];
+    if (steps <= 0 || steps > c0->cfg.seq_len || n_prompt < 0 || n_prompt > c0->cfg.seq_len || (n_prompt > 0 && !prompt) ||
+        !out_tokens)
+        return fail(c0, L2J_E_INVALID, "bad arguments: steps %d (seq_len %d), n_prompt %d", steps, c0->cfg.seq_len, n_prompt);
+    for (int i = 0; i < n_prompt; ++i)
+        if (prompt[i] < 0 || prompt[i] >= c0->cfg.vocab_size)
+            return fail(c0, L2J_E_INVALID, "prompt token %d outside the vocabulary", prompt[i]);
+    for (int i = 0; i < n_stages; ++i) {
+        l2j_ctx *c = stages[i];
+        std::lock_guard<std::mutex> lock(c->mu);
+        CK(c, cudaSetDevice(c->device));
+        if (c->is_last && n_prompt > 0)
+            CK(c, cudaMemcpyAsync(c->prompt_dev, prompt, sizeof(int32_t) * (size_t)n_prompt, cudaMemcpyHostToDevice, c->stream));
+        SeqState init{};
+        init.token = 1;   // BOS, Run.java:614
+        init.pos = 0;
+        init.n_prompt = n_prompt;
+        CK(c, cudaMemcpyAsync(c->state, &init, sizeof(SeqState), cudaMemcpyHostToDevice, c->stream));
+        CK(c, cudaStreamSynchronize(c->stream));
+        const int flags = (i > 0 ? kCmdXFromPeer : 0) | (i == 0 && n_stages > 1 ? kCmdTokenFromPeer : 0) |
+                          (!c->is_last ? kCmdAdvancePos : 0);
+        rc = post_cmd(c, 0, 0, 0, flags);
+        if (rc != L2J_OK)
+            return rc;
+        CK(c, cudaEventRecord(c->ev_stage, c->stream));   // complete before the loop starts
+        CK(c, cudaStreamSynchronize(c->stream));
+    }
+    CK(c0, cudaSetDevice(c0->device));
+    CK(c0, cudaEventRecord(c0->ev0, c0->stream));
+    for (int s = 0; s < steps; ++s)
+        for (int i = 0; i < n_stages; ++i) {
+            // step s of stage 0 waits for step s-1 of the last stage: it reads the chosen token there
+            rc = enqueue_stage(stages, n_stages, i);
+            if (rc != L2J_OK)
+                return rc;
+        }
+    CK(c0, cudaSetDevice(c0->device));
+    if (n_stages > 1)
+        CK(c0, cudaStreamWaitEvent(c0->stream, cl->ev_stage, 0));
+    CK(c0, cudaEventRecord(c0->ev1, c0->stream));
+    int status = L2J_OK;
+    for (int i = 0; i < n_stages; ++i) {
+        l2j_ctx *c = stages[i];
+        CK(c, cudaSetDevice(c->device));
+        CK(c, cudaMemcpyAsync(c->state_host, c->state, sizeof(SeqState), cudaMemcpyDeviceToHost, c->stream));
+        CK(c, cudaStreamSynchronize(c->stream));
+        const int r = finish_status(c);
+        if (r != L2J_OK && status == L2J_OK) {
+            status = r;
+            if (c != c0)
+                fail(c0, r, "stage %d: %s", i, c->err.c_str());
+        }
+    }
+    CK(cl, cudaSetDevice(cl->device));
+    CK(cl, cudaMemcpy(out_tokens, cl->out_tokens_dev, sizeof(int32_t) * (size_t)steps, cudaMemcpyDeviceToHost));
+    float ms = 0.f;
+    CK(c0, cudaSetDevice(c0->device));
+    CK(c0, cudaEventElapsedTime(&ms, c0->ev0, c0->ev1));
+    c0->last_generate_us = (double)ms * 1000.0;
+    return status;
+}
+
 extern "C" int l2j_last_generate_us(l2j_ctx *c, double *total_us)
 {
     if (!c || !total_us)
@@ -1160,7 +1356,7 @@ extern "C" int l2j_time_kernels(l2j_ctx *c, int pos, int reps, double *us)
     if (rc != L2J_OK)
         return rc;
     LaunchCfg lc{c->stream, false, c->ring_grid};
-    CK(c, launch_begin(lc, c->state, c->cmd_dev, c->emb, c->x, c->dim, c->cfg.vocab_size, c->cfg.seq_len, c->is_first ? 1 : 0, c->reps, c->dim_stride, nullptr));
+    CK(c, launch_begin(lc, c->state, c->cmd_dev, c->emb, c->x, c->dim, c->cfg.vocab_size, c->cfg.seq_len, c->is_first ? 1 : 0, c->reps, c->dim_stride, nullptr, c->link_dev));
     for (int kind = 0; kind < 6; ++kind) {
         us[kind] = 0.0;
         if (kind == 5 && !c->is_last)
@@ -1236,7 +1432,7 @@ extern "C" int l2j_trace_kernel(l2j_ctx *c, int kind, int layer, int pos, uint64
     cudaDeviceSynchronize();
     rc = post_cmd(c, 1, 1, pos);
     LaunchCfg lc{c->stream, false, c->ring_grid};
-    cudaError_t e = launch_begin(lc, c->state, c->cmd_dev, c->emb, c->x, c->dim, c->cfg.vocab_size, c->cfg.seq_len, c->is_first ? 1 : 0, c->reps, c->dim_stride, nullptr);
+    cudaError_t e = launch_begin(lc, c->state, c->cmd_dev, c->emb, c->x, c->dim, c->cfg.vocab_size, c->cfg.seq_len, c->is_first ? 1 : 0, c->reps, c->dim_stride, nullptr, c->link_dev);
     LayerLaunch &L = c->layers[(size_t)li];
     for (int rep = 0; rep < 2 && e == cudaSuccess; ++rep) {   // the second launch is the one recorded
         MvParams p = kind == 0 ? L.qkv : kind == 2 ? L.wo : kind == 3 ? L.w13 : kind == 4 ? L.w2 : c->cls;

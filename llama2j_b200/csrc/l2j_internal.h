@@ -45,7 +45,18 @@ struct Cmd {
     int mode;    // 1: feed (token, pos) from the host; 0: continue the device-side greedy loop
     int token;
     int pos;
-    int pad;
+    int flags;   // kCmd* bits: how a stage of a layer split gets its inputs
+};
+
+constexpr int kCmdXFromPeer = 1;       // x is read from the previous stage's device (StageLink::x_src)
+constexpr int kCmdTokenFromPeer = 2;   // greedy loop: the next token is read from the last stage's device
+constexpr int kCmdAdvancePos = 4;      // greedy loop on a stage without the classifier: count the positions here
+
+// Where a stage of a layer split finds the data of its neighbours (peer device memory); written when
+// the stages are linked, read by the begin kernel.
+struct StageLink {
+    const float *x_src;     // x of the previous stage (dim floats)
+    const int *token_src;   // SeqState::token of the last stage
 };
 
 // One quantised tensor (or the slice of it a context owns) after the upload re-layout:
@@ -176,7 +187,7 @@ cudaError_t prepare_kernels();
 cudaError_t launch_matvec_ring(const LaunchCfg &lc, const MvPlan &plan, bool f32, const MvParams &p);
 cudaError_t launch_attention(const LaunchCfg &lc, const AttnParams &p);
 cudaError_t launch_begin(const LaunchCfg &lc, SeqState *state, const Cmd *cmd, const float *emb, float *x, int dim,
-                         int vocab, int seq_len, int gather, int x_reps, int x_stride, unsigned int *epoch);
+                         int vocab, int seq_len, int gather, int x_reps, int x_stride, unsigned int *epoch, const StageLink *link);
 
 // plain (cross-check) kernels
 cudaError_t launch_rmsnorm_plain(cudaStream_t s, const float *x, const float *w, float *out, int n);

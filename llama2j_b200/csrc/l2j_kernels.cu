@@ -649,6 +649,8 @@ __global__ void __launch_bounds__(kRingMaxThreads, 1) matvec_ring_kernel(const _
             const int idx = tid + j * ncons;
             xr[j] = make_float4(0.f, 0.f, 0.f, 0.f);
             wr[j] = make_float4(1.f, 1.f, 1.f, 1.f);
+            if (j * ncons >= n4)
+                break;
             if (idx < n4) {
                 xr[j] = ld_cg_f4_issue(xin + (int64_t)idx * 4);
                 if (has_rms)
@@ -658,6 +660,8 @@ __global__ void __launch_bounds__(kRingMaxThreads, 1) matvec_ring_kernel(const _
         float ssq = 0.f, amax = 0.f;
 #pragma unroll
         for (int j = 0; j < kPrologueRounds; ++j) {
+            if (j * ncons >= n4)   // block-uniform: the remaining rounds hold nothing
+                break;
             ssq = fmaf(xr[j].x, xr[j].x, ssq);
             ssq = fmaf(xr[j].y, xr[j].y, ssq);
             ssq = fmaf(xr[j].z, xr[j].z, ssq);
@@ -685,6 +689,8 @@ __global__ void __launch_bounds__(kRingMaxThreads, 1) matvec_ring_kernel(const _
             const float ss = __fdiv_rn(1.0f, __fsqrt_rn(tot));
 #pragma unroll
             for (int j = 0; j < kPrologueRounds; ++j) {
+                if (j * ncons >= n4)
+                    break;
                 xr[j].x = __fmul_rn(wr[j].x, __fmul_rn(ss, xr[j].x));
                 xr[j].y = __fmul_rn(wr[j].y, __fmul_rn(ss, xr[j].y));
                 xr[j].z = __fmul_rn(wr[j].z, __fmul_rn(ss, xr[j].z));
@@ -696,6 +702,8 @@ __global__ void __launch_bounds__(kRingMaxThreads, 1) matvec_ring_kernel(const _
 #pragma unroll
             for (int j = 0; j < kPrologueRounds; ++j) {
                 const int idx = tid + j * ncons;
+                if (j * ncons >= n4)
+                    break;
                 if (idx < n4)
                     *reinterpret_cast<float4 *>(share + (size_t)idx * 16) = xr[j];
             }
@@ -709,6 +717,8 @@ __global__ void __launch_bounds__(kRingMaxThreads, 1) matvec_ring_kernel(const _
 #pragma unroll
             for (int j = 0; j < kPrologueRounds; ++j) {
                 const int idx = tid + j * ncons;
+                if (j * ncons >= n4)
+                    break;
                 if (idx < n4) {
                     // 24-bit fixed point as three balanced signed byte limbs: after the add-and-flip, bytes
                     // 0..2 of z are l0, l1, l2 in [-128, 127] with X = l0 + 256 l1 + 65536 l2
@@ -1047,20 +1057,31 @@ cudaError_t launch_matvec_ring(const LaunchCfg &lc, const MvPlan &plan, bool f32
 // =============================================================================================
 
 __global__ void __launch_bounds__(256) begin_kernel(SeqState *state, const Cmd *cmd, const float *emb, float *x, int dim,
-                                                    int vocab, int seq_len, int gather, int x_reps, int x_stride, unsigned int *epoch)
+                                                    int vocab, int seq_len, int gather, int x_reps, int x_stride, unsigned int *epoch,
+                                                    const StageLink *link)
 {
     __shared__ int s_tok;
+    __shared__ const float *s_xsrc;
     pdl_launch_dependents();
     pdl_wait();
     if (threadIdx.x == 0) {
         int tok, pos;
+        const int cflags = __ldcg(&cmd->flags);
         if (__ldcg(&cmd->mode) == 1) {
             tok = __ldcg(&cmd->token);
             pos = __ldcg(&cmd->pos);
         } else {
-            tok = __ldcg(&state->token);
+            // greedy loop; over a layer split the chosen token lives on the last stage's device
+            tok = (cflags & kCmdTokenFromPeer)
+                      ? __ldcg(reinterpret_cast<const int *>(__ldcg(reinterpret_cast<const unsigned long long *>(&link->token_src))))
+                      : __ldcg(&state->token);
             pos = __ldcg(&state->pos);
+            if (cflags & kCmdAdvancePos)
+                state->pos = pos + 1;
         }
+        s_xsrc = (cflags & kCmdXFromPeer)
+                     ? reinterpret_cast<const float *>(__ldcg(reinterpret_cast<const unsigned long long *>(&link->x_src)))
+                     : nullptr;
         int st = 0;
         if (pos < 0 || pos >= seq_len) {
             st |= L2J_DS_BAD_POS;
@@ -1087,17 +1108,21 @@ __global__ void __launch_bounds__(256) begin_kernel(SeqState *state, const Cmd *
                 reinterpret_cast<float4 *>(x + (int64_t)r * x_stride)[i] = v;
         }
     } else {
-        // a later pipeline stage: the caller put x into copy 0, spread it to the other copies
+        // a later stage of a layer split: x comes from the previous stage, either read here from that
+        // stage's device over the peer link (Run.java:368-413 without the host array) or put into copy 0
+        // by the caller
+        const float *src = s_xsrc ? s_xsrc : x;
         for (int i = threadIdx.x; i < dim / 4; i += blockDim.x) {
-            const float4 v = __ldcg(reinterpret_cast<const float4 *>(x) + i);
-            for (int r = 1; r < x_reps; ++r)
+            const float4 v = __ldcg(reinterpret_cast<const float4 *>(src) + i);
+            for (int r = s_xsrc ? 0 : 1; r < x_reps; ++r)
                 reinterpret_cast<float4 *>(x + (int64_t)r * x_stride)[i] = v;
         }
     }
 }
 
 cudaError_t launch_begin(const LaunchCfg &lc, SeqState *state, const Cmd *cmd, const float *emb, float *x, int dim,
-                         int vocab, int seq_len, int gather, int x_reps, int x_stride, unsigned int *epoch)
+                         int vocab, int seq_len, int gather, int x_reps, int x_stride, unsigned int *epoch,
+                         const StageLink *link)
 {
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(1);
@@ -1109,7 +1134,7 @@ cudaError_t launch_begin(const LaunchCfg &lc, SeqState *state, const Cmd *cmd, c
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = lc.pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, begin_kernel, state, cmd, emb, x, dim, vocab, seq_len, gather, x_reps, x_stride, epoch);
+    return cudaLaunchKernelEx(&cfg, begin_kernel, state, cmd, emb, x, dim, vocab, seq_len, gather, x_reps, x_stride, epoch, link);
 }
 
 // =============================================================================================

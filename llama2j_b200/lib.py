@@ -58,6 +58,9 @@ _SIGNATURES = {
     "l2j_forward_stage_async": (C.c_int, [_P, C.c_int, C.c_int]),
     "l2j_sync": (C.c_int, [_P]),
     "l2j_generate_greedy": (C.c_int, [_P, _P, C.c_int, C.c_int, _P]),
+    "l2j_pipeline_link": (C.c_int, [C.POINTER(_P), C.c_int]),
+    "l2j_pipeline_forward": (C.c_int, [C.POINTER(_P), C.c_int, C.c_int, C.c_int, _P, C.POINTER(C.c_int)]),
+    "l2j_pipeline_generate_greedy": (C.c_int, [C.POINTER(_P), C.c_int, _P, C.c_int, C.c_int, _P]),
     "l2j_reset": (C.c_int, [_P]),
     "l2j_get_stats": (C.c_int, [_P, C.POINTER(Stats)]),
     "l2j_launch_mode": (C.c_int, [_P]),

@@ -200,3 +200,53 @@ def run_greedy_host_loop(model: Transformer, prompt, steps: int, stop_on_bos: bo
             break
         token = nxt
     return np.asarray(chosen, dtype=np.int32), np.stack(all_logits) if all_logits else np.zeros((0, model.cfg.vocab_size))
+
+
+class LinkedStages:
+    """A layer split driven by one host thread, the reference's multi-GPU mode (Run.java:368-413,
+    Context.java:16-23): stage i is a Transformer on its own device holding a contiguous layer range,
+    and each stage reads x from the device of the stage in front over the peer link."""
+
+    def __init__(self, stages):
+        self.stages = list(stages)
+        if not self.stages:
+            raise ValueError("no stages")
+        self._lib = _lib.load()
+        self._arr = (C.c_void_p * len(self.stages))(*[s._ctx for s in self.stages])
+        rc = self._lib.l2j_pipeline_link(self._arr, len(self.stages))
+        _lib.check(rc, self.stages[0]._ctx)
+        self._logits = np.zeros(self.stages[0].cfg.vocab_size, dtype=np.float32)
+
+    @classmethod
+    def from_allocation(cls, cfg: ModelConfig, first_layers, last_layers, tensors: dict, devices=None, flags: int = 0):
+        """One stage per (first, last) layer range, e.g. the ranges LayerAllocation computes from --gpuMem."""
+        devices = list(range(len(first_layers))) if devices is None else list(devices)
+        stages = []
+        for dev, a, b in zip(devices, first_layers, last_layers):
+            t = Transformer(cfg, device=dev, first_layer=a, last_layer=b, flags=flags)
+            t.upload_all(tensors)
+            t.finalize()
+            stages.append(t)
+        return cls(stages)
+
+    def forward(self, token: int, pos: int, want_logits: bool = True):
+        am = C.c_int(-1)
+        ptr = self._logits.ctypes.data if want_logits else None
+        rc = self._lib.l2j_pipeline_forward(self._arr, len(self.stages), int(token), int(pos), ptr, C.byref(am))
+        _lib.check(rc, self.stages[0]._ctx)
+        return (self._logits if want_logits else None), am.value
+
+    def generate_greedy(self, prompt, steps: int) -> np.ndarray:
+        prompt = np.ascontiguousarray(prompt, dtype=np.int32).reshape(-1)
+        out = np.zeros(steps, dtype=np.int32)
+        rc = self._lib.l2j_pipeline_generate_greedy(self._arr, len(self.stages), prompt.ctypes.data if prompt.size else None,
+                                                    int(prompt.size), int(steps), out.ctypes.data)
+        _lib.check(rc, self.stages[0]._ctx)
+        return out
+
+    def last_generate_us(self) -> float:
+        return self.stages[0].last_generate_us()
+
+    def close(self) -> None:
+        for s in self.stages:
+            s.close()
