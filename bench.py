@@ -350,7 +350,7 @@ def main() -> None:
         "vs_baseline": value / (PUBLISHED_TOK_S * world), "dtype": "f32 activations x u8 group-quantised weights",
         "data": "synthetic",
         "config": {"workload": workload_name(args.shape), "parallelism": f"replicas x{world}",
-                   "l2": "inputs larger than L2: 7.2 GB of weights are streamed per forward",
+                   "l2": "inputs larger than L2: %.1f GB of weights are streamed per forward" % (bytes_per_token(cfg, 0)["total"] / 1e9),
                    "baseline_note": "vs_baseline divides by the reference's published 20.9 tok/s per RTX 4090 (README.md:46)",
                    "launch": mode, "tokens_agree_host_vs_device_loop": tokens_agree},
         "clocks": clocks, "roofline": roofline,

@@ -24,8 +24,12 @@ constexpr int kCmdRing = 256;
 
 struct LayerLaunch {
     MvParams qkv, wo, w13, w2;
-    AttnParams attn;
+    AttnParams attn;        // short contexts: the blocks of a head are a cluster (latency matters)
+    AttnParams attn_long;   // long contexts: no cluster, two blocks per SM everywhere (bandwidth matters)
 };
+
+// From this position on a forward uses the long-context attention launch.
+constexpr int kLongContextPos = 768;
 
 }  // namespace
 
@@ -84,8 +88,8 @@ struct l2j_ctx {
     MvParams cls{};
     bool finalized = false;
     bool pdl_on = false;
-    cudaGraph_t graph = nullptr;
-    cudaGraphExec_t exec = nullptr;
+    cudaGraph_t graph = nullptr, graph_long = nullptr;
+    cudaGraphExec_t exec = nullptr, exec_long = nullptr;   // one captured forward per attention regime
     int kernels_per_forward = 0;
     int64_t forwards = 0;
     int32_t status_accum = 0;
@@ -328,6 +332,7 @@ void build_launch_params(l2j_ctx *c)
         t.timeout_us = 50000;
         t.trace = c->trace ? c->trace + (int64_t)(4 * c->nl + 1 + li) * c->ring_grid * 16 : nullptr;
         t.trace_blocks = c->ring_grid;
+        t.smem_pad = 0;
 
         // x += Wo att                                          (Run.java:483-485)
         MvParams &o = L.wo;
@@ -420,6 +425,12 @@ void build_launch_params(l2j_ctx *c)
         k.trace = c->trace ? c->trace + (int64_t)(4 * c->nl) * c->ring_grid * 16 : nullptr;
     }
     link_chain(c);
+    for (int li = 0; li < c->nl; ++li) {
+        LayerLaunch &L = c->layers[(size_t)li];
+        L.attn_long = L.attn;          // same grid and hand-over counters
+        L.attn_long.cluster = 0;
+        L.attn_long.smem_pad = 1;
+    }
 }
 
 // A kernel launched on its own (timing, tracing) must neither wait on nor bump the hand-over counters.
@@ -431,7 +442,7 @@ P unchained(P p)
 }
 
 // Enqueues the kernels of one forward of this context's layer range on its stream.
-cudaError_t enqueue_forward(l2j_ctx *c, bool pdl, int *n_kernels)
+cudaError_t enqueue_forward(l2j_ctx *c, bool pdl, int *n_kernels, bool long_ctx)
 {
     cudaError_t e;
     int nk = 0;
@@ -452,7 +463,7 @@ cudaError_t enqueue_forward(l2j_ctx *c, bool pdl, int *n_kernels)
             LaunchCfg first = lc;
             first.pdl = lc.pdl && li > 0;
             if ((e = launch_matvec_ring(first, c->plan_qkv, false, L.qkv)) != cudaSuccess) return e;
-            if ((e = launch_attention(lc, L.attn)) != cudaSuccess) return e;
+            if ((e = launch_attention(lc, long_ctx ? L.attn_long : L.attn)) != cudaSuccess) return e;
             if ((e = launch_matvec_ring(lc, c->plan_wo, false, L.wo)) != cudaSuccess) return e;
             if ((e = launch_matvec_ring(lc, c->plan_w13, false, L.w13)) != cudaSuccess) return e;
             if ((e = launch_matvec_ring(lc, c->plan_hidden, false, L.w2)) != cudaSuccess) return e;
@@ -492,7 +503,7 @@ cudaError_t enqueue_forward(l2j_ctx *c, bool pdl, int *n_kernels)
     return cudaSuccess;
 }
 
-bool try_capture(l2j_ctx *c, bool pdl)
+bool try_capture(l2j_ctx *c, bool pdl, bool long_ctx)
 {
     cudaGraph_t g = nullptr;
     if (cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
@@ -500,7 +511,7 @@ bool try_capture(l2j_ctx *c, bool pdl)
         return false;
     }
     int nk = 0;
-    cudaError_t e = enqueue_forward(c, pdl, &nk);
+    cudaError_t e = enqueue_forward(c, pdl, &nk, long_ctx);
     cudaError_t e2 = cudaStreamEndCapture(c->stream, &g);
     if (e != cudaSuccess || e2 != cudaSuccess || !g) {
         if (g)
@@ -514,19 +525,23 @@ bool try_capture(l2j_ctx *c, bool pdl)
         cudaGetLastError();
         return false;
     }
-    c->graph = g;
-    c->exec = ex;
+    (long_ctx ? c->graph_long : c->graph) = g;
+    (long_ctx ? c->exec_long : c->exec) = ex;
     c->kernels_per_forward = nk;
     return true;
 }
 
-int launch_forward(l2j_ctx *c)
+// `pos` is the position of the forward being launched (the host always knows it: it is an argument, or the
+// step number of a greedy loop); it selects the attention regime.
+int launch_forward(l2j_ctx *c, int pos)
 {
-    if (c->exec) {
-        CK(c, cudaGraphLaunch(c->exec, c->stream));
+    const bool long_ctx = c->use_ring && pos >= kLongContextPos;
+    cudaGraphExec_t ex = long_ctx ? c->exec_long : c->exec;
+    if (ex) {
+        CK(c, cudaGraphLaunch(ex, c->stream));
     } else {
         int nk = 0;
-        CK(c, enqueue_forward(c, c->pdl_on, &nk));
+        CK(c, enqueue_forward(c, c->pdl_on, &nk, long_ctx));
         c->kernels_per_forward = nk;
     }
     c->forwards++;
@@ -772,6 +787,10 @@ extern "C" void l2j_destroy(l2j_ctx *c)
         cudaStreamSynchronize(c->stream);
     if (c->exec)
         cudaGraphExecDestroy(c->exec);
+    if (c->exec_long)
+        cudaGraphExecDestroy(c->exec_long);
+    if (c->graph_long)
+        cudaGraphDestroy(c->graph_long);
     if (c->graph)
         cudaGraphDestroy(c->graph);
     for (void *p : c->allocs)
@@ -966,12 +985,14 @@ extern "C" int l2j_finalize(l2j_ctx *c)
     }
     c->pdl_on = c->use_ring && !(c->flags & L2J_F_NO_PDL);
     if (!(c->flags & L2J_F_NO_GRAPH)) {
-        if (!try_capture(c, c->pdl_on)) {
+        if (!try_capture(c, c->pdl_on, false)) {
             if (c->pdl_on) {
                 c->pdl_on = false;
-                try_capture(c, false);
+                try_capture(c, false, false);
             }
         }
+        if (c->exec && c->use_ring && c->cfg.seq_len > kLongContextPos)
+            try_capture(c, c->pdl_on, true);   // without it the long regime is enqueued kernel by kernel
     }
     c->finalized = true;
     return L2J_OK;
@@ -994,7 +1015,7 @@ extern "C" int l2j_forward_stage_async(l2j_ctx *c, int token, int pos)
     rc = post_cmd(c, 1, c->is_first ? token : 0, pos);
     if (rc != L2J_OK)
         return rc;
-    return launch_forward(c);
+    return launch_forward(c, pos);
 }
 
 extern "C" int l2j_sync(l2j_ctx *c)
@@ -1029,7 +1050,7 @@ extern "C" int l2j_forward_stage(l2j_ctx *c, int token, int pos, const float *x_
     rc = post_cmd(c, 1, c->is_first ? token : 0, pos);
     if (rc != L2J_OK)
         return rc;
-    rc = launch_forward(c);
+    rc = launch_forward(c, pos);
     if (rc != L2J_OK)
         return rc;
     if (c->is_last && logits)
@@ -1097,7 +1118,7 @@ extern "C" int l2j_generate_greedy(l2j_ctx *c, const int32_t *prompt, int n_prom
         return rc;
     CK(c, cudaEventRecord(c->ev0, c->stream));
     for (int s = 0; s < steps; ++s) {
-        rc = launch_forward(c);
+        rc = launch_forward(c, s);
         if (rc != L2J_OK)
             return rc;
     }
@@ -1140,13 +1161,13 @@ int check_stages(l2j_ctx *const *stages, int n)
 
 // Stage i's stream waits for stage i-1's step, then runs its own; the hand-off itself is the peer read
 // in the stage's begin kernel.
-int enqueue_stage(l2j_ctx *const *stages, int n, int i)
+int enqueue_stage(l2j_ctx *const *stages, int n, int i, int pos)
 {
     l2j_ctx *c = stages[i];
     CK(c, cudaSetDevice(c->device));
     if (n > 1)
         CK(c, cudaStreamWaitEvent(c->stream, stages[(i + n - 1) % n]->ev_stage, 0));
-    int rc = launch_forward(c);
+    int rc = launch_forward(c, pos);
     if (rc != L2J_OK)
         return rc;
     CK(c, cudaEventRecord(c->ev_stage, c->stream));
@@ -1204,7 +1225,7 @@ extern "C" int l2j_pipeline_forward(l2j_ctx *const *stages, int n_stages, int to
             return rc;
         if (i > 0)
             CK(c, cudaStreamWaitEvent(c->stream, stages[i - 1]->ev_stage, 0));
-        rc = launch_forward(c);
+        rc = launch_forward(c, pos);
         if (rc != L2J_OK)
             return rc;
         CK(c, cudaEventRecord(c->ev_stage, c->stream));
@@ -1271,7 +1292,7 @@ extern "C" int l2j_pipeline_generate_greedy(l2j_ctx *const *stages, int n_stages
     for (int s = 0; s < steps; ++s)
         for (int i = 0; i < n_stages; ++i) {
             // step s of stage 0 waits for step s-1 of the last stage: it reads the chosen token there
-            rc = enqueue_stage(stages, n_stages, i);
+            rc = enqueue_stage(stages, n_stages, i, s);
             if (rc != L2J_OK)
                 return rc;
         }
@@ -1373,7 +1394,7 @@ extern "C" int l2j_time_kernels(l2j_ctx *c, int pos, int reps, double *us)
                     cudaError_t e = cudaSuccess;
                     switch (kind) {
                     case 0: e = launch_matvec_ring(lc, c->plan_qkv, false, unchained(L.qkv)); break;
-                    case 1: e = launch_attention(lc, unchained(L.attn)); break;
+                    case 1: e = launch_attention(lc, unchained(pos >= kLongContextPos ? L.attn_long : L.attn)); break;
                     case 2: e = launch_matvec_ring(lc, c->plan_wo, false, unchained(L.wo)); break;
                     case 3: e = launch_matvec_ring(lc, c->plan_w13, false, unchained(L.w13)); break;
                     case 4: e = launch_matvec_ring(lc, c->plan_hidden, false, unchained(L.w2)); break;

@@ -154,6 +154,9 @@ struct AttnParams {
                              // their partial results through distributed shared memory instead of `part`
     ChainLink chain;
     int timeout_us;          // bound of the wait on the hand-over counter
+    int smem_pad;            // 1: ask for so much shared memory that only two blocks fit an SM; under programmatic
+                             // dependent launch blocks are placed on whichever SMs drain first, and three per SM
+                             // would leave a third of the GPU without a stream of its own
     unsigned long long *trace;   // optional timeline of the first trace_blocks blocks (16 slots each), else nullptr
     int trace_blocks;
 };

@@ -1035,9 +1035,13 @@ static cudaError_t prepare_ring_t()
 
 // Opts the ring kernels of the current device into their dynamic shared memory size.  Call once
 // per device before the first launch (and outside stream capture).
+static cudaError_t prepare_attention();
+
 cudaError_t prepare_kernels()
 {
     cudaError_t e;
+    if ((e = prepare_attention()) != cudaSuccess)
+        return e;
 #define X(F, G, C, R) if ((e = prepare_ring_t<F, G, C, R>()) != cudaSuccess) return e;
     L2J_RING_VARIANTS(X)
 #undef X
@@ -1149,6 +1153,7 @@ cudaError_t launch_begin(const LaunchCfg &lc, SeqState *state, const Cmd *cmd, c
 
 constexpr int kAttnThreads = 256;
 constexpr int kAttnWarps = kAttnThreads / 32;
+constexpr size_t kAttnPadSmem = 80 * 1024;   // more than a third of an SM's shared memory
 constexpr int kAttnMinChunk = 32;   // positions per block before the work is split further: one round of loads
 
 // Streams positions [t0, t0 + cnt) of head h and merges the block's lane groups: afterwards thread
@@ -1199,19 +1204,29 @@ __device__ __forceinline__ void attention_block(const AttnParams &p, int h, int 
 
     float m = -INFINITY, l = 0.f;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int ib = 0; ib < cnt; ib += 4 * nslots) {   // uniform trip count for the whole block
+    // rows of the first round that could not be fetched early (the newest position)
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const int i0 = u * nslots + slot;
+        if (active && i0 < cnt && t0 + i0 >= pos) {
+            kk[u] = __ldcg(reinterpret_cast<const float4 *>(kb + (int64_t)i0 * head + 4 * li));
+            vv[u] = __ldcg(reinterpret_cast<const float4 *>(vb + (int64_t)i0 * head + 4 * li));
+        }
+    }
+    const int step = 4 * nslots;
+    for (int ib = 0; ib < cnt; ib += step) {   // uniform trip count for the whole block
+        // the next round's rows are requested before this round's arithmetic: two rounds in flight per warp
+        float4 kn[4], vn[4];
         int idx[4];
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
             idx[u] = ib + u * nslots + slot;
-            const bool preloaded = ib == 0 && t0 + idx[u] < pos;
-            if (!preloaded) {
-                kk[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-                vv[u] = kk[u];
-                if (active && idx[u] < cnt) {
-                    kk[u] = __ldcg(reinterpret_cast<const float4 *>(kb + (int64_t)idx[u] * head + 4 * li));
-                    vv[u] = __ldcg(reinterpret_cast<const float4 *>(vb + (int64_t)idx[u] * head + 4 * li));
-                }
+            const int nx = idx[u] + step;
+            kn[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            vn[u] = kn[u];
+            if (active && nx < cnt) {
+                kn[u] = __ldcg(reinterpret_cast<const float4 *>(kb + (int64_t)nx * head + 4 * li));
+                vn[u] = __ldcg(reinterpret_cast<const float4 *>(vb + (int64_t)nx * head + 4 * li));
             }
         }
         float s[4];
@@ -1242,6 +1257,11 @@ __device__ __forceinline__ void attention_block(const AttnParams &p, int h, int 
                 acc.w = fmaf(pw, vv[u].w, acc.w);
             }
             m = mn;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            kk[u] = kn[u];
+            vv[u] = vn[u];
         }
     }
     if (tr)
@@ -1287,7 +1307,7 @@ __device__ __forceinline__ void attention_signal(const AttnParams &p)
     }
 }
 
-__global__ void __launch_bounds__(kAttnThreads) attention_kernel(const __grid_constant__ AttnParams p)
+__global__ void __launch_bounds__(kAttnThreads, 3) attention_kernel(const __grid_constant__ AttnParams p)
 {
     extern __shared__ __align__(16) float asmem[];   // [slots][head + 4]: o, then m, l (16-byte aligned rows); [head + 4] block result
     __shared__ int s_last;
@@ -1429,6 +1449,11 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const __grid_co
     attention_signal(p);
 }
 
+static cudaError_t prepare_attention()
+{
+    return cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAttnPadSmem);
+}
+
 cudaError_t launch_attention(const LaunchCfg &lc, const AttnParams &p)
 {
     int gw = 1;
@@ -1441,6 +1466,8 @@ cudaError_t launch_attention(const LaunchCfg &lc, const AttnParams &p)
     cfg.gridDim = dim3((unsigned)p.n_heads, (unsigned)p.nsplit);
     cfg.blockDim = dim3(kAttnThreads);
     cfg.dynamicSmemBytes = (size_t)(nslots + 1) * (p.head + 4) * sizeof(float);
+    if (p.smem_pad && cfg.dynamicSmemBytes < kAttnPadSmem)
+        cfg.dynamicSmemBytes = kAttnPadSmem;
     cfg.stream = lc.stream;
     cudaLaunchAttribute attr[2];
     int na = 0;
