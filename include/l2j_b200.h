@@ -180,6 +180,27 @@ L2J_API int l2j_pipeline_forward(l2j_ctx *const *stages, int n_stages, int token
 L2J_API int l2j_pipeline_generate_greedy(l2j_ctx *const *stages, int n_stages, const int32_t *prompt, int n_prompt, int steps,
                                          int32_t *out_tokens);
 
+/* ---- tensor-parallel group, one host thread (no counterpart in the reference) ---------------- */
+
+/* A context that holds every layer but works on rank `tp_rank`'s block of rows of each matrix
+ * (whole heads for Wq/Wk/Wv and the attention, hidden_dim / tp_size rows of W1/W3, dim / tp_size
+ * rows of Wo/W2); the classifier is replicated.  Each rank stores its results into every rank's
+ * copy of the output vector over the peer links, so the copies stay bitwise equal and equal to a
+ * single device's vectors.  Weights are uploaded to every rank with the usual calls.  n_heads,
+ * n_kv_heads and hidden_dim must divide by tp_size (at most 8).  The reference has no such mode
+ * (its multi-GPU mode is the layer split above). */
+L2J_API int l2j_create_tp(const l2j_config *cfg, int device, int tp_rank, int tp_size, uint32_t flags, l2j_ctx **ctx);
+
+/* Connects the finalized contexts of ranks 0..n-1, each on a device of its own with peer access to
+ * the others (kernels of different ranks wait for each other, with a time limit: they must not
+ * share a device). */
+L2J_API int l2j_tp_link(l2j_ctx *const *ranks, int n_ranks);
+
+/* l2j_forward / l2j_generate_greedy over a linked group; results are read from rank 0. */
+L2J_API int l2j_tp_forward(l2j_ctx *const *ranks, int n_ranks, int token, int pos, float *logits, int *argmax);
+L2J_API int l2j_tp_generate_greedy(l2j_ctx *const *ranks, int n_ranks, const int32_t *prompt, int n_prompt, int steps,
+                                   int32_t *out_tokens);
+
 /* Clears the KV cache position bookkeeping and the statistics (a new sequence). */
 L2J_API int l2j_reset(l2j_ctx *ctx);
 

@@ -77,6 +77,9 @@ struct l2j_ctx {
     Cmd *cmd_dev = nullptr;
     Cmd *cmd_host = nullptr;       // pinned ring
     StageLink *link_dev = nullptr; // peer pointers of a linked layer split (zero until linked)
+    int tp_rank = 0, tp_size = 1;  // tensor parallel group this context belongs to
+    TpTable *tp_dev = nullptr;     // the group's vectors and counters (n = 0 until linked)
+    bool tp_linked = false;
     cudaEvent_t ev_stage = nullptr;   // "this stage's step is done", waited for by the next stage's stream
     float *logits_host = nullptr;  // pinned
     float *x_host = nullptr;       // pinned
@@ -184,13 +187,18 @@ int choose_nsplit(int sm_count, int n_heads, int seq_len)
     return ns;
 }
 
-MvSeg make_seg(const QTensor &t, int64_t weight_index, int rows)
+// Rows [rank * rows / parts, (rank + 1) * rows / parts) of a matrix of `rows` rows of n elements that starts
+// at element weight_index of tensor t: the block of rows a tensor-parallel rank works on (all rows for
+// parts == 1).
+MvSeg make_seg(const QTensor &t, int64_t weight_index, int rows, int n = 0, int rank = 0, int parts = 1)
 {
     MvSeg s;
+    const int per = rows / parts;
     s.payload = t.payload;
     s.hdr = t.hdr;
-    s.flat0 = weight_index - t.base_float;
-    s.rows = rows;
+    s.flat0 = weight_index - t.base_float + (int64_t)rank * per * n;
+    s.rows = per;
+    s.out0 = rank * per;
     return s;
 }
 
@@ -208,20 +216,7 @@ void fill_plan(MvParams &p, const MvPlan &pl)
         const int rs = p.paired ? (pl.rt * pl.rpp) / 2 : pl.rt * pl.rpp;
         p.rs = rs;
         p.rowbytes = p.f32 ? p.n * 4 : p.n;
-        {
-            const char *e = getenv("L2J_PREFETCH_MB");
-            const double mb = e ? atof(e) : 0.0;
-            const int64_t stage_bytes = (int64_t)pl.rt * pl.rpp * p.rowbytes;
-            p.pf_distance = mb > 0 ? (int)((int64_t)(mb * 1048576.0) / stage_bytes) : 0;
-        }
-        {
-            const char *e = getenv("L2J_TAIL_PREFETCH");
-            p.tail_prefetch = e ? atoi(e) : 3;
-            const char *e2 = getenv("L2J_HEAD_PREFETCH");
-            p.head_prefetch = e2 ? atoi(e2) : 0;
-            const char *e3 = getenv("L2J_STATIC_SHARE");
-            p.static_share = e3 ? atoi(e3) : 0;
-        }
+        p.tail_prefetch = 3;
         p.total_stages = 0;
         const int nseg = p.paired ? 1 : p.nseg;
         for (int i = 0; i < 3; ++i) {
@@ -229,10 +224,6 @@ void fill_plan(MvParams &p, const MvPlan &pl)
             p.total_stages += p.seg_stages[i];
         }
     }
-    const char *pm = getenv("L2J_PDL_MODE");
-    p.pdl_mode = pm ? atoi(pm) : 0;
-    const char *pw = getenv("L2J_PRODUCER_WAIT");
-    p.producer_wait = pw ? atoi(pw) : 0;
 }
 
 constexpr int kChainStride = 32;   // unsigned ints between two hand-over counters (128 bytes)
@@ -243,16 +234,19 @@ void link_chain(l2j_ctx *c)
 {
     if (!c->use_ring || !c->chain_on)
         return;
-    const unsigned int ring_blocks = (unsigned int)c->ring_grid;
-    const unsigned int attn_blocks = (unsigned int)(c->cfg.n_heads * c->nsplit);
+    // in a tensor-parallel group every rank's blocks bump every rank's counters
+    const unsigned int ring_blocks = (unsigned int)(c->ring_grid * c->tp_size);
+    const unsigned int attn_blocks = (unsigned int)(c->cfg.n_heads / c->tp_size * c->nsplit * c->tp_size);
     const unsigned int *prev = nullptr;
     unsigned int prev_blocks = 0;
     int idx = 0;
     auto link = [&](ChainLink &ch, unsigned int blocks) {
         ch.wait_counter = prev;
         ch.wait_blocks = prev_blocks;
+        ch.done_off = kChainStride * idx;
         ch.done_counter = c->chain + (int64_t)kChainStride * idx++;
         ch.epoch = c->chain + (int64_t)kChainStride * (5 * c->nl + 1);
+        ch.tp = c->tp_size > 1 ? c->tp_dev : nullptr;
         prev = ch.done_counter;
         prev_blocks = blocks;
     };
@@ -291,9 +285,9 @@ void build_launch_params(l2j_ctx *c)
         // q, k, v = W(rmsnorm(x)); RoPE; KV append            (Run.java:418-446)
         MvParams &a = L.qkv;
         a = base;
-        a.seg[0] = make_seg(c->qt[L2J_T_WQ], l * dim * dim, dim);
-        a.seg[1] = make_seg(c->qt[L2J_T_WK], l * (int64_t)kv_dim * dim, kv_dim);
-        a.seg[2] = make_seg(c->qt[L2J_T_WV], l * (int64_t)kv_dim * dim, kv_dim);
+        a.seg[0] = make_seg(c->qt[L2J_T_WQ], l * dim * dim, dim, dim, c->tp_rank, c->tp_size);
+        a.seg[1] = make_seg(c->qt[L2J_T_WK], l * (int64_t)kv_dim * dim, kv_dim, dim, c->tp_rank, c->tp_size);
+        a.seg[2] = make_seg(c->qt[L2J_T_WV], l * (int64_t)kv_dim * dim, kv_dim, dim, c->tp_rank, c->tp_size);
         a.nseg = 3;
         a.paired = 0;
         a.n = dim;
@@ -333,11 +327,14 @@ void build_launch_params(l2j_ctx *c)
         t.trace = c->trace ? c->trace + (int64_t)(4 * c->nl + 1 + li) * c->ring_grid * 16 : nullptr;
         t.trace_blocks = c->ring_grid;
         t.smem_pad = 0;
+        t.tp = c->tp_size > 1 ? c->tp_dev : nullptr;
+        t.n_heads = c->cfg.n_heads / c->tp_size;   // the heads whose q rows this rank computed
+        t.h0 = c->tp_rank * t.n_heads;
 
         // x += Wo att                                          (Run.java:483-485)
         MvParams &o = L.wo;
         o = base;
-        o.seg[0] = make_seg(c->qt[L2J_T_WO], l * dim * dim, dim);
+        o.seg[0] = make_seg(c->qt[L2J_T_WO], l * dim * dim, dim, dim, c->tp_rank, c->tp_size);
         o.nseg = 1;
         o.n = dim;
         fill_plan(o, c->plan_wo);
@@ -346,6 +343,8 @@ void build_launch_params(l2j_ctx *c)
         o.x_stride = c->dim_stride;
         o.rms_w = nullptr;
         o.epilogue = EPI_RESIDUAL;
+        o.tp = c->tp_size > 1 ? c->tp_dev : nullptr;
+        o.tp_vec = TPV_X;
         o.y = c->x;
         o.y_reps = c->reps;
         o.y_stride = c->dim_stride;
@@ -355,8 +354,8 @@ void build_launch_params(l2j_ctx *c)
         // hb = silu(W1 rmsnorm(x)) * W3 rmsnorm(x)              (Run.java:490-502)
         MvParams &f = L.w13;
         f = base;
-        f.seg[0] = make_seg(c->qt[L2J_T_W1], l * (int64_t)hidden * dim, hidden);
-        f.seg[1] = make_seg(c->qt[L2J_T_W3], l * (int64_t)hidden * dim, hidden);
+        f.seg[0] = make_seg(c->qt[L2J_T_W1], l * (int64_t)hidden * dim, hidden, dim, c->tp_rank, c->tp_size);
+        f.seg[1] = make_seg(c->qt[L2J_T_W3], l * (int64_t)hidden * dim, hidden, dim, c->tp_rank, c->tp_size);
         f.nseg = 1;
         f.paired = 1;
         f.n = dim;
@@ -367,6 +366,8 @@ void build_launch_params(l2j_ctx *c)
         f.x_stride = c->dim_stride;
         f.rms_w = c->rms_ffn + (int64_t)li * c->reps * c->dim_stride;
         f.epilogue = EPI_SWIGLU;
+        f.tp = c->tp_size > 1 ? c->tp_dev : nullptr;
+        f.tp_vec = TPV_HB;
         f.y = c->hb;
         f.y_reps = c->reps;
         f.y_stride = c->hid_stride;
@@ -376,7 +377,7 @@ void build_launch_params(l2j_ctx *c)
         // x += W2 hb                                           (Run.java:505-508)
         MvParams &w = L.w2;
         w = base;
-        w.seg[0] = make_seg(c->qt[L2J_T_W2], l * (int64_t)hidden * dim, dim);
+        w.seg[0] = make_seg(c->qt[L2J_T_W2], l * (int64_t)hidden * dim, dim, hidden, c->tp_rank, c->tp_size);
         w.nseg = 1;
         w.n = hidden;
         fill_plan(w, c->plan_hidden);
@@ -386,6 +387,8 @@ void build_launch_params(l2j_ctx *c)
         w.x_stride = c->hid_stride;
         w.rms_w = nullptr;
         w.epilogue = EPI_RESIDUAL;
+        w.tp = c->tp_size > 1 ? c->tp_dev : nullptr;
+        w.tp_vec = TPV_X;
         w.y = c->x;
         w.y_reps = c->reps;
         w.y_stride = c->dim_stride;
@@ -583,11 +586,16 @@ int finish_status(l2j_ctx *c)
 // context
 // ===============================================================================================
 
-extern "C" int l2j_create(const l2j_config *cfg, int device, int first_layer, int last_layer, uint32_t flags, l2j_ctx **out)
+static int create_impl(const l2j_config *cfg, int device, int first_layer, int last_layer, uint32_t flags, int tp_rank,
+                       int tp_size, l2j_ctx **out)
 {
     if (!cfg || !out)
         return fail(nullptr, L2J_E_INVALID, "null argument");
     *out = nullptr;
+    if (tp_size < 1 || tp_size > kMaxTp || tp_rank < 0 || tp_rank >= tp_size)
+        return fail(nullptr, L2J_E_INVALID, "tensor-parallel rank %d of %d (at most %d ranks)", tp_rank, tp_size, kMaxTp);
+    if (tp_size > 1 && (flags & L2J_F_SIMPLE))
+        return fail(nullptr, L2J_E_INVALID, "the plain kernels have no tensor-parallel mode");
     if (cfg->dim <= 0 || cfg->hidden_dim <= 0 || cfg->n_layers <= 0 || cfg->n_heads <= 0 || cfg->n_kv_heads <= 0 ||
         cfg->vocab_size <= 0 || cfg->seq_len <= 0)
         return fail(nullptr, L2J_E_INVALID, "config fields must be positive");
@@ -600,6 +608,9 @@ extern "C" int l2j_create(const l2j_config *cfg, int device, int first_layer, in
         return fail(nullptr, L2J_E_INVALID, "dim must be a multiple of 4");
     if (first_layer < 0 || last_layer >= cfg->n_layers || first_layer > last_layer)
         return fail(nullptr, L2J_E_INVALID, "layer range [%d, %d] outside the model", first_layer, last_layer);
+    if (tp_size > 1 && (cfg->n_heads % tp_size != 0 || cfg->n_kv_heads % tp_size != 0 || cfg->hidden_dim % tp_size != 0 ||
+                        (cfg->dim / tp_size) % 2 != 0))
+        return fail(nullptr, L2J_E_INVALID, "heads, kv heads and hidden_dim must divide by the %d tensor-parallel ranks", tp_size);
     int ndev = 0;
     cudaError_t e = cudaGetDeviceCount(&ndev);
     if (e != cudaSuccess || ndev <= 0)
@@ -617,6 +628,8 @@ extern "C" int l2j_create(const l2j_config *cfg, int device, int first_layer, in
     c->last_layer = last_layer;
     c->nl = last_layer - first_layer + 1;
     c->flags = flags;
+    c->tp_rank = tp_rank;
+    c->tp_size = tp_size;
     c->is_first = first_layer == 0;
     c->is_last = last_layer == cfg->n_layers - 1;
     c->dim = cfg->dim;
@@ -757,16 +770,24 @@ extern "C" int l2j_create(const l2j_config *cfg, int device, int first_layer, in
     CREATE_CK(dev_alloc(c, &c->cmd_dev, 1, true));
     CREATE_CUDA(cudaHostAlloc((void **)&c->cmd_host, sizeof(Cmd) * kCmdRing, cudaHostAllocDefault));
     CREATE_CK(dev_alloc(c, &c->link_dev, 1, true));
+    CREATE_CK(dev_alloc(c, &c->tp_dev, 1, true));
     CREATE_CUDA(cudaEventCreateWithFlags(&c->ev_stage, cudaEventDisableTiming));
     CREATE_CUDA(cudaHostAlloc((void **)&c->logits_host, sizeof(float) * (size_t)cfg->vocab_size, cudaHostAllocDefault));
     CREATE_CUDA(cudaHostAlloc((void **)&c->x_host, sizeof(float) * (size_t)c->reps * c->dim_stride, cudaHostAllocDefault));
     CREATE_CUDA(cudaHostAlloc((void **)&c->state_host, sizeof(SeqState), cudaHostAllocDefault));
     memset(c->state_host, 0, sizeof(SeqState));
 
-    c->plan_qkv = plan_matvec(c->dim, false, false, 0, 0, 2);   // RoPE works on row pairs: stages of an even number of rows
-    c->plan_wo = plan_matvec(c->dim, false, false, c->dim, c->ring_grid);
-    c->plan_w13 = plan_matvec(c->dim, false, true);
-    c->plan_hidden = plan_matvec(c->hidden, false, false);
+    if (tp_size == 1) {
+        c->plan_qkv = plan_matvec(c->dim, false, false, 0, 0, 2);   // RoPE works on row pairs: stages of an even number of rows
+        c->plan_wo = plan_matvec(c->dim, false, false, c->dim, c->ring_grid);
+        c->plan_w13 = plan_matvec(c->dim, false, true);
+        c->plan_hidden = plan_matvec(c->hidden, false, false);
+    } else {   // a rank's block of rows is small: let the planner shrink the stages
+        c->plan_qkv = plan_matvec(c->dim, false, false, c->dim / tp_size, c->ring_grid, 2);
+        c->plan_wo = plan_matvec(c->dim, false, false, c->dim / tp_size, c->ring_grid);
+        c->plan_w13 = plan_matvec(c->dim, false, true, 2 * (c->hidden / tp_size), c->ring_grid);
+        c->plan_hidden = plan_matvec(c->hidden, false, false, c->dim / tp_size, c->ring_grid);
+    }
     c->plan_cls = plan_matvec(c->dim, true, false);
     c->use_ring = !(flags & L2J_F_SIMPLE) && c->plan_qkv.ok && c->plan_wo.ok && c->plan_w13.ok && c->plan_hidden.ok &&
                   c->plan_cls.ok && (head % 2 == 0);
@@ -776,6 +797,18 @@ extern "C" int l2j_create(const l2j_config *cfg, int device, int first_layer, in
 #undef CREATE_CUDA
     *out = c;
     return L2J_OK;
+}
+
+extern "C" int l2j_create(const l2j_config *cfg, int device, int first_layer, int last_layer, uint32_t flags, l2j_ctx **out)
+{
+    return create_impl(cfg, device, first_layer, last_layer, flags, 0, 1, out);
+}
+
+extern "C" int l2j_create_tp(const l2j_config *cfg, int device, int tp_rank, int tp_size, uint32_t flags, l2j_ctx **out)
+{
+    if (!cfg)
+        return fail(nullptr, L2J_E_INVALID, "null argument");
+    return create_impl(cfg, device, 0, cfg->n_layers - 1, flags, tp_rank, tp_size, out);
 }
 
 extern "C" void l2j_destroy(l2j_ctx *c)
@@ -1008,6 +1041,8 @@ extern "C" int l2j_forward_stage_async(l2j_ctx *c, int token, int pos)
         return L2J_E_INVALID;
     if (!c->finalized)
         return fail(c, L2J_E_STATE, "forward before finalize");
+    if (c->tp_size > 1)
+        return fail(c, L2J_E_STATE, "a rank of a tensor-parallel group runs through l2j_tp_forward");
     int rc = check_range(c, token, pos, c->is_first);
     if (rc != L2J_OK)
         return rc;
@@ -1035,6 +1070,8 @@ extern "C" int l2j_forward_stage(l2j_ctx *c, int token, int pos, const float *x_
     std::lock_guard<std::mutex> lock(c->mu);
     if (!c->finalized)
         return fail(c, L2J_E_STATE, "forward before finalize");
+    if (c->tp_size > 1)
+        return fail(c, L2J_E_STATE, "a rank of a tensor-parallel group runs through l2j_tp_forward");
     if (!c->is_first && !x_in)
         return fail(c, L2J_E_INVALID, "a stage that does not start at layer 0 needs x_in");
     int rc = check_range(c, token, pos, c->is_first);
@@ -1096,8 +1133,8 @@ extern "C" int l2j_generate_greedy(l2j_ctx *c, const int32_t *prompt, int n_prom
     std::lock_guard<std::mutex> lock(c->mu);
     if (!c->finalized)
         return fail(c, L2J_E_STATE, "generate before finalize");
-    if (!(c->is_first && c->is_last))
-        return fail(c, L2J_E_STATE, "l2j_generate_greedy needs a context that holds every layer");
+    if (!(c->is_first && c->is_last) || c->tp_size > 1)
+        return fail(c, L2J_E_STATE, "l2j_generate_greedy needs a context that holds every layer and all rows");
     if (steps <= 0 || steps > c->cfg.seq_len || n_prompt < 0 || n_prompt > c->cfg.seq_len || (n_prompt > 0 && !prompt) ||
         !out_tokens)
         return fail(c, L2J_E_INVALID, "bad arguments: steps %d (seq_len %d), n_prompt %d", steps, c->cfg.seq_len, n_prompt);
@@ -1317,6 +1354,190 @@ extern "C" int l2j_pipeline_generate_greedy(l2j_ctx *const *stages, int n_stages
     CK(cl, cudaMemcpy(out_tokens, cl->out_tokens_dev, sizeof(int32_t) * (size_t)steps, cudaMemcpyDeviceToHost));
     float ms = 0.f;
     CK(c0, cudaSetDevice(c0->device));
+    CK(c0, cudaEventElapsedTime(&ms, c0->ev0, c0->ev1));
+    c0->last_generate_us = (double)ms * 1000.0;
+    return status;
+}
+
+// ===============================================================================================
+// tensor-parallel group driven by one host thread
+// ===============================================================================================
+
+namespace {
+
+int check_tp_group(l2j_ctx *const *ranks, int n, bool need_link)
+{
+    if (!ranks || n <= 0 || n > kMaxTp)
+        return L2J_E_INVALID;
+    for (int i = 0; i < n; ++i)
+        if (!ranks[i])
+            return L2J_E_INVALID;
+    l2j_ctx *c0 = ranks[0];
+    for (int i = 0; i < n; ++i) {
+        l2j_ctx *c = ranks[i];
+        if (!c->finalized)
+            return fail(c0, L2J_E_STATE, "rank %d is not finalized", i);
+        if (memcmp(&c->cfg, &c0->cfg, sizeof(l2j_config)) != 0)
+            return fail(c0, L2J_E_INVALID, "rank %d was created for another model", i);
+        if (c->tp_size != n || c->tp_rank != i || !(c->is_first && c->is_last))
+            return fail(c0, L2J_E_INVALID, "context %d is rank %d of %d, expected rank %d of %d", i, c->tp_rank, c->tp_size, i, n);
+        if (!c->use_ring || !c->chain_on)
+            return fail(c0, L2J_E_STATE, "a tensor-parallel group needs the ring kernels and the hand-over counters");
+        for (int j = 0; j < i; ++j)
+            if (ranks[j]->device == c->device)
+                return fail(c0, L2J_E_INVALID, "ranks %d and %d share device %d: kernels that wait for each other need a device each",
+                            j, i, c->device);
+        if (need_link && n > 1 && !c->tp_linked)
+            return fail(c0, L2J_E_STATE, "the group is not linked (l2j_tp_link)");
+    }
+    return L2J_OK;
+}
+
+}  // namespace
+
+extern "C" int l2j_tp_link(l2j_ctx *const *ranks, int n_ranks)
+{
+    int rc = check_tp_group(ranks, n_ranks, false);
+    if (rc != L2J_OK)
+        return rc;
+    for (int i = 0; i < n_ranks; ++i) {
+        l2j_ctx *c = ranks[i];
+        std::lock_guard<std::mutex> lock(c->mu);
+        CK(c, cudaSetDevice(c->device));
+        TpTable t{};
+        t.n = n_ranks;
+        t.rank = i;
+        for (int j = 0; j < n_ranks; ++j) {
+            l2j_ctx *o = ranks[j];
+            if (j != i) {
+                int can = 0;
+                CK(c, cudaDeviceCanAccessPeer(&can, c->device, o->device));
+                if (!can)
+                    return fail(ranks[0], L2J_E_STATE, "device %d cannot reach the memory of device %d", c->device, o->device);
+                cudaError_t e = cudaDeviceEnablePeerAccess(o->device, 0);
+                if (e == cudaErrorPeerAccessAlreadyEnabled)
+                    cudaGetLastError();
+                else
+                    CK(c, e);
+            }
+            t.vec[TPV_X][j] = o->x;
+            t.vec[TPV_XB][j] = o->xb;
+            t.vec[TPV_HB][j] = o->hb;
+            t.chain[j] = o->chain;
+        }
+        CK(c, cudaMemcpy(c->tp_dev, &t, sizeof(TpTable), cudaMemcpyHostToDevice));
+        CK(c, cudaDeviceSynchronize());
+        c->tp_linked = true;
+    }
+    return L2J_OK;
+}
+
+extern "C" int l2j_tp_forward(l2j_ctx *const *ranks, int n_ranks, int token, int pos, float *logits, int *argmax)
+{
+    int rc = check_tp_group(ranks, n_ranks, true);
+    if (rc != L2J_OK)
+        return rc;
+    rc = check_range(ranks[0], token, pos, true);
+    if (rc != L2J_OK)
+        return rc;
+    // every rank's kernels wait (bounded) for the other ranks' kernels: put all of them on their way first
+    for (int i = 0; i < n_ranks; ++i) {
+        l2j_ctx *c = ranks[i];
+        std::lock_guard<std::mutex> lock(c->mu);
+        CK(c, cudaSetDevice(c->device));
+        rc = post_cmd(c, 1, token, pos);
+        if (rc != L2J_OK)
+            return rc;
+    }
+    for (int i = 0; i < n_ranks; ++i) {
+        l2j_ctx *c = ranks[i];
+        CK(c, cudaSetDevice(c->device));
+        rc = launch_forward(c, pos);
+        if (rc != L2J_OK)
+            return rc;
+    }
+    int status = L2J_OK;
+    for (int i = 0; i < n_ranks; ++i) {
+        l2j_ctx *c = ranks[i];
+        CK(c, cudaSetDevice(c->device));
+        if (i == 0 && logits)
+            CK(c, cudaMemcpyAsync(c->logits_host, c->logits, sizeof(float) * (size_t)c->cfg.vocab_size, cudaMemcpyDeviceToHost,
+                                  c->stream));
+        CK(c, cudaMemcpyAsync(c->state_host, c->state, sizeof(SeqState), cudaMemcpyDeviceToHost, c->stream));
+        CK(c, cudaStreamSynchronize(c->stream));
+        if (i == 0 && logits)
+            memcpy(logits, c->logits_host, sizeof(float) * (size_t)c->cfg.vocab_size);
+        if (i == 0 && argmax)
+            *argmax = c->state_host->argmax;
+        const int r = finish_status(c);
+        if (r != L2J_OK && status == L2J_OK) {
+            status = r;
+            if (c != ranks[0])
+                fail(ranks[0], r, "rank %d: %s", i, c->err.c_str());
+        }
+    }
+    return status;
+}
+
+extern "C" int l2j_tp_generate_greedy(l2j_ctx *const *ranks, int n_ranks, const int32_t *prompt, int n_prompt, int steps,
+                                      int32_t *out_tokens)
+{
+    int rc = check_tp_group(ranks, n_ranks, true);
+    if (rc != L2J_OK)
+        return rc;
+    l2j_ctx *c0 = ranks[0];
+    if (steps <= 0 || steps > c0->cfg.seq_len || n_prompt < 0 || n_prompt > c0->cfg.seq_len || (n_prompt > 0 && !prompt) ||
+        !out_tokens)
+        return fail(c0, L2J_E_INVALID, "bad arguments: steps %d (seq_len %d), n_prompt %d", steps, c0->cfg.seq_len, n_prompt);
+    for (int i = 0; i < n_prompt; ++i)
+        if (prompt[i] < 0 || prompt[i] >= c0->cfg.vocab_size)
+            return fail(c0, L2J_E_INVALID, "prompt token %d outside the vocabulary", prompt[i]);
+    // every rank runs the whole greedy loop on its own device: the classifier is replicated, so all ranks
+    // choose the same token from bitwise equal logits
+    for (int i = 0; i < n_ranks; ++i) {
+        l2j_ctx *c = ranks[i];
+        std::lock_guard<std::mutex> lock(c->mu);
+        CK(c, cudaSetDevice(c->device));
+        if (n_prompt > 0)
+            CK(c, cudaMemcpyAsync(c->prompt_dev, prompt, sizeof(int32_t) * (size_t)n_prompt, cudaMemcpyHostToDevice, c->stream));
+        SeqState init{};
+        init.token = 1;   // BOS, Run.java:614
+        init.pos = 0;
+        init.n_prompt = n_prompt;
+        CK(c, cudaMemcpyAsync(c->state, &init, sizeof(SeqState), cudaMemcpyHostToDevice, c->stream));
+        rc = post_cmd(c, 0, 0, 0);
+        if (rc != L2J_OK)
+            return rc;
+        CK(c, cudaStreamSynchronize(c->stream));
+    }
+    CK(c0, cudaSetDevice(c0->device));
+    CK(c0, cudaEventRecord(c0->ev0, c0->stream));
+    for (int s = 0; s < steps; ++s)
+        for (int i = 0; i < n_ranks; ++i) {
+            l2j_ctx *c = ranks[i];
+            CK(c, cudaSetDevice(c->device));
+            rc = launch_forward(c, s);
+            if (rc != L2J_OK)
+                return rc;
+        }
+    CK(c0, cudaSetDevice(c0->device));
+    CK(c0, cudaEventRecord(c0->ev1, c0->stream));
+    int status = L2J_OK;
+    for (int i = 0; i < n_ranks; ++i) {
+        l2j_ctx *c = ranks[i];
+        CK(c, cudaSetDevice(c->device));
+        CK(c, cudaMemcpyAsync(c->state_host, c->state, sizeof(SeqState), cudaMemcpyDeviceToHost, c->stream));
+        CK(c, cudaStreamSynchronize(c->stream));
+        const int r = finish_status(c);
+        if (r != L2J_OK && status == L2J_OK) {
+            status = r;
+            if (c != c0)
+                fail(c0, r, "rank %d: %s", i, c->err.c_str());
+        }
+    }
+    CK(c0, cudaSetDevice(c0->device));
+    CK(c0, cudaMemcpy(out_tokens, c0->out_tokens_dev, sizeof(int32_t) * (size_t)steps, cudaMemcpyDeviceToHost));
+    float ms = 0.f;
     CK(c0, cudaEventElapsedTime(&ms, c0->ev0, c0->ev1));
     c0->last_generate_us = (double)ms * 1000.0;
     return status;

@@ -141,15 +141,28 @@ __device__ __forceinline__ void red_release_add_u32(unsigned int *p, unsigned in
     asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
+// The same at system scope, for counters that peers on other devices bump or poll.
+__device__ __forceinline__ unsigned int ld_acquire_sys_u32(const unsigned int *p)
+{
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ void red_release_sys_add_u32(unsigned int *p, unsigned int v)
+{
+    asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
 // Polls until the counter has reached `target` (wrap-around safe); gives up after timeout_ns and
 // returns false, so a lost predecessor can never hang the GPU.
-__device__ __forceinline__ bool counter_wait_bounded(const unsigned int *ctr, unsigned int target, uint64_t timeout_ns)
+__device__ __forceinline__ bool counter_wait_bounded(const unsigned int *ctr, unsigned int target, uint64_t timeout_ns, bool sys)
 {
-    if ((int)(ld_acquire_u32(ctr) - target) >= 0)
+    if ((int)((sys ? ld_acquire_sys_u32(ctr) : ld_acquire_u32(ctr)) - target) >= 0)
         return true;
     const uint64_t t0 = global_timer_ns();
     for (;;) {
-        if ((int)(ld_acquire_u32(ctr) - target) >= 0)
+        if ((int)((sys ? ld_acquire_sys_u32(ctr) : ld_acquire_u32(ctr)) - target) >= 0)
             return true;
         if (global_timer_ns() - t0 > timeout_ns)
             return false;

@@ -29,6 +29,8 @@ struct SeqState {
     unsigned int cls_counter;   // arrival counter of the classifier's argmax reduction
 };
 
+struct TpTable;
+
 // Hand-over between consecutive kernels of a forward.  Waiting for the grid in front to complete costs
 // microseconds after its last block has finished; instead every block bumps a counter once its results
 // are visible, and the blocks of the next kernel (already resident under programmatic dependent launch)
@@ -39,6 +41,8 @@ struct ChainLink {
     unsigned int wait_blocks;           // bumps per forward on that counter
     unsigned int *done_counter;         // counter this launch bumps once per block, or nullptr
     const unsigned int *epoch;          // forwards started on this context
+    const TpTable *tp;                  // tensor parallel: bump the counter at the same offset on every rank
+    int done_off;                       // offset of done_counter in the rank's counter array (unsigned ints)
 };
 
 struct Cmd {
@@ -82,8 +86,22 @@ struct MvParams;
 struct MvSeg {
     const uint8_t *payload;   // u8 payload, or the float rows for FP32 weights
     const float2 *hdr;
-    int64_t flat0;            // element offset of row 0 relative to payload
-    int rows;
+    int64_t flat0;            // element offset of the first row this launch works on, relative to payload
+    int rows;                 // rows this launch works on
+    int out0;                 // index of the first of them in the output vector (tensor parallel: a rank's rows)
+};
+
+// Tensor-parallel group of up to kMaxTp devices driven by one process.  Every rank computes a block of
+// rows of each matrix from the full input vector and stores its results into every rank's copy of the
+// output vector over the peer links, so each output element is produced by one rank in the same order
+// as on a single device: the ranks' vectors stay bitwise equal, and equal to the single-device ones.
+constexpr int kMaxTp = 8;
+enum TpVector { TPV_X = 0, TPV_XB = 1, TPV_HB = 2, TPV_COUNT = 3 };
+struct TpTable {
+    int n;                             // ranks (0 until the group is linked)
+    int rank;
+    float *vec[TPV_COUNT][kMaxTp];     // every rank's x, attention output and FFN hidden vector
+    unsigned int *chain[kMaxTp];       // every rank's hand-over counters (same layout on all ranks)
 };
 
 // Parameters of the ring matvec kernel.
@@ -105,9 +123,6 @@ struct MvParams {
     int rs;            // matrix rows (row pairs in paired mode) a stage advances
     int rowbytes;      // bytes of one matrix row
     int f32;           // 1: FP32 weights
-    int pf_distance;   // stages the L2 prefetch runs ahead of the claims (0: off)
-    int head_prefetch; // fixed stages each block prefetches into L2 at its start, beyond the early ring fill
-    int static_share;  // > 0: all but this many stages per block are fixed, the rest is claimed dynamically
     int tail_prefetch; // stages of the next launch each block prefetches into L2 when it runs out of work
     int early_fill;    // stages the producer may issue before the previous kernel has finished (0: none)
     const MvParams *next;   // device copy of the next ring launch's parameters (prefetch target) or nullptr
@@ -120,6 +135,8 @@ struct MvParams {
     int epilogue;
     float *y;                // STORE / RESIDUAL / SWIGLU / LOGITS target (replica 0)
     int y_reps, y_stride;    // copies of the target vector that every result is written to
+    const TpTable *tp;       // tensor parallel: the target vector `tp_vec` of every rank gets the results
+    int tp_vec;
     float *q_out;            // QKV: q (dim)
     float *k_cache;          // QKV: layer base of the K cache [kv_head][seq][head]
     float *v_cache;
@@ -134,8 +151,6 @@ struct MvParams {
     SeqState *state;
     ChainLink chain;
     unsigned int *work;  // {next unclaimed stage, blocks that ran out of work}; zero between launches
-    int pdl_mode;        // experiment: 0 trigger dependents at block start, 1 after the main loop, 2 never
-    int producer_wait;   // experiment: producer waits for the previous kernel before its first copy
     unsigned long long *trace;   // optional per-block timeline (8 slots per block), else nullptr
 };
 
@@ -145,6 +160,8 @@ struct AttnParams {
     const float *v_cache;
     float *out;              // (n_heads * head), replica 0
     int out_reps, out_stride;   // copies of the output vector and their distance in floats
+    const TpTable *tp;       // tensor parallel: every rank's attention output vector gets the results
+    int h0;                  // first head of this launch (block x works on head h0 + x)
     float *part;             // scratch: [n_heads][nsplit][head + 2]
     unsigned int *counters;  // [n_heads], zero between launches
     SeqState *state;

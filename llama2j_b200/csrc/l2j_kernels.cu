@@ -196,9 +196,24 @@ __device__ __forceinline__ bool chain_wait_group(const ChainLink &c, bool poller
     }
     // One thread polls: thousands of pollers on one line would stand in the way of the bumps themselves.
     if (poller)
-        *flag = counter_wait_bounded(c.wait_counter, __ldcg(c.epoch) * c.wait_blocks, timeout_ns) ? 1 : 0;
+        *flag = counter_wait_bounded(c.wait_counter, __ldcg(c.epoch) * c.wait_blocks, timeout_ns, c.tp != nullptr) ? 1 : 0;
     named_barrier_sync(bar_id, nthreads);   // orders the other threads' loads behind the poller's acquire
     return *flag != 0;
+}
+
+// Reports a block's results as visible: bumps the launch's counter, on every rank of a tensor-parallel
+// group.  Called by one thread after a barrier with the threads that wrote the results.
+__device__ __forceinline__ void chain_signal(const ChainLink &c)
+{
+    if (c.done_counter == nullptr)
+        return;
+    if (c.tp == nullptr) {
+        red_release_add_u32(c.done_counter, 1u);
+        return;
+    }
+    const int n = c.tp->n;
+    for (int r = 0; r < n; ++r)
+        red_release_sys_add_u32(c.tp->chain[r] + c.done_off, 1u);
 }
 
 constexpr int kRedBufs = 4;
@@ -285,7 +300,7 @@ __global__ void __launch_bounds__(kRingMaxThreads, 1) matvec_ring_kernel(const _
     // its 128-byte lines up front makes the block pay one miss instead of one per line along the
     // serial set-up below.
     {
-        const int t0 = p.nseg, t1 = p.epilogue, t2 = p.pdl_mode;
+        const int t0 = p.nseg, t1 = p.epilogue, t2 = p.tail_prefetch;
         asm volatile("" ::"r"(t0), "r"(t1), "r"(t2));
     }
 
@@ -307,8 +322,7 @@ __global__ void __launch_bounds__(kRingMaxThreads, 1) matvec_ring_kernel(const _
     if (tid < 32)
         mbar_fence_init();
     __syncthreads();
-    if ((p.pdl_mode & 3) == 0)
-        pdl_launch_dependents();
+    pdl_launch_dependents();   // the next kernel's blocks may take the SMs as they free up
 
     const int R = RT * p.rpp;                       // rows of a stage in shared memory
     const int rs = p.paired ? R / 2 : R;            // matrix rows (row pairs) a stage advances
@@ -322,24 +336,13 @@ __global__ void __launch_bounds__(kRingMaxThreads, 1) matvec_ring_kernel(const _
             const uint64_t pol = policy_evict_first();
             bool lost = false, first = true;
             int slot = 0, round = 0;
-            if (p.producer_wait)
-                pdl_wait();
             // The first `nstatic` stages of a block are fixed (block index + j * grid), so that the blocks
             // do not all queue up on the counter at kernel start; the rest is claimed from the global
             // counter, always one claim ahead of the stage being issued.
             const unsigned int grid = gridDim.x;
-            const unsigned int nstatic = p.static_share < 0 ? 0x3fffffffu / grid : (unsigned int)max(1, p.static_share > 0 ? S / (int)grid - p.static_share : S / (2 * (int)grid));
+            const unsigned int nstatic = (unsigned int)max(1, S / (2 * (int)grid));
             unsigned int issued = 0;
             unsigned int pending = 0xfffffffeu, pending2 = 0xfffffffeu;   // two claims in flight once the first stage is on its way
-            // HBM -> L2 for the block's first stages starts at once; the copies into shared memory wait
-            // until the consumers have put their loads of x on the wire.  A ring fill issued earlier
-            // would sit in front of those small, latency-critical loads (and of the attention kernel's,
-            // if that is still running) in the SM's load path.
-            // HBM -> L2 for the block's fixed stages that are not fetched into the ring right away: the ring
-            // then fills from L2 once the gate opens, and HBM keeps working while the block sets up.
-            for (unsigned int j = (unsigned int)p.early_fill; j < (unsigned int)(p.early_fill + p.head_prefetch) && j < nstatic; ++j)
-                if (blockIdx.x + j * grid < (unsigned int)S)
-                    prefetch_stage(p, (int)(blockIdx.x + j * grid));
             bool gate_open = false;
             for (;;) {
                 // Only `early_fill` stages are issued before the consumers have put their loads of x on the
@@ -393,14 +396,9 @@ __global__ void __launch_bounds__(kRingMaxThreads, 1) matvec_ring_kernel(const _
                     const uint32_t hbytes = (uint32_t)(((gl - ga + 2) & ~(int64_t)1) * 8);
                     desc->e0a = (int)(flat - ga * 256);
                     desc->e0b = 0;
-                    if (p.pdl_mode & 16) {
-                        mbar_arrive_expect_tx(full, pbytes);
-                        bulk_g2s(dst, p.seg[seg].payload + flat, pbytes, full, pol);
-                    } else {
                     mbar_arrive_expect_tx(full, pbytes + hbytes);
                     bulk_g2s(dst, p.seg[seg].payload + flat, pbytes, full, pol);
                     bulk_g2s(dst + (uint32_t)p.hdr_off, p.seg[seg].hdr + ga, hbytes, full, pol);
-                    }
                 } else {
                     int64_t flat[2], ga[2];
                     uint32_t hbytes[2];
@@ -412,12 +410,6 @@ __global__ void __launch_bounds__(kRingMaxThreads, 1) matvec_ring_kernel(const _
                     }
                     desc->e0a = (int)(flat[0] - ga[0] * 256);
                     desc->e0b = (int)(flat[1] - ga[1] * 256);
-                    if (p.pdl_mode & 16) {
-                        mbar_arrive_expect_tx(full, 2 * pbytes);
-                        for (int h = 0; h < 2; ++h)
-                            bulk_g2s(dst + (uint32_t)(h * (R / 2)) * (uint32_t)rowbytes, p.seg[h].payload + flat[h], pbytes,
-                                     full, pol);
-                    } else {
                     mbar_arrive_expect_tx(full, 2 * pbytes + hbytes[0] + hbytes[1]);
                     for (int h = 0; h < 2; ++h) {
                         bulk_g2s(dst + (uint32_t)(h * (R / 2)) * (uint32_t)rowbytes, p.seg[h].payload + flat[h], pbytes,
@@ -425,26 +417,12 @@ __global__ void __launch_bounds__(kRingMaxThreads, 1) matvec_ring_kernel(const _
                         bulk_g2s(dst + (uint32_t)p.hdr_off + (uint32_t)(h * p.half_hdr), p.seg[h].hdr + ga[h], hbytes[h],
                                  full, pol);
                     }
-                    }
                 }
                 if (first) {
                     trace_mark(p, 1);
                     first = false;
                     pending = nstatic * grid + atomicAdd(p.work, 1u);
                     pending2 = nstatic * grid + atomicAdd(p.work, 1u);
-                }
-                if (p.pf_distance > 0) {
-                    // Keep HBM -> L2 running a fixed distance ahead of the claims, across the boundary to
-                    // the next launch: the ring then fills from L2 and the weight stream does not pause
-                    // while a kernel drains, starts or normalises its input.
-                    const unsigned int pf = cur + (unsigned int)p.pf_distance;
-                    if (pf < (unsigned int)S) {
-                        prefetch_stage(p, (int)pf);
-                    } else if (p.next) {
-                        const int j = (int)(pf - (unsigned int)S);
-                        if (j < p.next->total_stages)
-                            prefetch_stage(*p.next, j);
-                    }
                 }
                 if (++slot == nstage) {
                     slot = 0;
@@ -498,13 +476,15 @@ __global__ void __launch_bounds__(kRingMaxThreads, 1) matvec_ring_kernel(const _
         float best_v = -FLT_MAX;
         int best_i = 0x7fffffff;
         int rb = 0, rround = 0;
+        const int tp_n = p.tp ? p.tp->n : 0;
         for (;;) {
             if (!mbar_wait_bounded(sbase + kBarRedFull + 8 * rb, (uint32_t)rround & 1u, lost ? kShortWaitNs : wait_ns))
                 lost = true;
             const int *rh = reinterpret_cast<const int *>(smem + kRedOff + rb * kRedStride);
-            const int seg = rh[0], row0 = rh[1], nrows = rh[2];
+            const int seg = rh[0], nrows = rh[2];
             if (nrows <= 0 || (lost && !lost_before))
                 break;
+            const int row0 = rh[1] + p.seg[p.paired ? 0 : seg].out0;   // index in the output vector
             const float *red = reinterpret_cast<const float *>(rh + 4);
             if (p.epilogue == EPI_QKV_ROPE) {
                 if (lane < (nrows >> 1)) {
@@ -523,15 +503,25 @@ __global__ void __launch_bounds__(kRingMaxThreads, 1) matvec_ring_kernel(const _
                         v3 += red[(R / 2 + lane) * p.wpr + w];
                     }
                     const float g = epi_swiglu(v1, v3);
-                    for (int r = 0; r < p.y_reps; ++r)
-                        p.y[(int64_t)r * p.y_stride + row0 + lane] = g;
+                    if (p.tp) {
+                        for (int r = 0; r < tp_n; ++r)
+                            p.tp->vec[p.tp_vec][r][row0 + lane] = g;
+                    } else {
+                        for (int r = 0; r < p.y_reps; ++r)
+                            p.y[(int64_t)r * p.y_stride + row0 + lane] = g;
+                    }
                 }
             } else if (lane < nrows) {
                 float a = 0.f;
                 for (int w = 0; w < p.wpr; ++w)
                     a += red[lane * p.wpr + w];
                 const int row = row0 + lane;
-                if (p.epilogue == EPI_RESIDUAL) {
+                if (p.epilogue == EPI_RESIDUAL && p.tp) {
+                    // this rank owns the row: one add on the local copy (all copies are equal), the sum to every rank
+                    const float xn = __fadd_rn(__ldcg(p.y + row), a);
+                    for (int r = 0; r < tp_n; ++r)
+                        p.tp->vec[p.tp_vec][r][row] = xn;
+                } else if (p.epilogue == EPI_RESIDUAL) {
                     for (int r = 0; r < p.y_reps; ++r)   // one add per element, copy and launch: no read round trip
                         atomicAdd(p.y + (int64_t)r * p.y_stride + row, a);
                 } else {
@@ -552,11 +542,10 @@ __global__ void __launch_bounds__(kRingMaxThreads, 1) matvec_ring_kernel(const _
         }
         if (lost && !lost_before && lane == 0)
             atomicOr(&p.state->status, L2J_DS_WAIT_TIMEOUT);
-        if (p.chain.done_counter) {   // all results of the block were written by this warp; the release is cumulative
-            __syncwarp();
-            if (lane == 0)
-                red_release_add_u32(p.chain.done_counter, 1u);
-        }
+        // all results of the block were written by this warp; the release is cumulative
+        __syncwarp();
+        if (lane == 0)
+            chain_signal(p.chain);
         if (lane == 0) {
             trace_mark(p, 6);
             if (p.trace)
@@ -802,7 +791,7 @@ __global__ void __launch_bounds__(kRingMaxThreads, 1) matvec_ring_kernel(const _
             const int r = rsub + t * p.rpp;                      // row of the stage in shared memory
             const int half = (p.paired && t >= RT / 2) ? 1 : 0;  // second half of a paired stage: the partner matrix
             const int local = r - half * (R / 2);
-            if (!done && local < d.nrows && !(p.pdl_mode & 32)) {
+            if (!done && local < d.nrows) {
                 const uint8_t *rowp = slot_ptr + (size_t)r * rowbytes;
                 if constexpr (F32) {
                     float a = 0.f;
@@ -909,8 +898,6 @@ __global__ void __launch_bounds__(kRingMaxThreads, 1) matvec_ring_kernel(const _
     }
     if (tid == 0)
         trace_mark(p, 5);
-    if ((p.pdl_mode & 3) == 1)
-        pdl_launch_dependents();
     if (lost && !lost_before)
         atomicOr(&p.state->status, L2J_DS_WAIT_TIMEOUT);
 }
@@ -1193,7 +1180,9 @@ __device__ __forceinline__ void attention_block(const AttnParams &p, int h, int 
     }
 
     // q and the newest K/V row come from the kernel in front
-    if (!chain_wait_group(p.chain, tid == 0, 1, kAttnThreads, (uint64_t)p.timeout_us * 1000ull, s_flag) && tid == 0)
+    const bool lost_before = p.state && (__ldcg(&p.state->status) & L2J_DS_WAIT_TIMEOUT) != 0;   // then every later wait is short
+    if (!chain_wait_group(p.chain, tid == 0, 1, kAttnThreads, lost_before ? kShortWaitNs : (uint64_t)p.timeout_us * 1000ull, s_flag) &&
+        tid == 0)
         atomicOr(&p.state->status, L2J_DS_WAIT_TIMEOUT);
     if (tr)
         tr[1] = global_timer_ns();
@@ -1303,7 +1292,20 @@ __device__ __forceinline__ void attention_signal(const AttnParams &p)
     if (p.chain.done_counter) {
         __syncthreads();
         if (threadIdx.x == 0)
-            red_release_add_u32(p.chain.done_counter, 1u);
+            chain_signal(p.chain);
+    }
+}
+
+// One element of the attention output: to the local vector (and its copies), or to every rank's.
+__device__ __forceinline__ void attention_store(const AttnParams &p, int index, float o)
+{
+    if (p.tp) {
+        const int n = p.tp->n;
+        for (int r = 0; r < n; ++r)
+            p.tp->vec[TPV_XB][r][index] = o;
+    } else {
+        for (int r = 0; r < p.out_reps; ++r)
+            p.out[(int64_t)r * p.out_stride + index] = o;
     }
 }
 
@@ -1312,12 +1314,12 @@ __global__ void __launch_bounds__(kAttnThreads, 3) attention_kernel(const __grid
     extern __shared__ __align__(16) float asmem[];   // [slots][head + 4]: o, then m, l (16-byte aligned rows); [head + 4] block result
     __shared__ int s_last;
 
-    const int h = blockIdx.x, sp = blockIdx.y;
+    const int h = p.h0 + blockIdx.x, sp = blockIdx.y;
     const int tid = threadIdx.x;
     const int head = p.head;
 
     pdl_launch_dependents();
-    const int bl = sp * (int)gridDim.x + h;
+    const int bl = sp * (int)gridDim.x + (int)blockIdx.x;
     unsigned long long *tr = (p.trace && bl < p.trace_blocks && tid == 0) ? p.trace + bl * 16 : nullptr;
     if (tr)
         tr[0] = global_timer_ns();
@@ -1334,7 +1336,7 @@ __global__ void __launch_bounds__(kAttnThreads, 3) attention_kernel(const __grid
     if (sp >= nact && !cluster_merge) {   // no work, no results, nobody to meet: report at once
         if (p.chain.done_counter) {
             if (tid == 0)
-                red_release_add_u32(p.chain.done_counter, 1u);
+                chain_signal(p.chain);
         } else {
             pdl_wait();
         }
@@ -1351,8 +1353,7 @@ __global__ void __launch_bounds__(kAttnThreads, 3) attention_kernel(const __grid
     if (nact == 1) {
         const float o = __fdiv_rn(O, L);   // ExpSumNormalize.java:33-37 folded into the sum
         if (tid < head)
-            for (int r = 0; r < p.out_reps; ++r)
-                p.out[(int64_t)r * p.out_stride + (int64_t)h * head + tid] = o;
+            attention_store(p, h * head + tid, o);
         attention_signal(p);
         return;
     }
@@ -1389,8 +1390,7 @@ __global__ void __launch_bounds__(kAttnThreads, 3) attention_kernel(const __grid
                 }
             }
             const float o = __fdiv_rn(OO, LL);
-            for (int r = 0; r < p.out_reps; ++r)
-                p.out[(int64_t)r * p.out_stride + (int64_t)h * head + tid] = o;
+            attention_store(p, h * head + tid, o);
         }
         if (tr)
             tr[5] = global_timer_ns();
@@ -1416,8 +1416,8 @@ __global__ void __launch_bounds__(kAttnThreads, 3) attention_kernel(const __grid
     if (tr)
         tr[4] = global_timer_ns();
     if (!s_last) {
-        if (tid == 0 && p.chain.done_counter)   // the partials were fenced before the ticket
-            red_release_add_u32(p.chain.done_counter, 1u);
+        if (tid == 0)   // the partials were fenced before the ticket
+            chain_signal(p.chain);
         return;
     }
 
@@ -1439,8 +1439,7 @@ __global__ void __launch_bounds__(kAttnThreads, 3) attention_kernel(const __grid
             }
         }
         const float o = __fdiv_rn(OO, LL);
-        for (int r = 0; r < p.out_reps; ++r)
-            p.out[(int64_t)r * p.out_stride + (int64_t)h * head + tid] = o;
+        attention_store(p, h * head + tid, o);
     }
     if (tid == 0)
         p.counters[h] = 0;

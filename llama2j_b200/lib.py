@@ -61,6 +61,10 @@ _SIGNATURES = {
     "l2j_pipeline_link": (C.c_int, [C.POINTER(_P), C.c_int]),
     "l2j_pipeline_forward": (C.c_int, [C.POINTER(_P), C.c_int, C.c_int, C.c_int, _P, C.POINTER(C.c_int)]),
     "l2j_pipeline_generate_greedy": (C.c_int, [C.POINTER(_P), C.c_int, _P, C.c_int, C.c_int, _P]),
+    "l2j_create_tp": (C.c_int, [C.POINTER(Config), C.c_int, C.c_int, C.c_int, C.c_uint32, C.POINTER(_P)]),
+    "l2j_tp_link": (C.c_int, [C.POINTER(_P), C.c_int]),
+    "l2j_tp_forward": (C.c_int, [C.POINTER(_P), C.c_int, C.c_int, C.c_int, _P, C.POINTER(C.c_int)]),
+    "l2j_tp_generate_greedy": (C.c_int, [C.POINTER(_P), C.c_int, _P, C.c_int, C.c_int, _P]),
     "l2j_reset": (C.c_int, [_P]),
     "l2j_get_stats": (C.c_int, [_P, C.POINTER(Stats)]),
     "l2j_launch_mode": (C.c_int, [_P]),

@@ -30,7 +30,7 @@ class Transformer:
     """One device, layers [first_layer, last_layer] of the model (LayerAllocation.java:67-95)."""
 
     def __init__(self, cfg: ModelConfig, device: int = 0, first_layer: int = 0, last_layer: int | None = None,
-                 flags: int = 0):
+                 flags: int = 0, tp_rank: int = 0, tp_size: int = 1):
         self.cfg = cfg
         self.device = device
         self.first_layer = first_layer
@@ -38,7 +38,10 @@ class Transformer:
         self._lib = _lib.load()
         self._ctx = C.c_void_p()
         ccfg = cfg.to_c()
-        rc = self._lib.l2j_create(C.byref(ccfg), device, self.first_layer, self.last_layer, flags, C.byref(self._ctx))
+        if tp_size > 1:
+            rc = self._lib.l2j_create_tp(C.byref(ccfg), device, tp_rank, tp_size, flags, C.byref(self._ctx))
+        else:
+            rc = self._lib.l2j_create(C.byref(ccfg), device, self.first_layer, self.last_layer, flags, C.byref(self._ctx))
         _lib.check(rc, None)
         self._logits = np.zeros(cfg.vocab_size, dtype=np.float32)
 
@@ -250,3 +253,49 @@ class LinkedStages:
     def close(self) -> None:
         for s in self.stages:
             s.close()
+
+
+class TensorParallel:
+    """A tensor-parallel group driven by one host thread: rank r (a Transformer created with tp_rank=r on a
+    device of its own) computes a block of rows of every matrix and stores its results into all ranks'
+    vectors over the peer links.  The reference has no such mode; results are bitwise those of one device."""
+
+    def __init__(self, ranks):
+        self.ranks = list(ranks)
+        self._lib = _lib.load()
+        self._arr = (C.c_void_p * len(self.ranks))(*[r._ctx for r in self.ranks])
+        _lib.check(self._lib.l2j_tp_link(self._arr, len(self.ranks)), self.ranks[0]._ctx)
+        self._logits = np.zeros(self.ranks[0].cfg.vocab_size, dtype=np.float32)
+
+    @classmethod
+    def from_devices(cls, cfg: ModelConfig, tensors: dict, devices, flags: int = 0):
+        devices = list(devices)
+        ranks = []
+        for r, dev in enumerate(devices):
+            t = Transformer(cfg, device=dev, flags=flags, tp_rank=r, tp_size=len(devices))
+            t.upload_all(tensors)
+            t.finalize()
+            ranks.append(t)
+        return cls(ranks)
+
+    def forward(self, token: int, pos: int, want_logits: bool = True):
+        am = C.c_int(-1)
+        ptr = self._logits.ctypes.data if want_logits else None
+        rc = self._lib.l2j_tp_forward(self._arr, len(self.ranks), int(token), int(pos), ptr, C.byref(am))
+        _lib.check(rc, self.ranks[0]._ctx)
+        return (self._logits if want_logits else None), am.value
+
+    def generate_greedy(self, prompt, steps: int) -> np.ndarray:
+        prompt = np.ascontiguousarray(prompt, dtype=np.int32).reshape(-1)
+        out = np.zeros(steps, dtype=np.int32)
+        rc = self._lib.l2j_tp_generate_greedy(self._arr, len(self.ranks), prompt.ctypes.data if prompt.size else None,
+                                              int(prompt.size), int(steps), out.ctypes.data)
+        _lib.check(rc, self.ranks[0]._ctx)
+        return out
+
+    def last_generate_us(self) -> float:
+        return self.ranks[0].last_generate_us()
+
+    def close(self) -> None:
+        for r in self.ranks:
+            r.close()

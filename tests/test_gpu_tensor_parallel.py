@@ -1,0 +1,91 @@
+"""Tensor-parallel group (l2j_create_tp / l2j_tp_*): every output element is computed by one rank in the
+single-device order, so logits and greedy tokens must be bitwise those of one device.  Ranks wait for each
+other inside their kernels (with a time limit) and therefore need a GPU each: the tests with more than
+one rank are skipped on a single GPU."""
+import numpy as np
+import pytest
+
+from llama2j_b200 import lib as L
+from llama2j_b200 import synthetic as syn
+from llama2j_b200.model_files import ModelConfig
+from llama2j_b200.transformer import TensorParallel, Transformer
+
+pytestmark = pytest.mark.gpu
+
+
+def _device_count() -> int:
+    import torch
+    return torch.cuda.device_count()
+
+
+def _whole(cfg, tensors):
+    m = Transformer(cfg)
+    m.upload_all(tensors)
+    m.finalize()
+    return m
+
+
+def _check_group(cfg, tensors, n_ranks, steps, n_prompt):
+    prompt = syn.synthetic_prompt(n_prompt, 1, cfg.vocab_size)
+    whole = _whole(cfg, tensors)
+    ref_tokens = whole.generate_greedy(prompt, steps)
+    whole.reset()
+    group = TensorParallel.from_devices(cfg, tensors, list(range(n_ranks)))
+    token = 1
+    for pos in range(12):
+        lg, am = whole.forward(token, pos)
+        lg2, am2 = group.forward(token, pos)
+        assert np.array_equal(lg.view(np.uint32), lg2.view(np.uint32)), pos
+        assert am == am2
+        token = int(prompt[pos]) if pos < n_prompt else am
+    toks = group.generate_greedy(prompt, steps)
+    assert np.array_equal(toks, ref_tokens)
+    assert np.array_equal(group.generate_greedy(prompt, steps), ref_tokens)
+    whole.close()
+    group.close()
+
+
+def test_group_of_one_is_the_plain_context():
+    cfg = syn.SHAPES["stories15M"]
+    tensors = syn.synthetic_tensors(cfg, 0)
+    _check_group(cfg, tensors, 1, steps=48, n_prompt=8)
+
+
+def test_two_ranks_stories15m_unaligned_rows():
+    if _device_count() < 2:
+        pytest.skip("needs two GPUs")
+    cfg = syn.SHAPES["stories15M"]          # dim 288: rows straddle quantisation groups
+    tensors = syn.synthetic_tensors(cfg, 0)
+    _check_group(cfg, tensors, 2, steps=200, n_prompt=16)
+
+
+def test_ranks_stories110m():
+    n = min(_device_count(), 4)
+    if n < 2:
+        pytest.skip("needs two GPUs")
+    cfg = syn.SHAPES["stories110M"]         # 12 heads: 2 or 4 ranks
+    tensors = syn.synthetic_tensors(cfg, 0)
+    _check_group(cfg, tensors, n, steps=300, n_prompt=16)
+
+
+def test_rejects_bad_groups():
+    cfg = syn.SHAPES["stories15M"]          # 6 heads
+    with pytest.raises(L.L2jError) as e:
+        Transformer(cfg, tp_rank=0, tp_size=4)          # 6 heads do not divide by 4
+    assert e.value.code == L.E_INVALID
+    with pytest.raises(L.L2jError):
+        Transformer(cfg, tp_rank=2, tp_size=2)
+    tensors = syn.synthetic_tensors(cfg, 0)
+    a = Transformer(cfg, device=0, tp_rank=0, tp_size=2)
+    b = Transformer(cfg, device=0, tp_rank=1, tp_size=2)
+    for m in (a, b):
+        m.upload_all(tensors)
+        m.finalize()
+    with pytest.raises(L.L2jError) as e:
+        TensorParallel([a, b])                           # two ranks on one device are refused
+    assert e.value.code == L.E_INVALID
+    with pytest.raises(L.L2jError) as e:
+        a.forward(1, 0)                                  # a rank does not run alone
+    assert e.value.code == L.E_STATE
+    a.close()
+    b.close()
