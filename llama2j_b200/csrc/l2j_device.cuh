@@ -149,9 +149,10 @@ __device__ __forceinline__ unsigned int ld_acquire_sys_u32(const unsigned int *p
     return v;
 }
 
-__device__ __forceinline__ void red_release_sys_add_u32(unsigned int *p, unsigned int v)
+// Bump without ordering of its own: the caller has issued a system-scope fence after its writes.
+__device__ __forceinline__ void red_relaxed_sys_add_u32(unsigned int *p, unsigned int v)
 {
-    asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+    asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
 // Polls until the counter has reached `target` (wrap-around safe); gives up after timeout_ns and

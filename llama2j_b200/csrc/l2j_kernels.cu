@@ -212,8 +212,9 @@ __device__ __forceinline__ void chain_signal(const ChainLink &c)
         return;
     }
     const int n = c.tp->n;
+    __threadfence_system();   // one fence for all ranks' counters
     for (int r = 0; r < n; ++r)
-        red_release_sys_add_u32(c.tp->chain[r] + c.done_off, 1u);
+        red_relaxed_sys_add_u32(c.tp->chain[r] + c.done_off, 1u);
 }
 
 constexpr int kRedBufs = 4;
@@ -517,10 +518,10 @@ __global__ void __launch_bounds__(kRingMaxThreads, 1) matvec_ring_kernel(const _
                     a += red[lane * p.wpr + w];
                 const int row = row0 + lane;
                 if (p.epilogue == EPI_RESIDUAL && p.tp) {
-                    // this rank owns the row: one add on the local copy (all copies are equal), the sum to every rank
-                    const float xn = __fadd_rn(__ldcg(p.y + row), a);
+                    // every copy of x gets the same single add for this row (no other rank computes it), so the
+                    // copies stay bitwise equal without a read round trip here
                     for (int r = 0; r < tp_n; ++r)
-                        p.tp->vec[p.tp_vec][r][row] = xn;
+                        atomicAdd(p.tp->vec[p.tp_vec][r] + row, a);
                 } else if (p.epilogue == EPI_RESIDUAL) {
                     for (int r = 0; r < p.y_reps; ++r)   // one add per element, copy and launch: no read round trip
                         atomicAdd(p.y + (int64_t)r * p.y_stride + row, a);
