@@ -78,7 +78,9 @@ struct l2j_ctx {
     Cmd *cmd_host = nullptr;       // pinned ring
     StageLink *link_dev = nullptr; // peer pointers of a linked layer split (zero until linked)
     int tp_rank = 0, tp_size = 1;  // tensor parallel group this context belongs to
-    TpTable *tp_dev = nullptr;     // the group's vectors and counters (n = 0 until linked)
+    TpTable *tp_dev = nullptr;     // the group's receive buffers (n = 0 until linked)
+    float *x2 = nullptr;           // tensor parallel: second copy of the residual stream (the two alternate)
+    float2 *ll_buf[TPV_COUNT] = {nullptr, nullptr, nullptr};   // receive buffers: x increments, attention output, hidden vector
     bool tp_linked = false;
     cudaEvent_t ev_stage = nullptr;   // "this stage's step is done", waited for by the next stage's stream
     float *logits_host = nullptr;  // pinned
@@ -234,32 +236,88 @@ void link_chain(l2j_ctx *c)
 {
     if (!c->use_ring || !c->chain_on)
         return;
-    // in a tensor-parallel group every rank's blocks bump every rank's counters
-    const unsigned int ring_blocks = (unsigned int)(c->ring_grid * c->tp_size);
-    const unsigned int attn_blocks = (unsigned int)(c->cfg.n_heads / c->tp_size * c->nsplit * c->tp_size);
+    const unsigned int ring_blocks = (unsigned int)c->ring_grid;
+    const unsigned int attn_blocks = (unsigned int)(c->cfg.n_heads * c->nsplit);
     const unsigned int *prev = nullptr;
     unsigned int prev_blocks = 0;
     int idx = 0;
     auto link = [&](ChainLink &ch, unsigned int blocks) {
         ch.wait_counter = prev;
         ch.wait_blocks = prev_blocks;
-        ch.done_off = kChainStride * idx;
         ch.done_counter = c->chain + (int64_t)kChainStride * idx++;
         ch.epoch = c->chain + (int64_t)kChainStride * (5 * c->nl + 1);
-        ch.tp = c->tp_size > 1 ? c->tp_dev : nullptr;
         prev = ch.done_counter;
         prev_blocks = blocks;
     };
     for (int li = 0; li < c->nl; ++li) {
         LayerLaunch &L = c->layers[(size_t)li];
+        if (c->tp_size > 1) {
+            // Across the ranks data travels with sequence numbers (link_ranks); the only hand-over inside a
+            // rank is QKV -> attention.
+            prev = nullptr;
+            link(L.qkv.chain, ring_blocks);
+            link(L.attn.chain, attn_blocks);
+            L.attn.chain.done_counter = nullptr;
+            continue;
+        }
         link(L.qkv.chain, ring_blocks);
         link(L.attn.chain, attn_blocks);
         link(L.wo.chain, ring_blocks);
         link(L.w13.chain, ring_blocks);
         link(L.w2.chain, ring_blocks);
     }
-    if (c->is_last)
+    if (c->is_last && c->tp_size == 1)
         link(c->cls.chain, ring_blocks);
+}
+
+// Tensor parallel: which receive buffer every kernel reads and writes, and under which sequence numbers.
+// Kernel indices within a forward: layer li -> 5 li + {0 QKV, 1 attention, 2 Wo, 3 W1/W3, 4 W2}; classifier 5 L.
+// The residual stream alternates between two buffers: QKV (and the classifier) read x2 + the increments
+// of W2 and leave the sum in x; W1/W3 read x + the increments of Wo and leave the sum in x2.
+void link_ranks(l2j_ctx *c)
+{
+    if (c->tp_size <= 1)
+        return;
+    LlLink base{};
+    base.tp = c->tp_dev;
+    base.epoch = c->chain + (int64_t)kChainStride * (5 * c->nl + 1);
+    base.kernels = 5 * c->nl + 1;
+    base.in_vec = base.out_vec = -1;
+    for (int li = 0; li < c->nl; ++li) {
+        LayerLaunch &L = c->layers[(size_t)li];
+        const int k0 = 5 * li;
+        L.qkv.ll = base;
+        if (li > 0) {
+            L.qkv.ll.in_vec = TPV_X;
+            L.qkv.ll.in_idx = k0 - 1;
+            L.qkv.ll.base = c->x2;
+            L.qkv.ll.write_back = c->x;
+        }
+        L.attn.ll = base;
+        L.attn.ll.out_vec = TPV_XB;
+        L.attn.ll.out_idx = k0 + 1;
+        L.wo.ll = base;
+        L.wo.ll.in_vec = TPV_XB;
+        L.wo.ll.in_idx = k0 + 1;
+        L.wo.ll.out_vec = TPV_X;
+        L.wo.ll.out_idx = k0 + 2;
+        L.w13.ll = base;
+        L.w13.ll.in_vec = TPV_X;
+        L.w13.ll.in_idx = k0 + 2;
+        L.w13.ll.base = c->x;
+        L.w13.ll.write_back = c->x2;
+        L.w13.ll.out_vec = TPV_HB;
+        L.w13.ll.out_idx = k0 + 3;
+        L.w2.ll = base;
+        L.w2.ll.in_vec = TPV_HB;
+        L.w2.ll.in_idx = k0 + 3;
+        L.w2.ll.out_vec = TPV_X;
+        L.w2.ll.out_idx = k0 + 4;
+    }
+    c->cls.ll = base;
+    c->cls.ll.in_vec = TPV_X;
+    c->cls.ll.in_idx = 5 * c->nl - 1;
+    c->cls.ll.base = c->x2;
 }
 
 // Builds the static kernel parameter blocks of every layer this context owns.
@@ -327,7 +385,6 @@ void build_launch_params(l2j_ctx *c)
         t.trace = c->trace ? c->trace + (int64_t)(4 * c->nl + 1 + li) * c->ring_grid * 16 : nullptr;
         t.trace_blocks = c->ring_grid;
         t.smem_pad = 0;
-        t.tp = c->tp_size > 1 ? c->tp_dev : nullptr;
         t.n_heads = c->cfg.n_heads / c->tp_size;   // the heads whose q rows this rank computed
         t.h0 = c->tp_rank * t.n_heads;
 
@@ -343,8 +400,6 @@ void build_launch_params(l2j_ctx *c)
         o.x_stride = c->dim_stride;
         o.rms_w = nullptr;
         o.epilogue = EPI_RESIDUAL;
-        o.tp = c->tp_size > 1 ? c->tp_dev : nullptr;
-        o.tp_vec = TPV_X;
         o.y = c->x;
         o.y_reps = c->reps;
         o.y_stride = c->dim_stride;
@@ -366,8 +421,6 @@ void build_launch_params(l2j_ctx *c)
         f.x_stride = c->dim_stride;
         f.rms_w = c->rms_ffn + (int64_t)li * c->reps * c->dim_stride;
         f.epilogue = EPI_SWIGLU;
-        f.tp = c->tp_size > 1 ? c->tp_dev : nullptr;
-        f.tp_vec = TPV_HB;
         f.y = c->hb;
         f.y_reps = c->reps;
         f.y_stride = c->hid_stride;
@@ -387,8 +440,6 @@ void build_launch_params(l2j_ctx *c)
         w.x_stride = c->hid_stride;
         w.rms_w = nullptr;
         w.epilogue = EPI_RESIDUAL;
-        w.tp = c->tp_size > 1 ? c->tp_dev : nullptr;
-        w.tp_vec = TPV_X;
         w.y = c->x;
         w.y_reps = c->reps;
         w.y_stride = c->dim_stride;
@@ -428,6 +479,7 @@ void build_launch_params(l2j_ctx *c)
         k.trace = c->trace ? c->trace + (int64_t)(4 * c->nl) * c->ring_grid * 16 : nullptr;
     }
     link_chain(c);
+    link_ranks(c);
     for (int li = 0; li < c->nl; ++li) {
         LayerLaunch &L = c->layers[(size_t)li];
         L.attn_long = L.attn;          // same grid and hand-over counters
@@ -771,6 +823,12 @@ static int create_impl(const l2j_config *cfg, int device, int first_layer, int l
     CREATE_CUDA(cudaHostAlloc((void **)&c->cmd_host, sizeof(Cmd) * kCmdRing, cudaHostAllocDefault));
     CREATE_CK(dev_alloc(c, &c->link_dev, 1, true));
     CREATE_CK(dev_alloc(c, &c->tp_dev, 1, true));
+    if (tp_size > 1) {
+        CREATE_CK(dev_alloc(c, &c->x2, (int64_t)c->reps * c->dim_stride, true));
+        CREATE_CK(dev_alloc(c, &c->ll_buf[TPV_X], c->dim, true));
+        CREATE_CK(dev_alloc(c, &c->ll_buf[TPV_XB], c->dim, true));
+        CREATE_CK(dev_alloc(c, &c->ll_buf[TPV_HB], c->hidden, true));
+    }
     CREATE_CUDA(cudaEventCreateWithFlags(&c->ev_stage, cudaEventDisableTiming));
     CREATE_CUDA(cudaHostAlloc((void **)&c->logits_host, sizeof(float) * (size_t)cfg->vocab_size, cudaHostAllocDefault));
     CREATE_CUDA(cudaHostAlloc((void **)&c->x_host, sizeof(float) * (size_t)c->reps * c->dim_stride, cudaHostAllocDefault));
@@ -1420,10 +1478,8 @@ extern "C" int l2j_tp_link(l2j_ctx *const *ranks, int n_ranks)
                 else
                     CK(c, e);
             }
-            t.vec[TPV_X][j] = o->x;
-            t.vec[TPV_XB][j] = o->xb;
-            t.vec[TPV_HB][j] = o->hb;
-            t.chain[j] = o->chain;
+            for (int v = 0; v < TPV_COUNT; ++v)
+                t.ll[v][j] = o->ll_buf[v];
         }
         CK(c, cudaMemcpy(c->tp_dev, &t, sizeof(TpTable), cudaMemcpyHostToDevice));
         CK(c, cudaDeviceSynchronize());
@@ -1562,6 +1618,11 @@ extern "C" int l2j_reset(l2j_ctx *c)
     CK(c, cudaMemset(c->attn_counters, 0, sizeof(unsigned int) * (size_t)c->cfg.n_heads));
     CK(c, cudaMemset(c->work, 0, sizeof(unsigned int) * 2 * (4 * (size_t)c->nl + 1)));
     CK(c, cudaMemset(c->chain, 0, sizeof(unsigned int) * kChainStride * (5 * (size_t)c->nl + 2)));   // the epoch word too
+    if (c->tp_size > 1) {   // the sequence numbers start again: no old pair may match a new one
+        CK(c, cudaMemset(c->ll_buf[TPV_X], 0, sizeof(float2) * (size_t)c->dim));
+        CK(c, cudaMemset(c->ll_buf[TPV_XB], 0, sizeof(float2) * (size_t)c->dim));
+        CK(c, cudaMemset(c->ll_buf[TPV_HB], 0, sizeof(float2) * (size_t)c->hidden));
+    }
     CK(c, cudaDeviceSynchronize());
     c->forwards = 0;
     c->status_accum = 0;
@@ -1588,8 +1649,8 @@ extern "C" int l2j_time_kernels(l2j_ctx *c, int pos, int reps, double *us)
     if (!c || !us || reps <= 0)
         return L2J_E_INVALID;
     std::lock_guard<std::mutex> lock(c->mu);
-    if (!c->finalized || !c->use_ring)
-        return fail(c, L2J_E_STATE, "kernel timing needs a finalized context on the ring kernels");
+    if (!c->finalized || !c->use_ring || c->tp_size > 1)
+        return fail(c, L2J_E_STATE, "kernel timing needs a finalized context on the ring kernels that holds all rows");
     int rc = check_range(c, 1, pos, true);
     if (rc != L2J_OK)
         return rc;
@@ -1658,8 +1719,8 @@ extern "C" int l2j_trace_kernel(l2j_ctx *c, int kind, int layer, int pos, uint64
     if (!c || !out || kind < 0 || kind > 5 || kind == 1 || max_blocks <= 0)
         return L2J_E_INVALID;
     std::lock_guard<std::mutex> lock(c->mu);
-    if (!c->finalized || !c->use_ring)
-        return fail(c, L2J_E_STATE, "kernel tracing needs a finalized context on the ring kernels");
+    if (!c->finalized || !c->use_ring || c->tp_size > 1)
+        return fail(c, L2J_E_STATE, "kernel tracing needs a finalized context on the ring kernels that holds all rows");
     const int li = layer - c->first_layer;
     if (li < 0 || li >= c->nl || (kind == 5 && !c->is_last))
         return fail(c, L2J_E_INVALID, "layer %d is not held by this context", layer);

@@ -141,29 +141,29 @@ __device__ __forceinline__ void red_release_add_u32(unsigned int *p, unsigned in
     asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
-// The same at system scope, for counters that peers on other devices bump or poll.
-__device__ __forceinline__ unsigned int ld_acquire_sys_u32(const unsigned int *p)
+// (value, sequence number) pairs of the tensor-parallel hand-over: one 8-byte store carries both, so the
+// reader needs no fence; loads go to L2, where the peers' stores arrive.
+__device__ __forceinline__ void st_pair(float2 *p, float v, int seq)
 {
-    unsigned int v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
+    asm volatile("st.volatile.global.v2.f32 [%0], {%1, %2};" ::"l"(p), "f"(v), "f"(__int_as_float(seq)) : "memory");
 }
 
-// Bump without ordering of its own: the caller has issued a system-scope fence after its writes.
-__device__ __forceinline__ void red_relaxed_sys_add_u32(unsigned int *p, unsigned int v)
+__device__ __forceinline__ float4 ld_pairs2(const float2 *p)
 {
-    asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+    float4 v;
+    asm volatile("ld.volatile.global.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+    return v;
 }
 
 // Polls until the counter has reached `target` (wrap-around safe); gives up after timeout_ns and
 // returns false, so a lost predecessor can never hang the GPU.
-__device__ __forceinline__ bool counter_wait_bounded(const unsigned int *ctr, unsigned int target, uint64_t timeout_ns, bool sys)
+__device__ __forceinline__ bool counter_wait_bounded(const unsigned int *ctr, unsigned int target, uint64_t timeout_ns)
 {
-    if ((int)((sys ? ld_acquire_sys_u32(ctr) : ld_acquire_u32(ctr)) - target) >= 0)
+    if ((int)(ld_acquire_u32(ctr) - target) >= 0)
         return true;
     const uint64_t t0 = global_timer_ns();
     for (;;) {
-        if ((int)((sys ? ld_acquire_sys_u32(ctr) : ld_acquire_u32(ctr)) - target) >= 0)
+        if ((int)(ld_acquire_u32(ctr) - target) >= 0)
             return true;
         if (global_timer_ns() - t0 > timeout_ns)
             return false;

@@ -41,8 +41,6 @@ struct ChainLink {
     unsigned int wait_blocks;           // bumps per forward on that counter
     unsigned int *done_counter;         // counter this launch bumps once per block, or nullptr
     const unsigned int *epoch;          // forwards started on this context
-    const TpTable *tp;                  // tensor parallel: bump the counter at the same offset on every rank
-    int done_off;                       // offset of done_counter in the rank's counter array (unsigned ints)
 };
 
 struct Cmd {
@@ -100,8 +98,22 @@ enum TpVector { TPV_X = 0, TPV_XB = 1, TPV_HB = 2, TPV_COUNT = 3 };
 struct TpTable {
     int n;                             // ranks (0 until the group is linked)
     int rank;
-    float *vec[TPV_COUNT][kMaxTp];     // every rank's x, attention output and FFN hidden vector
-    unsigned int *chain[kMaxTp];       // every rank's hand-over counters (same layout on all ranks)
+    float2 *ll[TPV_COUNT][kMaxTp];     // every rank's receive buffers: (value, sequence number) per element
+};
+
+// Hand-over between the ranks of a tensor-parallel group: every result travels as an 8-byte (value,
+// sequence number) pair written with one store into the receive buffer of every rank, and the kernel that
+// consumes the vector polls the pairs of the elements it loads until they carry the number it expects.
+// No fence, no counter and no second message: the latency is one trip over the link.  A number is used
+// once: forward e, kernel i of the forward -> e * kernels_per_forward + i + 1.
+struct LlLink {
+    const TpTable *tp;         // nullptr: not a tensor-parallel launch
+    const unsigned int *epoch; // forwards started on this context (same on every rank of the group)
+    int kernels;               // kernel launches per forward (the multiplier of the epoch)
+    int in_vec, in_idx;        // input: receive buffer to read (-1: the plain input vector) and the producing kernel's index
+    int out_vec, out_idx;      // output: receive buffer to write on every rank (-1: local outputs only) and this kernel's index
+    const float *base;         // input = base + received (the residual stream), or nullptr: input = received
+    float *write_back;         // block 0 stores the assembled input here for the next residual step, or nullptr
 };
 
 // Parameters of the ring matvec kernel.
@@ -135,8 +147,7 @@ struct MvParams {
     int epilogue;
     float *y;                // STORE / RESIDUAL / SWIGLU / LOGITS target (replica 0)
     int y_reps, y_stride;    // copies of the target vector that every result is written to
-    const TpTable *tp;       // tensor parallel: the target vector `tp_vec` of every rank gets the results
-    int tp_vec;
+    LlLink ll;               // tensor parallel: where the input comes from and where the results go
     float *q_out;            // QKV: q (dim)
     float *k_cache;          // QKV: layer base of the K cache [kv_head][seq][head]
     float *v_cache;
@@ -160,7 +171,7 @@ struct AttnParams {
     const float *v_cache;
     float *out;              // (n_heads * head), replica 0
     int out_reps, out_stride;   // copies of the output vector and their distance in floats
-    const TpTable *tp;       // tensor parallel: every rank's attention output vector gets the results
+    LlLink ll;               // tensor parallel: the results go to every rank's receive buffer
     int h0;                  // first head of this launch (block x works on head h0 + x)
     float *part;             // scratch: [n_heads][nsplit][head + 2]
     unsigned int *counters;  // [n_heads], zero between launches

@@ -196,25 +196,30 @@ __device__ __forceinline__ bool chain_wait_group(const ChainLink &c, bool poller
     }
     // One thread polls: thousands of pollers on one line would stand in the way of the bumps themselves.
     if (poller)
-        *flag = counter_wait_bounded(c.wait_counter, __ldcg(c.epoch) * c.wait_blocks, timeout_ns, c.tp != nullptr) ? 1 : 0;
+        *flag = counter_wait_bounded(c.wait_counter, __ldcg(c.epoch) * c.wait_blocks, timeout_ns) ? 1 : 0;
     named_barrier_sync(bar_id, nthreads);   // orders the other threads' loads behind the poller's acquire
     return *flag != 0;
 }
 
-// Reports a block's results as visible: bumps the launch's counter, on every rank of a tensor-parallel
-// group.  Called by one thread after a barrier with the threads that wrote the results.
+// Reports a block's results as visible: bumps the launch's counter.  Called by one thread after a barrier
+// with the threads that wrote the results.
 __device__ __forceinline__ void chain_signal(const ChainLink &c)
 {
-    if (c.done_counter == nullptr)
-        return;
-    if (c.tp == nullptr) {
+    if (c.done_counter != nullptr)
         red_release_add_u32(c.done_counter, 1u);
-        return;
-    }
-    const int n = c.tp->n;
-    __threadfence_system();   // one fence for all ranks' counters
-    for (int r = 0; r < n; ++r)
-        red_relaxed_sys_add_u32(c.tp->chain[r] + c.done_off, 1u);
+}
+
+// Sequence number of kernel `idx` of the forward in flight (see LlLink).
+__device__ __forceinline__ int ll_seq(const LlLink &l, int idx)
+{
+    return (int)(__ldcg(l.epoch) * (unsigned int)l.kernels + (unsigned int)idx + 1u);
+}
+
+// One result to every rank's receive buffer.
+__device__ __forceinline__ void ll_send(const LlLink &l, int n_ranks, int index, float v, int seq)
+{
+    for (int r = 0; r < n_ranks; ++r)
+        st_pair(l.tp->ll[l.out_vec][r] + index, v, seq);
 }
 
 constexpr int kRedBufs = 4;
@@ -459,7 +464,7 @@ __global__ void __launch_bounds__(kRingMaxThreads, 1) matvec_ring_kernel(const _
     if (warp == nw + 1) {
         // With a hand-over counter nothing is needed here: the position was fixed when the forward began and
         // every result this warp writes is computed from data the consumers have waited for.
-        if (p.chain.wait_counter == nullptr)
+        if (p.chain.wait_counter == nullptr && !(p.ll.tp && p.ll.in_vec >= 0))
             pdl_wait();
         const int pos = __ldcg(&p.state->cur_pos);
         bool lost = (__ldcg(&p.state->status) & L2J_DS_WAIT_TIMEOUT) != 0;
@@ -477,7 +482,8 @@ __global__ void __launch_bounds__(kRingMaxThreads, 1) matvec_ring_kernel(const _
         float best_v = -FLT_MAX;
         int best_i = 0x7fffffff;
         int rb = 0, rround = 0;
-        const int tp_n = p.tp ? p.tp->n : 0;
+        const int tp_n = (p.ll.tp && p.ll.out_vec >= 0) ? p.ll.tp->n : 0;
+        const int seq_out = tp_n ? ll_seq(p.ll, p.ll.out_idx) : 0;
         for (;;) {
             if (!mbar_wait_bounded(sbase + kBarRedFull + 8 * rb, (uint32_t)rround & 1u, lost ? kShortWaitNs : wait_ns))
                 lost = true;
@@ -504,9 +510,8 @@ __global__ void __launch_bounds__(kRingMaxThreads, 1) matvec_ring_kernel(const _
                         v3 += red[(R / 2 + lane) * p.wpr + w];
                     }
                     const float g = epi_swiglu(v1, v3);
-                    if (p.tp) {
-                        for (int r = 0; r < tp_n; ++r)
-                            p.tp->vec[p.tp_vec][r][row0 + lane] = g;
+                    if (tp_n) {
+                        ll_send(p.ll, tp_n, row0 + lane, g, seq_out);
                     } else {
                         for (int r = 0; r < p.y_reps; ++r)
                             p.y[(int64_t)r * p.y_stride + row0 + lane] = g;
@@ -517,11 +522,10 @@ __global__ void __launch_bounds__(kRingMaxThreads, 1) matvec_ring_kernel(const _
                 for (int w = 0; w < p.wpr; ++w)
                     a += red[lane * p.wpr + w];
                 const int row = row0 + lane;
-                if (p.epilogue == EPI_RESIDUAL && p.tp) {
-                    // every copy of x gets the same single add for this row (no other rank computes it), so the
-                    // copies stay bitwise equal without a read round trip here
-                    for (int r = 0; r < tp_n; ++r)
-                        atomicAdd(p.tp->vec[p.tp_vec][r] + row, a);
+                if (p.epilogue == EPI_RESIDUAL && tp_n) {
+                    // the consumer adds this to its copy of the residual stream: one add per element and launch on
+                    // every rank, as on a single device
+                    ll_send(p.ll, tp_n, row, a, seq_out);
                 } else if (p.epilogue == EPI_RESIDUAL) {
                     for (int r = 0; r < p.y_reps; ++r)   // one add per element, copy and launch: no read round trip
                         atomicAdd(p.y + (int64_t)r * p.y_stride + row, a);
@@ -608,8 +612,10 @@ __global__ void __launch_bounds__(kRingMaxThreads, 1) matvec_ring_kernel(const _
     }
 
     bool lost = false;
-    // the input vector comes from the previous kernel
-    if (!chain_wait_group(p.chain, tid == 0, 1, ncons, wait_ns, reinterpret_cast<volatile int *>(smem + kScratchOff + 252)))
+    // The input vector comes from the previous kernel.  In a tensor-parallel group it arrives element by
+    // element with its sequence number and the loads below poll for it; otherwise wait for the kernel.
+    const bool ll_in = p.ll.tp != nullptr && p.ll.in_vec >= 0;
+    if (!ll_in && !chain_wait_group(p.chain, tid == 0, 1, ncons, wait_ns, reinterpret_cast<volatile int *>(smem + kScratchOff + 252)))
         lost = true;
     if (tid == 0)
         trace_mark(p, 12);
@@ -634,18 +640,92 @@ __global__ void __launch_bounds__(kRingMaxThreads, 1) matvec_ring_kernel(const _
         const int64_t rep_off = (int64_t)(blockIdx.x % (unsigned)p.x_reps) * p.x_stride;
         const float *xin = p.x_in + rep_off;
         const float *rmsw = has_rms ? p.rms_w + rep_off : nullptr;
+        if (!ll_in) {
 #pragma unroll
-        for (int j = 0; j < kPrologueRounds; ++j) {
-            const int idx = tid + j * ncons;
-            xr[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-            wr[j] = make_float4(1.f, 1.f, 1.f, 1.f);
-            if (j * ncons >= n4)
-                break;
-            if (idx < n4) {
-                xr[j] = ld_cg_f4_issue(xin + (int64_t)idx * 4);
-                if (has_rms)
-                    wr[j] = ld_cg_f4_issue(rmsw + (int64_t)idx * 4);
+            for (int j = 0; j < kPrologueRounds; ++j) {
+                const int idx = tid + j * ncons;
+                xr[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+                wr[j] = make_float4(1.f, 1.f, 1.f, 1.f);
+                if (j * ncons >= n4)
+                    break;
+                if (idx < n4) {
+                    xr[j] = ld_cg_f4_issue(xin + (int64_t)idx * 4);
+                    if (has_rms)
+                        wr[j] = ld_cg_f4_issue(rmsw + (int64_t)idx * 4);
+                }
             }
+        } else {
+            // A block without a stage of its own (its first stage is fixed: block index < number of stages)
+            // contributes nothing and must not wait for data that later kernels may already have replaced.
+            const bool has_work = blockIdx.x < (unsigned)p.total_stages;
+            const float2 *rx = p.ll.tp->ll[p.ll.in_vec][p.ll.tp->rank];
+            const int seq_in = ll_seq(p.ll, p.ll.in_idx);
+            float4 pa[kPrologueRounds], pb[kPrologueRounds];
+#pragma unroll
+            for (int j = 0; j < kPrologueRounds; ++j) {
+                const int idx = tid + j * ncons;
+                xr[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+                wr[j] = make_float4(1.f, 1.f, 1.f, 1.f);
+                if (j * ncons >= n4)
+                    break;
+                if (idx < n4 && has_work) {
+                    pa[j] = ld_pairs2(rx + (int64_t)idx * 4);
+                    pb[j] = ld_pairs2(rx + (int64_t)idx * 4 + 2);
+                    if (has_rms)
+                        wr[j] = ld_cg_f4_issue(rmsw + (int64_t)idx * 4);
+                }
+            }
+            uint64_t t_first = 0;
+#pragma unroll
+            for (int j = 0; j < kPrologueRounds; ++j) {
+                const int idx = tid + j * ncons;
+                if (j * ncons >= n4)
+                    break;
+                if (idx < n4 && has_work) {
+                    while (__float_as_int(pa[j].y) != seq_in || __float_as_int(pa[j].w) != seq_in ||
+                           __float_as_int(pb[j].y) != seq_in || __float_as_int(pb[j].w) != seq_in) {
+                        const uint64_t now = global_timer_ns();
+                        if (t_first == 0)
+                            t_first = now;
+                        if (now - t_first > (lost ? kShortWaitNs : wait_ns)) {
+                            lost = true;
+                            break;
+                        }
+                        pa[j] = ld_pairs2(rx + (int64_t)idx * 4);
+                        pb[j] = ld_pairs2(rx + (int64_t)idx * 4 + 2);
+                    }
+                }
+            }
+            // The residual stream this rank keeps is read only now: the block may have started before the
+            // kernel that stored it had run (blocks of consecutive kernels share SMs), but the increments
+            // cannot be complete before that store is visible.
+            if (p.ll.base) {
+#pragma unroll
+                for (int j = 0; j < kPrologueRounds; ++j) {
+                    const int idx = tid + j * ncons;
+                    if (j * ncons >= n4)
+                        break;
+                    if (idx < n4 && has_work)
+                        xr[j] = ld_cg_f4_issue(p.ll.base + (int64_t)idx * 4);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < kPrologueRounds; ++j) {
+                const int idx = tid + j * ncons;
+                if (j * ncons >= n4)
+                    break;
+                if (idx < n4 && has_work) {
+                    // residual stream: one add per element, as the single device's red.add does it
+                    xr[j].x = p.ll.base ? __fadd_rn(xr[j].x, pa[j].x) : pa[j].x;
+                    xr[j].y = p.ll.base ? __fadd_rn(xr[j].y, pa[j].z) : pa[j].z;
+                    xr[j].z = p.ll.base ? __fadd_rn(xr[j].z, pb[j].x) : pb[j].x;
+                    xr[j].w = p.ll.base ? __fadd_rn(xr[j].w, pb[j].z) : pb[j].z;
+                    if (p.ll.write_back && blockIdx.x == 0)
+                        __stcg(reinterpret_cast<float4 *>(p.ll.write_back + (int64_t)idx * 4), xr[j]);
+                }
+            }
+            if (p.ll.write_back && blockIdx.x == 0)
+                __threadfence();   // the stored vector is read by a later kernel's blocks on other SMs
         }
         float ssq = 0.f, amax = 0.f;
 #pragma unroll
@@ -1298,12 +1378,10 @@ __device__ __forceinline__ void attention_signal(const AttnParams &p)
 }
 
 // One element of the attention output: to the local vector (and its copies), or to every rank's.
-__device__ __forceinline__ void attention_store(const AttnParams &p, int index, float o)
+__device__ __forceinline__ void attention_store(const AttnParams &p, int index, float o, int seq)
 {
-    if (p.tp) {
-        const int n = p.tp->n;
-        for (int r = 0; r < n; ++r)
-            p.tp->vec[TPV_XB][r][index] = o;
+    if (p.ll.tp) {
+        ll_send(p.ll, p.ll.tp->n, index, o, seq);
     } else {
         for (int r = 0; r < p.out_reps; ++r)
             p.out[(int64_t)r * p.out_stride + index] = o;
@@ -1344,6 +1422,7 @@ __global__ void __launch_bounds__(kAttnThreads, 3) attention_kernel(const __grid
         return;
     }
 
+    const int seq_out = p.ll.tp ? ll_seq(p.ll, p.ll.out_idx) : 0;
     float M = -INFINITY, L = 0.f, O = 0.f;
     if (sp < nact) {
         const int t0 = sp * chunk;
@@ -1354,7 +1433,7 @@ __global__ void __launch_bounds__(kAttnThreads, 3) attention_kernel(const __grid
     if (nact == 1) {
         const float o = __fdiv_rn(O, L);   // ExpSumNormalize.java:33-37 folded into the sum
         if (tid < head)
-            attention_store(p, h * head + tid, o);
+            attention_store(p, h * head + tid, o, seq_out);
         attention_signal(p);
         return;
     }
@@ -1391,7 +1470,7 @@ __global__ void __launch_bounds__(kAttnThreads, 3) attention_kernel(const __grid
                 }
             }
             const float o = __fdiv_rn(OO, LL);
-            attention_store(p, h * head + tid, o);
+            attention_store(p, h * head + tid, o, seq_out);
         }
         if (tr)
             tr[5] = global_timer_ns();
@@ -1440,7 +1519,7 @@ __global__ void __launch_bounds__(kAttnThreads, 3) attention_kernel(const __grid
             }
         }
         const float o = __fdiv_rn(OO, LL);
-        attention_store(p, h * head + tid, o);
+        attention_store(p, h * head + tid, o, seq_out);
     }
     if (tid == 0)
         p.counters[h] = 0;
