@@ -63,6 +63,7 @@ struct l2j_ctx {
     float *attn_part = nullptr;
     unsigned int *attn_counters = nullptr;
     int nsplit = 1, chunk_max = 1;
+    int nsplit_long = 1;           // splits per head of the long-context attention launch
     float *blk_val = nullptr;
     int *blk_idx = nullptr;
     int *prompt_dev = nullptr, *out_tokens_dev = nullptr;
@@ -485,6 +486,7 @@ void build_launch_params(l2j_ctx *c)
         L.attn_long = L.attn;          // same grid and hand-over counters
         L.attn_long.cluster = 0;
         L.attn_long.smem_pad = 1;
+        L.attn_long.nsplit = c->nsplit_long;
     }
 }
 
@@ -801,7 +803,21 @@ static int create_impl(const l2j_config *cfg, int device, int first_layer, int l
     if (c->attn_cluster && c->nsplit > 8)
         c->nsplit = 8;   // portable cluster size
     c->chunk_max = (((cfg->seq_len + c->nsplit - 1) / c->nsplit) + 3) & ~3;   // keeps the float4 scratch behind it aligned
-    CREATE_CK(dev_alloc(c, &c->attn_part, (int64_t)cfg->n_heads * c->nsplit * (head + 2), true));
+    // A tensor-parallel rank has few heads: the long-context launch splits them further so that its blocks
+    // still cover the SMs (its results travel with sequence numbers, no block count is baked in anywhere).
+    c->nsplit_long = c->nsplit;
+    if (tp_size > 1) {
+        const int heads_local = cfg->n_heads / tp_size;
+        int ns = (2 * c->sm_count) / heads_local;
+        const int cap = cfg->seq_len / 64 > 0 ? cfg->seq_len / 64 : 1;
+        if (ns > cap)
+            ns = cap;
+        if (ns > 64)
+            ns = 64;
+        if (ns > c->nsplit_long)
+            c->nsplit_long = ns;
+    }
+    CREATE_CK(dev_alloc(c, &c->attn_part, (int64_t)cfg->n_heads * c->nsplit_long * (head + 2), true));
     CREATE_CK(dev_alloc(c, &c->attn_counters, cfg->n_heads, true));
     {   // blocks per ring kernel: one per SM, holding nearly all of its shared memory as the ring
         const char *g = getenv("L2J_BLOCKS_PER_SM");
