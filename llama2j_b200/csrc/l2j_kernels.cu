@@ -184,19 +184,30 @@ __device__ __forceinline__ void prefetch_stage(const MvParams &q, int s)
     }
 }
 
+constexpr uint64_t kShortWaitNs = 2000;   // limit of every wait once one has run out
+
 // Waits for the kernel in front: on its hand-over counter if the launch has one, else for the grid to
 // complete.  Called by all `nthreads` threads that share barrier `bar_id`; `flag` is a shared-memory word
 // of theirs.  Returns false if the bounded wait ran out.
 __device__ __forceinline__ bool chain_wait_group(const ChainLink &c, bool poller, int bar_id, int nthreads, uint64_t timeout_ns,
-                                                 volatile int *flag)
+                                                 volatile int *flag, const SeqState *st = nullptr)
 {
     if (c.wait_counter == nullptr) {
         pdl_wait();
         return true;
     }
     // One thread polls: thousands of pollers on one line would stand in the way of the bumps themselves.
-    if (poller)
-        *flag = counter_wait_bounded(c.wait_counter, __ldcg(c.epoch) * c.wait_blocks, timeout_ns) ? 1 : 0;
+    if (poller) {
+        const unsigned int target = __ldcg(c.epoch) * c.wait_blocks;
+        int ok = (int)(ld_acquire_u32(c.wait_counter) - target) >= 0;
+        if (!ok) {
+            // once a wait has run out somewhere in this forward, every later one gives up quickly
+            if (st && (__ldcg(&st->status) & L2J_DS_WAIT_TIMEOUT))
+                timeout_ns = kShortWaitNs;
+            ok = counter_wait_bounded(c.wait_counter, target, timeout_ns) ? 1 : 0;
+        }
+        *flag = ok;
+    }
     named_barrier_sync(bar_id, nthreads);   // orders the other threads' loads behind the poller's acquire
     return *flag != 0;
 }
@@ -234,7 +245,6 @@ constexpr int kRedOff = 1152;                     // 4 x (16-byte header + 128 f
 constexpr int kRedStride = 528;
 constexpr int kRopeOff = 3328;                    // float cos[64], sin[64] of the current position
 constexpr int kSmemHeader = 3840;                 // end of the fixed part (128-byte aligned)
-constexpr uint64_t kShortWaitNs = 2000;
 constexpr int kRingMaxThreads = 640;              // 18 consumer warps + producer + epilogue warp: 102 registers per thread
 constexpr int kPrologueRounds = 8;                // 16-byte loads of x per consumer thread in the prologue
 
@@ -289,7 +299,7 @@ __device__ __forceinline__ void trace_mark(const MvParams &p, int k)
         p.trace[blockIdx.x * 16 + k] = (unsigned long long)global_timer_ns();
 }
 
-template <bool F32, bool GRP, int CPT, int RT>
+template <bool F32, bool GRP, int CPT, int RT, bool LL>
 __global__ void __launch_bounds__(kRingMaxThreads, 1) matvec_ring_kernel(const __grid_constant__ MvParams p)
 {
     constexpr int EPC = F32 ? 4 : 16;   // elements per 16-byte chunk
@@ -464,7 +474,7 @@ __global__ void __launch_bounds__(kRingMaxThreads, 1) matvec_ring_kernel(const _
     if (warp == nw + 1) {
         // With a hand-over counter nothing is needed here: the position was fixed when the forward began and
         // every result this warp writes is computed from data the consumers have waited for.
-        if (p.chain.wait_counter == nullptr && !(p.ll.tp && p.ll.in_vec >= 0))
+        if (p.chain.wait_counter == nullptr && !LL)
             pdl_wait();
         const int pos = __ldcg(&p.state->cur_pos);
         bool lost = (__ldcg(&p.state->status) & L2J_DS_WAIT_TIMEOUT) != 0;
@@ -614,7 +624,7 @@ __global__ void __launch_bounds__(kRingMaxThreads, 1) matvec_ring_kernel(const _
     bool lost = false;
     // The input vector comes from the previous kernel.  In a tensor-parallel group it arrives element by
     // element with its sequence number and the loads below poll for it; otherwise wait for the kernel.
-    const bool ll_in = p.ll.tp != nullptr && p.ll.in_vec >= 0;
+    constexpr bool ll_in = LL;   // instantiated apart: the receive path needs registers the plain path must not pay for
     if (!ll_in && !chain_wait_group(p.chain, tid == 0, 1, ncons, wait_ns, reinterpret_cast<volatile int *>(smem + kScratchOff + 252)))
         lost = true;
     if (tid == 0)
@@ -640,7 +650,7 @@ __global__ void __launch_bounds__(kRingMaxThreads, 1) matvec_ring_kernel(const _
         const int64_t rep_off = (int64_t)(blockIdx.x % (unsigned)p.x_reps) * p.x_stride;
         const float *xin = p.x_in + rep_off;
         const float *rmsw = has_rms ? p.rms_w + rep_off : nullptr;
-        if (!ll_in) {
+        if constexpr (!ll_in) {
 #pragma unroll
             for (int j = 0; j < kPrologueRounds; ++j) {
                 const int idx = tid + j * ncons;
@@ -660,66 +670,65 @@ __global__ void __launch_bounds__(kRingMaxThreads, 1) matvec_ring_kernel(const _
             const bool has_work = blockIdx.x < (unsigned)p.total_stages;
             const float2 *rx = p.ll.tp->ll[p.ll.in_vec][p.ll.tp->rank];
             const int seq_in = ll_seq(p.ll, p.ll.in_idx);
-            float4 pa[kPrologueRounds], pb[kPrologueRounds];
 #pragma unroll
             for (int j = 0; j < kPrologueRounds; ++j) {
-                const int idx = tid + j * ncons;
                 xr[j] = make_float4(0.f, 0.f, 0.f, 0.f);
                 wr[j] = make_float4(1.f, 1.f, 1.f, 1.f);
-                if (j * ncons >= n4)
-                    break;
-                if (idx < n4 && has_work) {
-                    pa[j] = ld_pairs2(rx + (int64_t)idx * 4);
-                    pb[j] = ld_pairs2(rx + (int64_t)idx * 4 + 2);
-                    if (has_rms)
-                        wr[j] = ld_cg_f4_issue(rmsw + (int64_t)idx * 4);
-                }
             }
             uint64_t t_first = 0;
+            // four rounds of pairs in flight at a time (their sequence numbers double the registers a round needs)
 #pragma unroll
-            for (int j = 0; j < kPrologueRounds; ++j) {
-                const int idx = tid + j * ncons;
-                if (j * ncons >= n4)
+            for (int c0 = 0; c0 < kPrologueRounds; c0 += 4) {
+                if (c0 * ncons >= n4)
                     break;
-                if (idx < n4 && has_work) {
-                    while (__float_as_int(pa[j].y) != seq_in || __float_as_int(pa[j].w) != seq_in ||
-                           __float_as_int(pb[j].y) != seq_in || __float_as_int(pb[j].w) != seq_in) {
-                        const uint64_t now = global_timer_ns();
-                        if (t_first == 0)
-                            t_first = now;
-                        if (now - t_first > (lost ? kShortWaitNs : wait_ns)) {
-                            lost = true;
-                            break;
+                float4 pa[4], pb[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int idx = tid + (c0 + q) * ncons;
+                    if (idx < n4 && has_work) {
+                        pa[q] = ld_pairs2(rx + (int64_t)idx * 4);
+                        pb[q] = ld_pairs2(rx + (int64_t)idx * 4 + 2);
+                    }
+                }
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int idx = tid + (c0 + q) * ncons;
+                    if (idx < n4 && has_work) {
+                        while (__float_as_int(pa[q].y) != seq_in || __float_as_int(pa[q].w) != seq_in ||
+                               __float_as_int(pb[q].y) != seq_in || __float_as_int(pb[q].w) != seq_in) {
+                            const uint64_t now = global_timer_ns();
+                            if (t_first == 0)
+                                t_first = now;
+                            if (now - t_first > (lost ? kShortWaitNs : wait_ns)) {
+                                lost = true;
+                                break;
+                            }
+                            pa[q] = ld_pairs2(rx + (int64_t)idx * 4);
+                            pb[q] = ld_pairs2(rx + (int64_t)idx * 4 + 2);
                         }
-                        pa[j] = ld_pairs2(rx + (int64_t)idx * 4);
-                        pb[j] = ld_pairs2(rx + (int64_t)idx * 4 + 2);
+                        xr[c0 + q] = make_float4(pa[q].x, pa[q].z, pb[q].x, pb[q].z);
                     }
                 }
             }
             // The residual stream this rank keeps is read only now: the block may have started before the
-            // kernel that stored it had run (blocks of consecutive kernels share SMs), but the increments
-            // cannot be complete before that store is visible.
-            if (p.ll.base) {
-#pragma unroll
-                for (int j = 0; j < kPrologueRounds; ++j) {
-                    const int idx = tid + j * ncons;
-                    if (j * ncons >= n4)
-                        break;
-                    if (idx < n4 && has_work)
-                        xr[j] = ld_cg_f4_issue(p.ll.base + (int64_t)idx * 4);
-                }
-            }
+            // kernel that stored it had run (blocks of consecutive kernels share SMs at small shapes), but no
+            // increment can exist before that store is visible.  One add per element, as the single device's
+            // red.add does it.
 #pragma unroll
             for (int j = 0; j < kPrologueRounds; ++j) {
                 const int idx = tid + j * ncons;
                 if (j * ncons >= n4)
                     break;
                 if (idx < n4 && has_work) {
-                    // residual stream: one add per element, as the single device's red.add does it
-                    xr[j].x = p.ll.base ? __fadd_rn(xr[j].x, pa[j].x) : pa[j].x;
-                    xr[j].y = p.ll.base ? __fadd_rn(xr[j].y, pa[j].z) : pa[j].z;
-                    xr[j].z = p.ll.base ? __fadd_rn(xr[j].z, pb[j].x) : pb[j].x;
-                    xr[j].w = p.ll.base ? __fadd_rn(xr[j].w, pb[j].z) : pb[j].z;
+                    if (p.ll.base) {
+                        const float4 xo = ld_cg_f4_issue(p.ll.base + (int64_t)idx * 4);
+                        xr[j].x = __fadd_rn(xo.x, xr[j].x);
+                        xr[j].y = __fadd_rn(xo.y, xr[j].y);
+                        xr[j].z = __fadd_rn(xo.z, xr[j].z);
+                        xr[j].w = __fadd_rn(xo.w, xr[j].w);
+                    }
+                    if (has_rms)
+                        wr[j] = ld_cg_f4_issue(rmsw + (int64_t)idx * 4);
                     if (p.ll.write_back && blockIdx.x == 0)
                         __stcg(reinterpret_cast<float4 *>(p.ll.write_back + (int64_t)idx * 4), xr[j]);
                 }
@@ -1064,10 +1073,10 @@ MvPlan plan_matvec(int n, bool f32, bool paired, int rows, int blocks, int row_a
     return pl;
 }
 
-template <bool F32, bool GRP, int CPT, int RT>
+template <bool F32, bool GRP, int CPT, int RT, bool LL>
 static cudaError_t launch_ring_t(const LaunchCfg &lc, const MvPlan &plan, const MvParams &p)
 {
-    auto kern = matvec_ring_kernel<F32, GRP, CPT, RT>;
+    auto kern = matvec_ring_kernel<F32, GRP, CPT, RT, LL>;
     if (plan.threads > kRingMaxThreads)
         return cudaErrorInvalidConfiguration;
     cudaLaunchConfig_t cfg{};
@@ -1083,10 +1092,10 @@ static cudaError_t launch_ring_t(const LaunchCfg &lc, const MvPlan &plan, const 
     return cudaLaunchKernelEx(&cfg, kern, p);
 }
 
-template <bool F32, bool GRP, int CPT, int RT>
+template <bool F32, bool GRP, int CPT, int RT, bool LL>
 static cudaError_t prepare_ring_t()
 {
-    auto kern = matvec_ring_kernel<F32, GRP, CPT, RT>;
+    auto kern = matvec_ring_kernel<F32, GRP, CPT, RT, LL>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmemBlock);
     if (e != cudaSuccess)
         return e;
@@ -1110,7 +1119,9 @@ cudaError_t prepare_kernels()
     cudaError_t e;
     if ((e = prepare_attention()) != cudaSuccess)
         return e;
-#define X(F, G, C, R) if ((e = prepare_ring_t<F, G, C, R>()) != cudaSuccess) return e;
+#define X(F, G, C, R) \
+    if ((e = prepare_ring_t<F, G, C, R, false>()) != cudaSuccess) return e; \
+    if ((e = prepare_ring_t<F, G, C, R, true>()) != cudaSuccess) return e;
     L2J_RING_VARIANTS(X)
 #undef X
     return cudaSuccess;
@@ -1118,7 +1129,10 @@ cudaError_t prepare_kernels()
 
 cudaError_t launch_matvec_ring(const LaunchCfg &lc, const MvPlan &plan, bool f32, const MvParams &p)
 {
-#define X(F, G, C, R) if (f32 == F && plan.grouped == G && plan.cpt == C && plan.rt == R) return launch_ring_t<F, G, C, R>(lc, plan, p);
+    const bool ll = p.ll.tp != nullptr && p.ll.in_vec >= 0;   // the input arrives as (value, sequence number) pairs
+#define X(F, G, C, R) \
+    if (f32 == F && plan.grouped == G && plan.cpt == C && plan.rt == R) \
+        return ll ? launch_ring_t<F, G, C, R, true>(lc, plan, p) : launch_ring_t<F, G, C, R, false>(lc, plan, p);
     L2J_RING_VARIANTS(X)
 #undef X
     return cudaErrorInvalidConfiguration;
@@ -1226,6 +1240,10 @@ constexpr int kAttnMinChunk = 32;   // positions per block before the work is sp
 
 // Streams positions [t0, t0 + cnt) of head h and merges the block's lane groups: afterwards thread
 // tid < head holds (M, L, O[tid]) of those positions.  Called by the whole block.
+// PIPE: the next round of rows is requested before the arithmetic of the current one (long contexts: two
+// rounds in flight per warp); without it the loop is shorter and needs fewer registers (short contexts:
+// one round covers a block's positions and only latency counts).
+template <bool PIPE>
 __device__ __forceinline__ void attention_block(const AttnParams &p, int h, int t0, int cnt, int pos, float *asmem, int *s_flag,
                                                 unsigned long long *tr, float &M, float &L, float &O)
 {
@@ -1261,9 +1279,7 @@ __device__ __forceinline__ void attention_block(const AttnParams &p, int h, int 
     }
 
     // q and the newest K/V row come from the kernel in front
-    const bool lost_before = p.state && (__ldcg(&p.state->status) & L2J_DS_WAIT_TIMEOUT) != 0;   // then every later wait is short
-    if (!chain_wait_group(p.chain, tid == 0, 1, kAttnThreads, lost_before ? kShortWaitNs : (uint64_t)p.timeout_us * 1000ull, s_flag) &&
-        tid == 0)
+    if (!chain_wait_group(p.chain, tid == 0, 1, kAttnThreads, (uint64_t)p.timeout_us * 1000ull, s_flag, p.state) && tid == 0)
         atomicOr(&p.state->status, L2J_DS_WAIT_TIMEOUT);
     if (tr)
         tr[1] = global_timer_ns();
@@ -1285,18 +1301,26 @@ __device__ __forceinline__ void attention_block(const AttnParams &p, int h, int 
     }
     const int step = 4 * nslots;
     for (int ib = 0; ib < cnt; ib += step) {   // uniform trip count for the whole block
-        // the next round's rows are requested before this round's arithmetic: two rounds in flight per warp
-        float4 kn[4], vn[4];
+        float4 kn[PIPE ? 4 : 1], vn[PIPE ? 4 : 1];
         int idx[4];
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
             idx[u] = ib + u * nslots + slot;
-            const int nx = idx[u] + step;
-            kn[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-            vn[u] = kn[u];
-            if (active && nx < cnt) {
-                kn[u] = __ldcg(reinterpret_cast<const float4 *>(kb + (int64_t)nx * head + 4 * li));
-                vn[u] = __ldcg(reinterpret_cast<const float4 *>(vb + (int64_t)nx * head + 4 * li));
+            if constexpr (PIPE) {
+                const int nx = idx[u] + step;
+                kn[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                vn[u] = kn[u];
+                if (active && nx < cnt) {
+                    kn[u] = __ldcg(reinterpret_cast<const float4 *>(kb + (int64_t)nx * head + 4 * li));
+                    vn[u] = __ldcg(reinterpret_cast<const float4 *>(vb + (int64_t)nx * head + 4 * li));
+                }
+            } else if (ib > 0) {
+                kk[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                vv[u] = kk[u];
+                if (active && idx[u] < cnt) {
+                    kk[u] = __ldcg(reinterpret_cast<const float4 *>(kb + (int64_t)idx[u] * head + 4 * li));
+                    vv[u] = __ldcg(reinterpret_cast<const float4 *>(vb + (int64_t)idx[u] * head + 4 * li));
+                }
             }
         }
         float s[4];
@@ -1328,10 +1352,12 @@ __device__ __forceinline__ void attention_block(const AttnParams &p, int h, int 
             }
             m = mn;
         }
+        if constexpr (PIPE) {
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            kk[u] = kn[u];
-            vv[u] = vn[u];
+            for (int u = 0; u < 4; ++u) {
+                kk[u] = kn[u];
+                vv[u] = vn[u];
+            }
         }
     }
     if (tr)
@@ -1388,7 +1414,8 @@ __device__ __forceinline__ void attention_store(const AttnParams &p, int index, 
     }
 }
 
-__global__ void __launch_bounds__(kAttnThreads, 3) attention_kernel(const __grid_constant__ AttnParams p)
+template <bool PIPE>
+__global__ void __launch_bounds__(kAttnThreads, PIPE ? 2 : 3) attention_kernel(const __grid_constant__ AttnParams p)
 {
     extern __shared__ __align__(16) float asmem[];   // [slots][head + 4]: o, then m, l (16-byte aligned rows); [head + 4] block result
     __shared__ int s_last;
@@ -1427,7 +1454,7 @@ __global__ void __launch_bounds__(kAttnThreads, 3) attention_kernel(const __grid
     if (sp < nact) {
         const int t0 = sp * chunk;
         const int cnt = min(npos, t0 + chunk) - t0;
-        attention_block(p, h, t0, cnt, pos, asmem, &s_last, tr, M, L, O);
+        attention_block<PIPE>(p, h, t0, cnt, pos, asmem, &s_last, tr, M, L, O);
     }
 
     if (nact == 1) {
@@ -1530,7 +1557,7 @@ __global__ void __launch_bounds__(kAttnThreads, 3) attention_kernel(const __grid
 
 static cudaError_t prepare_attention()
 {
-    return cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAttnPadSmem);
+    return cudaFuncSetAttribute(attention_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAttnPadSmem);
 }
 
 cudaError_t launch_attention(const LaunchCfg &lc, const AttnParams &p)
@@ -1564,7 +1591,8 @@ cudaError_t launch_attention(const LaunchCfg &lc, const AttnParams &p)
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    return cudaLaunchKernelEx(&cfg, attention_kernel, p);
+    // the long-context launch (two blocks per SM, no cluster) is the one that streams
+    return p.smem_pad ? cudaLaunchKernelEx(&cfg, attention_kernel<true>, p) : cudaLaunchKernelEx(&cfg, attention_kernel<false>, p);
 }
 
 // =============================================================================================

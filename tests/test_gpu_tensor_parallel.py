@@ -68,6 +68,15 @@ def test_ranks_stories110m():
     _check_group(cfg, tensors, n, steps=900, n_prompt=16)   # crosses into the long-context attention launch
 
 
+def test_two_ranks_grouped_query_attention():
+    if _device_count() < 2:
+        pytest.skip("needs two GPUs")
+    cfg = ModelConfig(dim=256, hidden_dim=704, n_layers=3, n_heads=8, n_kv_heads=4, vocab_size=512, seq_len=128,
+                      shared_classifier=False)       # two query heads per kv head; hidden_dim not a multiple of 256
+    tensors = syn.synthetic_tensors(cfg, 3)
+    _check_group(cfg, tensors, 2, steps=128, n_prompt=8)
+
+
 def test_rejects_bad_groups():
     cfg = syn.SHAPES["stories15M"]          # 6 heads
     with pytest.raises(L.L2jError) as e:
