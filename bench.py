@@ -33,9 +33,11 @@ FORWARDS_PER_STEP = 288
 PUBLISHED_TOK_S = 20.9      # llama2j --mode CUDA, Llama-2-7B-chat, one RTX 4090 (reference README.md:46,63)
 FALLBACK_HBM_GBS = 6650.0
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu capture
-# summarised in profiles/; None until a capture exists for the shape.
-NCU_TRAFFIC_BYTES = {}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel (mean of the QKV, Wo, W1/W3 and
+# W2 launches of a layer), from the ncu capture summarised in profiles/matvec_ring_u8_llama2-7b-4layer_full.md,
+# taken with the cross-launch L2 prefetch switched off: ncu flushes the caches between kernels, so what a
+# launch prefetches for the next one would be counted here and read again there.  None for other shapes.
+NCU_TRAFFIC_BYTES = {"llama2-7b": 52351360}
 
 
 def bytes_per_token(cfg, pos: int) -> dict:

@@ -219,7 +219,10 @@ void fill_plan(MvParams &p, const MvPlan &pl)
         const int rs = p.paired ? (pl.rt * pl.rpp) / 2 : pl.rt * pl.rpp;
         p.rs = rs;
         p.rowbytes = p.f32 ? p.n * 4 : p.n;
-        p.tail_prefetch = 3;
+        {
+            const char *e = getenv("L2J_TAIL_PREFETCH");   // diagnostic: stages of the next launch asked into L2 by a block that ran out of work
+            p.tail_prefetch = e ? atoi(e) : 3;
+        }
         p.total_stages = 0;
         const int nseg = p.paired ? 1 : p.nseg;
         for (int i = 0; i < 3; ++i) {
