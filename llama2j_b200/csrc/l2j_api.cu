@@ -322,6 +322,7 @@ void link_ranks(l2j_ctx *c)
     c->cls.ll.in_vec = TPV_X;
     c->cls.ll.in_idx = 5 * c->nl - 1;
     c->cls.ll.base = c->x2;
+    c->cls.ll.write_back = c->x;   // the final residual stream stays readable (l2j_read_buffer)
 }
 
 // Builds the static kernel parameter blocks of every layer this context owns.
@@ -498,6 +499,8 @@ template <typename P>
 P unchained(P p)
 {
     p.chain = ChainLink{};
+    p.ll = LlLink{};
+    p.ll.in_vec = p.ll.out_vec = -1;
     return p;
 }
 
@@ -1835,6 +1838,14 @@ extern "C" int l2j_read_buffer(l2j_ctx *c, int which, int layer, int pos, float 
     }
     if (n > len)
         return fail(c, L2J_E_INVALID, "buffer %d holds %d floats", which, len);
+    if (c->tp_size > 1 && (which == 1 || which == 3)) {
+        // these vectors exist only as (value, sequence number) pairs in the receive buffers
+        std::vector<float2> pairs((size_t)n);
+        CK(c, cudaMemcpy(pairs.data(), c->ll_buf[which == 1 ? TPV_XB : TPV_HB], sizeof(float2) * (size_t)n, cudaMemcpyDeviceToHost));
+        for (int i = 0; i < n; ++i)
+            out[i] = pairs[(size_t)i].x;
+        return L2J_OK;
+    }
     CK(c, cudaMemcpy(out, src, sizeof(float) * (size_t)n, cudaMemcpyDeviceToHost));
     return L2J_OK;
 }

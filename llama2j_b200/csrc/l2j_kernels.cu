@@ -494,6 +494,10 @@ __global__ void __launch_bounds__(kRingMaxThreads, 1) matvec_ring_kernel(const _
         int rb = 0, rround = 0;
         const int tp_n = (p.ll.tp && p.ll.out_vec >= 0) ? p.ll.tp->n : 0;
         const int seq_out = tp_n ? ll_seq(p.ll, p.ll.out_idx) : 0;
+        // Block 0's consumer threads stored the assembled residual stream for a later kernel; its results must
+        // not be seen before that vector.  The fence is cumulative over what the consumers wrote before they
+        // handed the first partial sums to this warp, and it runs while they work on the next stage.
+        bool fence_first = LL && p.ll.write_back != nullptr && blockIdx.x == 0;
         for (;;) {
             if (!mbar_wait_bounded(sbase + kBarRedFull + 8 * rb, (uint32_t)rround & 1u, lost ? kShortWaitNs : wait_ns))
                 lost = true;
@@ -503,6 +507,10 @@ __global__ void __launch_bounds__(kRingMaxThreads, 1) matvec_ring_kernel(const _
                 break;
             const int row0 = rh[1] + p.seg[p.paired ? 0 : seg].out0;   // index in the output vector
             const float *red = reinterpret_cast<const float *>(rh + 4);
+            if (fence_first) {
+                __threadfence();
+                fence_first = false;
+            }
             if (p.epilogue == EPI_QKV_ROPE) {
                 if (lane < (nrows >> 1)) {
                     float v0 = 0.f, v1 = 0.f;
@@ -733,8 +741,7 @@ __global__ void __launch_bounds__(kRingMaxThreads, 1) matvec_ring_kernel(const _
                         __stcg(reinterpret_cast<float4 *>(p.ll.write_back + (int64_t)idx * 4), xr[j]);
                 }
             }
-            if (p.ll.write_back && blockIdx.x == 0)
-                __threadfence();   // the stored vector is read by a later kernel's blocks on other SMs
+            // (the epilogue warp of block 0 fences these stores before it publishes the block's first results)
         }
         float ssq = 0.f, amax = 0.f;
 #pragma unroll
