@@ -117,11 +117,12 @@ __device__ void finish_argmax_warp(const MvParams &p, int nblocks, int lane)
 // =============================================================================================
 // matvec_ring_kernel
 //
-// Persistent blocks, two per SM, that pull work (stages of a few matrix rows) from a global counter.
+// Persistent blocks, one per SM, that pull work (stages of a few matrix rows) from a global counter.
 // Warp roles:
-//   consumer warps 0..nw-1   wpr warps span one row (each lane owns CPT 16-byte chunks of it, with
-//                            the matching slice of x in registers); rpp such groups work on rpp
-//                            rows at once, RT rows each per stage
+//   consumer warps 0..nw-1   wpr warps span one row, rpp such groups work on rpp rows at once, RT rows
+//                            each per stage; every thread keeps its slice of x in registers.  Rows of
+//                            whole quantisation groups (GRP): four lanes share a group, a thread owns
+//                            64 bytes of it.  Otherwise a lane owns CPT 16-byte chunks a warp apart
 //   producer warp nw         one thread claims stages and streams their rows into the shared-memory
 //                            ring with bulk copies, as far ahead as the ring allows.  It does not
 //                            wait for the previous kernel (weights never depend on activations), so
@@ -134,11 +135,17 @@ __device__ void finish_argmax_warp(const MvParams &p, int nblocks, int lane)
 // place two blocks of one kernel on one SM and none on another, and a static split would then leave
 // the kernel waiting for the doubly loaded SM.
 //
-// u8 weights: x is converted once per block to 32-bit fixed point (one power-of-two scale per
-// vector) and split into four balanced signed byte limbs, so that a 16-byte chunk costs 16 dp4a
+// u8 weights: x is converted once per block to 24-bit fixed point (one power-of-two scale per
+// vector) and split into three balanced signed byte limbs, so that 16 weight bytes cost 12 dp4a
 // instructions (u8 weight x s8 limb, exact s32 accumulation) instead of 16 conversions + 16 FMAs.
-// Per chunk the four limb sums are recombined in FP32 and scaled by the group's (min, scale):
+// The limb sums (per 64 bytes in the grouped mapping, per 16 bytes otherwise) are recombined in FP32
+// and scaled by the group's (min, scale):
 //   sum_j (b_j * s + m) * x_j  =  s * sum_j b_j x_j  +  m * sum_j x_j.
+// The grid's step is at most 2^-25 of the vector's largest element, the order of one FP32 rounding of
+// a product.
+//
+// LL: the input vector arrives as (value, sequence number) pairs from the ranks of a tensor-parallel
+// group (see LlLink); instantiated apart so that the plain kernels do not pay for its registers.
 // =============================================================================================
 
 struct StageDesc {
@@ -1487,6 +1494,10 @@ __global__ void __launch_bounds__(kAttnThreads, PIPE ? 2 : 3) attention_kernel(c
             res[head] = M;
             res[head + 1] = L;
         }
+        // Only block 0 of the cluster writes results for the kernel behind; the others report at once, so that
+        // kernel does not wait for the cluster's second barrier.
+        if (sp != 0 && tid == 0)
+            chain_signal(p.chain);
         cl.sync();
         if (sp == 0 && tid < head) {
             float gm = -INFINITY;
@@ -1508,8 +1519,9 @@ __global__ void __launch_bounds__(kAttnThreads, PIPE ? 2 : 3) attention_kernel(c
         }
         if (tr)
             tr[5] = global_timer_ns();
+        if (sp == 0)
+            attention_signal(p);
         cl.sync();   // a block's shared memory must outlive the reads of block 0
-        attention_signal(p);
         return;
     }
 
