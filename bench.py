@@ -313,6 +313,17 @@ def main() -> None:
     value = world * args.steps * forwards / dev_s
     launches = int(stats.kernels_per_forward) * args.steps * forwards
 
+    # ---- the same loop by the reference's two other accounts (outside the timed region) -------------
+    # decode only: the sampled forwards after the prompt, by difference of two device-timed runs;
+    # reference style: (positions - 1) / time from the end of the first iteration (Run.java:682-706).
+    model.generate_greedy(prompt, PROMPT_LEN + 1)
+    head_us = model.last_generate_us()
+    model.generate_greedy(prompt, 1)
+    first_us = model.last_generate_us()
+    step_us = dev_us / args.steps
+    decode_only = (forwards - PROMPT_LEN - 1) / ((step_us - head_us) * 1e-6) if step_us > head_us else None
+    reference_style = (forwards - 1) / ((step_us - first_us) * 1e-6) if step_us > first_us else None
+
     # ---- end-to-end arm: the call the Java host makes, once per token, logits back to the host ----
     run_greedy_host_loop(model, prompt, min(forwards, 64), stop_on_bos=False)
     barrier()
@@ -359,6 +370,10 @@ def main() -> None:
         "e2e": {"value": e2e_value, "unit": "tok/s", "h2d_bytes_per_step": 16 * forwards,
                 "d2h_bytes_per_step": (4 * cfg.vocab_size + 32) * forwards},
         "gpu_launches": launches,
+        "accounts": {"all_forwards_tok_s": value / world, "decode_only_tok_s": decode_only,
+                     "reference_style_tok_s": reference_style,
+                     "note": "per GPU; decode only = the forwards after the forced prompt; reference style = "
+                             "(positions - 1) / time from the end of the first iteration (Run.java:682-706)"},
     }
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         model.close()

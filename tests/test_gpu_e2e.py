@@ -173,6 +173,22 @@ def test_config2_stories110m_to_position_1024(oracle):
     assert not flips, flips
 
 
+def test_long_context_positions_to_4096(oracle):
+    """The long-context workload at a small width: a 3840-token forced prompt through the decode path, then
+    greedy decode to position 4095 (the sequence length).  Every position is compared with the oracle; past
+    position 768 the forward runs the long-context attention launch (no cluster, pipelined loop, partial
+    results merged by the last block of a head), with up to 512 positions per block at the end."""
+    cfg = ModelConfig(dim=256, hidden_dim=704, n_layers=2, n_heads=4, n_kv_heads=2, vocab_size=2048, seq_len=4096,
+                      shared_classifier=False)
+    tensors = syn.synthetic_tensors(cfg, 5)
+    prompt = syn.synthetic_prompt(3840, 7, cfg.vocab_size)
+    toks, worst, flips, mode, _ = _compare_run(oracle, cfg, tensors, prompt, 4096)
+    assert mode["ring"]
+    assert worst < TOL, worst
+    assert not flips, flips
+    assert np.array_equal(toks[:3840], prompt)
+
+
 def test_host_side_faults(oracle):
     cfg = ModelConfig(dim=64, hidden_dim=176, n_layers=2, n_heads=4, n_kv_heads=2, vocab_size=96, seq_len=32,
                       shared_classifier=False)
