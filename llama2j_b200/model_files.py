@@ -107,6 +107,72 @@ def read_quant_cache(path: str, expected_floats: int) -> np.ndarray:
     return data
 
 
+MAX_CACHE_BYTES = 0x7FFFFFFF   # the length field is a Java int (BinFileWriter.java:26)
+
+
+def quant_cache_part_path(checkpoint_path: str, tensor: int, part: int) -> str:
+    """<dir>/<basename>_<tensor>.part<K>_<group>_<bits>.quant: one part of a tensor whose encoding does not fit
+    the reference's single cache file (every quantised matrix of the 13B shape: 3.4-7.4 GB encoded).  Each
+    part is a file in the reference's own format."""
+    single = quant_cache_path(checkpoint_path, tensor)
+    stem = single[: -len(f"_{QUANT_GROUP_SIZE}_{QUANT_BITS}.quant")]
+    return f"{stem}.part{part}_{QUANT_GROUP_SIZE}_{QUANT_BITS}.quant"
+
+
+def quant_cache_parts(n_floats: int, n_layers: int = 1, max_bytes: int = MAX_CACHE_BYTES):
+    """Splits a tensor of n_floats into parts of at most max_bytes encoded bytes: [(first_float, floats), ...].
+    Parts end on layer boundaries when the layers are whole groups (so a stage of a layer split needs whole
+    files only), else on group boundaries; one part if the tensor fits."""
+    if quant_bytes(n_floats) <= max_bytes:
+        return [(0, n_floats)]
+    max_groups = max_bytes // GROUP_BYTES
+    if max_groups <= 0:
+        raise ValueError("max_bytes is smaller than one group")
+    per_layer = n_floats // n_layers if n_layers > 0 and n_floats % n_layers == 0 else 0
+    unit = per_layer if per_layer and per_layer % QUANT_GROUP_SIZE == 0 and per_layer // QUANT_GROUP_SIZE <= max_groups \
+        else QUANT_GROUP_SIZE
+    units_per_part = (max_groups * QUANT_GROUP_SIZE) // unit
+    parts, start = [], 0
+    while start < n_floats:
+        count = min(units_per_part * unit, n_floats - start)
+        parts.append((start, count))
+        start += count
+    return parts
+
+
+def write_quant_cache_parts(checkpoint_path: str, tensor: int, groups: np.ndarray, n_floats: int, n_layers: int = 1,
+                            max_bytes: int = MAX_CACHE_BYTES) -> list:
+    """Writes the cache of one tensor: the reference's single file if it fits, else numbered parts."""
+    data = np.ascontiguousarray(groups, dtype=np.uint8).reshape(-1)
+    if data.size != quant_bytes(n_floats):
+        raise ValueError(f"{data.size} bytes for {n_floats} floats, expected {quant_bytes(n_floats)}")
+    parts = quant_cache_parts(n_floats, n_layers, max_bytes)
+    if len(parts) == 1:
+        path = quant_cache_path(checkpoint_path, tensor)
+        write_quant_cache(path, data)
+        return [path]
+    paths = []
+    for k, (first, count) in enumerate(parts):
+        g0 = first // QUANT_GROUP_SIZE
+        path = quant_cache_part_path(checkpoint_path, tensor, k)
+        write_quant_cache(path, data[g0 * GROUP_BYTES: g0 * GROUP_BYTES + quant_bytes(count)])
+        paths.append(path)
+    return paths
+
+
+def read_quant_cache_parts(checkpoint_path: str, tensor: int, n_floats: int, n_layers: int = 1,
+                           max_bytes: int = MAX_CACHE_BYTES):
+    """Reads the cache of one tensor, single file or parts; None if (any part of) it is missing."""
+    parts = quant_cache_parts(n_floats, n_layers, max_bytes)
+    if len(parts) == 1:
+        path = quant_cache_path(checkpoint_path, tensor)
+        return read_quant_cache(path, n_floats) if os.path.exists(path) else None
+    paths = [quant_cache_part_path(checkpoint_path, tensor, k) for k in range(len(parts))]
+    if not all(os.path.exists(p) for p in paths):
+        return None
+    return np.concatenate([read_quant_cache(p, count) for p, (_, count) in zip(paths, parts)])
+
+
 def read_checkpoint_header(path: str) -> ModelConfig:
     """Seven little-endian int32; a negative vocab size signals an unshared classifier (Run.java:563-573)."""
     with open(path, "rb") as f:

@@ -43,12 +43,13 @@ def parse_args(argv):
 def load_quant_tensor(path: str, cfg: mf.ModelConfig, tensor: int, device: int) -> np.ndarray:
     """readAsQuant (TransformerWeights.java:191-232): use the cache file if present, otherwise quantise the
     checkpoint tensor (on the GPU, bit-exact Quant.encode) and write the cache."""
-    cache = mf.quant_cache_path(path, tensor)
     n = cfg.tensor_floats(tensor)
-    if os.path.exists(cache):
-        return mf.read_quant_cache(cache, n)
+    layers = 1 if tensor == _lib.T_RMS_FINAL else cfg.n_layers
+    cached = mf.read_quant_cache_parts(path, tensor, n, layers)
+    if cached is not None:
+        return cached
     groups = syn.quant_encode(np.asarray(mf.read_checkpoint_tensor(path, cfg, tensor)), device)
-    mf.write_quant_cache(cache, groups)
+    mf.write_quant_cache_parts(path, tensor, groups, n, layers)   # numbered parts when one file cannot hold it
     return groups
 
 

@@ -106,3 +106,38 @@ def test_layer_allocation_uneven_budgets_and_parsing():
         assert a.static_bytes + (l - f + 1) * a.bytes_per_layer <= m
     with pytest.raises(ValueError):
         LayerAllocation.from_gpu_mem([], SHAPES["llama2-7b"])
+
+
+def test_quant_cache_parts_for_tensors_beyond_one_file(tmp_path):
+    """Tensors whose encoding exceeds the cache format's 2^31-1 bytes (every matrix of the 13B shape) are kept
+    as numbered parts, each a file in the reference's own format, split on layer boundaries."""
+    cfg13 = SHAPES["llama2-13b"]
+    n = cfg13.tensor_floats(L.T_W1)                                  # 40 x 13824 x 5120 floats
+    parts = mf.quant_cache_parts(n, cfg13.n_layers)
+    assert len(parts) > 1 and sum(c for _, c in parts) == n
+    per_layer = n // cfg13.n_layers
+    assert all(first % per_layer == 0 and count % per_layer == 0 for first, count in parts)
+    assert all(mf.quant_bytes(count) <= mf.MAX_CACHE_BYTES for _, count in parts)
+    assert mf.quant_cache_parts(cfg13.tensor_floats(L.T_RMS_ATT), cfg13.n_layers) == [(0, cfg13.tensor_floats(L.T_RMS_ATT))]
+    n7 = SHAPES["llama2-7b"].tensor_floats(L.T_W1)               # 1.49 GB encoded: one file, as in the reference
+    assert mf.quant_cache_parts(n7, 32) == [(0, n7)]
+
+    # round trip at a small size with a small limit: 6 layers of 3 groups, at most 2 layers per part
+    layers, per = 6, 3 * 256
+    rng = np.random.default_rng(0)
+    data = rng.integers(0, 256, mf.quant_bytes(layers * per), dtype=np.uint8)
+    ckpt = str(tmp_path / "model.bin")
+    limit = 2 * mf.quant_bytes(per) + 100
+    paths = mf.write_quant_cache_parts(ckpt, L.T_WQ, data, layers * per, layers, max_bytes=limit)
+    assert [os.path.basename(p) for p in paths] == [f"model_l_wq.part{k}_256_8.quant" for k in range(3)]
+    back = mf.read_quant_cache_parts(ckpt, L.T_WQ, layers * per, layers, max_bytes=limit)
+    assert np.array_equal(back, data)
+    assert np.array_equal(mf.read_quant_cache(paths[1], 2 * per), data[2 * mf.quant_bytes(per): 4 * mf.quant_bytes(per)])
+    os.remove(paths[2])
+    assert mf.read_quant_cache_parts(ckpt, L.T_WQ, layers * per, layers, max_bytes=limit) is None
+    # layers that are not whole groups: parts end on group boundaries instead
+    odd = mf.quant_cache_parts(6 * 288, 6, max_bytes=3 * 264)
+    assert sum(c for _, c in odd) == 6 * 288 and all(f % 256 == 0 for f, _ in odd)
+    # a tensor that fits keeps the reference's single file name
+    one = mf.write_quant_cache_parts(ckpt, L.T_WK, data[: mf.quant_bytes(per)], per, 1)
+    assert [os.path.basename(p) for p in one] == ["model_l_wk_256_8.quant"]
