@@ -70,6 +70,7 @@ struct l2j_ctx {
     unsigned int *work = nullptr;   // two counters per ring-kernel launch of a forward
     unsigned int *chain = nullptr;  // hand-over counters, one per kernel of a forward, each on its own 128-byte line
     bool chain_on = true;
+    bool kv_prefetch = true;
     bool attn_cluster = true;       // one thread-block cluster per head in the attention kernel
     unsigned long long *trace = nullptr;   // per-launch timelines, only when L2J_TRACE is set
     int ring_grid = 0;              // blocks per ring kernel
@@ -361,6 +362,7 @@ void build_launch_params(l2j_ctx *c)
         a.x_stride = c->dim_stride;
         a.rms_w = c->rms_att + (int64_t)li * c->reps * c->dim_stride;
         a.epilogue = EPI_QKV_ROPE;
+        a.kv_prefetch_below = c->kv_prefetch ? kLongContextPos : 0;   // beyond it the rows of a layer outgrow what L2 should hold
         a.q_out = c->q;
         a.k_cache = kc;
         a.v_cache = vc;
@@ -848,6 +850,8 @@ static int create_impl(const l2j_config *cfg, int device, int first_layer, int l
     CREATE_CK(dev_alloc(c, &c->blk_idx, c->ring_grid + 8, true));
     CREATE_CK(dev_alloc(c, &c->work, 2 * (4 * (int64_t)c->nl + 1), true));
     CREATE_CK(dev_alloc(c, &c->chain, kChainStride * (5 * (int64_t)c->nl + 2), true));   // + the epoch word
+    if (const char *e = getenv("L2J_KV_PREFETCH"))
+        c->kv_prefetch = atoi(e) != 0;
     if (const char *e = getenv("L2J_CHAIN"))
         c->chain_on = atoi(e) != 0;
     if (getenv("L2J_TRACE"))

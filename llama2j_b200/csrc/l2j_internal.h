@@ -154,6 +154,7 @@ struct MvParams {
     const float *rope_cos;   // [seq][head/2]
     const float *rope_sin;
     int dim, kv_dim, head, seq_len;
+    int kv_prefetch_below;   // QKV: below this position the cached K/V rows are asked into L2 for the attention kernel (0: never)
     // logits
     float *blk_val;          // per-block argmax candidates
     int *blk_idx;

@@ -495,6 +495,21 @@ __global__ void __launch_bounds__(kRingMaxThreads, 1) matvec_ring_kernel(const _
                 rope_s[i] = __ldg(p.rope_sin + (int64_t)pos * half + i);
             }
             __syncwarp();
+            // This warp has nothing to do until the first stage is reduced: ask L2 for the cached K and V rows
+            // of the heads this launch computes.  The attention kernel behind starts with a load of exactly
+            // those rows, and at short contexts that round trip (to HBM otherwise) is most of its run time.
+            if (pos > 0 && pos < p.kv_prefetch_below) {
+                constexpr int kRows = 32;                                  // 16 KB at head size 128
+                const int h0 = p.seg[1].out0 / p.head, nkv = p.seg[1].rows / p.head;
+                const int cpp = (pos + kRows - 1) / kRows;                 // chunks per head
+                const int total = 2 * nkv * cpp;
+                for (int i = (int)blockIdx.x * 32 + lane; i < total; i += (int)gridDim.x * 32) {
+                    const int which = i / (nkv * cpp), rem = i - which * nkv * cpp;
+                    const int h = rem / cpp, c = rem - h * cpp;
+                    const float *row = (which ? p.v_cache : p.k_cache) + ((int64_t)(h0 + h) * p.seq_len + c * kRows) * p.head;
+                    bulk_prefetch_l2(row, (uint32_t)(min(kRows, pos - c * kRows) * p.head) * 4u);
+                }
+            }
         }
         float best_v = -FLT_MAX;
         int best_i = 0x7fffffff;
