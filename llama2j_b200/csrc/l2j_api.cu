@@ -82,8 +82,9 @@ struct l2j_ctx {
     int tp_rank = 0, tp_size = 1;  // tensor parallel group this context belongs to
     TpTable *tp_dev = nullptr;     // the group's receive buffers (n = 0 until linked)
     float *x2 = nullptr;           // tensor parallel: second copy of the residual stream (the two alternate)
-    float2 *ll_buf[TPV_COUNT] = {nullptr, nullptr, nullptr};   // receive buffers: x increments, attention output, hidden vector
+    float2 *ll_buf[TPV_COUNT] = {nullptr, nullptr, nullptr, nullptr};   // receive buffers: x increments, attention output, hidden vector
     bool tp_linked = false;
+    bool cls_split = false;        // tensor parallel: the classifier's rows are split too (vocab divides by the ranks)
     cudaEvent_t ev_stage = nullptr;   // "this stage's step is done", waited for by the next stage's stream
     float *logits_host = nullptr;  // pinned
     float *x_host = nullptr;       // pinned
@@ -324,6 +325,10 @@ void link_ranks(l2j_ctx *c)
     c->cls.ll.in_idx = 5 * c->nl - 1;
     c->cls.ll.base = c->x2;
     c->cls.ll.write_back = c->x;   // the final residual stream stays readable (l2j_read_buffer)
+    if (c->cls_split) {
+        c->cls.ll.out_vec = TPV_CAND;
+        c->cls.ll.out_idx = 5 * c->nl;
+    }
 }
 
 // Builds the static kernel parameter blocks of every layer this context owns.
@@ -466,6 +471,12 @@ void build_launch_params(l2j_ctx *c)
         k.seg[0].hdr = nullptr;
         k.seg[0].flat0 = 0;
         k.seg[0].rows = c->cfg.vocab_size;
+        if (c->cls_split) {   // a block of the vocabulary per rank
+            const int per = c->cfg.vocab_size / c->tp_size;
+            k.seg[0].flat0 = (int64_t)c->tp_rank * per * c->dim;
+            k.seg[0].rows = per;
+            k.seg[0].out0 = c->tp_rank * per;
+        }
         k.nseg = 1;
         k.n = c->dim;
         k.f32 = 1;
@@ -706,6 +717,9 @@ static int create_impl(const l2j_config *cfg, int device, int first_layer, int l
     c->flags = flags;
     c->tp_rank = tp_rank;
     c->tp_size = tp_size;
+    c->cls_split = tp_size > 1 && cfg->vocab_size % tp_size == 0;
+    if (const char *e = getenv("L2J_TP_CLS_SPLIT"))
+        c->cls_split = c->cls_split && atoi(e) != 0;
     c->is_first = first_layer == 0;
     c->is_last = last_layer == cfg->n_layers - 1;
     c->dim = cfg->dim;
@@ -868,6 +882,7 @@ static int create_impl(const l2j_config *cfg, int device, int first_layer, int l
         CREATE_CK(dev_alloc(c, &c->ll_buf[TPV_X], c->dim, true));
         CREATE_CK(dev_alloc(c, &c->ll_buf[TPV_XB], c->dim, true));
         CREATE_CK(dev_alloc(c, &c->ll_buf[TPV_HB], c->hidden, true));
+        CREATE_CK(dev_alloc(c, &c->ll_buf[TPV_CAND], 2 * kMaxTp, true));
     }
     CREATE_CUDA(cudaEventCreateWithFlags(&c->ev_stage, cudaEventDisableTiming));
     CREATE_CUDA(cudaHostAlloc((void **)&c->logits_host, sizeof(float) * (size_t)cfg->vocab_size, cudaHostAllocDefault));
@@ -1553,16 +1568,20 @@ extern "C" int l2j_tp_forward(l2j_ctx *const *ranks, int n_ranks, int token, int
             return rc;
     }
     int status = L2J_OK;
+    const int vocab = ranks[0]->cfg.vocab_size;
     for (int i = 0; i < n_ranks; ++i) {
         l2j_ctx *c = ranks[i];
         CK(c, cudaSetDevice(c->device));
-        if (i == 0 && logits)
-            CK(c, cudaMemcpyAsync(c->logits_host, c->logits, sizeof(float) * (size_t)c->cfg.vocab_size, cudaMemcpyDeviceToHost,
+        // the whole logits from rank 0, or every rank's block of the vocabulary
+        const int first = c->cls_split ? i * (vocab / n_ranks) : 0;
+        const int count = c->cls_split ? vocab / n_ranks : (i == 0 ? vocab : 0);
+        if (logits && count > 0)
+            CK(c, cudaMemcpyAsync(c->logits_host + first, c->logits + first, sizeof(float) * (size_t)count, cudaMemcpyDeviceToHost,
                                   c->stream));
         CK(c, cudaMemcpyAsync(c->state_host, c->state, sizeof(SeqState), cudaMemcpyDeviceToHost, c->stream));
         CK(c, cudaStreamSynchronize(c->stream));
-        if (i == 0 && logits)
-            memcpy(logits, c->logits_host, sizeof(float) * (size_t)c->cfg.vocab_size);
+        if (logits && count > 0)
+            memcpy(logits + first, c->logits_host + first, sizeof(float) * (size_t)count);
         if (i == 0 && argmax)
             *argmax = c->state_host->argmax;
         const int r = finish_status(c);
@@ -1662,6 +1681,7 @@ extern "C" int l2j_reset(l2j_ctx *c)
         CK(c, cudaMemset(c->ll_buf[TPV_X], 0, sizeof(float2) * (size_t)c->dim));
         CK(c, cudaMemset(c->ll_buf[TPV_XB], 0, sizeof(float2) * (size_t)c->dim));
         CK(c, cudaMemset(c->ll_buf[TPV_HB], 0, sizeof(float2) * (size_t)c->hidden));
+        CK(c, cudaMemset(c->ll_buf[TPV_CAND], 0, sizeof(float2) * 2 * kMaxTp));
     }
     CK(c, cudaDeviceSynchronize());
     c->forwards = 0;

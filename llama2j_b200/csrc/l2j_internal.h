@@ -94,7 +94,7 @@ struct MvSeg {
 // output vector over the peer links, so each output element is produced by one rank in the same order
 // as on a single device: the ranks' vectors stay bitwise equal, and equal to the single-device ones.
 constexpr int kMaxTp = 8;
-enum TpVector { TPV_X = 0, TPV_XB = 1, TPV_HB = 2, TPV_COUNT = 3 };
+enum TpVector { TPV_X = 0, TPV_XB = 1, TPV_HB = 2, TPV_CAND = 3, TPV_COUNT = 4 };   // CAND: (max, index) of every rank's block of logits
 struct TpTable {
     int n;                             // ranks (0 until the group is linked)
     int rank;

@@ -96,6 +96,43 @@ __device__ void finish_argmax_warp(const MvParams &p, int nblocks, int lane)
             bi = oi;
         }
     }
+    if (p.ll.tp && p.ll.out_vec == TPV_CAND) {
+        // Tensor parallel: this rank holds a block of the vocabulary.  Its (maximum, index) goes to every rank
+        // as two (value, sequence number) pairs; every rank then takes the best of all candidates, lowest
+        // index first, so all ranks choose the same token without a further message.
+        const int n = p.ll.tp->n, me = p.ll.tp->rank;
+        const int seq = (int)(__ldcg(p.ll.epoch) * (unsigned int)p.ll.kernels + (unsigned int)p.ll.out_idx + 1u);
+        if (lane == 0)
+            for (int r = 0; r < n; ++r) {
+                st_pair(p.ll.tp->ll[TPV_CAND][r] + 2 * me, bv, seq);
+                st_pair(p.ll.tp->ll[TPV_CAND][r] + 2 * me + 1, __int_as_float(bi), seq);
+            }
+        bv = -FLT_MAX;
+        bi = 0x7fffffff;
+        if (lane < n) {
+            const float2 *mine = p.ll.tp->ll[TPV_CAND][me] + 2 * lane;
+            float4 c = ld_pairs2(mine);
+            const uint64_t t0 = global_timer_ns();
+            while (__float_as_int(c.y) != seq || __float_as_int(c.w) != seq) {
+                if (global_timer_ns() - t0 > (uint64_t)p.timeout_us * 1000ull) {
+                    atomicOr(&p.state->status, 0x1);   // L2J_DS_WAIT_TIMEOUT
+                    break;
+                }
+                c = ld_pairs2(mine);
+            }
+            bv = c.x;
+            bi = __float_as_int(c.z);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) {
+                bv = ov;
+                bi = oi;
+            }
+        }
+    }
     if (lane == 0) {
         SeqState *st = p.state;
         if (bi == 0x7fffffff)
