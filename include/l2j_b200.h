@@ -184,9 +184,10 @@ L2J_API int l2j_pipeline_generate_greedy(l2j_ctx *const *stages, int n_stages, c
 
 /* A context that holds every layer but works on rank `tp_rank`'s block of rows of each matrix
  * (whole heads for Wq/Wk/Wv and the attention, hidden_dim / tp_size rows of W1/W3, dim / tp_size
- * rows of Wo/W2); the classifier is replicated.  Each rank stores its results into every rank's
- * copy of the output vector over the peer links, so the copies stay bitwise equal and equal to a
- * single device's vectors.  Weights are uploaded to every rank with the usual calls.  n_heads,
+ * rows of Wo/W2, vocab_size / tp_size rows of the classifier when that divides, else all of them).
+ * Each rank sends its results to every rank over the peer links as (value, sequence number) pairs;
+ * every output element is computed by one rank in the single-device order, so logits and tokens
+ * are bitwise those of one device.  Weights are uploaded to every rank with the usual calls.  n_heads,
  * n_kv_heads and hidden_dim must divide by tp_size (at most 8).  The reference has no such mode
  * (its multi-GPU mode is the layer split above). */
 L2J_API int l2j_create_tp(const l2j_config *cfg, int device, int tp_rank, int tp_size, uint32_t flags, l2j_ctx **ctx);
