@@ -184,7 +184,8 @@ L2J_API int l2j_pipeline_generate_greedy(l2j_ctx *const *stages, int n_stages, c
 
 /* A context that holds every layer but works on rank `tp_rank`'s block of rows of each matrix
  * (whole heads for Wq/Wk/Wv and the attention, hidden_dim / tp_size rows of W1/W3, dim / tp_size
- * rows of Wo/W2, vocab_size / tp_size rows of the classifier when that divides, else all of them).
+ * rows of Wo/W2; the classifier is computed by every rank unless L2J_TP_CLS_SPLIT=1 is set in the
+ * environment, which splits its rows too and lets the ranks exchange their best candidates).
  * Each rank sends its results to every rank over the peer links as (value, sequence number) pairs;
  * every output element is computed by one rank in the single-device order, so logits and tokens
  * are bitwise those of one device.  Weights are uploaded to every rank with the usual calls.  n_heads,

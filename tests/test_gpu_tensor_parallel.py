@@ -77,6 +77,16 @@ def test_two_ranks_grouped_query_attention():
     _check_group(cfg, tensors, 2, steps=128, n_prompt=8)
 
 
+def test_two_ranks_split_classifier(monkeypatch):
+    """Opt-in mode: the classifier's rows are split too and the ranks exchange their best candidates."""
+    if _device_count() < 2:
+        pytest.skip("needs two GPUs")
+    monkeypatch.setenv("L2J_TP_CLS_SPLIT", "1")
+    cfg = syn.SHAPES["stories110M"]
+    tensors = syn.synthetic_tensors(cfg, 0)
+    _check_group(cfg, tensors, 2, steps=96, n_prompt=16)
+
+
 def test_rejects_bad_groups():
     cfg = syn.SHAPES["stories15M"]          # 6 heads
     with pytest.raises(L.L2jError) as e:
