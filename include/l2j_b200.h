@@ -80,6 +80,7 @@ enum l2j_tensor {
 #define L2J_F_NO_GRAPH 0x1    /* launch kernels directly instead of replaying a CUDA graph */
 #define L2J_F_NO_PDL 0x2      /* no programmatic dependent launch between consecutive kernels */
 #define L2J_F_SIMPLE 0x4      /* plain direct-load matvec kernels (cross-check path, slower) */
+#define L2J_F_STEP_KERNELS 0x8 /* one kernel per step of a layer (5 per layer) instead of one persistent kernel per token */
 
 typedef struct l2j_ctx l2j_ctx;
 

@@ -73,6 +73,7 @@ struct l2j_ctx {
     bool kv_prefetch = true;
     bool attn_cluster = true;       // one thread-block cluster per head in the attention kernel
     unsigned long long *trace = nullptr;   // per-launch timelines, only when L2J_TRACE is set
+    int wait_limit_us = 50000;      // bound of every device-side wait (copy barriers, hand-over counters, pair polls)
     int ring_grid = 0;              // blocks per ring kernel
     int early_fill = 1;             // ring stages a kernel may fetch before its predecessor has finished
     SeqState *state = nullptr;
@@ -92,6 +93,13 @@ struct l2j_ctx {
 
     MvPlan plan_qkv{}, plan_wo{}, plan_w13{}, plan_hidden{}, plan_cls{};
     bool use_ring = false;
+    bool use_fused = false;        // all layers of a token in one persistent launch (l2j_fused.cu)
+    MvPlan fplan[4]{};             // its stage geometry for QKV, Wo, W1/W3, W2
+    FusedParams fused{};
+    int fused_smem = 0, max_smem = 0;
+    float *rms_wmax_dev = nullptr;
+    float *fused_part = nullptr;
+    unsigned long long *fused_trace = nullptr;
     std::vector<LayerLaunch> layers;
     MvParams cls{};
     bool finalized = false;
@@ -216,10 +224,10 @@ void fill_plan(MvParams &p, const MvPlan &pl)
     p.hdr_off = pl.hdr_off;
     p.half_hdr = pl.half_hdr;
     p.xshare_bytes = pl.xshare_bytes;
-    p.timeout_us = 50000;
     {   // stage bookkeeping: a stage advances rt*rpp rows (half of that per matrix in paired mode)
         const int rs = p.paired ? (pl.rt * pl.rpp) / 2 : pl.rt * pl.rpp;
         p.rs = rs;
+        p.rt = pl.rt;
         p.rowbytes = p.f32 ? p.n * 4 : p.n;
         {
             const char *e = getenv("L2J_TAIL_PREFETCH");   // diagnostic: stages of the next launch asked into L2 by a block that ran out of work
@@ -331,6 +339,75 @@ void link_ranks(l2j_ctx *c)
     }
 }
 
+// Stage geometry of a phase of the persistent kernel: the lane mapping of plan_matvec (so that every
+// output element is computed exactly as by the per-step kernels), but stages of rpp rows (32 KB at the 7B
+// shape): the phases share one byte ring, and small stages keep more of it in flight and waste less where
+// it wraps.
+MvPlan plan_fused_phase(int n, bool paired, int row_align)
+{
+    MvPlan pl = plan_matvec(n, false, paired, 0, 0, row_align);
+    if (!pl.ok || !pl.grouped)
+        return MvPlan{};
+    const int rt = 1;   // one row per group of wpr warps and stage (the persistent kernel's consumers are built for that)
+    int rpp = pl.rpp;
+    const int align = paired ? (row_align > 2 ? row_align : 2) : row_align;
+    while (rpp > 1 && (rt * rpp) % align != 0)
+        --rpp;
+    if ((rt * rpp) % align != 0)
+        return MvPlan{};
+    pl.rt = rt;
+    pl.rpp = rpp;
+    pl.half_hdr = ((((rt * rpp * n / 2 + 255) / 256) + 4) * 8 + 15) & ~15;
+    const int payload = rt * rpp * n;
+    pl.hdr_off = payload;
+    pl.slot_bytes = (payload + 2 * pl.half_hdr + 127) & ~127;
+    pl.threads = kFusedThreads;
+    return pl;
+}
+
+// Parameters of the persistent kernel: the four matrix-vector phases of the first layer (the kernel adds
+// the per-layer steps) and the attention step's shape.
+void build_fused_params(l2j_ctx *c)
+{
+    FusedParams &F = c->fused;
+    F = FusedParams{};
+    const LayerLaunch &L = c->layers[0];
+    const MvParams *src[4] = {&L.qkv, &L.wo, &L.w13, &L.w2};
+    const int tensors[4][3] = {{L2J_T_WQ, L2J_T_WK, L2J_T_WV}, {L2J_T_WO, -1, -1}, {L2J_T_W1, L2J_T_W3, -1}, {L2J_T_W2, -1, -1}};
+    for (int k = 0; k < 4; ++k) {
+        MvParams &p = F.mv[k];
+        p = *src[k];
+        fill_plan(p, c->fplan[k]);
+        p.chain = ChainLink{};
+        p.next = nullptr;
+        p.trace = nullptr;
+        for (int s = 0; s < 3; ++s)
+            F.seg_step[k][s] = tensors[k][s] >= 0 ? c->per_layer[tensors[k][s]] : 0;
+    }
+    F.kv_step = (long long)c->cfg.n_kv_heads * c->cfg.seq_len * c->head;
+    F.rms_step = c->reps * c->dim_stride;
+    F.n_layers = c->nl;
+    F.rms_wmax = c->rms_wmax_dev;
+    F.q = c->q;
+    F.att_part = c->fused_part;
+    F.n_heads = c->cfg.n_heads;
+    F.kv_mul = c->kv_mul;
+    F.head = c->head;
+    F.seq_len = c->cfg.seq_len;
+    int gw = 1;
+    while (gw < c->head / 4)
+        gw <<= 1;
+    const int merge_bytes = kFusedConsWarps * (32 / gw) * (c->head + 4) * 4;
+    const int limb_bytes = 3 * (c->dim > c->hidden ? c->dim : c->hidden);
+    F.xarea_bytes = ((merge_bytes > limb_bytes ? merge_bytes : limb_bytes) + 127) & ~127;
+    F.ring_bytes = (c->fused_smem - 3840 - F.xarea_bytes) & ~127;
+    F.sync = c->chain;
+    F.epoch = c->chain + (int64_t)kChainStride * (5 * c->nl + 1);
+    F.state = c->state;
+    F.timeout_us = c->wait_limit_us;
+    F.trace = c->fused_trace;
+}
+
 // Builds the static kernel parameter blocks of every layer this context owns.
 void build_launch_params(l2j_ctx *c)
 {
@@ -348,6 +425,7 @@ void build_launch_params(l2j_ctx *c)
         base.head = c->head;
         base.seq_len = c->cfg.seq_len;
         base.state = c->state;
+        base.timeout_us = c->wait_limit_us;
         base.rope_cos = c->rope_cos;
         base.rope_sin = c->rope_sin;
 
@@ -393,7 +471,7 @@ void build_launch_params(l2j_ctx *c)
         t.chunk_max = c->chunk_max;
         t.pos_override = -1;
         t.cluster = c->attn_cluster ? 1 : 0;
-        t.timeout_us = 50000;
+        t.timeout_us = c->wait_limit_us;
         t.trace = c->trace ? c->trace + (int64_t)(4 * c->nl + 1 + li) * c->ring_grid * 16 : nullptr;
         t.trace_blocks = c->ring_grid;
         t.smem_pad = 0;
@@ -467,6 +545,7 @@ void build_launch_params(l2j_ctx *c)
         k.head = c->head;
         k.seq_len = c->cfg.seq_len;
         k.state = c->state;
+        k.timeout_us = c->wait_limit_us;
         k.seg[0].payload = reinterpret_cast<const uint8_t *>(c->wcls);
         k.seg[0].hdr = nullptr;
         k.seg[0].flat0 = 0;
@@ -498,6 +577,8 @@ void build_launch_params(l2j_ctx *c)
     }
     link_chain(c);
     link_ranks(c);
+    if (c->use_fused)
+        build_fused_params(c);
     for (int li = 0; li < c->nl; ++li) {
         LayerLaunch &L = c->layers[(size_t)li];
         L.attn_long = L.attn;          // same grid and hand-over counters
@@ -531,7 +612,13 @@ cudaError_t enqueue_forward(l2j_ctx *c, bool pdl, int *n_kernels, bool long_ctx)
     ++nk;
     lc.pdl = pdl;
     const int dim = c->dim, hidden = c->hidden;
-    for (int li = 0; li < c->nl; ++li) {
+    if (c->use_fused) {
+        // every layer of the range in one persistent launch; it waits for the begin kernel itself (the position
+        // and x are read behind a dependency wait, the weight stream starts before it)
+        if ((e = launch_fused(c->stream, pdl, c->ring_grid, c->fused_smem, c->fused)) != cudaSuccess) return e;
+        ++nk;
+    }
+    for (int li = 0; li < c->nl && !c->use_fused; ++li) {
         LayerLaunch &L = c->layers[(size_t)li];
         if (c->use_ring) {
             // The first ring kernel of a forward takes a full dependency on the begin kernel: the attention
@@ -611,7 +698,7 @@ bool try_capture(l2j_ctx *c, bool pdl, bool long_ctx)
 // step number of a greedy loop); it selects the attention regime.
 int launch_forward(l2j_ctx *c, int pos)
 {
-    const bool long_ctx = c->use_ring && pos >= kLongContextPos;
+    const bool long_ctx = c->use_ring && !c->use_fused && pos >= kLongContextPos;
     cudaGraphExec_t ex = long_ctx ? c->exec_long : c->exec;
     if (ex) {
         CK(c, cudaGraphLaunch(ex, c->stream));
@@ -906,6 +993,36 @@ static int create_impl(const l2j_config *cfg, int device, int first_layer, int l
     c->plan_cls = plan_matvec(c->dim, true, false);
     c->use_ring = !(flags & L2J_F_SIMPLE) && c->plan_qkv.ok && c->plan_wo.ok && c->plan_w13.ok && c->plan_hidden.ok &&
                   c->plan_cls.ok && (head % 2 == 0);
+    {   // one persistent launch per token where every matrix has rows of whole quantisation groups
+        bool fused = c->use_ring && tp_size == 1 && !(flags & L2J_F_STEP_KERNELS) && c->reps == 1 && c->dim % kGroup == 0 &&
+                     c->hidden % kGroup == 0;
+        if (const char *e = getenv("L2J_FUSED"))   // diagnostic: A/B against the per-step kernels
+            fused = fused && atoi(e) != 0;
+        if (fused) {
+            c->fplan[0] = plan_fused_phase(c->dim, false, 2);
+            c->fplan[1] = plan_fused_phase(c->dim, false, 1);
+            c->fplan[2] = plan_fused_phase(c->dim, true, 1);
+            c->fplan[3] = plan_fused_phase(c->hidden, false, 1);
+            fused = c->fplan[0].ok && c->fplan[1].ok && c->fplan[2].ok && c->fplan[3].ok;
+        }
+        if (fused) {
+            CREATE_CUDA(prepare_fused(&c->max_smem));
+            c->fused_smem = c->max_smem < 232448 ? c->max_smem : 232448;
+            int largest = 0;
+            for (int k = 0; k < 4; ++k)
+                largest = c->fplan[k].slot_bytes > largest ? c->fplan[k].slot_bytes : largest;
+            const int limb_bytes = 3 * (c->dim > c->hidden ? c->dim : c->hidden);
+            if (c->fused_smem - 3840 - limb_bytes - 4096 < 3 * largest)
+                fused = false;   // the ring would not hold three stages
+        }
+        if (fused) {
+            CREATE_CK(dev_alloc(c, &c->rms_wmax_dev, 2 * (int64_t)c->nl, true));
+            CREATE_CK(dev_alloc(c, &c->fused_part, (int64_t)cfg->n_heads * kAttSlots * (head + 4), true));
+            if (getenv("L2J_TRACE"))
+                CREATE_CK(dev_alloc(c, &c->fused_trace, (int64_t)c->ring_grid * 5 * c->nl * 4, true));
+        }
+        c->use_fused = fused;
+    }
     CREATE_CUDA(cudaStreamSynchronize(c->stream));
     CREATE_CUDA(cudaDeviceSynchronize());
 #undef CREATE_CK
@@ -1108,6 +1225,14 @@ extern "C" int l2j_finalize(l2j_ctx *c)
             CK(c, cudaMemcpy(w.data(), c->rms_final, sizeof(float) * (size_t)dim, cudaMemcpyDeviceToHost));
             c->cls.rms_wmax = vmax(w.data(), dim);
         }
+        if (c->use_fused) {
+            std::vector<float> wm(2 * (size_t)c->nl);
+            for (int li = 0; li < c->nl; ++li) {
+                wm[2 * (size_t)li] = c->layers[(size_t)li].qkv.rms_wmax;
+                wm[2 * (size_t)li + 1] = c->layers[(size_t)li].w13.rms_wmax;
+            }
+            CK(c, cudaMemcpy(c->rms_wmax_dev, wm.data(), sizeof(float) * wm.size(), cudaMemcpyHostToDevice));
+        }
     }
 
     {   // device copies of the launch parameters, chained in launch order, for the cross-launch L2 prefetch
@@ -1139,7 +1264,7 @@ extern "C" int l2j_finalize(l2j_ctx *c)
                 try_capture(c, false, false);
             }
         }
-        if (c->exec && c->use_ring && c->cfg.seq_len > kLongContextPos)
+        if (c->exec && c->use_ring && !c->use_fused && c->cfg.seq_len > kLongContextPos)
             try_capture(c, c->pdl_on, true);   // without it the long regime is enqueued kernel by kernel
     }
     c->finalized = true;
@@ -2041,6 +2166,7 @@ extern "C" int l2j_k_matvec_i8(int device, uint32_t flags, const void *groups, i
         p.nseg = 1;
         p.n = n;
         fill_plan(p, pl);
+        p.timeout_us = 50000;
         p.x_in = dx;
         p.x_reps = 1;
         p.y_reps = 1;
@@ -2102,6 +2228,7 @@ extern "C" int l2j_k_matvec_f32(int device, uint32_t flags, const float *w, int 
     p.f32 = 1;
     if (!(flags & L2J_F_SIMPLE) && pl.ok) {
         fill_plan(p, pl);
+        p.timeout_us = 50000;
         LaunchCfg lc{nullptr, false, prop.multiProcessorCount};
         KCK(launch_matvec_ring(lc, pl, true, p));
     } else {

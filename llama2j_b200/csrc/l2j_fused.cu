@@ -1,0 +1,986 @@
+// fused_layers_kernel: every layer of a token in ONE persistent launch (sm_100a).
+//
+// The per-step kernels of l2j_kernels.cu stream at HBM speed but pay a start-up chain at each of
+// their five boundaries per layer: a block holds nearly all of an SM's shared memory, so the next
+// kernel's block cannot become resident, let alone prefetch, before the one in front has left.
+// Here the blocks never leave.  One block per SM; its warps keep their roles for the whole token:
+//
+//   producer thread   walks the fixed sequence of stages of this block (layer by layer: QKV rows,
+//                     cached K/V rows of the attention step, Wo rows, W1/W3 row pairs, W2 rows) and
+//                     streams them with bulk copies (TMA engine) into ONE shared-memory byte ring,
+//                     as far ahead as the ring has room.  Weights and old cache rows never depend
+//                     on this token's activations, so while the consumers wait at a phase boundary
+//                     the ring fills with the next phase: HBM does not idle.
+//   consumer warps    per phase: wait for the hand-over counter of the phase in front, load the
+//                     input vector (for Wo: merge the attention partials), RMSNorm, fixed-point
+//                     limbs, then dp4a over the block's stages as they land.
+//   epilogue warp     folds the per-warp partial sums of a stage and applies RoPE + cache write,
+//                     residual add or SwiGLU; after the block's last stage of a phase it bumps the
+//                     phase's counter (release), which is what the other blocks' consumers poll.
+//
+// Stages are dealt to the blocks round-robin, continuing across phases, so every block streams the
+// same number of bytes per token (+- one stage).  The attention step's units (head, 64 positions)
+// are dealt in contiguous runs, a block folds the units of one head into one partial (m, l, o), and
+// the Wo phase's prologue merges the few partials of a head (at most kAttSlots) in a fixed order.
+//
+// Arithmetic per output element is that of matvec_ring_kernel (same lane mapping, same reduction
+// order), so the matrix-vector products are bitwise those of the per-step kernels.
+//
+// Blocks wait for each other, so all of them must be resident: the grid is one block per SM and the
+// launch is cooperative where the driver allows it.  Every wait is bounded by the global timer; a wait
+// that runs out raises L2J_DS_WAIT_TIMEOUT in the status word and the block drains without stalling.
+//
+// Reference counterparts (paths relative to src/main/java/com/lastbot/llama2j/): the layer body of
+// Run.java:418-508 with kernel/MatMul.java:360-444, RootMeanSquare.java:78-118,
+// WeightNormalizeAndScale.java:191-239, ApplyRope.java:144-182, AttentionLoop.java:116-164,
+// ExpSumNormalize.java:82-131, AccumWeightedValue.java:148-173, Accum.java:70-83, Silu.java:118-135.
+
+#include "l2j_device.cuh"
+#include "l2j_internal.h"
+
+#include <cfloat>
+#include <cmath>
+
+#define L2J_DS_WAIT_TIMEOUT 0x1
+
+namespace l2j {
+
+static_assert(sizeof(FusedParams) <= 4000, "the parameter block must fit the kernel parameter space");
+
+namespace {
+
+constexpr int kFDesc = 16;              // stage descriptors (and full/empty barrier pairs) in flight
+constexpr int kFRedBufs = 4;
+constexpr int kFBarFull = 0;            // uint64 full[16]
+constexpr int kFBarEmpty = 128;         // uint64 empty[16]
+constexpr int kFBarRedFull = 256;       // uint64 red_full[4]
+constexpr int kFBarRedEmpty = 288;      // uint64 red_empty[4]
+constexpr int kFFlag = 320;             // int: result of the poll of a hand-over counter
+constexpr int kFVStart = 3264;          // int vstart[16]: the producer's bookkeeping of where each stage in flight begins
+constexpr int kFScratch = 384;          // float scratch[64]
+constexpr int kFDescOff = 640;          // FStage desc[16]
+constexpr int kFRedOff = 1152;          // 4 x (16-byte header + 128 floats)
+constexpr int kFRedStride = 528;
+constexpr int kFRopeOff = 3328;         // float cos[64], sin[64] of the token's position
+constexpr int kFHeader = 3840;          // end of the fixed part (128-byte aligned)
+constexpr int kFCons = kFusedConsWarps * 32;
+constexpr int kFRounds = 8;             // 16-byte loads of the input vector per consumer thread at most
+constexpr int kFMergeRounds = 4;        // the same for the phase that merges the attention partials (its vector has dim elements)
+constexpr uint64_t kFShortWaitNs = 2000;
+
+struct FStage {
+    int seg, row0, nrows, e0a, e0b, off, aux, pad;
+    // attention stage: seg = head, row0 = first position, nrows = positions (newest included),
+    // e0a = positions that travel through the ring (older than the token), aux = byte offset of the V rows
+};
+
+__device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c)
+{
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+// Bulk copy without a cache hint (cached K/V rows are read again by the next token).
+__device__ __forceinline__ void bulk_g2s_plain(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
+                 "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
+template <int RT, int STEP>
+struct Fold {
+    static __device__ __forceinline__ float run(const float (&v)[RT], int lane)
+    {
+        if constexpr (RT == 1) {
+            float k = v[0];
+#pragma unroll
+            for (int o = STEP; o > 0; o >>= 1)
+                k += __shfl_xor_sync(0xffffffffu, k, o);
+            return k;
+        } else {
+            constexpr int H = RT / 2;
+            const bool up = (lane & STEP) != 0;
+            float k[H];
+#pragma unroll
+            for (int i = 0; i < H; ++i) {
+                const float keep = up ? v[H + i] : v[i];
+                const float send = up ? v[i] : v[H + i];
+                k[i] = keep + __shfl_xor_sync(0xffffffffu, send, STEP);
+            }
+            return Fold<H, STEP / 2>::run(k, lane);
+        }
+    }
+};
+
+// How the attention step of a token at position `pos` is dealt to the blocks: units of (head, chunk of
+// kAttChunk positions), head-major, in contiguous runs over the first `ga` blocks.
+struct AttSplit {
+    int nchunk, units, ga;
+};
+
+__device__ __forceinline__ AttSplit att_split(const FusedParams &P, int pos, int grid)
+{
+    AttSplit a;
+    a.nchunk = (pos + kAttChunk) / kAttChunk;   // ceil((pos + 1) / chunk)
+    a.units = P.n_heads * a.nchunk;
+    a.ga = min(min(grid, P.n_heads * kAttMaxSplit), a.units);
+    return a;
+}
+
+__device__ __forceinline__ int att_first_unit(const AttSplit &a, int b)
+{
+    return (int)(((long long)b * a.units) / a.ga);
+}
+
+__device__ __forceinline__ int att_block_of(const AttSplit &a, int u)
+{
+    return (int)((((long long)(u + 1)) * a.ga + a.units - 1) / a.units) - 1;
+}
+
+// Stage index -> (segment, first row, row count) of a ring phase.
+__device__ __forceinline__ void stage_rows(const MvParams &p, int s, int &seg, int &row0, int &nrows)
+{
+    seg = 0;
+    if (!p.paired && p.nseg > 1) {
+        if (s >= p.seg_stages[0]) {
+            s -= p.seg_stages[0];
+            seg = 1;
+            if (s >= p.seg_stages[1]) {
+                s -= p.seg_stages[1];
+                seg = 2;
+            }
+        }
+    }
+    row0 = s * p.rs;
+    nrows = min(p.rs, p.seg[seg].rows - row0);
+}
+
+__device__ __forceinline__ int first_stage_of(int b, int rot, int grid)
+{
+    int f = b - rot;
+    return f < 0 ? f + grid : f;
+}
+
+__device__ __forceinline__ void fused_trace(const FusedParams &P, int phase_index, int k)
+{
+    if (P.trace)
+        P.trace[((int64_t)blockIdx.x * (5 * P.n_layers) + phase_index) * 4 + k] = (unsigned long long)global_timer_ns();
+}
+
+// -------------------------------------------------------------------------------------------------
+// producer
+// -------------------------------------------------------------------------------------------------
+
+struct Producer {
+    uint8_t *smem;
+    uint32_t sbase, ring_base;
+    int vhead;              // bytes handed out so far (positions in the ring are vhead mod ring_bytes); < 2^31 per token and block
+    int ring_bytes;
+    int seq, tail;          // descriptors issued / known to be released
+    bool lost;
+    uint64_t wait_ns;
+
+    // Room for `bytes` contiguous bytes and a free descriptor; returns the offset in the ring.
+    __device__ __forceinline__ uint32_t acquire(uint32_t bytes)
+    {
+        int *vstart = reinterpret_cast<int *>(smem + kFVStart);
+        int off = vhead % ring_bytes;
+        if (off + (int)bytes > ring_bytes) {
+            vhead += ring_bytes - off;
+            off = 0;
+        }
+        const int vend = vhead + (int)bytes;
+        while (tail < seq && (seq - tail >= kFDesc || vend - ring_bytes > vstart[tail % kFDesc])) {
+            if (!mbar_wait_bounded(sbase + kFBarEmpty + 8 * (tail % kFDesc), (uint32_t)(tail / kFDesc) & 1u,
+                                   lost ? kFShortWaitNs : wait_ns))
+                lost = true;
+            ++tail;
+        }
+        vstart[seq % kFDesc] = vhead;
+        vhead = (vend + 127) & ~127;
+        return (uint32_t)off;
+    }
+};
+
+__device__ __forceinline__ void produce_ring_stage(Producer &pr, const FusedParams &P, const MvParams &p, int k, int layer, int s,
+                                                   uint64_t pol)
+{
+    const uint32_t off = pr.acquire((uint32_t)p.slot_bytes);
+    const int e = pr.seq % kFDesc;
+    const uint32_t full = pr.sbase + kFBarFull + 8 * e;
+    FStage *desc = reinterpret_cast<FStage *>(pr.smem + kFDescOff) + e;
+    int seg, row0, nrows;
+    stage_rows(p, s, seg, row0, nrows);
+    const uint32_t dst = pr.ring_base + off;
+    const uint32_t pbytes = (uint32_t)nrows * (uint32_t)p.rowbytes;
+    desc->seg = seg;
+    desc->row0 = row0;
+    desc->nrows = nrows;
+    desc->off = (int)off;
+    if (!p.paired) {
+        const int64_t flat = p.seg[seg].flat0 + (int64_t)layer * P.seg_step[k][seg] + (int64_t)row0 * p.n;
+        const int64_t ga = (flat >> 8) & ~(int64_t)1;
+        const int64_t gl = (flat + pbytes - 1) >> 8;
+        const uint32_t hbytes = (uint32_t)(((gl - ga + 2) & ~(int64_t)1) * 8);
+        desc->e0a = (int)(flat - ga * 256);
+        desc->e0b = 0;
+        mbar_arrive_expect_tx(full, pbytes + hbytes);
+        bulk_g2s(dst, p.seg[seg].payload + flat, pbytes, full, pol);
+        bulk_g2s(dst + (uint32_t)p.hdr_off, p.seg[seg].hdr + ga, hbytes, full, pol);
+    } else {
+        int64_t flat[2], ga[2];
+        uint32_t hbytes[2];
+        const int R = p.rt * p.rpp;
+        for (int h = 0; h < 2; ++h) {
+            flat[h] = p.seg[h].flat0 + (int64_t)layer * P.seg_step[k][h] + (int64_t)row0 * p.n;
+            ga[h] = (flat[h] >> 8) & ~(int64_t)1;
+            const int64_t gl = (flat[h] + pbytes - 1) >> 8;
+            hbytes[h] = (uint32_t)(((gl - ga[h] + 2) & ~(int64_t)1) * 8);
+        }
+        desc->e0a = (int)(flat[0] - ga[0] * 256);
+        desc->e0b = (int)(flat[1] - ga[1] * 256);
+        mbar_arrive_expect_tx(full, 2 * pbytes + hbytes[0] + hbytes[1]);
+        for (int h = 0; h < 2; ++h) {
+            bulk_g2s(dst + (uint32_t)(h * (R / 2)) * (uint32_t)p.rowbytes, p.seg[h].payload + flat[h], pbytes, full, pol);
+            bulk_g2s(dst + (uint32_t)p.hdr_off + (uint32_t)(h * p.half_hdr), p.seg[h].hdr + ga[h], hbytes[h], full, pol);
+        }
+    }
+    ++pr.seq;
+}
+
+__device__ __forceinline__ void produce_att_stage(Producer &pr, const FusedParams &P, int layer, int unit, const AttSplit &a, int pos)
+{
+    const int h = unit / a.nchunk, c = unit - h * a.nchunk;
+    const int t0 = c * kAttChunk;
+    const int cnt = min(pos + 1, t0 + kAttChunk) - t0;       // positions of the unit, the token's own included
+    const int old = min(pos, t0 + kAttChunk) - t0;           // those that were cached by earlier tokens
+    const uint32_t kbytes = (uint32_t)old * (uint32_t)P.head * 4u;
+    const uint32_t voff = (kbytes + 127u) & ~127u;
+    const uint32_t off = pr.acquire(2 * voff);
+    const int e = pr.seq % kFDesc;
+    const uint32_t full = pr.sbase + kFBarFull + 8 * e;
+    FStage *desc = reinterpret_cast<FStage *>(pr.smem + kFDescOff) + e;
+    desc->seg = h;
+    desc->row0 = t0;
+    desc->nrows = cnt;
+    desc->e0a = old;
+    desc->off = (int)off;
+    desc->aux = (int)voff;
+    if (old > 0) {
+        const int kvh = h / P.kv_mul;
+        const int64_t row = ((int64_t)kvh * P.seq_len + t0) * P.head;
+        const float *kc = P.mv[0].k_cache + (int64_t)layer * P.kv_step + row;
+        const float *vc = P.mv[0].v_cache + (int64_t)layer * P.kv_step + row;
+        mbar_arrive_expect_tx(full, 2 * kbytes);
+        bulk_g2s_plain(pr.ring_base + off, kc, kbytes, full);
+        bulk_g2s_plain(pr.ring_base + off + voff, vc, kbytes, full);
+    } else {
+        mbar_arrive(full);   // only the token's own row: nothing travels through the ring
+    }
+    ++pr.seq;
+}
+
+// -------------------------------------------------------------------------------------------------
+// consumers
+// -------------------------------------------------------------------------------------------------
+
+struct Consumer {
+    int seq;             // stages consumed so far (descriptor index = seq mod kFDesc)
+    int rb, rround;      // position in the ring of reduction buffers
+    bool lost, lost_before;
+};
+
+// Waits until counter `ctr` has reached `target`: one thread polls, the others follow through barrier 1.
+__device__ __forceinline__ void consumers_wait(const unsigned int *ctr, unsigned int target, uint8_t *smem, Consumer &cs, uint64_t wait_ns)
+{
+    volatile int *flag = reinterpret_cast<volatile int *>(smem + kFFlag);
+    if (threadIdx.x == 0) {
+        int ok = (int)(ld_acquire_u32(ctr) - target) >= 0;
+        if (!ok)
+            ok = counter_wait_bounded(ctr, target, cs.lost ? kFShortWaitNs : wait_ns) ? 1 : 0;
+        *flag = ok;
+    }
+    named_barrier_sync(1, kFCons);
+    if (*flag == 0)
+        cs.lost = true;
+}
+
+// One matrix-vector phase of the block: prologue (input vector -> fixed-point limbs in shared memory)
+// and the block's `nmine` stages.  MERGE: the input is the attention output, assembled from the partial
+// results of the blocks that worked on each head.
+enum InputMode { IN_RMS = 0, IN_PLAIN = 1, IN_MERGE = 2 };
+
+template <int MODE>
+__device__ __forceinline__ void consume_ring_phase(const FusedParams &P, const MvParams &p, int layer, int nmine, const float *rms_w,
+                                                   float rms_wmax, const AttSplit &as, uint8_t *smem, uint32_t sbase, Consumer &cs,
+                                                   uint64_t wait_ns, int pidx)
+{
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int nw = p.rpp * p.wpr;
+    const int ncons = nw * 32;
+    const bool active = warp < nw;
+    const int rsub = warp / p.wpr;
+    const int wi = warp - rsub * p.wpr;
+    constexpr bool MERGE = MODE == IN_MERGE;
+    constexpr int RT = 1;   // rows per thread and stage: a stage holds one row per group of wpr warps
+    const int n = p.n;
+    const int R = RT * p.rpp;
+    const int rowbytes = n;
+    uint8_t *share = smem + kFHeader;
+    float *scratch = reinterpret_cast<float *>(smem + kFScratch);
+
+    int chunk[4];
+    const int g = wi * 8 + (lane >> 2);
+    const bool gvalid = active && g < (n >> 8);
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+        chunk[k] = g * 16 + 4 * (k ^ ((lane >> 2) & 1)) + (lane & 3);
+
+    float inv = 1.0f;
+    {
+        const int n4 = n >> 2;
+        // a vector of dim elements (RMSNorm'd input, merged attention output) takes four rounds at most, the
+        // hidden vector eight: the host checks it
+        constexpr int kRounds = MODE == IN_PLAIN ? kFRounds : kFMergeRounds;
+        constexpr bool has_rms = MODE == IN_RMS;
+        float4 xr[kRounds], wr[has_rms ? kRounds : 1];
+#pragma unroll
+        for (int j = 0; j < kRounds; ++j) {
+            const int idx = tid + j * ncons;
+            xr[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if constexpr (has_rms)
+                wr[j] = make_float4(1.f, 1.f, 1.f, 1.f);
+            if (j * ncons >= n4)
+                break;
+            if (active && idx < n4) {
+                if constexpr (!MERGE) {
+                    xr[j] = ld_cg_f4_issue(p.x_in + (int64_t)idx * 4);
+                    if constexpr (has_rms)
+                        wr[j] = ld_cg_f4_issue(rms_w + (int64_t)idx * 4);
+                } else {
+                    // The partials of head h were written by blocks b0..b1 of the attention phase, one slot each, in
+                    // block order; merged here in that order (the result does not depend on which SM ran what).
+                    const int e = idx * 4;
+                    const int h = e / P.head, d = e - h * P.head;
+                    const int u0 = h * as.nchunk;
+                    const int b0 = att_block_of(as, u0), b1 = att_block_of(as, u0 + as.nchunk - 1);
+                    const int np = min(b1 - b0 + 1, kAttSlots);
+                    const int ps = P.head + 4;
+                    const float *hp = P.att_part + (int64_t)h * kAttSlots * ps;
+                    float4 o4[kAttSlots];
+                    float ms[kAttSlots], ls[kAttSlots];
+#pragma unroll
+                    for (int s = 0; s < kAttSlots; ++s) {
+                        ms[s] = -INFINITY;
+                        ls[s] = 0.f;
+                        o4[s] = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (s < np) {
+                            o4[s] = ld_cg_f4_issue(hp + (int64_t)s * ps + d);
+                            ms[s] = __ldcg(hp + (int64_t)s * ps + P.head);
+                            ls[s] = __ldcg(hp + (int64_t)s * ps + P.head + 1);
+                        }
+                    }
+                    float gm = -INFINITY;
+#pragma unroll
+                    for (int s = 0; s < kAttSlots; ++s)
+                        gm = fmaxf(gm, ms[s]);
+                    float L = 0.f;
+                    float4 O = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                    for (int s = 0; s < kAttSlots; ++s) {
+                        if (ls[s] > 0.f) {
+                            const float w = expf(ms[s] - gm);
+                            L = fmaf(ls[s], w, L);
+                            O.x = fmaf(o4[s].x, w, O.x);
+                            O.y = fmaf(o4[s].y, w, O.y);
+                            O.z = fmaf(o4[s].z, w, O.z);
+                            O.w = fmaf(o4[s].w, w, O.w);
+                        }
+                    }
+                    // ExpSumNormalize.java:33-37 folded into the weighted sum
+                    xr[j] = make_float4(__fdiv_rn(O.x, L), __fdiv_rn(O.y, L), __fdiv_rn(O.z, L), __fdiv_rn(O.w, L));
+                }
+            }
+        }
+        float ssq = 0.f, amax = 0.f;
+#pragma unroll
+        for (int j = 0; j < kRounds; ++j) {
+            if (j * ncons >= n4)
+                break;
+            ssq = fmaf(xr[j].x, xr[j].x, ssq);
+            ssq = fmaf(xr[j].y, xr[j].y, ssq);
+            ssq = fmaf(xr[j].z, xr[j].z, ssq);
+            ssq = fmaf(xr[j].w, xr[j].w, ssq);
+            amax = fmaxf(fmaxf(amax, fmaxf(fabsf(xr[j].x), fabsf(xr[j].y))), fmaxf(fabsf(xr[j].z), fabsf(xr[j].w)));
+        }
+        ssq = warp_sum(ssq);
+        amax = warp_max(amax);
+        if (lane == 0 && active) {
+            scratch[warp] = ssq;
+            scratch[32 + warp] = amax;
+        }
+        named_barrier_sync(2, kFCons);
+        ssq = warp_sum(lane < nw ? scratch[lane] : 0.f);
+        amax = warp_max(lane < nw ? scratch[32 + lane] : 0.f);
+        if constexpr (has_rms) {
+            float tot = __fdiv_rn(ssq, (float)n);
+            tot = __fadd_rn(tot, 1e-5f);
+            const float ss = __fdiv_rn(1.0f, __fsqrt_rn(tot));
+#pragma unroll
+            for (int j = 0; j < kRounds; ++j) {
+                if (j * ncons >= n4)
+                    break;
+                xr[j].x = __fmul_rn(wr[j].x, __fmul_rn(ss, xr[j].x));
+                xr[j].y = __fmul_rn(wr[j].y, __fmul_rn(ss, xr[j].y));
+                xr[j].z = __fmul_rn(wr[j].z, __fmul_rn(ss, xr[j].z));
+                xr[j].w = __fmul_rn(wr[j].w, __fmul_rn(ss, xr[j].w));
+            }
+            amax = amax * ss * rms_wmax * 1.000001f;
+        }
+        int ex = 0;
+        if (amax > 0.f && amax < 3.0e38f)
+            frexpf(amax, &ex);
+        ex = max(-90, min(126, ex));
+        const float f = __int_as_float((127 + 22 - ex) << 23);
+        inv = __int_as_float((127 + ex - 22) << 23);
+#pragma unroll
+        for (int j = 0; j < kRounds; ++j) {
+            const int idx = tid + j * ncons;
+            if (j * ncons >= n4)
+                break;
+            if (active && idx < n4) {
+                const uint32_t z0 = ((uint32_t)__float2int_rn(xr[j].x * f) + 0x00008080u) ^ 0x00008080u;
+                const uint32_t z1 = ((uint32_t)__float2int_rn(xr[j].y * f) + 0x00008080u) ^ 0x00008080u;
+                const uint32_t z2 = ((uint32_t)__float2int_rn(xr[j].z * f) + 0x00008080u) ^ 0x00008080u;
+                const uint32_t z3 = ((uint32_t)__float2int_rn(xr[j].w * f) + 0x00008080u) ^ 0x00008080u;
+                const uint32_t t0 = __byte_perm(z0, z1, 0x5140);
+                const uint32_t t2 = __byte_perm(z2, z3, 0x5140);
+                const uint32_t t1 = __byte_perm(z0, z1, 0x0062);
+                const uint32_t t3 = __byte_perm(z2, z3, 0x0062);
+                uint32_t *dst = reinterpret_cast<uint32_t *>(share) + idx;
+                dst[0] = __byte_perm(t0, t2, 0x5410);
+                dst[n >> 2] = __byte_perm(t0, t2, 0x7632);
+                dst[n >> 1] = __byte_perm(t1, t3, 0x5410);
+            }
+        }
+    }
+    named_barrier_sync(1, kFCons);
+
+    uint32_t xl[4][4][3];
+    float xs;
+    {
+        int s0 = 0, s1 = 0, s2 = 0;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+#pragma unroll
+            for (int l = 0; l < 3; ++l) {
+                uint4 t = make_uint4(0u, 0u, 0u, 0u);
+                if (gvalid)
+                    t = *reinterpret_cast<const uint4 *>(share + (size_t)l * n + (size_t)chunk[k] * 16);
+                xl[k][0][l] = t.x; xl[k][1][l] = t.y; xl[k][2][l] = t.z; xl[k][3][l] = t.w;
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                s0 = dp4a_us(0x01010101u, xl[k][q][0], s0);
+                s1 = dp4a_us(0x01010101u, xl[k][q][1], s1);
+                s2 = dp4a_us(0x01010101u, xl[k][q][2], s2);
+            }
+        }
+        xs = fmaf((float)s2, 65536.0f, fmaf((float)s1, 256.0f, (float)s0));
+    }
+    if (tid == 0)
+        fused_trace(P, pidx, 1);
+
+    for (int it = 0; it < nmine; ++it) {
+        const int e = cs.seq % kFDesc;
+        if (!mbar_wait_bounded(sbase + kFBarFull + 8 * e, (uint32_t)(cs.seq / kFDesc) & 1u, cs.lost ? kFShortWaitNs : wait_ns))
+            cs.lost = true;
+        const FStage d = *(reinterpret_cast<const FStage *>(smem + kFDescOff) + e);
+        const bool skip = cs.lost && !cs.lost_before;
+        const uint8_t *slot_ptr = smem + kFHeader + P.xarea_bytes + (size_t)d.off;
+        float v[RT];
+#pragma unroll
+        for (int t = 0; t < RT; ++t) {
+            v[t] = 0.f;
+            const int r = rsub + t * p.rpp;
+            const int half = (p.paired && r >= R / 2) ? 1 : 0;   // second half of a paired stage: the partner matrix
+            const int local = r - half * (R / 2);
+            if (!skip && gvalid && local < d.nrows) {
+                const uint8_t *rowp = slot_ptr + (size_t)r * rowbytes;
+                const int e0 = (half ? d.e0b : d.e0a) + local * n;
+                const float2 *hp = reinterpret_cast<const float2 *>(slot_ptr + p.hdr_off + half * p.half_hdr);
+                const float2 ms = hp[(e0 + chunk[0] * 16) >> 8];
+                int a0 = 0, a1 = 0, a2 = 0;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const uint4 w = *reinterpret_cast<const uint4 *>(rowp + (size_t)chunk[k] * 16);
+                    a0 = dp4a_us(w.x, xl[k][0][0], a0);
+                    a1 = dp4a_us(w.x, xl[k][0][1], a1);
+                    a2 = dp4a_us(w.x, xl[k][0][2], a2);
+                    a0 = dp4a_us(w.y, xl[k][1][0], a0);
+                    a1 = dp4a_us(w.y, xl[k][1][1], a1);
+                    a2 = dp4a_us(w.y, xl[k][1][2], a2);
+                    a0 = dp4a_us(w.z, xl[k][2][0], a0);
+                    a1 = dp4a_us(w.z, xl[k][2][1], a1);
+                    a2 = dp4a_us(w.z, xl[k][2][2], a2);
+                    a0 = dp4a_us(w.w, xl[k][3][0], a0);
+                    a1 = dp4a_us(w.w, xl[k][3][1], a1);
+                    a2 = dp4a_us(w.w, xl[k][3][2], a2);
+                }
+                const float dsum = fmaf((float)a2, 65536.0f, fmaf((float)a1, 256.0f, (float)a0));
+                v[t] = fmaf(ms.y, dsum, ms.x * xs);
+            }
+        }
+        const float tot = Fold<RT, 16>::run(v, lane) * inv;
+        __syncwarp();
+        if (lane == 0)
+            mbar_arrive(sbase + kFBarEmpty + 8 * e);
+        if (cs.rround > 0) {
+            if (!mbar_wait_bounded(sbase + kFBarRedEmpty + 8 * cs.rb, (uint32_t)(cs.rround - 1) & 1u, cs.lost ? kFShortWaitNs : wait_ns))
+                cs.lost = true;
+        }
+        int *rh = reinterpret_cast<int *>(smem + kFRedOff + cs.rb * kFRedStride);
+        float *red = reinterpret_cast<float *>(rh + 4);
+        if (tid == 0) {
+            rh[0] = d.seg;
+            rh[1] = d.row0;
+            rh[2] = skip ? 0 : d.nrows;
+        }
+        if (active && (lane & (32 / RT - 1)) == 0) {
+            const int t = lane / (32 / RT);
+            red[(rsub + t * p.rpp) * p.wpr + wi] = tot;
+        }
+        __syncwarp();
+        if (lane == 0)
+            mbar_arrive(sbase + kFBarRedFull + 8 * cs.rb);
+        ++cs.seq;
+        if (++cs.rb == kFRedBufs) {
+            cs.rb = 0;
+            ++cs.rround;
+        }
+    }
+    if (tid == 0)
+        fused_trace(P, pidx, 2);
+}
+
+// The attention step of the block: its run of units, each a stage of cached K and V rows in the ring (the
+// token's own row comes straight from the cache in global memory).  One pass with an online softmax per
+// lane group; the lane groups of the block are merged through shared memory whenever the head changes.
+__device__ __forceinline__ void consume_attention(const FusedParams &P, int layer, const AttSplit &as, int pos, uint8_t *smem,
+                                                  uint32_t sbase, Consumer &cs, uint64_t wait_ns)
+{
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int b = blockIdx.x;
+    const int head = P.head;
+    const int u0 = att_first_unit(as, b), u1 = att_first_unit(as, b + 1);
+    const int lpp = head >> 2;
+    int gw = 1;
+    while (gw < lpp)
+        gw <<= 1;
+    const int ppw = 32 / gw;
+    const int g = lane / gw, li = lane - g * gw;
+    const bool act = li < lpp;
+    const int nslots = kFusedConsWarps * ppw;
+    const int slot = warp * ppw + g;
+    const int sstride = head + 4;
+    float *marea = reinterpret_cast<float *>(smem + kFHeader);
+    const float sq = sqrtf((float)head);
+    const float *kc = P.mv[0].k_cache + (int64_t)layer * P.kv_step;
+    const float *vc = P.mv[0].v_cache + (int64_t)layer * P.kv_step;
+
+    int cur_h = -1;
+    float4 q4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    float m = -INFINITY, l = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+
+    auto flush = [&](int h) {
+        // merge the lane groups in slot order and write the block's partial of head h
+        float *mine = marea + slot * sstride;
+        if (act)
+            *reinterpret_cast<float4 *>(mine + 4 * li) = acc;
+        if (li == 0) {
+            mine[head] = m;
+            mine[head + 1] = l;
+        }
+        named_barrier_sync(2, kFCons);
+        if (tid < head) {
+            float M = -INFINITY;
+            for (int s = 0; s < nslots; ++s)
+                M = fmaxf(M, marea[s * sstride + head]);
+            float L = 0.f, O = 0.f;
+            for (int s = 0; s < nslots; ++s) {
+                const float ms = marea[s * sstride + head];
+                const float ls = marea[s * sstride + head + 1];
+                if (ls > 0.f) {
+                    const float w = expf(ms - M);
+                    L = fmaf(ls, w, L);
+                    O = fmaf(marea[s * sstride + tid], w, O);
+                }
+            }
+            const int pslot = b - att_block_of(as, h * as.nchunk);
+            float *part = P.att_part + ((int64_t)h * kAttSlots + pslot) * sstride;
+            __stcg(part + tid, O);
+            if (tid == 0) {
+                __stcg(part + head, M);
+                __stcg(part + head + 1, L);
+            }
+        }
+        named_barrier_sync(2, kFCons);   // the merge area is free again
+    };
+
+    for (int u = u0; u < u1; ++u) {
+        const int e = cs.seq % kFDesc;
+        if (!mbar_wait_bounded(sbase + kFBarFull + 8 * e, (uint32_t)(cs.seq / kFDesc) & 1u, cs.lost ? kFShortWaitNs : wait_ns))
+            cs.lost = true;
+        cs.lost = __any_sync(0xffffffffu, cs.lost) != 0;   // the shuffles below need a warp-uniform decision
+        const FStage d = *(reinterpret_cast<const FStage *>(smem + kFDescOff) + e);
+        const int h = d.seg;
+        if (h != cur_h) {
+            if (cur_h >= 0)
+                flush(cur_h);
+            cur_h = h;
+            m = -INFINITY;
+            l = 0.f;
+            acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (act)
+                q4 = __ldcg(reinterpret_cast<const float4 *>(P.q + (int64_t)h * head + 4 * li));
+        }
+        const bool skip = cs.lost && !cs.lost_before;
+        const float *ks = reinterpret_cast<const float *>(smem + kFHeader + P.xarea_bytes + (size_t)d.off);
+        const float *vs = reinterpret_cast<const float *>(smem + kFHeader + P.xarea_bytes + (size_t)d.off + (size_t)d.aux);
+        const int kvh = h / P.kv_mul;
+        for (int i0 = 0; i0 < d.nrows && !skip; i0 += 2 * nslots) {
+            float4 kk[2], vv[2];
+            float s[2];
+#pragma unroll
+            for (int u2 = 0; u2 < 2; ++u2) {
+                const int i = i0 + u2 * nslots + slot;
+                kk[u2] = make_float4(0.f, 0.f, 0.f, 0.f);
+                vv[u2] = kk[u2];
+                if (act && i < d.nrows) {
+                    if (i < d.e0a) {
+                        kk[u2] = *reinterpret_cast<const float4 *>(ks + (size_t)i * head + 4 * li);
+                        vv[u2] = *reinterpret_cast<const float4 *>(vs + (size_t)i * head + 4 * li);
+                    } else {   // the row this token's QKV phase has just written
+                        const int64_t row = ((int64_t)kvh * P.seq_len + d.row0 + i) * head + 4 * li;
+                        kk[u2] = __ldcg(reinterpret_cast<const float4 *>(kc + row));
+                        vv[u2] = __ldcg(reinterpret_cast<const float4 *>(vc + row));
+                    }
+                }
+            }
+            float mloc = -INFINITY;
+#pragma unroll
+            for (int u2 = 0; u2 < 2; ++u2) {
+                const int i = i0 + u2 * nslots + slot;
+                float dd = kk[u2].x * q4.x;
+                dd = fmaf(kk[u2].y, q4.y, dd);
+                dd = fmaf(kk[u2].z, q4.z, dd);
+                dd = fmaf(kk[u2].w, q4.w, dd);
+                for (int o = gw >> 1; o > 0; o >>= 1)
+                    dd += __shfl_xor_sync(0xffffffffu, dd, o);
+                s[u2] = i < d.nrows ? __fdiv_rn(dd, sq) : -INFINITY;   // AttentionLoop.java:48
+                mloc = fmaxf(mloc, s[u2]);
+            }
+            if (mloc > -INFINITY) {
+                const float mn = fmaxf(m, mloc);
+                const float sc = expf(m - mn);
+                l *= sc;
+                acc.x *= sc; acc.y *= sc; acc.z *= sc; acc.w *= sc;
+#pragma unroll
+                for (int u2 = 0; u2 < 2; ++u2) {
+                    const float pw = expf(s[u2] - mn);
+                    l += pw;
+                    acc.x = fmaf(pw, vv[u2].x, acc.x);
+                    acc.y = fmaf(pw, vv[u2].y, acc.y);
+                    acc.z = fmaf(pw, vv[u2].z, acc.z);
+                    acc.w = fmaf(pw, vv[u2].w, acc.w);
+                }
+                m = mn;
+            }
+        }
+        __syncwarp();
+        if (lane == 0)
+            mbar_arrive(sbase + kFBarEmpty + 8 * e);
+        ++cs.seq;
+    }
+    if (cur_h >= 0)
+        flush(cur_h);
+}
+
+// -------------------------------------------------------------------------------------------------
+// epilogue warp
+// -------------------------------------------------------------------------------------------------
+
+struct Epilogue {
+    int rb, rround;
+    bool lost, lost_before;
+};
+
+__device__ __forceinline__ void epilogue_phase(const FusedParams &P, const MvParams &p, int layer, int nmine, int pos, uint8_t *smem,
+                                               uint32_t sbase, Epilogue &es, uint64_t wait_ns)
+{
+    const int lane = threadIdx.x & 31;
+    const int R = p.rt * p.rpp;
+    const float *rope_c = reinterpret_cast<const float *>(smem + kFRopeOff);
+    const float *rope_s = rope_c + 64;
+    for (int it = 0; it < nmine; ++it) {
+        if (!mbar_wait_bounded(sbase + kFBarRedFull + 8 * es.rb, (uint32_t)es.rround & 1u, es.lost ? kFShortWaitNs : wait_ns))
+            es.lost = true;
+        const int *rh = reinterpret_cast<const int *>(smem + kFRedOff + es.rb * kFRedStride);
+        const int seg = rh[0], row0 = rh[1];
+        const int nrows = (es.lost && !es.lost_before) ? 0 : rh[2];
+        const float *red = reinterpret_cast<const float *>(rh + 4);
+        if (p.epilogue == EPI_QKV_ROPE) {
+            if (lane < (nrows >> 1)) {
+                float v0 = 0.f, v1 = 0.f;
+                for (int w = 0; w < p.wpr; ++w) {
+                    v0 += red[(2 * lane) * p.wpr + w];
+                    v1 += red[(2 * lane + 1) * p.wpr + w];
+                }
+                const int row = row0 + 2 * lane;
+                if (seg == 2) {
+                    const int kvh = row / p.head, d = row - kvh * p.head;
+                    float *dst = p.v_cache + (int64_t)layer * P.kv_step + ((int64_t)kvh * p.seq_len + pos) * p.head + d;
+                    dst[0] = v0;
+                    dst[1] = v1;
+                } else {
+                    const int d = row % p.head;
+                    const float c = rope_c[d >> 1], s = rope_s[d >> 1];
+                    const float r0 = __fsub_rn(__fmul_rn(v0, c), __fmul_rn(v1, s));   // ApplyRope.java:61-92
+                    const float r1 = __fadd_rn(__fmul_rn(v0, s), __fmul_rn(v1, c));
+                    if (seg == 0) {
+                        p.q_out[row] = r0;
+                        p.q_out[row + 1] = r1;
+                    } else {
+                        const int kvh = row / p.head;
+                        float *dst = p.k_cache + (int64_t)layer * P.kv_step + ((int64_t)kvh * p.seq_len + pos) * p.head + d;
+                        dst[0] = r0;
+                        dst[1] = r1;
+                    }
+                }
+            }
+        } else if (p.epilogue == EPI_SWIGLU) {
+            if (lane < nrows) {
+                float v1 = 0.f, v3 = 0.f;
+                for (int w = 0; w < p.wpr; ++w) {
+                    v1 += red[lane * p.wpr + w];
+                    v3 += red[(R / 2 + lane) * p.wpr + w];
+                }
+                p.y[row0 + lane] = __fmul_rn(__fmul_rn(v1, sigmoid_accurate(v1)), v3);   // Silu.java:122-132 order
+            }
+        } else if (lane < nrows) {   // EPI_RESIDUAL
+            float a = 0.f;
+            for (int w = 0; w < p.wpr; ++w)
+                a += red[lane * p.wpr + w];
+            atomicAdd(p.y + row0 + lane, a);   // one add per element and phase: deterministic
+        }
+        __syncwarp();
+        if (lane == 0)
+            mbar_arrive(sbase + kFBarRedEmpty + 8 * es.rb);
+        if (++es.rb == kFRedBufs) {
+            es.rb = 0;
+            ++es.rround;
+        }
+    }
+}
+
+}  // namespace
+
+// =============================================================================================
+// the kernel
+// =============================================================================================
+
+__global__ void __launch_bounds__(kFusedThreads, 1) fused_layers_kernel(const __grid_constant__ FusedParams P)
+{
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5, lane = tid & 31;
+    const int b = blockIdx.x, G = gridDim.x;
+    const uint32_t sbase = smem_u32(smem);
+    const uint64_t wait_ns = (uint64_t)P.timeout_us * 1000ull;
+
+    if (tid < kFDesc) {
+        mbar_init(sbase + kFBarFull + 8 * tid, 1);
+        mbar_init(sbase + kFBarEmpty + 8 * tid, kFusedConsWarps);
+    }
+    if (tid < kFRedBufs) {
+        mbar_init(sbase + kFBarRedFull + 8 * tid, kFusedConsWarps);
+        mbar_init(sbase + kFBarRedEmpty + 8 * tid, 1);
+    }
+    if (tid < 32)
+        mbar_fence_init();
+    __syncthreads();
+    pdl_launch_dependents();   // the classifier kernel behind may take the SMs as they free up
+
+    // ------------------------------------------------------------------------------ producer
+    if (warp == kFusedConsWarps) {
+        if (lane != 0)
+            return;
+        Producer pr;
+        pr.smem = smem;
+        pr.sbase = sbase;
+        pr.ring_base = sbase + kFHeader + (uint32_t)P.xarea_bytes;
+        pr.vhead = 0;
+        pr.ring_bytes = P.ring_bytes;
+        pr.seq = pr.tail = 0;
+        pr.lost = false;
+        pr.wait_ns = wait_ns;
+        const uint64_t pol = policy_evict_first();
+        int rot = 0, pos = -1;
+        AttSplit as{};
+        for (int layer = 0; layer < P.n_layers; ++layer) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const MvParams &p = P.mv[k];
+                const int S = p.total_stages;
+                for (int s = first_stage_of(b, rot, G); s < S; s += G)
+                    produce_ring_stage(pr, P, p, k, layer, s, pol);
+                rot = (rot + S) % G;
+                if (k == 0) {
+                    if (pos < 0) {
+                        // The position is set by the kernel in front; everything issued so far was weights.
+                        pdl_wait();
+                        pos = __ldcg(&P.state->cur_pos);
+                        as = att_split(P, pos, G);
+                    }
+                    if (b < as.ga) {
+                        const int u0 = att_first_unit(as, b), u1 = att_first_unit(as, b + 1);
+                        for (int u = u0; u < u1; ++u)
+                            produce_att_stage(pr, P, layer, u, as, pos);
+                    }
+                }
+            }
+        }
+        if (pr.lost)
+            atomicOr(&P.state->status, L2J_DS_WAIT_TIMEOUT);
+        return;
+    }
+
+    // Everything below reads what the kernel in front wrote (x, the position).
+    pdl_wait();
+    const int pos = __ldcg(&P.state->cur_pos);
+    const AttSplit as = att_split(P, pos, G);
+    const unsigned int target = __ldcg(P.epoch) * (unsigned int)G;
+    const bool lost_at_entry = (__ldcg(&P.state->status) & L2J_DS_WAIT_TIMEOUT) != 0;
+
+    // ------------------------------------------------------------------------------ epilogue warp
+    if (warp == kFusedConsWarps + 1) {
+        Epilogue es;
+        es.rb = es.rround = 0;
+        es.lost = es.lost_before = lost_at_entry;
+        {
+            float *rope_c = reinterpret_cast<float *>(smem + kFRopeOff);
+            const int half = P.head >> 1;
+            for (int i = lane; i < half; i += 32) {
+                rope_c[i] = __ldg(P.mv[0].rope_cos + (int64_t)pos * half + i);
+                rope_c[64 + i] = __ldg(P.mv[0].rope_sin + (int64_t)pos * half + i);
+            }
+            __syncwarp();
+        }
+        int rot = 0;
+        for (int layer = 0; layer < P.n_layers; ++layer) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const MvParams &p = P.mv[k];
+                const int S = p.total_stages;
+                const int first = first_stage_of(b, rot, G);
+                const int nmine = first < S ? (S - first + G - 1) / G : 0;
+                rot = (rot + S) % G;
+                epilogue_phase(P, p, layer, nmine, pos, smem, sbase, es, wait_ns);
+                // every result of the block in this phase was written by this warp; the release is cumulative
+                __syncwarp();
+                const int pidx = layer * 5 + (k == 0 ? 0 : k + 1);
+                if (lane == 0) {
+                    red_release_add_u32(P.sync + (int64_t)kSyncStride * pidx, 1u);
+                    fused_trace(P, pidx, 3);
+                }
+            }
+        }
+        if (es.lost && !es.lost_before && lane == 0)
+            atomicOr(&P.state->status, L2J_DS_WAIT_TIMEOUT);
+        return;
+    }
+
+    // ------------------------------------------------------------------------------ consumers
+    Consumer cs;
+    cs.seq = 0;
+    cs.rb = cs.rround = 0;
+    cs.lost = cs.lost_before = lost_at_entry;
+    int rot = 0;
+    for (int layer = 0; layer < P.n_layers; ++layer) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const MvParams &p = P.mv[k];
+            const int S = p.total_stages;
+            const int first = first_stage_of(b, rot, G);
+            const int nmine = first < S ? (S - first + G - 1) / G : 0;
+            rot = (rot + S) % G;
+            const int pidx = layer * 5 + (k == 0 ? 0 : k + 1);
+            if (nmine > 0) {
+                if (pidx > 0)   // the first phase's input came from the kernel in front
+                    consumers_wait(P.sync + (int64_t)kSyncStride * (pidx - 1), target, smem, cs, wait_ns);
+                if (tid == 0)
+                    fused_trace(P, pidx, 0);
+                const float *rms_w = p.rms_w ? p.rms_w + (int64_t)layer * P.rms_step : nullptr;
+                const float wmax = p.rms_w ? __ldg(P.rms_wmax + 2 * layer + (k == 2 ? 1 : 0)) : 1.0f;
+                if (k == 1)
+                    consume_ring_phase<IN_MERGE>(P, p, layer, nmine, nullptr, 1.0f, as, smem, sbase, cs, wait_ns, pidx);
+                else if (k == 3)
+                    consume_ring_phase<IN_PLAIN>(P, p, layer, nmine, nullptr, 1.0f, as, smem, sbase, cs, wait_ns, pidx);
+                else
+                    consume_ring_phase<IN_RMS>(P, p, layer, nmine, rms_w, wmax, as, smem, sbase, cs, wait_ns, pidx);
+            }
+            if (k == 0) {
+                // attention over positions 0..pos (Run.java:450-478)
+                const int aidx = layer * 5 + 1;
+                if (b < as.ga) {
+                    consumers_wait(P.sync + (int64_t)kSyncStride * (aidx - 1), target, smem, cs, wait_ns);
+                    if (tid == 0)
+                        fused_trace(P, aidx, 0);
+                    consume_attention(P, layer, as, pos, smem, sbase, cs, wait_ns);
+                    // flush() ended with a barrier of all consumers: their partials are written
+                }
+                if (tid == 0) {
+                    red_release_add_u32(P.sync + (int64_t)kSyncStride * aidx, 1u);
+                    fused_trace(P, aidx, 3);
+                }
+            }
+        }
+    }
+    if (cs.lost && !cs.lost_before && lane == 0)
+        atomicOr(&P.state->status, L2J_DS_WAIT_TIMEOUT);
+}
+
+cudaError_t prepare_fused(int *max_smem)
+{
+    int dev = 0, optin = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess)
+        return e;
+    if ((e = cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev)) != cudaSuccess)
+        return e;
+    if (max_smem)
+        *max_smem = optin;
+    if ((e = cudaFuncSetAttribute(fused_layers_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, optin)) != cudaSuccess)
+        return e;
+    return cudaFuncSetAttribute(fused_layers_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+}
+
+cudaError_t launch_fused(cudaStream_t stream, bool pdl, int grid, int smem_bytes, const FusedParams &p)
+{
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(kFusedThreads);
+    cfg.dynamicSmemBytes = (size_t)smem_bytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, fused_layers_kernel, p);
+}
+
+}  // namespace l2j

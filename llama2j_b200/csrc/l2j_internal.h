@@ -133,6 +133,7 @@ struct MvParams {
     int seg_stages[3]; // stages per segment
     int total_stages;
     int rs;            // matrix rows (row pairs in paired mode) a stage advances
+    int rt;            // rows per consumer thread and stage (the kernels' RT template parameter)
     int rowbytes;      // bytes of one matrix row
     int f32;           // 1: FP32 weights
     int tail_prefetch; // stages of the next launch each block prefetches into L2 when it runs out of work
@@ -189,6 +190,42 @@ struct AttnParams {
     unsigned long long *trace;   // optional timeline of the first trace_blocks blocks (16 slots each), else nullptr
     int trace_blocks;
 };
+
+// ---- one launch for all layers of a token (l2j_fused.cu) --------------------------------------
+//
+// The five steps of a layer (QKV, attention, Wo, W1/W3, W2) run as phases of one persistent kernel:
+// the blocks never leave their SMs, the producer thread of a block keeps streaming the stages of the
+// phases ahead into one shared-memory byte ring while the consumers wait at a phase boundary, and the
+// cached K and V rows of the attention phase travel through the same ring.  The parameters of the
+// first layer are given; those of layer l follow by adding l times a step to the pointers.
+constexpr int kAttSlots = 8;        // partial results per head that the step after the attention phase can merge
+constexpr int kAttMaxSplit = 6;     // blocks per head in the attention phase (a head gets at most kAttMaxSplit + 1 partials)
+constexpr int kAttChunk = 64;       // cached positions per ring stage of the attention phase
+
+struct FusedParams {
+    MvParams mv[4];            // QKV, Wo, W1/W3, W2 of the first layer of the context's range
+    long long seg_step[4][3];  // elements between the matrices of consecutive layers, per segment
+    long long kv_step;         // floats between the KV caches of consecutive layers
+    int rms_step;              // floats between the RMSNorm weight vectors of consecutive layers
+    int n_layers;
+    const float *rms_wmax;     // [n_layers][2]: max |w| of the attention and the FFN RMSNorm weights
+    const float *q;            // query vector written by the QKV phase (n_heads * head)
+    float *att_part;           // [n_heads][kAttSlots][head + 4]: o, then m, l
+    int n_heads, kv_mul, head, seq_len;
+    int xarea_bytes;           // shared memory between the fixed header and the ring: limbs of the input vector / merge area
+    int ring_bytes;            // bytes of the ring
+    unsigned int *sync;        // hand-over counters, kSyncStride words apart, five per layer
+    const unsigned int *epoch; // forwards started on this context
+    SeqState *state;
+    int timeout_us;
+    unsigned long long *trace; // optional: [block][5 * n_layers][4] global-timer marks, else nullptr
+};
+constexpr int kSyncStride = 32;     // unsigned ints between two hand-over counters (128 bytes)
+constexpr int kFusedThreads = 640;  // 18 consumer warps, the producer warp, the epilogue warp
+constexpr int kFusedConsWarps = 18;
+
+cudaError_t prepare_fused(int *max_smem);
+cudaError_t launch_fused(cudaStream_t stream, bool pdl, int grid, int smem_bytes, const FusedParams &p);
 
 struct MvPlan {
     bool grouped;  // u8 rows of whole groups: four lanes share a group (template selector)
