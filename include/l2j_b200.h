@@ -221,6 +221,13 @@ L2J_API int l2j_launch_mode(l2j_ctx *ctx);
  * 5 K row, 6 V row of (layer, pos) in the reference's (kv_dim) order, n must be kv_dim. */
 L2J_API int l2j_read_buffer(l2j_ctx *ctx, int which, int layer, int pos, float *out, int n);
 
+/* Restores part of the KV cache from the host: rows [pos0, pos0 + n_pos) of `layer`, given as the
+ * reference holds them, (position, kv_dim) floats (RunState.java:141-151, Run.java:438-444); the
+ * library re-lays them out into its own (kv_head, position, head) order.  With it a harness can put a
+ * long prompt's cache back instead of pushing the prompt through the decode path again, and a test can
+ * give the device and the CPU checker the same cache.  Blocks until the rows are on the device. */
+L2J_API int l2j_kv_write(l2j_ctx *ctx, int layer, int pos0, int n_pos, const float *k_rows, const float *v_rows);
+
 /* Average device time in microseconds of the last l2j_generate_greedy call per forward, measured
  * with CUDA events on the context's stream. */
 L2J_API int l2j_last_generate_us(l2j_ctx *ctx, double *total_us);

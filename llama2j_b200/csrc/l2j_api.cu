@@ -406,6 +406,8 @@ void build_fused_params(l2j_ctx *c)
     F.state = c->state;
     F.timeout_us = c->wait_limit_us;
     F.trace = c->fused_trace;
+    if (const char *e = getenv("L2J_FUSED_NO_COPY"))   // measurement aid: consumers run on whatever the ring holds
+        F.debug_no_copy = atoi(e);
 }
 
 // Builds the static kernel parameter blocks of every layer this context owns.
@@ -994,8 +996,9 @@ static int create_impl(const l2j_config *cfg, int device, int first_layer, int l
     c->use_ring = !(flags & L2J_F_SIMPLE) && c->plan_qkv.ok && c->plan_wo.ok && c->plan_w13.ok && c->plan_hidden.ok &&
                   c->plan_cls.ok && (head % 2 == 0);
     {   // one persistent launch per token where every matrix has rows of whole quantisation groups
+        // (its consumers hold a vector of dim elements in four rounds of 16-byte loads, the hidden vector in eight)
         bool fused = c->use_ring && tp_size == 1 && !(flags & L2J_F_STEP_KERNELS) && c->reps == 1 && c->dim % kGroup == 0 &&
-                     c->hidden % kGroup == 0;
+                     c->hidden % kGroup == 0 && c->dim <= 4 * 4 * kFusedConsWarps * 32 && c->hidden <= 8 * 4 * kFusedConsWarps * 32;
         if (const char *e = getenv("L2J_FUSED"))   // diagnostic: A/B against the per-step kernels
             fused = fused && atoi(e) != 0;
         if (fused) {
@@ -1019,7 +1022,7 @@ static int create_impl(const l2j_config *cfg, int device, int first_layer, int l
             CREATE_CK(dev_alloc(c, &c->rms_wmax_dev, 2 * (int64_t)c->nl, true));
             CREATE_CK(dev_alloc(c, &c->fused_part, (int64_t)cfg->n_heads * kAttSlots * (head + 4), true));
             if (getenv("L2J_TRACE"))
-                CREATE_CK(dev_alloc(c, &c->fused_trace, (int64_t)c->ring_grid * 5 * c->nl * 4, true));
+                CREATE_CK(dev_alloc(c, &c->fused_trace, (int64_t)c->ring_grid * 5 * c->nl * 8, true));
         }
         c->use_fused = fused;
     }
@@ -1407,6 +1410,45 @@ extern "C" int l2j_generate_greedy(l2j_ctx *c, const int32_t *prompt, int n_prom
     CK(c, cudaEventElapsedTime(&ms, c->ev0, c->ev1));
     c->last_generate_us = (double)ms * 1000.0;
     return finish_status(c);
+}
+
+extern "C" int l2j_kv_write(l2j_ctx *c, int layer, int pos0, int n_pos, const float *k_rows, const float *v_rows)
+{
+    if (!c || !k_rows || !v_rows)
+        return L2J_E_INVALID;
+    std::lock_guard<std::mutex> lock(c->mu);
+    const int li = layer - c->first_layer;
+    if (li < 0 || li >= c->nl || pos0 < 0 || n_pos <= 0 || pos0 + n_pos > c->cfg.seq_len)
+        return fail(c, L2J_E_INVALID, "KV rows [%d, %d) of layer %d outside this context", pos0, pos0 + n_pos, layer);
+    if (c->tp_size > 1)
+        return fail(c, L2J_E_STATE, "a tensor-parallel rank holds only its own heads of the cache");
+    CK(c, cudaSetDevice(c->device));
+    CK(c, cudaStreamSynchronize(c->stream));
+    const int64_t layer_floats = (int64_t)c->cfg.n_kv_heads * c->cfg.seq_len * c->head;
+    const int piece = 256;   // positions per staging copy
+    float *stage = nullptr;
+    cudaError_t e = cudaMalloc((void **)&stage, sizeof(float) * (size_t)piece * c->kv_dim);
+    if (e != cudaSuccess)
+        return fail(c, L2J_E_NOMEM, "staging allocation failed: %s", cudaGetErrorString(e));
+    int rc = L2J_OK;
+    for (int which = 0; which < 2 && rc == L2J_OK; ++which) {
+        const float *src = which ? v_rows : k_rows;
+        float *dst = (which ? c->vc : c->kc) + li * layer_floats;
+        for (int done = 0; done < n_pos && rc == L2J_OK; done += piece) {
+            const int np = n_pos - done < piece ? n_pos - done : piece;
+            e = cudaMemcpyAsync(stage, src + (int64_t)done * c->kv_dim, sizeof(float) * (size_t)np * c->kv_dim,
+                                cudaMemcpyHostToDevice, c->stream);
+            if (e == cudaSuccess)
+                e = launch_kv_relayout(c->stream, stage, dst + (int64_t)(pos0 + done) * c->head, c->cfg.n_kv_heads, c->head,
+                                       c->cfg.seq_len, np);
+            if (e == cudaSuccess)
+                e = cudaStreamSynchronize(c->stream);
+            if (e != cudaSuccess)
+                rc = fail(c, L2J_E_CUDA, "KV restore failed: %s", cudaGetErrorString(e));
+        }
+    }
+    cudaFree(stage);
+    return rc;
 }
 
 // ===============================================================================================
@@ -1894,6 +1936,13 @@ extern "C" int l2j_read_trace(l2j_ctx *c, uint64_t *out, int64_t max_values)
         return fail(c, L2J_E_STATE, "the context was created without L2J_TRACE in the environment");
     CK(c, cudaSetDevice(c->device));
     CK(c, cudaStreamSynchronize(c->stream));
+    if (c->use_fused && c->fused_trace) {   // [block][5 * layers][8] marks of the persistent kernel's last launch
+        int64_t nf = (int64_t)c->ring_grid * 5 * c->nl * 8;
+        if (nf > max_values)
+            nf = max_values;
+        CK(c, cudaMemcpy(out, c->fused_trace, sizeof(uint64_t) * (size_t)nf, cudaMemcpyDeviceToHost));
+        return L2J_OK;
+    }
     int64_t n = (5 * (int64_t)c->nl + 1) * c->ring_grid * 16;
     if (n > max_values)
         n = max_values;

@@ -59,17 +59,29 @@ __device__ __forceinline__ uint64_t global_timer_ns()
     return t;
 }
 
+// Time base of the bounded waits: the SM's own cycle counter.  Reading %globaltimer costs on the order of a
+// microsecond, which a wait loop that reads it pays on every poll that fails, i.e. on every hand-over inside a
+// block; %clock64 is a register read.  A limit of t nanoseconds is taken as 2 t cycles (the SM clock is at
+// most 2 GHz here, so the wait lasts at least t and at most about twice that at low clocks).
+__device__ __forceinline__ long long sm_clock()
+{
+    long long c;
+    asm volatile("mov.u64 %0, %%clock64;" : "=l"(c));
+    return c;
+}
+
 // Bounded wait: gives up `timeout_ns` after the first failed poll and returns false; the caller
 // records the fault in the device status word and carries on, so a lost copy can never hang the GPU.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, uint64_t timeout_ns)
 {
     if (mbar_try_wait(bar, parity))
         return true;
-    const uint64_t t0 = global_timer_ns();
+    const long long c0 = sm_clock();
+    const long long limit = (long long)(2 * timeout_ns);
     for (;;) {
         if (mbar_try_wait(bar, parity))
             return true;
-        if (global_timer_ns() - t0 > timeout_ns)
+        if (sm_clock() - c0 > limit)
             return false;
     }
 }
@@ -161,11 +173,12 @@ __device__ __forceinline__ bool counter_wait_bounded(const unsigned int *ctr, un
 {
     if ((int)(ld_acquire_u32(ctr) - target) >= 0)
         return true;
-    const uint64_t t0 = global_timer_ns();
+    const long long c0 = sm_clock();
+    const long long limit = (long long)(2 * timeout_ns);
     for (;;) {
         if ((int)(ld_acquire_u32(ctr) - target) >= 0)
             return true;
-        if (global_timer_ns() - t0 > timeout_ns)
+        if (sm_clock() - c0 > limit)
             return false;
     }
 }

@@ -51,6 +51,7 @@ namespace {
 
 constexpr int kFDesc = 16;              // stage descriptors (and full/empty barrier pairs) in flight
 constexpr int kFRedBufs = 4;
+constexpr int kFGroup = 4;               // stages of a block that are folded and handed to the epilogue warp together
 constexpr int kFBarFull = 0;            // uint64 full[16]
 constexpr int kFBarEmpty = 128;         // uint64 empty[16]
 constexpr int kFBarRedFull = 256;       // uint64 red_full[4]
@@ -59,13 +60,13 @@ constexpr int kFFlag = 320;             // int: result of the poll of a hand-ove
 constexpr int kFVStart = 3264;          // int vstart[16]: the producer's bookkeeping of where each stage in flight begins
 constexpr int kFScratch = 384;          // float scratch[64]
 constexpr int kFDescOff = 640;          // FStage desc[16]
-constexpr int kFRedOff = 1152;          // 4 x (16-byte header + 128 floats)
+constexpr int kFRedOff = 1152;          // 4 x 132 floats: [stage of the group][row of the stage][warp of the row]
 constexpr int kFRedStride = 528;
 constexpr int kFRopeOff = 3328;         // float cos[64], sin[64] of the token's position
 constexpr int kFHeader = 3840;          // end of the fixed part (128-byte aligned)
 constexpr int kFCons = kFusedConsWarps * 32;
 constexpr int kFRounds = 8;             // 16-byte loads of the input vector per consumer thread at most
-constexpr int kFMergeRounds = 4;        // the same for the phase that merges the attention partials (its vector has dim elements)
+constexpr int kFRmsRounds = 4;          // the same for a vector of dim elements (RMSNorm'd input, merged attention output)
 constexpr uint64_t kFShortWaitNs = 2000;
 
 struct FStage {
@@ -166,7 +167,7 @@ __device__ __forceinline__ int first_stage_of(int b, int rot, int grid)
 __device__ __forceinline__ void fused_trace(const FusedParams &P, int phase_index, int k)
 {
     if (P.trace)
-        P.trace[((int64_t)blockIdx.x * (5 * P.n_layers) + phase_index) * 4 + k] = (unsigned long long)global_timer_ns();
+        P.trace[((int64_t)blockIdx.x * (5 * P.n_layers) + phase_index) * 8 + k] = (unsigned long long)global_timer_ns();
 }
 
 // -------------------------------------------------------------------------------------------------
@@ -219,7 +220,10 @@ __device__ __forceinline__ void produce_ring_stage(Producer &pr, const FusedPara
     desc->row0 = row0;
     desc->nrows = nrows;
     desc->off = (int)off;
-    if (!p.paired) {
+    if (P.debug_no_copy) {
+        desc->e0a = desc->e0b = 0;
+        mbar_arrive(full);
+    } else if (!p.paired) {
         const int64_t flat = p.seg[seg].flat0 + (int64_t)layer * P.seg_step[k][seg] + (int64_t)row0 * p.n;
         const int64_t ga = (flat >> 8) & ~(int64_t)1;
         const int64_t gl = (flat + pbytes - 1) >> 8;
@@ -268,7 +272,7 @@ __device__ __forceinline__ void produce_att_stage(Producer &pr, const FusedParam
     desc->e0a = old;
     desc->off = (int)off;
     desc->aux = (int)voff;
-    if (old > 0) {
+    if (old > 0 && !P.debug_no_copy) {
         const int kvh = h / P.kv_mul;
         const int64_t row = ((int64_t)kvh * P.seq_len + t0) * P.head;
         const float *kc = P.mv[0].k_cache + (int64_t)layer * P.kv_step + row;
@@ -308,22 +312,20 @@ __device__ __forceinline__ void consumers_wait(const unsigned int *ctr, unsigned
 }
 
 // One matrix-vector phase of the block: prologue (input vector -> fixed-point limbs in shared memory)
-// and the block's `nmine` stages.  MERGE: the input is the attention output, assembled from the partial
-// results of the blocks that worked on each head.
-enum InputMode { IN_RMS = 0, IN_PLAIN = 1, IN_MERGE = 2 };
-
-template <int MODE>
-__device__ __forceinline__ void consume_ring_phase(const FusedParams &P, const MvParams &p, int layer, int nmine, const float *rms_w,
-                                                   float rms_wmax, const AttSplit &as, uint8_t *smem, uint32_t sbase, Consumer &cs,
-                                                   uint64_t wait_ns, int pidx)
+// and the block's `nmine` stages.  One copy of this code serves all four phases (the differences are run-time
+// parameters): the prologue runs once per phase, so its instructions come from the L2 every time, and four
+// inlined copies of it cost more in instruction fetches than the branches cost here.
+// merge: the input is the attention output, assembled from the partial results of the blocks that worked on
+// each head.
+__device__ __forceinline__ void consume_ring_phase(const FusedParams &P, const MvParams &p, int layer, int nmine, bool merge,
+                                                   const float *rms_w, float rms_wmax, const AttSplit &as, uint8_t *smem,
+                                                   uint32_t sbase, Consumer &cs, uint64_t wait_ns, int pidx)
 {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nw = p.rpp * p.wpr;
-    const int ncons = nw * 32;
     const bool active = warp < nw;
     const int rsub = warp / p.wpr;
     const int wi = warp - rsub * p.wpr;
-    constexpr bool MERGE = MODE == IN_MERGE;
     constexpr int RT = 1;   // rows per thread and stage: a stage holds one row per group of wpr warps
     const int n = p.n;
     const int R = RT * p.rpp;
@@ -340,117 +342,138 @@ __device__ __forceinline__ void consume_ring_phase(const FusedParams &P, const M
 
     float inv = 1.0f;
     {
+        // All 576 consumer threads share the vector: thread t owns the float4s t, t + 576, ...
         const int n4 = n >> 2;
-        // a vector of dim elements (RMSNorm'd input, merged attention output) takes four rounds at most, the
-        // hidden vector eight: the host checks it
-        constexpr int kRounds = MODE == IN_PLAIN ? kFRounds : kFMergeRounds;
-        constexpr bool has_rms = MODE == IN_RMS;
-        float4 xr[kRounds], wr[has_rms ? kRounds : 1];
+        const bool has_rms = rms_w != nullptr;
+        float4 xr[kFRounds], wr[kFRmsRounds];   // the RMSNorm'd vectors have dim elements: kFRmsRounds rounds (host-checked)
+        if (!merge) {
 #pragma unroll
-        for (int j = 0; j < kRounds; ++j) {
-            const int idx = tid + j * ncons;
-            xr[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if constexpr (has_rms)
-                wr[j] = make_float4(1.f, 1.f, 1.f, 1.f);
-            if (j * ncons >= n4)
-                break;
-            if (active && idx < n4) {
-                if constexpr (!MERGE) {
+            for (int j = 0; j < kFRounds; ++j) {
+                const int idx = tid + j * kFCons;
+                xr[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (j < kFRmsRounds)
+                    wr[j] = make_float4(1.f, 1.f, 1.f, 1.f);
+                if (idx < n4) {
                     xr[j] = ld_cg_f4_issue(p.x_in + (int64_t)idx * 4);
-                    if constexpr (has_rms)
+                    if (j < kFRmsRounds && has_rms)
                         wr[j] = ld_cg_f4_issue(rms_w + (int64_t)idx * 4);
-                } else {
-                    // The partials of head h were written by blocks b0..b1 of the attention phase, one slot each, in
-                    // block order; merged here in that order (the result does not depend on which SM ran what).
+                }
+            }
+        } else {
+            // The partials of head h were written by blocks b0..b1 of the attention phase, one slot each, in block
+            // order.  First a table of their weights in shared memory (one thread per head), then every thread
+            // folds the partial outputs of its elements with those weights, in slot order: the result does not
+            // depend on which SM ran what.
+            float *tw = reinterpret_cast<float *>(share);            // [n_heads][kAttSlots] weights, then [n_heads] 1 / sum
+            const int ps = P.head + 4;
+            if (tid < P.n_heads) {
+                const int h = tid;
+                const int u0 = h * as.nchunk;
+                const int np = min(att_block_of(as, u0 + as.nchunk - 1) - att_block_of(as, u0) + 1, kAttSlots);
+                const float *hp = P.att_part + (int64_t)h * kAttSlots * ps + P.head;
+                float ms[kAttSlots], ls[kAttSlots];
+#pragma unroll
+                for (int s2 = 0; s2 < kAttSlots; ++s2) {
+                    ms[s2] = -INFINITY;
+                    ls[s2] = 0.f;
+                    if (s2 < np) {
+                        const float2 ml = __ldcg(reinterpret_cast<const float2 *>(hp + (int64_t)s2 * ps));
+                        ms[s2] = ml.x;
+                        ls[s2] = ml.y;
+                    }
+                }
+                float gm = -INFINITY;
+#pragma unroll
+                for (int s2 = 0; s2 < kAttSlots; ++s2)
+                    gm = fmaxf(gm, ms[s2]);
+                float L = 0.f;
+#pragma unroll
+                for (int s2 = 0; s2 < kAttSlots; ++s2) {
+                    const float w = ls[s2] > 0.f ? expf(ms[s2] - gm) : 0.f;
+                    L = fmaf(ls[s2], w, L);
+                    tw[h * kAttSlots + s2] = w;
+                }
+                tw[P.n_heads * kAttSlots + h] = L;
+            }
+#pragma unroll
+            for (int j = 0; j < kFRounds; ++j)
+                xr[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int j = 0; j < kFRmsRounds; ++j)
+                wr[j] = make_float4(1.f, 1.f, 1.f, 1.f);
+            named_barrier_sync(2, kFCons);
+#pragma unroll
+            for (int j = 0; j < kFRmsRounds; ++j) {
+                const int idx = tid + j * kFCons;
+                if (idx < n4) {
                     const int e = idx * 4;
                     const int h = e / P.head, d = e - h * P.head;
-                    const int u0 = h * as.nchunk;
-                    const int b0 = att_block_of(as, u0), b1 = att_block_of(as, u0 + as.nchunk - 1);
-                    const int np = min(b1 - b0 + 1, kAttSlots);
-                    const int ps = P.head + 4;
-                    const float *hp = P.att_part + (int64_t)h * kAttSlots * ps;
-                    float4 o4[kAttSlots];
-                    float ms[kAttSlots], ls[kAttSlots];
-#pragma unroll
-                    for (int s = 0; s < kAttSlots; ++s) {
-                        ms[s] = -INFINITY;
-                        ls[s] = 0.f;
-                        o4[s] = make_float4(0.f, 0.f, 0.f, 0.f);
-                        if (s < np) {
-                            o4[s] = ld_cg_f4_issue(hp + (int64_t)s * ps + d);
-                            ms[s] = __ldcg(hp + (int64_t)s * ps + P.head);
-                            ls[s] = __ldcg(hp + (int64_t)s * ps + P.head + 1);
-                        }
-                    }
-                    float gm = -INFINITY;
-#pragma unroll
-                    for (int s = 0; s < kAttSlots; ++s)
-                        gm = fmaxf(gm, ms[s]);
-                    float L = 0.f;
+                    const float *hp = P.att_part + (int64_t)h * kAttSlots * ps + d;
                     float4 O = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-                    for (int s = 0; s < kAttSlots; ++s) {
-                        if (ls[s] > 0.f) {
-                            const float w = expf(ms[s] - gm);
-                            L = fmaf(ls[s], w, L);
-                            O.x = fmaf(o4[s].x, w, O.x);
-                            O.y = fmaf(o4[s].y, w, O.y);
-                            O.z = fmaf(o4[s].z, w, O.z);
-                            O.w = fmaf(o4[s].w, w, O.w);
+                    for (int s2 = 0; s2 < kAttSlots; ++s2) {
+                        const float w = tw[h * kAttSlots + s2];
+                        if (w > 0.f) {
+                            const float4 o = ld_cg_f4_issue(hp + (int64_t)s2 * ps);
+                            O.x = fmaf(o.x, w, O.x);
+                            O.y = fmaf(o.y, w, O.y);
+                            O.z = fmaf(o.z, w, O.z);
+                            O.w = fmaf(o.w, w, O.w);
                         }
                     }
+                    const float L = tw[P.n_heads * kAttSlots + h];
                     // ExpSumNormalize.java:33-37 folded into the weighted sum
                     xr[j] = make_float4(__fdiv_rn(O.x, L), __fdiv_rn(O.y, L), __fdiv_rn(O.z, L), __fdiv_rn(O.w, L));
                 }
             }
+            named_barrier_sync(2, kFCons);   // the table's place is taken by the limbs below
         }
         float ssq = 0.f, amax = 0.f;
 #pragma unroll
-        for (int j = 0; j < kRounds; ++j) {
-            if (j * ncons >= n4)
-                break;
+        for (int j = 0; j < kFRounds; ++j) {
             ssq = fmaf(xr[j].x, xr[j].x, ssq);
             ssq = fmaf(xr[j].y, xr[j].y, ssq);
             ssq = fmaf(xr[j].z, xr[j].z, ssq);
             ssq = fmaf(xr[j].w, xr[j].w, ssq);
             amax = fmaxf(fmaxf(amax, fmaxf(fabsf(xr[j].x), fabsf(xr[j].y))), fmaxf(fabsf(xr[j].z), fabsf(xr[j].w)));
         }
+        if (tid == 0 && (P.debug_no_copy & 8)) fused_trace(P, pidx, 5);
         ssq = warp_sum(ssq);
-        amax = warp_max(amax);
-        if (lane == 0 && active) {
+        amax = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(amax)));   // non-negative floats order like their bits
+        if (lane == 0) {
             scratch[warp] = ssq;
             scratch[32 + warp] = amax;
         }
         named_barrier_sync(2, kFCons);
-        ssq = warp_sum(lane < nw ? scratch[lane] : 0.f);
-        amax = warp_max(lane < nw ? scratch[32 + lane] : 0.f);
-        if constexpr (has_rms) {
+        if (tid == 0 && (P.debug_no_copy & 8)) fused_trace(P, pidx, 6);
+        ssq = warp_sum(lane < kFusedConsWarps ? scratch[lane] : 0.f);   // the same order in every warp and block
+        amax = __uint_as_float(__reduce_max_sync(0xffffffffu, lane < kFusedConsWarps ? __float_as_uint(scratch[32 + lane]) : 0u));
+        if (has_rms) {
             float tot = __fdiv_rn(ssq, (float)n);
             tot = __fadd_rn(tot, 1e-5f);
             const float ss = __fdiv_rn(1.0f, __fsqrt_rn(tot));
 #pragma unroll
-            for (int j = 0; j < kRounds; ++j) {
-                if (j * ncons >= n4)
-                    break;
+            for (int j = 0; j < kFRmsRounds; ++j) {
                 xr[j].x = __fmul_rn(wr[j].x, __fmul_rn(ss, xr[j].x));
                 xr[j].y = __fmul_rn(wr[j].y, __fmul_rn(ss, xr[j].y));
                 xr[j].z = __fmul_rn(wr[j].z, __fmul_rn(ss, xr[j].z));
                 xr[j].w = __fmul_rn(wr[j].w, __fmul_rn(ss, xr[j].w));
             }
-            amax = amax * ss * rms_wmax * 1.000001f;
+            amax = amax * ss * rms_wmax * 1.000001f;   // bound of |w * (ss * x)| from max|x| and max|w|
         }
-        int ex = 0;
-        if (amax > 0.f && amax < 3.0e38f)
-            frexpf(amax, &ex);
+        // 24-bit fixed point: one power-of-two scale per vector, |x * f| <= 2^22
+        int ex = (int)((__float_as_uint(amax) >> 23) & 0xffu) - 126;   // amax < 2^ex for normal numbers
+        if (!(amax > 0.f) || !(amax < 3.0e38f))
+            ex = 0;
         ex = max(-90, min(126, ex));
         const float f = __int_as_float((127 + 22 - ex) << 23);
         inv = __int_as_float((127 + ex - 22) << 23);
 #pragma unroll
-        for (int j = 0; j < kRounds; ++j) {
-            const int idx = tid + j * ncons;
-            if (j * ncons >= n4)
-                break;
-            if (active && idx < n4) {
+        for (int j = 0; j < kFRounds; ++j) {
+            const int idx = tid + j * kFCons;
+            if (idx < n4) {
+                // three balanced signed byte limbs: after the add-and-flip, bytes 0..2 of z are l0, l1, l2 in
+                // [-128, 127] with X = l0 + 256 l1 + 65536 l2
                 const uint32_t z0 = ((uint32_t)__float2int_rn(xr[j].x * f) + 0x00008080u) ^ 0x00008080u;
                 const uint32_t z1 = ((uint32_t)__float2int_rn(xr[j].y * f) + 0x00008080u) ^ 0x00008080u;
                 const uint32_t z2 = ((uint32_t)__float2int_rn(xr[j].z * f) + 0x00008080u) ^ 0x00008080u;
@@ -493,21 +516,30 @@ __device__ __forceinline__ void consume_ring_phase(const FusedParams &P, const M
     if (tid == 0)
         fused_trace(P, pidx, 1);
 
-    for (int it = 0; it < nmine; ++it) {
-        const int e = cs.seq % kFDesc;
-        if (!mbar_wait_bounded(sbase + kFBarFull + 8 * e, (uint32_t)(cs.seq / kFDesc) & 1u, cs.lost ? kFShortWaitNs : wait_ns))
-            cs.lost = true;
-        const FStage d = *(reinterpret_cast<const FStage *>(smem + kFDescOff) + e);
-        const bool skip = cs.lost && !cs.lost_before;
-        const uint8_t *slot_ptr = smem + kFHeader + P.xarea_bytes + (size_t)d.off;
-        float v[RT];
+    // The block's stages are taken in groups of kFGroup: a warp works through the rows of a group one stage after
+    // the other, then folds the group's partial sums with one butterfly and hands them to the epilogue warp in one
+    // go.  A warp's chain of waits, loads, dot products, fold and hand-over is serial; per group instead of per
+    // stage it costs a quarter as much per row, while the ring still moves in stages of rpp rows.
+    for (int g0 = 0; g0 < nmine; g0 += kFGroup) {
+        const int cnt = min(kFGroup, nmine - g0);
+        float v[kFGroup];
 #pragma unroll
-        for (int t = 0; t < RT; ++t) {
+        for (int t = 0; t < kFGroup; ++t) {
             v[t] = 0.f;
-            const int r = rsub + t * p.rpp;
-            const int half = (p.paired && r >= R / 2) ? 1 : 0;   // second half of a paired stage: the partner matrix
+            if (t >= cnt)
+                continue;
+            const int e = cs.seq % kFDesc;
+            if (!mbar_wait_bounded(sbase + kFBarFull + 8 * e, (uint32_t)(cs.seq / kFDesc) & 1u, cs.lost ? kFShortWaitNs : wait_ns))
+                cs.lost = true;
+            if (g0 == 0 && t == 0 && tid == 0)
+                fused_trace(P, pidx, 4);
+            const FStage d = *(reinterpret_cast<const FStage *>(smem + kFDescOff) + e);
+            const bool skip = cs.lost && !cs.lost_before;
+            const uint8_t *slot_ptr = smem + kFHeader + P.xarea_bytes + (size_t)d.off;
+            const int r = rsub;                                     // row of the stage in shared memory
+            const int half = (p.paired && r >= R / 2) ? 1 : 0;      // second half of a paired stage: the partner matrix
             const int local = r - half * (R / 2);
-            if (!skip && gvalid && local < d.nrows) {
+            if (!skip && gvalid && local < d.nrows && !(P.debug_no_copy & 4)) {
                 const uint8_t *rowp = slot_ptr + (size_t)r * rowbytes;
                 const int e0 = (half ? d.e0b : d.e0a) + local * n;
                 const float2 *hp = reinterpret_cast<const float2 *>(slot_ptr + p.hdr_off + half * p.half_hdr);
@@ -529,33 +561,33 @@ __device__ __forceinline__ void consume_ring_phase(const FusedParams &P, const M
                     a1 = dp4a_us(w.w, xl[k][3][1], a1);
                     a2 = dp4a_us(w.w, xl[k][3][2], a2);
                 }
+                // |a_l| <= 64 * 255 * 128 < 2^24: the conversions are exact
                 const float dsum = fmaf((float)a2, 65536.0f, fmaf((float)a1, 256.0f, (float)a0));
                 v[t] = fmaf(ms.y, dsum, ms.x * xs);
             }
+            __syncwarp();
+            if (lane == 0)
+                mbar_arrive(sbase + kFBarEmpty + 8 * e);   // this warp is done with the stage's bytes
+            ++cs.seq;
         }
-        const float tot = Fold<RT, 16>::run(v, lane) * inv;
-        __syncwarp();
-        if (lane == 0)
-            mbar_arrive(sbase + kFBarEmpty + 8 * e);
+        const float tot = Fold<kFGroup, 16>::run(v, lane) * inv;   // lane t * (32 / kFGroup) holds the sum of stage t
+        if (P.debug_no_copy & 2) {
+            if (tot == 123.456f)
+                scratch[40] = tot;
+            continue;
+        }
         if (cs.rround > 0) {
             if (!mbar_wait_bounded(sbase + kFBarRedEmpty + 8 * cs.rb, (uint32_t)(cs.rround - 1) & 1u, cs.lost ? kFShortWaitNs : wait_ns))
                 cs.lost = true;
         }
-        int *rh = reinterpret_cast<int *>(smem + kFRedOff + cs.rb * kFRedStride);
-        float *red = reinterpret_cast<float *>(rh + 4);
-        if (tid == 0) {
-            rh[0] = d.seg;
-            rh[1] = d.row0;
-            rh[2] = skip ? 0 : d.nrows;
-        }
-        if (active && (lane & (32 / RT - 1)) == 0) {
-            const int t = lane / (32 / RT);
-            red[(rsub + t * p.rpp) * p.wpr + wi] = tot;
+        float *red = reinterpret_cast<float *>(smem + kFRedOff + cs.rb * kFRedStride);
+        if (active && (lane & (32 / kFGroup - 1)) == 0) {
+            const int t = lane / (32 / kFGroup);
+            red[(t * p.rpp + rsub) * p.wpr + wi] = (cs.lost && !cs.lost_before) ? 0.f : tot;
         }
         __syncwarp();
         if (lane == 0)
             mbar_arrive(sbase + kFBarRedFull + 8 * cs.rb);
-        ++cs.seq;
         if (++cs.rb == kFRedBufs) {
             cs.rb = 0;
             ++cs.rround;
@@ -718,63 +750,80 @@ struct Epilogue {
     bool lost, lost_before;
 };
 
-__device__ __forceinline__ void epilogue_phase(const FusedParams &P, const MvParams &p, int layer, int nmine, int pos, uint8_t *smem,
-                                               uint32_t sbase, Epilogue &es, uint64_t wait_ns)
+__device__ __forceinline__ void epilogue_phase(const FusedParams &P, const MvParams &p, int layer, int first, int nmine, int pos,
+                                               uint8_t *smem, uint32_t sbase, Epilogue &es, uint64_t wait_ns)
 {
     const int lane = threadIdx.x & 31;
+    const int G = gridDim.x;
     const int R = p.rt * p.rpp;
+    const int rs = p.rs;                 // output rows (row pairs) per stage: at most 8, so a group fits the 32 lanes
     const float *rope_c = reinterpret_cast<const float *>(smem + kFRopeOff);
     const float *rope_s = rope_c + 64;
-    for (int it = 0; it < nmine; ++it) {
+    for (int g0 = 0; g0 < nmine && !(P.debug_no_copy & 2); g0 += kFGroup) {
+        const int cnt = min(kFGroup, nmine - g0);
         if (!mbar_wait_bounded(sbase + kFBarRedFull + 8 * es.rb, (uint32_t)es.rround & 1u, es.lost ? kFShortWaitNs : wait_ns))
             es.lost = true;
-        const int *rh = reinterpret_cast<const int *>(smem + kFRedOff + es.rb * kFRedStride);
-        const int seg = rh[0], row0 = rh[1];
-        const int nrows = (es.lost && !es.lost_before) ? 0 : rh[2];
-        const float *red = reinterpret_cast<const float *>(rh + 4);
+        const float *red = reinterpret_cast<const float *>(smem + kFRedOff + es.rb * kFRedStride);
+        const bool skip = es.lost && !es.lost_before;
         if (p.epilogue == EPI_QKV_ROPE) {
-            if (lane < (nrows >> 1)) {
-                float v0 = 0.f, v1 = 0.f;
-                for (int w = 0; w < p.wpr; ++w) {
-                    v0 += red[(2 * lane) * p.wpr + w];
-                    v1 += red[(2 * lane + 1) * p.wpr + w];
-                }
-                const int row = row0 + 2 * lane;
-                if (seg == 2) {
-                    const int kvh = row / p.head, d = row - kvh * p.head;
-                    float *dst = p.v_cache + (int64_t)layer * P.kv_step + ((int64_t)kvh * p.seq_len + pos) * p.head + d;
-                    dst[0] = v0;
-                    dst[1] = v1;
-                } else {
-                    const int d = row % p.head;
-                    const float c = rope_c[d >> 1], s = rope_s[d >> 1];
-                    const float r0 = __fsub_rn(__fmul_rn(v0, c), __fmul_rn(v1, s));   // ApplyRope.java:61-92
-                    const float r1 = __fadd_rn(__fmul_rn(v0, s), __fmul_rn(v1, c));
-                    if (seg == 0) {
-                        p.q_out[row] = r0;
-                        p.q_out[row + 1] = r1;
+            // a lane owns a pair of rows: (v0, v1) are rotated together (ApplyRope.java:61-92)
+            const int pairs = rs >> 1;
+            const int t = lane / pairs, i = lane - t * pairs;
+            if (t < cnt && !skip) {
+                int seg, row0, nrows;
+                stage_rows(p, first + (g0 + t) * G, seg, row0, nrows);
+                if (2 * i < nrows) {
+                    const float *rt = red + (t * p.rpp) * p.wpr;
+                    float v0 = 0.f, v1 = 0.f;
+                    for (int w = 0; w < p.wpr; ++w) {
+                        v0 += rt[(2 * i) * p.wpr + w];
+                        v1 += rt[(2 * i + 1) * p.wpr + w];
+                    }
+                    const int row = row0 + 2 * i;
+                    if (seg == 2) {
+                        const int kvh = row / p.head, d = row - kvh * p.head;
+                        float *dst = p.v_cache + (int64_t)layer * P.kv_step + ((int64_t)kvh * p.seq_len + pos) * p.head + d;
+                        dst[0] = v0;
+                        dst[1] = v1;
                     } else {
-                        const int kvh = row / p.head;
-                        float *dst = p.k_cache + (int64_t)layer * P.kv_step + ((int64_t)kvh * p.seq_len + pos) * p.head + d;
-                        dst[0] = r0;
-                        dst[1] = r1;
+                        const int d = row % p.head;
+                        const float c = rope_c[d >> 1], sn = rope_s[d >> 1];
+                        const float r0 = __fsub_rn(__fmul_rn(v0, c), __fmul_rn(v1, sn));
+                        const float r1 = __fadd_rn(__fmul_rn(v0, sn), __fmul_rn(v1, c));
+                        if (seg == 0) {
+                            p.q_out[row] = r0;
+                            p.q_out[row + 1] = r1;
+                        } else {
+                            const int kvh = row / p.head;
+                            float *dst = p.k_cache + (int64_t)layer * P.kv_step + ((int64_t)kvh * p.seq_len + pos) * p.head + d;
+                            dst[0] = r0;
+                            dst[1] = r1;
+                        }
                     }
                 }
             }
-        } else if (p.epilogue == EPI_SWIGLU) {
-            if (lane < nrows) {
-                float v1 = 0.f, v3 = 0.f;
-                for (int w = 0; w < p.wpr; ++w) {
-                    v1 += red[lane * p.wpr + w];
-                    v3 += red[(R / 2 + lane) * p.wpr + w];
+        } else {
+            const int t = lane / rs, i = lane - t * rs;
+            if (t < cnt && !skip) {
+                int seg, row0, nrows;
+                stage_rows(p, first + (g0 + t) * G, seg, row0, nrows);
+                if (i < nrows) {
+                    const float *rt = red + (t * p.rpp) * p.wpr;
+                    if (p.epilogue == EPI_SWIGLU) {
+                        float v1 = 0.f, v3 = 0.f;
+                        for (int w = 0; w < p.wpr; ++w) {
+                            v1 += rt[i * p.wpr + w];
+                            v3 += rt[(R / 2 + i) * p.wpr + w];
+                        }
+                        p.y[row0 + i] = __fmul_rn(__fmul_rn(v1, sigmoid_accurate(v1)), v3);   // Silu.java:122-132 order
+                    } else {   // EPI_RESIDUAL
+                        float a = 0.f;
+                        for (int w = 0; w < p.wpr; ++w)
+                            a += rt[i * p.wpr + w];
+                        atomicAdd(p.y + row0 + i, a);   // one add per element and phase: deterministic
+                    }
                 }
-                p.y[row0 + lane] = __fmul_rn(__fmul_rn(v1, sigmoid_accurate(v1)), v3);   // Silu.java:122-132 order
             }
-        } else if (lane < nrows) {   // EPI_RESIDUAL
-            float a = 0.f;
-            for (int w = 0; w < p.wpr; ++w)
-                a += red[lane * p.wpr + w];
-            atomicAdd(p.y + row0 + lane, a);   // one add per element and phase: deterministic
         }
         __syncwarp();
         if (lane == 0)
@@ -831,12 +880,14 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_layers_kernel(const __
         int rot = 0, pos = -1;
         AttSplit as{};
         for (int layer = 0; layer < P.n_layers; ++layer) {
-#pragma unroll
+#pragma unroll 1
             for (int k = 0; k < 4; ++k) {
                 const MvParams &p = P.mv[k];
                 const int S = p.total_stages;
+                if (!(P.debug_no_copy & 8)) fused_trace(P, layer * 5 + (k == 0 ? 0 : k + 1), 5);
                 for (int s = first_stage_of(b, rot, G); s < S; s += G)
                     produce_ring_stage(pr, P, p, k, layer, s, pol);
+                if (!(P.debug_no_copy & 8)) fused_trace(P, layer * 5 + (k == 0 ? 0 : k + 1), 6);
                 rot = (rot + S) % G;
                 if (k == 0) {
                     if (pos < 0) {
@@ -847,8 +898,10 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_layers_kernel(const __
                     }
                     if (b < as.ga) {
                         const int u0 = att_first_unit(as, b), u1 = att_first_unit(as, b + 1);
+                        fused_trace(P, layer * 5 + 1, 5);
                         for (int u = u0; u < u1; ++u)
                             produce_att_stage(pr, P, layer, u, as, pos);
+                        fused_trace(P, layer * 5 + 1, 6);
                     }
                 }
             }
@@ -881,14 +934,14 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_layers_kernel(const __
         }
         int rot = 0;
         for (int layer = 0; layer < P.n_layers; ++layer) {
-#pragma unroll
+#pragma unroll 1
             for (int k = 0; k < 4; ++k) {
                 const MvParams &p = P.mv[k];
                 const int S = p.total_stages;
                 const int first = first_stage_of(b, rot, G);
                 const int nmine = first < S ? (S - first + G - 1) / G : 0;
                 rot = (rot + S) % G;
-                epilogue_phase(P, p, layer, nmine, pos, smem, sbase, es, wait_ns);
+                epilogue_phase(P, p, layer, first, nmine, pos, smem, sbase, es, wait_ns);
                 // every result of the block in this phase was written by this warp; the release is cumulative
                 __syncwarp();
                 const int pidx = layer * 5 + (k == 0 ? 0 : k + 1);
@@ -910,7 +963,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_layers_kernel(const __
     cs.lost = cs.lost_before = lost_at_entry;
     int rot = 0;
     for (int layer = 0; layer < P.n_layers; ++layer) {
-#pragma unroll
+#pragma unroll 1
         for (int k = 0; k < 4; ++k) {
             const MvParams &p = P.mv[k];
             const int S = p.total_stages;
@@ -919,18 +972,15 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_layers_kernel(const __
             rot = (rot + S) % G;
             const int pidx = layer * 5 + (k == 0 ? 0 : k + 1);
             if (nmine > 0) {
+                if (tid == 0)
+                    fused_trace(P, pidx, 7);
                 if (pidx > 0)   // the first phase's input came from the kernel in front
                     consumers_wait(P.sync + (int64_t)kSyncStride * (pidx - 1), target, smem, cs, wait_ns);
                 if (tid == 0)
                     fused_trace(P, pidx, 0);
                 const float *rms_w = p.rms_w ? p.rms_w + (int64_t)layer * P.rms_step : nullptr;
                 const float wmax = p.rms_w ? __ldg(P.rms_wmax + 2 * layer + (k == 2 ? 1 : 0)) : 1.0f;
-                if (k == 1)
-                    consume_ring_phase<IN_MERGE>(P, p, layer, nmine, nullptr, 1.0f, as, smem, sbase, cs, wait_ns, pidx);
-                else if (k == 3)
-                    consume_ring_phase<IN_PLAIN>(P, p, layer, nmine, nullptr, 1.0f, as, smem, sbase, cs, wait_ns, pidx);
-                else
-                    consume_ring_phase<IN_RMS>(P, p, layer, nmine, rms_w, wmax, as, smem, sbase, cs, wait_ns, pidx);
+                consume_ring_phase(P, p, layer, nmine, k == 1, rms_w, wmax, as, smem, sbase, cs, wait_ns, pidx);
             }
             if (k == 0) {
                 // attention over positions 0..pos (Run.java:450-478)
@@ -940,6 +990,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_layers_kernel(const __
                     if (tid == 0)
                         fused_trace(P, aidx, 0);
                     consume_attention(P, layer, as, pos, smem, sbase, cs, wait_ns);
+                    if (tid == 0)
+                        fused_trace(P, aidx, 2);
                     // flush() ended with a barrier of all consumers: their partials are written
                 }
                 if (tid == 0) {

@@ -218,7 +218,8 @@ struct FusedParams {
     const unsigned int *epoch; // forwards started on this context
     SeqState *state;
     int timeout_us;
-    unsigned long long *trace; // optional: [block][5 * n_layers][4] global-timer marks, else nullptr
+    unsigned long long *trace; // optional: [block][5 * n_layers][8] global-timer marks, else nullptr
+    int debug_no_copy;         // measurement aid: the producer hands out stages without copying (results are garbage)
 };
 constexpr int kSyncStride = 32;     // unsigned ints between two hand-over counters (128 bytes)
 constexpr int kFusedThreads = 640;  // 18 consumer warps, the producer warp, the epilogue warp

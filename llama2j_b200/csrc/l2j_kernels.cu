@@ -112,9 +112,9 @@ __device__ void finish_argmax_warp(const MvParams &p, int nblocks, int lane)
         if (lane < n) {
             const float2 *mine = p.ll.tp->ll[TPV_CAND][me] + 2 * lane;
             float4 c = ld_pairs2(mine);
-            const uint64_t t0 = global_timer_ns();
+            const long long c0 = sm_clock();
             while (__float_as_int(c.y) != seq || __float_as_int(c.w) != seq) {
-                if (global_timer_ns() - t0 > (uint64_t)p.timeout_us * 1000ull) {
+                if (sm_clock() - c0 > 2000ll * p.timeout_us) {
                     atomicOr(&p.state->status, 0x1);   // L2J_DS_WAIT_TIMEOUT
                     break;
                 }
@@ -742,7 +742,7 @@ __global__ void __launch_bounds__(kRingMaxThreads, 1) matvec_ring_kernel(const _
                 xr[j] = make_float4(0.f, 0.f, 0.f, 0.f);
                 wr[j] = make_float4(1.f, 1.f, 1.f, 1.f);
             }
-            uint64_t t_first = 0;
+            long long t_first = 0;
             // four rounds of pairs in flight at a time (their sequence numbers double the registers a round needs)
 #pragma unroll
             for (int c0 = 0; c0 < kPrologueRounds; c0 += 4) {
@@ -763,10 +763,10 @@ __global__ void __launch_bounds__(kRingMaxThreads, 1) matvec_ring_kernel(const _
                     if (idx < n4 && has_work) {
                         while (__float_as_int(pa[q].y) != seq_in || __float_as_int(pa[q].w) != seq_in ||
                                __float_as_int(pb[q].y) != seq_in || __float_as_int(pb[q].w) != seq_in) {
-                            const uint64_t now = global_timer_ns();
+                            const long long now = sm_clock();   // limit in cycles: two per nanosecond
                             if (t_first == 0)
                                 t_first = now;
-                            if (now - t_first > (lost ? kShortWaitNs : wait_ns)) {
+                            if (now - t_first > (long long)(2 * (lost ? kShortWaitNs : wait_ns))) {
                                 lost = true;
                                 break;
                             }

@@ -12,7 +12,7 @@ import os
 from . import build as _build
 
 E_INVALID, E_CUDA, E_STATE, E_DEVICE, E_NOMEM = -1, -2, -3, -4, -5
-F_NO_GRAPH, F_NO_PDL, F_SIMPLE = 0x1, 0x2, 0x4
+F_NO_GRAPH, F_NO_PDL, F_SIMPLE, F_STEP_KERNELS = 0x1, 0x2, 0x4, 0x8
 QUANT_GROUP, QUANT_GROUP_BYTES = 256, 264
 
 (T_TOKEN_EMBEDDING, T_RMS_ATT, T_WQ, T_WK, T_WV, T_WO, T_RMS_FFN, T_W1, T_W2, T_W3, T_RMS_FINAL, T_WCLS) = range(12)
@@ -69,6 +69,7 @@ _SIGNATURES = {
     "l2j_get_stats": (C.c_int, [_P, C.POINTER(Stats)]),
     "l2j_launch_mode": (C.c_int, [_P]),
     "l2j_read_buffer": (C.c_int, [_P, C.c_int, C.c_int, C.c_int, _P, C.c_int]),
+    "l2j_kv_write": (C.c_int, [_P, C.c_int, C.c_int, C.c_int, _P, _P]),
     "l2j_last_generate_us": (C.c_int, [_P, C.POINTER(C.c_double)]),
     "l2j_time_kernels": (C.c_int, [_P, C.c_int, C.c_int, C.POINTER(C.c_double)]),
     "l2j_trace_kernel": (C.c_int, [_P, C.c_int, C.c_int, C.c_int, _P, C.c_int]),

@@ -160,6 +160,16 @@ class Transformer:
         _lib.check(self._lib.l2j_read_trace(self._ctx, out.ctypes.data, out.size), self._ctx)
         return out
 
+    def kv_write(self, layer: int, pos0: int, k_rows: np.ndarray, v_rows: np.ndarray) -> None:
+        """Restores rows [pos0, pos0 + len) of a layer's KV cache from (position, kv_dim) float arrays, the
+        layout the reference keeps them in (RunState.java:141-151)."""
+        k = np.ascontiguousarray(k_rows, dtype=np.float32)
+        v = np.ascontiguousarray(v_rows, dtype=np.float32)
+        if k.shape != v.shape or k.ndim != 2 or k.shape[1] != self.cfg.kv_dim:
+            raise ValueError("k_rows and v_rows must both be (positions, kv_dim)")
+        _lib.check(self._lib.l2j_kv_write(self._ctx, int(layer), int(pos0), int(k.shape[0]), k.ctypes.data, v.ctypes.data),
+                   self._ctx)
+
     def reset(self) -> None:
         _lib.check(self._lib.l2j_reset(self._ctx), self._ctx)
 
