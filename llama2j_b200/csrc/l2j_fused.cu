@@ -57,6 +57,7 @@ constexpr int kFBarEmpty = 128;         // uint64 empty[16]
 constexpr int kFBarRedFull = 256;       // uint64 red_full[4]
 constexpr int kFBarRedEmpty = 288;      // uint64 red_empty[4]
 constexpr int kFFlag = 320;             // int: result of the poll of a hand-over counter
+constexpr int kFIssued = 324;           // int: bytes of the ring the producer has handed out so far
 constexpr int kFVStart = 3264;          // int vstart[16]: the producer's bookkeeping of where each stage in flight begins
 constexpr int kFScratch = 384;          // float scratch[64]
 constexpr int kFDescOff = 640;          // FStage desc[16]
@@ -66,14 +67,31 @@ constexpr int kFRopeOff = 3328;         // float cos[64], sin[64] of the token's
 constexpr int kFHeader = 3840;          // end of the fixed part (128-byte aligned)
 constexpr int kFCons = kFusedConsWarps * 32;
 constexpr int kFRounds = 8;             // 16-byte loads of the input vector per consumer thread at most
+constexpr int kAttFastSlots = 4, kAttFastRounds = 2;   // the merge that fetches all partials of a thread's elements at once
 constexpr int kFRmsRounds = 4;          // the same for a vector of dim elements (RMSNorm'd input, merged attention output)
 constexpr uint64_t kFShortWaitNs = 2000;
 
 struct FStage {
-    int seg, row0, nrows, e0a, e0b, off, aux, pad;
+    int off, nrows, e0a, e0b;   // what the consumers of a matrix stage need, in one 16-byte load: byte offset in the
+                                // ring, rows, element offset of the first row of each half relative to the headers
+    int seg, row0, aux, pad;
     // attention stage: seg = head, row0 = first position, nrows = positions (newest included),
     // e0a = positions that travel through the ring (older than the token), aux = byte offset of the V rows
 };
+
+__device__ __forceinline__ uint4 lds_v4(uint32_t addr)
+{
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+
+__device__ __forceinline__ float2 lds_f2(uint32_t addr)
+{
+    float2 v;
+    asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr));
+    return v;
+}
 
 __device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c)
 {
@@ -119,6 +137,7 @@ struct Fold {
 // kAttChunk positions), head-major, in contiguous runs over the first `ga` blocks.
 struct AttSplit {
     int nchunk, units, ga;
+    int np_max;   // partial results per head at most
 };
 
 __device__ __forceinline__ AttSplit att_split(const FusedParams &P, int pos, int grid)
@@ -126,7 +145,11 @@ __device__ __forceinline__ AttSplit att_split(const FusedParams &P, int pos, int
     AttSplit a;
     a.nchunk = (pos + kAttChunk) / kAttChunk;   // ceil((pos + 1) / chunk)
     a.units = P.n_heads * a.nchunk;
-    a.ga = min(min(grid, P.n_heads * kAttMaxSplit), a.units);
+    // Short contexts are a matter of latency, not bandwidth: three blocks per head keep the partials of a head
+    // few enough (four) for the step behind to fetch them in one round of loads.
+    const int per_head = a.nchunk <= 8 ? 3 : kAttMaxSplit;
+    a.ga = min(min(grid, P.n_heads * per_head), a.units);
+    a.np_max = min(a.nchunk, (a.ga + P.n_heads - 1) / P.n_heads + 1);
     return a;
 }
 
@@ -177,17 +200,20 @@ __device__ __forceinline__ void fused_trace(const FusedParams &P, int phase_inde
 struct Producer {
     uint8_t *smem;
     uint32_t sbase, ring_base;
-    int vhead;              // bytes handed out so far (positions in the ring are vhead mod ring_bytes); < 2^31 per token and block
+    int vhead;              // bytes handed out so far; < 2^31 per token and block
+    int off;                // vhead's position in the ring
     int ring_bytes;
     int seq, tail;          // descriptors issued / known to be released
     bool lost;
     uint64_t wait_ns;
+    int pos;                // the token's position, -1 until the kernel in front has set it
+    AttSplit as;
+    int issued;             // bytes of the stages issued so far (what the L2 prefetch cursor paces itself by)
 
     // Room for `bytes` contiguous bytes and a free descriptor; returns the offset in the ring.
     __device__ __forceinline__ uint32_t acquire(uint32_t bytes)
     {
         int *vstart = reinterpret_cast<int *>(smem + kFVStart);
-        int off = vhead % ring_bytes;
         if (off + (int)bytes > ring_bytes) {
             vhead += ring_bytes - off;
             off = 0;
@@ -200,13 +226,109 @@ struct Producer {
             ++tail;
         }
         vstart[seq % kFDesc] = vhead;
-        vhead = (vend + 127) & ~127;
-        return (uint32_t)off;
+        const uint32_t at = (uint32_t)off;
+        const int step = (int)((bytes + 127u) & ~127u);
+        vhead += step;
+        off += step;
+        return at;
     }
 };
 
+// The other cursor over the same sequence of stages, run by a warp of its own ahead of the producer: it asks L2
+// for the stages to come (cp.async.bulk.prefetch.L2).  The ring holds what the copies in flight need to keep
+// HBM busy; it cannot also buffer a phase boundary of several microseconds, so without this HBM idles at every
+// boundary.
+struct Prefetcher {
+    int pos;
+    AttSplit as;
+    int layer, part, idx, limit, rot, bytes;
+};
+
+// Position in the block's sequence of stages: part 0 QKV, 1 attention units, 2 Wo, 3 W1/W3, 4 W2.
+__device__ __forceinline__ int part_matrix(int part)
+{
+    return part == 0 ? 0 : part - 1;
+}
+
+template <typename T>
+__device__ __forceinline__ void producer_learn_pos(T &pr, const FusedParams &P, int grid)
+{
+    if (pr.pos < 0) {
+        // The position is set by the kernel in front; everything touched so far was weights.
+        pdl_wait();
+        pr.pos = __ldcg(&P.state->cur_pos);
+        pr.as = att_split(P, pr.pos, grid);
+    }
+}
+
+// Sets the prefetch cursor to the first item of its current part; empty parts are skipped by the caller.
+__device__ __forceinline__ void prefetch_enter(Prefetcher &pf, const FusedParams &P, int b, int grid)
+{
+    if (pf.part == 1) {
+        producer_learn_pos(pf, P, grid);
+        pf.idx = b < pf.as.ga ? att_first_unit(pf.as, b) : 0;
+        pf.limit = b < pf.as.ga ? att_first_unit(pf.as, b + 1) : 0;
+    } else {
+        pf.idx = first_stage_of(b, pf.rot, grid);
+        pf.limit = P.mv[part_matrix(pf.part)].total_stages;
+    }
+}
+
+// One step of the prefetch cursor: asks L2 for the next stage of the block.  Returns false at the end.
+__device__ __forceinline__ bool prefetch_step(Prefetcher &pf, const FusedParams &P, int b, int grid, int lane)
+{
+    while (pf.idx >= pf.limit) {   // next part
+        if (pf.part != 1)
+            pf.rot = (pf.rot + P.mv[part_matrix(pf.part)].total_stages) % grid;
+        if (++pf.part == 5) {
+            pf.part = 0;
+            if (++pf.layer == P.n_layers)
+                return false;
+        }
+        prefetch_enter(pf, P, b, grid);
+    }
+    if (pf.part == 1) {
+        const AttSplit &a = pf.as;
+        const int h = pf.idx / a.nchunk, c = pf.idx - h * a.nchunk;
+        const int t0 = c * kAttChunk;
+        const int old = min(pf.pos, t0 + kAttChunk) - t0;
+        const uint32_t kbytes = (uint32_t)old * (uint32_t)P.head * 4u;
+        if (old > 0 && lane < 2) {
+            const int64_t row = ((int64_t)(h / P.kv_mul) * P.seq_len + t0) * P.head;
+            bulk_prefetch_l2((lane ? P.mv[0].v_cache : P.mv[0].k_cache) + (int64_t)pf.layer * P.kv_step + row, kbytes);
+        }
+        pf.bytes += 2 * (int)((kbytes + 127u) & ~127u);
+        pf.idx += 1;
+    } else {
+        const int k = part_matrix(pf.part);
+        const MvParams &p = P.mv[k];
+        int seg, row0, nrows;
+        stage_rows(p, pf.idx, seg, row0, nrows);
+        const int h = lane & 1, is_hdr = lane >> 1;
+        const int sg = p.paired ? h : seg;
+        const uint32_t pbytes = (uint32_t)nrows * (uint32_t)p.rowbytes;
+        const int64_t flat = p.seg[sg].flat0 + (int64_t)pf.layer * P.seg_step[k][sg] + (int64_t)row0 * p.n;
+        const int64_t ga = (flat >> 8) & ~(int64_t)1;
+        const int64_t gl = (flat + pbytes - 1) >> 8;
+        const uint32_t hbytes = (uint32_t)(((gl - ga + 2) & ~(int64_t)1) * 8);
+        if (p.paired || h == 0) {
+            if (is_hdr)
+                bulk_prefetch_l2(p.seg[sg].hdr + ga, hbytes);
+            else
+                bulk_prefetch_l2(p.seg[sg].payload + flat, pbytes);
+        }
+        pf.bytes += p.slot_bytes;
+        pf.idx += grid;
+    }
+    return true;
+}
+
+// The producer is the first four lanes of its warp.  All four keep the same bookkeeping; a stage's (up to) four
+// bulk copies (rows of one or two matrices, their group headers) are one instruction stream with per-lane
+// operands: lane = 2 * is_header + half.  Every lane arrives on the stage's barrier with the bytes of its own
+// copy (the barrier counts four arrivals), so the lanes need not talk to each other.
 __device__ __forceinline__ void produce_ring_stage(Producer &pr, const FusedParams &P, const MvParams &p, int k, int layer, int s,
-                                                   uint64_t pol)
+                                                   uint64_t pol, int lane)
 {
     const uint32_t off = pr.acquire((uint32_t)p.slot_bytes);
     const int e = pr.seq % kFDesc;
@@ -214,47 +336,40 @@ __device__ __forceinline__ void produce_ring_stage(Producer &pr, const FusedPara
     FStage *desc = reinterpret_cast<FStage *>(pr.smem + kFDescOff) + e;
     int seg, row0, nrows;
     stage_rows(p, s, seg, row0, nrows);
-    const uint32_t dst = pr.ring_base + off;
+    const int h = lane & 1, is_hdr = lane >> 1;
+    const bool mine = (p.paired || h == 0) && !(P.debug_no_copy & 1);
+    const int sg = p.paired ? h : seg;
     const uint32_t pbytes = (uint32_t)nrows * (uint32_t)p.rowbytes;
-    desc->seg = seg;
-    desc->row0 = row0;
-    desc->nrows = nrows;
-    desc->off = (int)off;
-    if (P.debug_no_copy) {
-        desc->e0a = desc->e0b = 0;
-        mbar_arrive(full);
-    } else if (!p.paired) {
-        const int64_t flat = p.seg[seg].flat0 + (int64_t)layer * P.seg_step[k][seg] + (int64_t)row0 * p.n;
-        const int64_t ga = (flat >> 8) & ~(int64_t)1;
-        const int64_t gl = (flat + pbytes - 1) >> 8;
-        const uint32_t hbytes = (uint32_t)(((gl - ga + 2) & ~(int64_t)1) * 8);
+    const int64_t flat = p.seg[sg].flat0 + (int64_t)layer * P.seg_step[k][sg] + (int64_t)row0 * p.n;
+    const int64_t ga = (flat >> 8) & ~(int64_t)1;                 // headers are copied from an even group on: 16-byte aligned
+    const int64_t gl = (flat + pbytes - 1) >> 8;
+    const uint32_t hbytes = (uint32_t)(((gl - ga + 2) & ~(int64_t)1) * 8);
+    const uint32_t bytes = mine ? (is_hdr ? hbytes : pbytes) : 0u;
+    const int R = p.rt * p.rpp;
+    const uint32_t dst = pr.ring_base + off +
+                         (is_hdr ? (uint32_t)p.hdr_off + (uint32_t)(h * p.half_hdr) : (uint32_t)(h * (R / 2)) * (uint32_t)p.rowbytes);
+    const void *src = is_hdr ? static_cast<const void *>(p.seg[sg].hdr + ga) : static_cast<const void *>(p.seg[sg].payload + flat);
+    if (lane == 0) {
+        desc->off = (int)off;
+        desc->nrows = nrows;
         desc->e0a = (int)(flat - ga * 256);
-        desc->e0b = 0;
-        mbar_arrive_expect_tx(full, pbytes + hbytes);
-        bulk_g2s(dst, p.seg[seg].payload + flat, pbytes, full, pol);
-        bulk_g2s(dst + (uint32_t)p.hdr_off, p.seg[seg].hdr + ga, hbytes, full, pol);
+    }
+    if (lane == 1)
+        desc->e0b = p.paired ? (int)(flat - ga * 256) : 0;
+    if (bytes) {
+        mbar_arrive_expect_tx(full, bytes);
+        bulk_g2s(dst, src, bytes, full, pol);
     } else {
-        int64_t flat[2], ga[2];
-        uint32_t hbytes[2];
-        const int R = p.rt * p.rpp;
-        for (int h = 0; h < 2; ++h) {
-            flat[h] = p.seg[h].flat0 + (int64_t)layer * P.seg_step[k][h] + (int64_t)row0 * p.n;
-            ga[h] = (flat[h] >> 8) & ~(int64_t)1;
-            const int64_t gl = (flat[h] + pbytes - 1) >> 8;
-            hbytes[h] = (uint32_t)(((gl - ga[h] + 2) & ~(int64_t)1) * 8);
-        }
-        desc->e0a = (int)(flat[0] - ga[0] * 256);
-        desc->e0b = (int)(flat[1] - ga[1] * 256);
-        mbar_arrive_expect_tx(full, 2 * pbytes + hbytes[0] + hbytes[1]);
-        for (int h = 0; h < 2; ++h) {
-            bulk_g2s(dst + (uint32_t)(h * (R / 2)) * (uint32_t)p.rowbytes, p.seg[h].payload + flat[h], pbytes, full, pol);
-            bulk_g2s(dst + (uint32_t)p.hdr_off + (uint32_t)(h * p.half_hdr), p.seg[h].hdr + ga[h], hbytes[h], full, pol);
-        }
+        mbar_arrive(full);
     }
     ++pr.seq;
+    pr.issued += p.slot_bytes;
+    if (lane == 0)
+        *reinterpret_cast<volatile int *>(pr.smem + kFIssued) = pr.issued;
 }
 
-__device__ __forceinline__ void produce_att_stage(Producer &pr, const FusedParams &P, int layer, int unit, const AttSplit &a, int pos)
+__device__ __forceinline__ void produce_att_stage(Producer &pr, const FusedParams &P, int layer, int unit, const AttSplit &a, int pos,
+                                                  int lane)
 {
     const int h = unit / a.nchunk, c = unit - h * a.nchunk;
     const int t0 = c * kAttChunk;
@@ -266,24 +381,27 @@ __device__ __forceinline__ void produce_att_stage(Producer &pr, const FusedParam
     const int e = pr.seq % kFDesc;
     const uint32_t full = pr.sbase + kFBarFull + 8 * e;
     FStage *desc = reinterpret_cast<FStage *>(pr.smem + kFDescOff) + e;
-    desc->seg = h;
-    desc->row0 = t0;
-    desc->nrows = cnt;
-    desc->e0a = old;
-    desc->off = (int)off;
-    desc->aux = (int)voff;
-    if (old > 0 && !P.debug_no_copy) {
+    const bool copy = old > 0 && !(P.debug_no_copy & 1) && lane < 2;
+    if (lane == 0)
+        *reinterpret_cast<int4 *>(desc) = make_int4((int)off, cnt, old, 0);
+    if (lane == 1) {
+        desc->seg = h;
+        desc->row0 = t0;
+        desc->aux = (int)voff;
+    }
+    if (copy) {      // lane 0 the K rows, lane 1 the V rows
         const int kvh = h / P.kv_mul;
         const int64_t row = ((int64_t)kvh * P.seq_len + t0) * P.head;
-        const float *kc = P.mv[0].k_cache + (int64_t)layer * P.kv_step + row;
-        const float *vc = P.mv[0].v_cache + (int64_t)layer * P.kv_step + row;
-        mbar_arrive_expect_tx(full, 2 * kbytes);
-        bulk_g2s_plain(pr.ring_base + off, kc, kbytes, full);
-        bulk_g2s_plain(pr.ring_base + off + voff, vc, kbytes, full);
+        const float *src = (lane ? P.mv[0].v_cache : P.mv[0].k_cache) + (int64_t)layer * P.kv_step + row;
+        mbar_arrive_expect_tx(full, kbytes);
+        bulk_g2s_plain(pr.ring_base + off + (lane ? voff : 0u), src, kbytes, full);
     } else {
         mbar_arrive(full);   // only the token's own row: nothing travels through the ring
     }
     ++pr.seq;
+    pr.issued += 2 * (int)voff;
+    if (lane == 0)
+        *reinterpret_cast<volatile int *>(pr.smem + kFIssued) = pr.issued;
 }
 
 // -------------------------------------------------------------------------------------------------
@@ -358,6 +476,59 @@ __device__ __forceinline__ void consume_ring_phase(const FusedParams &P, const M
                     if (j < kFRmsRounds && has_rms)
                         wr[j] = ld_cg_f4_issue(rms_w + (int64_t)idx * 4);
                 }
+            }
+        } else if (as.np_max <= kAttFastSlots && n4 <= kAttFastRounds * kFCons) {
+            // The partials of head h were written by blocks b0..b1 of the attention phase, one slot each, in block
+            // order; merged here in that order, so the result does not depend on which SM ran what.  Few partials:
+            // every thread fetches those of its elements (weights included) in one round of loads.
+            const int ps = P.head + 4;
+            float4 o4[kAttFastRounds][kAttFastSlots];
+            float2 ml[kAttFastRounds][kAttFastSlots];
+#pragma unroll
+            for (int j = 0; j < kAttFastRounds; ++j) {
+                const int idx = tid + j * kFCons;
+                const int e = min(idx, n4 - 1) * 4;
+                const int h = e / P.head, d = e - h * P.head;
+                const int u0 = h * as.nchunk;
+                const int np = att_block_of(as, u0 + as.nchunk - 1) - att_block_of(as, u0) + 1;
+                const float *hp = P.att_part + (int64_t)h * kAttSlots * ps;
+#pragma unroll
+                for (int s2 = 0; s2 < kAttFastSlots; ++s2) {
+                    o4[j][s2] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    ml[j][s2] = make_float2(-INFINITY, 0.f);
+                    if (s2 < np && idx < n4) {
+                        o4[j][s2] = ld_cg_f4_issue(hp + (int64_t)s2 * ps + d);
+                        ml[j][s2] = __ldcg(reinterpret_cast<const float2 *>(hp + (int64_t)s2 * ps + P.head));
+                    }
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < kFRounds; ++j)
+                xr[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int j = 0; j < kFRmsRounds; ++j)
+                wr[j] = make_float4(1.f, 1.f, 1.f, 1.f);
+#pragma unroll
+            for (int j = 0; j < kAttFastRounds; ++j) {
+                float gm = -INFINITY;
+#pragma unroll
+                for (int s2 = 0; s2 < kAttFastSlots; ++s2)
+                    gm = fmaxf(gm, ml[j][s2].x);
+                float L = 0.f;
+                float4 O = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int s2 = 0; s2 < kAttFastSlots; ++s2) {
+                    if (ml[j][s2].y > 0.f) {
+                        const float w = expf(ml[j][s2].x - gm);
+                        L = fmaf(ml[j][s2].y, w, L);
+                        O.x = fmaf(o4[j][s2].x, w, O.x);
+                        O.y = fmaf(o4[j][s2].y, w, O.y);
+                        O.z = fmaf(o4[j][s2].z, w, O.z);
+                        O.w = fmaf(o4[j][s2].w, w, O.w);
+                    }
+                }
+                if (tid + j * kFCons < n4)   // ExpSumNormalize.java:33-37 folded into the weighted sum
+                    xr[j] = make_float4(__fdiv_rn(O.x, L), __fdiv_rn(O.y, L), __fdiv_rn(O.z, L), __fdiv_rn(O.w, L));
             }
         } else {
             // The partials of head h were written by blocks b0..b1 of the attention phase, one slot each, in block
@@ -516,6 +687,21 @@ __device__ __forceinline__ void consume_ring_phase(const FusedParams &P, const M
     if (tid == 0)
         fused_trace(P, pidx, 1);
 
+    // Per-thread constants of the stage loop.  The integer pipe runs at half rate and the dot products live on it,
+    // so every address computation in the loop costs as much as a dp4a: offsets inside a stage are fixed per
+    // thread and phase, shared memory is addressed with 32-bit window addresses, a stage's descriptor is one
+    // 16-byte load.
+    const int half = (p.paired && rsub >= R / 2) ? 1 : 0;      // second half of a paired stage: the partner matrix
+    const int local = rsub - half * (R / 2);                     // row of this thread inside its half
+    const int par = (lane >> 2) & 1;
+    const uint32_t ring32 = sbase + kFHeader + (uint32_t)P.xarea_bytes;
+    const uint32_t row_off = (uint32_t)(rsub * rowbytes + g * 256 + (lane & 3) * 16);
+    const uint32_t off_a = row_off + 64u * (uint32_t)par;       // chunks 0 and 2 of the thread (+0, +128)
+    const uint32_t off_b = row_off + 64u * (uint32_t)(1 - par); // chunks 1 and 3
+    const uint32_t hdr_off = (uint32_t)(p.hdr_off + half * p.half_hdr + 8 * (local * (n >> 8) + g));
+    const uint32_t desc32 = sbase + kFDescOff;
+    uint32_t e = (uint32_t)(cs.seq % kFDesc), parity = (uint32_t)(cs.seq / kFDesc) & 1u;
+
     // The block's stages are taken in groups of kFGroup: a warp works through the rows of a group one stage after
     // the other, then folds the group's partial sums with one butterfly and hands them to the epilogue warp in one
     // go.  A warp's chain of waits, loads, dot products, fold and hand-over is serial; per group instead of per
@@ -528,26 +714,20 @@ __device__ __forceinline__ void consume_ring_phase(const FusedParams &P, const M
             v[t] = 0.f;
             if (t >= cnt)
                 continue;
-            const int e = cs.seq % kFDesc;
-            if (!mbar_wait_bounded(sbase + kFBarFull + 8 * e, (uint32_t)(cs.seq / kFDesc) & 1u, cs.lost ? kFShortWaitNs : wait_ns))
+            if (!mbar_wait_bounded(sbase + kFBarFull + 8 * e, parity, cs.lost ? kFShortWaitNs : wait_ns))
                 cs.lost = true;
             if (g0 == 0 && t == 0 && tid == 0)
                 fused_trace(P, pidx, 4);
-            const FStage d = *(reinterpret_cast<const FStage *>(smem + kFDescOff) + e);
-            const bool skip = cs.lost && !cs.lost_before;
-            const uint8_t *slot_ptr = smem + kFHeader + P.xarea_bytes + (size_t)d.off;
-            const int r = rsub;                                     // row of the stage in shared memory
-            const int half = (p.paired && r >= R / 2) ? 1 : 0;      // second half of a paired stage: the partner matrix
-            const int local = r - half * (R / 2);
-            if (!skip && gvalid && local < d.nrows && !(P.debug_no_copy & 4)) {
-                const uint8_t *rowp = slot_ptr + (size_t)r * rowbytes;
-                const int e0 = (half ? d.e0b : d.e0a) + local * n;
-                const float2 *hp = reinterpret_cast<const float2 *>(slot_ptr + p.hdr_off + half * p.half_hdr);
-                const float2 ms = hp[(e0 + chunk[0] * 16) >> 8];
+            const uint4 d = lds_v4(desc32 + 32u * e);            // off, nrows, e0a, e0b
+            const uint32_t slot32 = ring32 + d.x;
+            if (gvalid && local < (int)d.y && !(cs.lost && !cs.lost_before)) {
+                // rows start on group boundaries: the header of the thread's group is (e0 >> 8) + local * groups per row + g
+                const float2 ms = lds_f2(slot32 + hdr_off + (((half ? d.w : d.z) >> 8) << 3));
+                const uint32_t sa = slot32 + off_a, sb = slot32 + off_b;
                 int a0 = 0, a1 = 0, a2 = 0;
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
-                    const uint4 w = *reinterpret_cast<const uint4 *>(rowp + (size_t)chunk[k] * 16);
+                    const uint4 w = lds_v4(((k & 1) ? sb : sa) + ((k & 2) ? 128u : 0u));
                     a0 = dp4a_us(w.x, xl[k][0][0], a0);
                     a1 = dp4a_us(w.x, xl[k][0][1], a1);
                     a2 = dp4a_us(w.x, xl[k][0][2], a2);
@@ -568,14 +748,11 @@ __device__ __forceinline__ void consume_ring_phase(const FusedParams &P, const M
             __syncwarp();
             if (lane == 0)
                 mbar_arrive(sbase + kFBarEmpty + 8 * e);   // this warp is done with the stage's bytes
+            e = (e + 1) & (kFDesc - 1);
+            parity ^= (e == 0);
             ++cs.seq;
         }
         const float tot = Fold<kFGroup, 16>::run(v, lane) * inv;   // lane t * (32 / kFGroup) holds the sum of stage t
-        if (P.debug_no_copy & 2) {
-            if (tot == 123.456f)
-                scratch[40] = tot;
-            continue;
-        }
         if (cs.rround > 0) {
             if (!mbar_wait_bounded(sbase + kFBarRedEmpty + 8 * cs.rb, (uint32_t)(cs.rround - 1) & 1u, cs.lost ? kFShortWaitNs : wait_ns))
                 cs.lost = true;
@@ -748,7 +925,28 @@ __device__ __forceinline__ void consume_attention(const FusedParams &P, int laye
 struct Epilogue {
     int rb, rround;
     bool lost, lost_before;
+    Prefetcher pf;      // this warp spends most of its time waiting: it runs the L2 prefetch cursor meanwhile
+    bool pf_on;
 };
+
+// Waits for the consumers' partial sums of the next group; while they are not there, asks L2 for stages ahead.
+__device__ __forceinline__ bool epilogue_wait(const FusedParams &P, Epilogue &es, uint8_t *smem, uint32_t bar, uint32_t parity,
+                                              uint64_t timeout_ns, int b, int grid, int lane)
+{
+    if (mbar_try_wait(bar, parity))
+        return true;
+    const long long c0 = sm_clock();
+    const long long limit = (long long)(2 * timeout_ns);
+    volatile int *issued = reinterpret_cast<volatile int *>(smem + kFIssued);
+    for (;;) {
+        if (mbar_try_wait(bar, parity))
+            return true;
+        if (es.pf_on && es.pf.bytes - *issued < P.l2_ahead_bytes)
+            es.pf_on = prefetch_step(es.pf, P, b, grid, lane);
+        if (sm_clock() - c0 > limit)
+            return false;
+    }
+}
 
 __device__ __forceinline__ void epilogue_phase(const FusedParams &P, const MvParams &p, int layer, int first, int nmine, int pos,
                                                uint8_t *smem, uint32_t sbase, Epilogue &es, uint64_t wait_ns)
@@ -759,9 +957,10 @@ __device__ __forceinline__ void epilogue_phase(const FusedParams &P, const MvPar
     const int rs = p.rs;                 // output rows (row pairs) per stage: at most 8, so a group fits the 32 lanes
     const float *rope_c = reinterpret_cast<const float *>(smem + kFRopeOff);
     const float *rope_s = rope_c + 64;
-    for (int g0 = 0; g0 < nmine && !(P.debug_no_copy & 2); g0 += kFGroup) {
+    for (int g0 = 0; g0 < nmine; g0 += kFGroup) {
         const int cnt = min(kFGroup, nmine - g0);
-        if (!mbar_wait_bounded(sbase + kFBarRedFull + 8 * es.rb, (uint32_t)es.rround & 1u, es.lost ? kFShortWaitNs : wait_ns))
+        if (!epilogue_wait(P, es, smem, sbase + kFBarRedFull + 8 * es.rb, (uint32_t)es.rround & 1u, es.lost ? kFShortWaitNs : wait_ns,
+                           blockIdx.x, G, lane))
             es.lost = true;
         const float *red = reinterpret_cast<const float *>(smem + kFRedOff + es.rb * kFRedStride);
         const bool skip = es.lost && !es.lost_before;
@@ -851,13 +1050,15 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_layers_kernel(const __
     const uint64_t wait_ns = (uint64_t)P.timeout_us * 1000ull;
 
     if (tid < kFDesc) {
-        mbar_init(sbase + kFBarFull + 8 * tid, 1);
+        mbar_init(sbase + kFBarFull + 8 * tid, 4);         // the four producer lanes
         mbar_init(sbase + kFBarEmpty + 8 * tid, kFusedConsWarps);
     }
     if (tid < kFRedBufs) {
         mbar_init(sbase + kFBarRedFull + 8 * tid, kFusedConsWarps);
         mbar_init(sbase + kFBarRedEmpty + 8 * tid, 1);
     }
+    if (tid == 0)
+        *reinterpret_cast<volatile int *>(smem + kFIssued) = 0;
     if (tid < 32)
         mbar_fence_init();
     __syncthreads();
@@ -865,7 +1066,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_layers_kernel(const __
 
     // ------------------------------------------------------------------------------ producer
     if (warp == kFusedConsWarps) {
-        if (lane != 0)
+        if (lane >= 4)
             return;
         Producer pr;
         pr.smem = smem;
@@ -877,36 +1078,38 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_layers_kernel(const __
         pr.lost = false;
         pr.wait_ns = wait_ns;
         const uint64_t pol = policy_evict_first();
-        int rot = 0, pos = -1;
-        AttSplit as{};
+        pr.pos = -1;
+        pr.as = AttSplit{};
+        pr.off = 0;
+        pr.issued = 0;
+        int rot = 0;
         for (int layer = 0; layer < P.n_layers; ++layer) {
 #pragma unroll 1
             for (int k = 0; k < 4; ++k) {
                 const MvParams &p = P.mv[k];
                 const int S = p.total_stages;
-                if (!(P.debug_no_copy & 8)) fused_trace(P, layer * 5 + (k == 0 ? 0 : k + 1), 5);
-                for (int s = first_stage_of(b, rot, G); s < S; s += G)
-                    produce_ring_stage(pr, P, p, k, layer, s, pol);
-                if (!(P.debug_no_copy & 8)) fused_trace(P, layer * 5 + (k == 0 ? 0 : k + 1), 6);
+                if (!(P.debug_no_copy & 8) && lane == 0) fused_trace(P, layer * 5 + (k == 0 ? 0 : k + 1), 5);
+                for (int s = first_stage_of(b, rot, G); s < S; s += G) {
+                    produce_ring_stage(pr, P, p, k, layer, s, pol, lane);
+                }
+                if (!(P.debug_no_copy & 8) && lane == 0) fused_trace(P, layer * 5 + (k == 0 ? 0 : k + 1), 6);
                 rot = (rot + S) % G;
                 if (k == 0) {
-                    if (pos < 0) {
-                        // The position is set by the kernel in front; everything issued so far was weights.
-                        pdl_wait();
-                        pos = __ldcg(&P.state->cur_pos);
-                        as = att_split(P, pos, G);
-                    }
-                    if (b < as.ga) {
-                        const int u0 = att_first_unit(as, b), u1 = att_first_unit(as, b + 1);
-                        fused_trace(P, layer * 5 + 1, 5);
-                        for (int u = u0; u < u1; ++u)
-                            produce_att_stage(pr, P, layer, u, as, pos);
-                        fused_trace(P, layer * 5 + 1, 6);
+                    producer_learn_pos(pr, P, G);
+                    if (b < pr.as.ga) {
+                        const int u0 = att_first_unit(pr.as, b), u1 = att_first_unit(pr.as, b + 1);
+                        if (lane == 0) fused_trace(P, layer * 5 + 1, 5);
+                        for (int u = u0; u < u1; ++u) {
+                            produce_att_stage(pr, P, layer, u, pr.as, pr.pos, lane);
+                        }
+                        if (lane == 0) fused_trace(P, layer * 5 + 1, 6);
                     }
                 }
             }
         }
-        if (pr.lost)
+        if (lane == 0)
+            *reinterpret_cast<volatile int *>(smem + kFIssued) = 0x7fffffff;   // lets the prefetch cursor run out
+        if (pr.lost && lane == 0)
             atomicOr(&P.state->status, L2J_DS_WAIT_TIMEOUT);
         return;
     }
@@ -923,6 +1126,11 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_layers_kernel(const __
         Epilogue es;
         es.rb = es.rround = 0;
         es.lost = es.lost_before = lost_at_entry;
+        es.pf.pos = pos;
+        es.pf.as = as;
+        es.pf.layer = es.pf.part = es.pf.rot = es.pf.bytes = 0;
+        es.pf_on = P.l2_ahead_bytes > 0;
+        prefetch_enter(es.pf, P, b, G);
         {
             float *rope_c = reinterpret_cast<float *>(smem + kFRopeOff);
             const int half = P.head >> 1;
