@@ -41,6 +41,7 @@ extern "C" {
 #define L2J_DS_WAIT_TIMEOUT 0x1  /* a bounded wait on a copy barrier ran out */
 #define L2J_DS_BAD_POS 0x2       /* pos outside [0, seq_len) reached a kernel */
 #define L2J_DS_BAD_TOKEN 0x4     /* token outside [0, vocab) reached a kernel */
+#define L2J_DS_BAD_LINK 0x8      /* a stage of a layer split was told to read its neighbour but holds no pointer to it */
 
 /* Quantisation group of the reference: Run.QUANT_GROUP_SIZE / QUANT_BITS, Run.java:27-28;
  * encoded group = 8-byte header (min, max as big-endian floats) + 256 bytes, Quant.java:35-37. */
@@ -204,14 +205,35 @@ L2J_API int l2j_tp_forward(l2j_ctx *const *ranks, int n_ranks, int token, int po
 L2J_API int l2j_tp_generate_greedy(l2j_ctx *const *ranks, int n_ranks, const int32_t *prompt, int n_prompt, int steps,
                                    int32_t *out_tokens);
 
-/* Clears the KV cache position bookkeeping and the statistics (a new sequence). */
+/* Clears the KV cache position bookkeeping, the statistics and the device status word (a new sequence).
+ * The status word is sticky: once a kernel has raised a bit, every later forward of the context returns
+ * L2J_E_DEVICE (and, after L2J_DS_WAIT_TIMEOUT, its waits give up after 2 us, so its results are not valid)
+ * until l2j_reset.  The hand-over counters of a context only agree with those of its partners (the ranks of
+ * a tensor-parallel group, the stages of a linked layer split) while all of them have run the same number of
+ * forwards: after a failure reset every member, l2j_tp_reset / l2j_pipeline_reset do that. */
 L2J_API int l2j_reset(l2j_ctx *ctx);
+L2J_API int l2j_tp_reset(l2j_ctx *const *ranks, int n_ranks);
+L2J_API int l2j_pipeline_reset(l2j_ctx *const *stages, int n_stages);
+
+/* Bound of every device-side wait of the context's kernels (copy barriers, hand-over counters between
+ * kernels and between the blocks of the persistent kernel, the pair polls of a tensor-parallel group), in
+ * microseconds; 50000 unless set.  A wait that runs out raises L2J_DS_WAIT_TIMEOUT and the kernel carries on,
+ * so the GPU never hangs on a lost partner (the reference's only failure handling is the exception of
+ * ContextCUDA.java:296-304).  Part of the captured launches: call before l2j_finalize. */
+L2J_API int l2j_set_wait_limit_us(l2j_ctx *ctx, int limit_us);
+
+/* Failure injection for tests, on the host: makes the context's next forward wait for hand-overs that never
+ * come (its forward counter is advanced as if a partner had run a forward that this context missed).  The
+ * forward then ends by its wait limit with L2J_E_DEVICE / L2J_DS_WAIT_TIMEOUT; l2j_reset makes the context
+ * usable again.  Nothing faults: every wait gives up and the kernels return. */
+L2J_API int l2j_debug_desync(l2j_ctx *ctx);
 
 L2J_API int l2j_get_stats(l2j_ctx *ctx, l2j_stats *out);
 
 /* How the per-token work is issued: bit 0 CUDA graph replay, bit 1 programmatic dependent launch
- * between kernels, bit 2 the bulk-copy ring kernels (else the plain kernels); bits 8 and up hold the
- * number of blocks a ring kernel is launched with.  The reference issues
+ * between kernels, bit 2 the bulk-copy ring kernels (else the plain kernels), bit 3 all layers of a token in
+ * one persistent launch (else five launches per layer); bits 8 and up hold the number of blocks a ring
+ * kernel is launched with.  The reference issues
  * every kernel with its own cuLaunchKernel (kernel/MatMul.java:338-354). */
 L2J_API int l2j_launch_mode(l2j_ctx *ctx);
 
@@ -238,6 +260,12 @@ L2J_API int l2j_last_generate_us(l2j_ctx *ctx, double *total_us);
  * the same weights).  us[0..5] = QKV+RoPE, attention, Wo+residual, W1/W3+SwiGLU, W2+residual,
  * classifier+argmax.  Leaves the sequence state undefined: call l2j_reset afterwards. */
 L2J_API int l2j_time_kernels(l2j_ctx *ctx, int pos, int reps, double *us);
+
+/* The same for the persistent kernel that runs all layers of a token in one launch (contexts created
+ * without L2J_F_STEP_KERNELS whose matrices have rows of whole quantisation groups): average device time
+ * of one launch at position `pos`, CUDA events on the context's stream around the launch alone, each
+ * launch after an embedding gather of its own.  Leaves the sequence state undefined: call l2j_reset. */
+L2J_API int l2j_time_layers_kernel(l2j_ctx *ctx, int pos, int reps, double *us_per_launch);
 
 /* Measurement aid (no counterpart in the reference): the in-kernel timeline of one launch of a ring
  * kernel (kind 0 QKV, 2 Wo, 3 W1/W3, 4 W2, 5 classifier; same numbering as l2j_time_kernels).

@@ -19,6 +19,7 @@ using namespace l2j;
 namespace {
 
 thread_local std::string g_create_error;
+std::mutex g_link_mu;   // guards the pipe_members lists of all contexts
 
 constexpr int kCmdRing = 256;
 
@@ -80,6 +81,7 @@ struct l2j_ctx {
     Cmd *cmd_dev = nullptr;
     Cmd *cmd_host = nullptr;       // pinned ring
     StageLink *link_dev = nullptr; // peer pointers of a linked layer split (zero until linked)
+    std::vector<l2j_ctx *> pipe_members;   // the stages this context was linked with by l2j_pipeline_link, in order (empty: not linked)
     int tp_rank = 0, tp_size = 1;  // tensor parallel group this context belongs to
     TpTable *tp_dev = nullptr;     // the group's receive buffers (n = 0 until linked)
     float *x2 = nullptr;           // tensor parallel: second copy of the residual stream (the two alternate)
@@ -1053,6 +1055,13 @@ extern "C" void l2j_destroy(l2j_ctx *c)
 {
     if (!c)
         return;
+    {   // the stages this one was linked with hold pointers into its memory: they are unlinked with it
+        std::lock_guard<std::mutex> lock(g_link_mu);
+        for (l2j_ctx *m : c->pipe_members)
+            if (m != c)
+                m->pipe_members.clear();
+        c->pipe_members.clear();
+    }
     cudaSetDevice(c->device);
     if (c->stream)
         cudaStreamSynchronize(c->stream);
@@ -1460,7 +1469,7 @@ extern "C" int l2j_kv_write(l2j_ctx *c, int layer, int pos0, int n_pos, const fl
 
 namespace {
 
-int check_stages(l2j_ctx *const *stages, int n)
+int check_stages(l2j_ctx *const *stages, int n, bool need_link = false)
 {
     if (!stages || n <= 0)
         return L2J_E_INVALID;
@@ -1477,6 +1486,19 @@ int check_stages(l2j_ctx *const *stages, int n)
         if ((i == 0) != c->is_first || (i == n - 1) != c->is_last || (i > 0 && c->first_layer != stages[i - 1]->last_layer + 1))
             return fail(c0, L2J_E_INVALID, "the stages do not tile the layers in order (stage %d holds %d..%d)", i,
                         c->first_layer, c->last_layer);
+    }
+    if (need_link && n > 1) {
+        // The begin kernel of a stage reads its neighbour's memory through pointers that l2j_pipeline_link wrote:
+        // without the link (or after a member was destroyed or linked elsewhere) they are null or stale.
+        std::lock_guard<std::mutex> lock(g_link_mu);
+        for (int i = 0; i < n; ++i) {
+            const std::vector<l2j_ctx *> &m = stages[i]->pipe_members;
+            bool same = (int)m.size() == n;
+            for (int j = 0; same && j < n; ++j)
+                same = m[(size_t)j] == stages[j];
+            if (!same)
+                return fail(c0, L2J_E_STATE, "stage %d is not linked with these stages: call l2j_pipeline_link first", i);
+        }
     }
     return L2J_OK;
 }
@@ -1527,12 +1549,22 @@ extern "C" int l2j_pipeline_link(l2j_ctx *const *stages, int n_stages)
         CK(c, cudaEventRecord(c->ev_stage, c->stream));
         CK(c, cudaStreamSynchronize(c->stream));
     }
+    {
+        std::lock_guard<std::mutex> lock(g_link_mu);
+        for (int i = 0; i < n_stages; ++i) {
+            // a stage that was linked elsewhere leaves that group: its old partners hold pointers it no longer serves
+            for (l2j_ctx *old : stages[i]->pipe_members)
+                if (old != stages[i])
+                    old->pipe_members.clear();
+            stages[i]->pipe_members.assign(stages, stages + n_stages);
+        }
+    }
     return L2J_OK;
 }
 
 extern "C" int l2j_pipeline_forward(l2j_ctx *const *stages, int n_stages, int token, int pos, float *logits, int *argmax)
 {
-    int rc = check_stages(stages, n_stages);
+    int rc = check_stages(stages, n_stages, true);
     if (rc != L2J_OK)
         return rc;
     rc = check_range(stages[0], token, pos, true);
@@ -1579,7 +1611,7 @@ extern "C" int l2j_pipeline_forward(l2j_ctx *const *stages, int n_stages, int to
 extern "C" int l2j_pipeline_generate_greedy(l2j_ctx *const *stages, int n_stages, const int32_t *prompt, int n_prompt, int steps,
                                             int32_t *out_tokens)
 {
-    int rc = check_stages(stages, n_stages);
+    int rc = check_stages(stages, n_stages, true);
     if (rc != L2J_OK)
         return rc;
     l2j_ctx *c0 = stages[0], *cl = stages[n_stages - 1];
@@ -1862,6 +1894,56 @@ extern "C" int l2j_reset(l2j_ctx *c)
     return L2J_OK;
 }
 
+extern "C" int l2j_tp_reset(l2j_ctx *const *ranks, int n_ranks)
+{
+    if (!ranks || n_ranks <= 0)
+        return L2J_E_INVALID;
+    int rc = L2J_OK;
+    for (int i = 0; i < n_ranks; ++i) {   // every member, also after a failure: the group's counters must agree again
+        const int r = l2j_reset(ranks[i]);
+        if (r != L2J_OK && rc == L2J_OK)
+            rc = r;
+    }
+    return rc;
+}
+
+extern "C" int l2j_pipeline_reset(l2j_ctx *const *stages, int n_stages)
+{
+    return l2j_tp_reset(stages, n_stages);
+}
+
+extern "C" int l2j_set_wait_limit_us(l2j_ctx *c, int limit_us)
+{
+    if (!c)
+        return L2J_E_INVALID;
+    std::lock_guard<std::mutex> lock(c->mu);
+    if (limit_us < 10 || limit_us > 10000000)
+        return fail(c, L2J_E_INVALID, "wait limit %d us outside [10, 10000000]", limit_us);
+    if (c->finalized)
+        return fail(c, L2J_E_STATE, "the wait limit is part of the captured launches: set it before l2j_finalize");
+    c->wait_limit_us = limit_us;
+    return L2J_OK;
+}
+
+extern "C" int l2j_debug_desync(l2j_ctx *c)
+{
+    if (!c)
+        return L2J_E_INVALID;
+    std::lock_guard<std::mutex> lock(c->mu);
+    if (!c->finalized || !c->use_ring || !c->chain_on)
+        return fail(c, L2J_E_STATE, "needs a finalized context that runs the hand-over counters");
+    CK(c, cudaSetDevice(c->device));
+    CK(c, cudaStreamSynchronize(c->stream));
+    // The forward counter on the device runs one ahead of the hand-over counters, as after a forward that a
+    // partner never ran: the next forward's kernels wait for bumps that nobody makes.
+    unsigned int *epoch = c->chain + (int64_t)kChainStride * (5 * c->nl + 1);
+    unsigned int v = 0;
+    CK(c, cudaMemcpy(&v, epoch, sizeof(v), cudaMemcpyDeviceToHost));
+    ++v;
+    CK(c, cudaMemcpy(epoch, &v, sizeof(v), cudaMemcpyHostToDevice));
+    return L2J_OK;
+}
+
 extern "C" int l2j_get_stats(l2j_ctx *c, l2j_stats *out)
 {
     if (!c || !out)
@@ -1927,6 +2009,39 @@ extern "C" int l2j_time_kernels(l2j_ctx *c, int pos, int reps, double *us)
         us[kind] = launches > 0 ? (double)ms * 1000.0 / launches : 0.0;
     }
     CK(c, cudaStreamSynchronize(c->stream));
+    return L2J_OK;
+}
+
+extern "C" int l2j_time_layers_kernel(l2j_ctx *c, int pos, int reps, double *us_per_launch)
+{
+    if (!c || !us_per_launch || reps <= 0)
+        return L2J_E_INVALID;
+    std::lock_guard<std::mutex> lock(c->mu);
+    if (!c->finalized || !c->use_fused)
+        return fail(c, L2J_E_STATE, "needs a finalized context that runs the persistent kernel");
+    int rc = check_range(c, 1, pos, true);
+    if (rc != L2J_OK)
+        return rc;
+    CK(c, cudaSetDevice(c->device));
+    LaunchCfg lc{c->stream, false, c->ring_grid};
+    double total_ms = 0.0;
+    for (int r = 0; r <= reps; ++r) {   // the first pass warms up
+        rc = post_cmd(c, 1, 1, pos);
+        if (rc != L2J_OK)
+            return rc;
+        CK(c, launch_begin(lc, c->state, c->cmd_dev, c->emb, c->x, c->dim, c->cfg.vocab_size, c->cfg.seq_len, c->is_first ? 1 : 0,
+                           c->reps, c->dim_stride, c->chain + (int64_t)kChainStride * (5 * c->nl + 1), c->link_dev));
+        CK(c, cudaEventRecord(c->ev0, c->stream));
+        CK(c, launch_fused(c->stream, false, c->ring_grid, c->fused_smem, c->fused));
+        CK(c, cudaEventRecord(c->ev1, c->stream));
+        CK(c, cudaEventSynchronize(c->ev1));
+        c->forwards++;
+        float ms = 0.f;
+        CK(c, cudaEventElapsedTime(&ms, c->ev0, c->ev1));
+        if (r > 0)
+            total_ms += ms;
+    }
+    *us_per_launch = total_ms * 1000.0 / reps;
     return L2J_OK;
 }
 
@@ -2005,7 +2120,7 @@ extern "C" int l2j_launch_mode(l2j_ctx *c)
 {
     if (!c)
         return 0;
-    return (c->exec ? 1 : 0) | (c->pdl_on ? 2 : 0) | (c->use_ring ? 4 : 0) | (c->ring_grid << 8);
+    return (c->exec ? 1 : 0) | (c->pdl_on ? 2 : 0) | (c->use_ring ? 4 : 0) | (c->use_fused ? 8 : 0) | (c->ring_grid << 8);
 }
 
 // Reads an internal buffer after a forward (debugging and per-stage parity checks):

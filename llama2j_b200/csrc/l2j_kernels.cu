@@ -30,6 +30,7 @@
 #define L2J_DS_WAIT_TIMEOUT 0x1
 #define L2J_DS_BAD_POS 0x2
 #define L2J_DS_BAD_TOKEN 0x4
+#define L2J_DS_BAD_LINK 0x8
 
 namespace l2j {
 
@@ -1219,22 +1220,30 @@ __global__ void __launch_bounds__(256) begin_kernel(SeqState *state, const Cmd *
     if (threadIdx.x == 0) {
         int tok, pos;
         const int cflags = __ldcg(&cmd->flags);
+        int st = 0;
         if (__ldcg(&cmd->mode) == 1) {
             tok = __ldcg(&cmd->token);
             pos = __ldcg(&cmd->pos);
         } else {
             // greedy loop; over a layer split the chosen token lives on the last stage's device
-            tok = (cflags & kCmdTokenFromPeer)
-                      ? __ldcg(reinterpret_cast<const int *>(__ldcg(reinterpret_cast<const unsigned long long *>(&link->token_src))))
-                      : __ldcg(&state->token);
+            tok = __ldcg(&state->token);
+            if (cflags & kCmdTokenFromPeer) {
+                const int *src = reinterpret_cast<const int *>(__ldcg(reinterpret_cast<const unsigned long long *>(&link->token_src)));
+                if (src)
+                    tok = __ldcg(src);
+                else
+                    st |= L2J_DS_BAD_LINK;   // the stages were not linked: report it, never follow a null pointer
+            }
             pos = __ldcg(&state->pos);
             if (cflags & kCmdAdvancePos)
                 state->pos = pos + 1;
         }
-        s_xsrc = (cflags & kCmdXFromPeer)
-                     ? reinterpret_cast<const float *>(__ldcg(reinterpret_cast<const unsigned long long *>(&link->x_src)))
-                     : nullptr;
-        int st = 0;
+        s_xsrc = nullptr;
+        if (cflags & kCmdXFromPeer) {
+            s_xsrc = reinterpret_cast<const float *>(__ldcg(reinterpret_cast<const unsigned long long *>(&link->x_src)));
+            if (!s_xsrc)
+                st |= L2J_DS_BAD_LINK;
+        }
         if (pos < 0 || pos >= seq_len) {
             st |= L2J_DS_BAD_POS;
             pos = pos < 0 ? 0 : seq_len - 1;

@@ -12,6 +12,7 @@ import os
 from . import build as _build
 
 E_INVALID, E_CUDA, E_STATE, E_DEVICE, E_NOMEM = -1, -2, -3, -4, -5
+DS_WAIT_TIMEOUT, DS_BAD_POS, DS_BAD_TOKEN, DS_BAD_LINK = 0x1, 0x2, 0x4, 0x8
 F_NO_GRAPH, F_NO_PDL, F_SIMPLE, F_STEP_KERNELS = 0x1, 0x2, 0x4, 0x8
 QUANT_GROUP, QUANT_GROUP_BYTES = 256, 264
 
@@ -66,12 +67,17 @@ _SIGNATURES = {
     "l2j_tp_forward": (C.c_int, [C.POINTER(_P), C.c_int, C.c_int, C.c_int, _P, C.POINTER(C.c_int)]),
     "l2j_tp_generate_greedy": (C.c_int, [C.POINTER(_P), C.c_int, _P, C.c_int, C.c_int, _P]),
     "l2j_reset": (C.c_int, [_P]),
+    "l2j_tp_reset": (C.c_int, [C.POINTER(_P), C.c_int]),
+    "l2j_pipeline_reset": (C.c_int, [C.POINTER(_P), C.c_int]),
+    "l2j_set_wait_limit_us": (C.c_int, [_P, C.c_int]),
+    "l2j_debug_desync": (C.c_int, [_P]),
     "l2j_get_stats": (C.c_int, [_P, C.POINTER(Stats)]),
     "l2j_launch_mode": (C.c_int, [_P]),
     "l2j_read_buffer": (C.c_int, [_P, C.c_int, C.c_int, C.c_int, _P, C.c_int]),
     "l2j_kv_write": (C.c_int, [_P, C.c_int, C.c_int, C.c_int, _P, _P]),
     "l2j_last_generate_us": (C.c_int, [_P, C.POINTER(C.c_double)]),
     "l2j_time_kernels": (C.c_int, [_P, C.c_int, C.c_int, C.POINTER(C.c_double)]),
+    "l2j_time_layers_kernel": (C.c_int, [_P, C.c_int, C.c_int, C.POINTER(C.c_double)]),
     "l2j_trace_kernel": (C.c_int, [_P, C.c_int, C.c_int, C.c_int, _P, C.c_int]),
     "l2j_read_trace": (C.c_int, [_P, _P, C.c_int64]),
     "l2j_quant_encode": (C.c_int, [C.c_int, _P, C.c_int64, _P]),

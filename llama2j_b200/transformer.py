@@ -144,6 +144,12 @@ class Transformer:
         _lib.check(self._lib.l2j_time_kernels(self._ctx, int(pos), int(reps), arr), self._ctx)
         return dict(zip(("qkv_rope", "attention", "wo_residual", "w13_swiglu", "w2_residual", "classifier_argmax"), arr))
 
+    def time_layers_kernel(self, pos: int, reps: int = 3) -> float:
+        """Average device microseconds of one launch of the persistent all-layers kernel at position `pos`."""
+        us = C.c_double(0.0)
+        _lib.check(self._lib.l2j_time_layers_kernel(self._ctx, int(pos), int(reps), C.byref(us)), self._ctx)
+        return us.value
+
     def trace_kernel(self, kind: int, layer: int = 0, pos: int = 0) -> np.ndarray:
         """In-kernel timeline of one ring-kernel launch: array (blocks, 8), see l2j_trace_kernel."""
         nb = self.launch_mode()["ring_blocks"]
@@ -173,6 +179,14 @@ class Transformer:
     def reset(self) -> None:
         _lib.check(self._lib.l2j_reset(self._ctx), self._ctx)
 
+    def set_wait_limit_us(self, limit_us: int) -> None:
+        """Bound of every device-side wait (before finalize); see l2j_set_wait_limit_us."""
+        _lib.check(self._lib.l2j_set_wait_limit_us(self._ctx, int(limit_us)), self._ctx)
+
+    def debug_desync(self) -> None:
+        """Host-side failure injection: the next forward waits for hand-overs that never come."""
+        _lib.check(self._lib.l2j_debug_desync(self._ctx), self._ctx)
+
     def stats(self) -> _lib.Stats:
         st = _lib.Stats()
         _lib.check(self._lib.l2j_get_stats(self._ctx, C.byref(st)), self._ctx)
@@ -180,7 +194,8 @@ class Transformer:
 
     def launch_mode(self) -> dict:
         m = self._lib.l2j_launch_mode(self._ctx)
-        return {"graph": bool(m & 1), "pdl": bool(m & 2), "ring": bool(m & 4), "ring_blocks": m >> 8}
+        return {"graph": bool(m & 1), "pdl": bool(m & 2), "ring": bool(m & 4), "persistent": bool(m & 8),
+                "ring_blocks": m >> 8}
 
     def read_buffer(self, which: int, n: int, layer: int = 0, pos: int = 0) -> np.ndarray:
         out = np.empty(n, dtype=np.float32)
@@ -220,15 +235,22 @@ class LinkedStages:
     Context.java:16-23): stage i is a Transformer on its own device holding a contiguous layer range,
     and each stage reads x from the device of the stage in front over the peer link."""
 
-    def __init__(self, stages):
+    def __init__(self, stages, link: bool = True):
         self.stages = list(stages)
         if not self.stages:
             raise ValueError("no stages")
         self._lib = _lib.load()
         self._arr = (C.c_void_p * len(self.stages))(*[s._ctx for s in self.stages])
-        rc = self._lib.l2j_pipeline_link(self._arr, len(self.stages))
-        _lib.check(rc, self.stages[0]._ctx)
         self._logits = np.zeros(self.stages[0].cfg.vocab_size, dtype=np.float32)
+        if link:
+            self.link()
+
+    def link(self) -> None:
+        """l2j_pipeline_link: every stage learns where its neighbour's x (and the chosen token) lives."""
+        _lib.check(self._lib.l2j_pipeline_link(self._arr, len(self.stages)), self.stages[0]._ctx)
+
+    def reset(self) -> None:
+        _lib.check(self._lib.l2j_pipeline_reset(self._arr, len(self.stages)), self.stages[0]._ctx)
 
     @classmethod
     def from_allocation(cls, cfg: ModelConfig, first_layers, last_layers, tensors: dict, devices=None, flags: int = 0):
