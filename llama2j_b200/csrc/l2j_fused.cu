@@ -26,9 +26,11 @@
 // Arithmetic per output element is that of matvec_ring_kernel (same lane mapping, same reduction
 // order), so the matrix-vector products are bitwise those of the per-step kernels.
 //
-// Blocks wait for each other, so all of them must be resident: the grid is one block per SM and the
-// launch is cooperative where the driver allows it.  Every wait is bounded by the global timer; a wait
-// that runs out raises L2J_DS_WAIT_TIMEOUT in the status word and the block drains without stalling.
+// Blocks wait for each other, so all of them must be resident: the grid is one block per SM.  Every wait is
+// bounded by the SM's cycle counter.  A hand-over between blocks that runs out raises L2J_DS_WAIT_TIMEOUT in
+// the status word, and every later hand-over of the forward gives up after 2 us; the block then still works
+// through all of its stages with the (wrong) inputs it has, so that producer, consumers and epilogue warp stay
+// in step and no bulk copy is in flight when the block ends.
 //
 // Reference counterparts (paths relative to src/main/java/com/lastbot/llama2j/): the layer body of
 // Run.java:418-508 with kernel/MatMul.java:360-444, RootMeanSquare.java:78-118,
@@ -221,7 +223,7 @@ struct Producer {
         const int vend = vhead + (int)bytes;
         while (tail < seq && (seq - tail >= kFDesc || vend - ring_bytes > vstart[tail % kFDesc])) {
             if (!mbar_wait_bounded(sbase + kFBarEmpty + 8 * (tail % kFDesc), (uint32_t)(tail / kFDesc) & 1u,
-                                   lost ? kFShortWaitNs : wait_ns))
+                                   wait_ns))
                 lost = true;
             ++tail;
         }
@@ -714,13 +716,13 @@ __device__ __forceinline__ void consume_ring_phase(const FusedParams &P, const M
             v[t] = 0.f;
             if (t >= cnt)
                 continue;
-            if (!mbar_wait_bounded(sbase + kFBarFull + 8 * e, parity, cs.lost ? kFShortWaitNs : wait_ns))
+            if (!mbar_wait_bounded(sbase + kFBarFull + 8 * e, parity, wait_ns))
                 cs.lost = true;
             if (g0 == 0 && t == 0 && tid == 0)
                 fused_trace(P, pidx, 4);
             const uint4 d = lds_v4(desc32 + 32u * e);            // off, nrows, e0a, e0b
             const uint32_t slot32 = ring32 + d.x;
-            if (gvalid && local < (int)d.y && !(cs.lost && !cs.lost_before)) {
+            if (gvalid && local < (int)d.y) {
                 // rows start on group boundaries: the header of the thread's group is (e0 >> 8) + local * groups per row + g
                 const float2 ms = lds_f2(slot32 + hdr_off + (((half ? d.w : d.z) >> 8) << 3));
                 const uint32_t sa = slot32 + off_a, sb = slot32 + off_b;
@@ -754,13 +756,13 @@ __device__ __forceinline__ void consume_ring_phase(const FusedParams &P, const M
         }
         const float tot = Fold<kFGroup, 16>::run(v, lane) * inv;   // lane t * (32 / kFGroup) holds the sum of stage t
         if (cs.rround > 0) {
-            if (!mbar_wait_bounded(sbase + kFBarRedEmpty + 8 * cs.rb, (uint32_t)(cs.rround - 1) & 1u, cs.lost ? kFShortWaitNs : wait_ns))
+            if (!mbar_wait_bounded(sbase + kFBarRedEmpty + 8 * cs.rb, (uint32_t)(cs.rround - 1) & 1u, wait_ns))
                 cs.lost = true;
         }
         float *red = reinterpret_cast<float *>(smem + kFRedOff + cs.rb * kFRedStride);
         if (active && (lane & (32 / kFGroup - 1)) == 0) {
             const int t = lane / (32 / kFGroup);
-            red[(t * p.rpp + rsub) * p.wpr + wi] = (cs.lost && !cs.lost_before) ? 0.f : tot;
+            red[(t * p.rpp + rsub) * p.wpr + wi] = tot;
         }
         __syncwarp();
         if (lane == 0)
@@ -841,7 +843,7 @@ __device__ __forceinline__ void consume_attention(const FusedParams &P, int laye
 
     for (int u = u0; u < u1; ++u) {
         const int e = cs.seq % kFDesc;
-        if (!mbar_wait_bounded(sbase + kFBarFull + 8 * e, (uint32_t)(cs.seq / kFDesc) & 1u, cs.lost ? kFShortWaitNs : wait_ns))
+        if (!mbar_wait_bounded(sbase + kFBarFull + 8 * e, (uint32_t)(cs.seq / kFDesc) & 1u, wait_ns))
             cs.lost = true;
         cs.lost = __any_sync(0xffffffffu, cs.lost) != 0;   // the shuffles below need a warp-uniform decision
         const FStage d = *(reinterpret_cast<const FStage *>(smem + kFDescOff) + e);
@@ -856,7 +858,7 @@ __device__ __forceinline__ void consume_attention(const FusedParams &P, int laye
             if (act)
                 q4 = __ldcg(reinterpret_cast<const float4 *>(P.q + (int64_t)h * head + 4 * li));
         }
-        const bool skip = cs.lost && !cs.lost_before;
+        const bool skip = false;   // a block whose hand-over ran out still works through its stages
         const float *ks = reinterpret_cast<const float *>(smem + kFHeader + P.xarea_bytes + (size_t)d.off);
         const float *vs = reinterpret_cast<const float *>(smem + kFHeader + P.xarea_bytes + (size_t)d.off + (size_t)d.aux);
         const int kvh = h / P.kv_mul;
@@ -959,11 +961,11 @@ __device__ __forceinline__ void epilogue_phase(const FusedParams &P, const MvPar
     const float *rope_s = rope_c + 64;
     for (int g0 = 0; g0 < nmine; g0 += kFGroup) {
         const int cnt = min(kFGroup, nmine - g0);
-        if (!epilogue_wait(P, es, smem, sbase + kFBarRedFull + 8 * es.rb, (uint32_t)es.rround & 1u, es.lost ? kFShortWaitNs : wait_ns,
+        if (!epilogue_wait(P, es, smem, sbase + kFBarRedFull + 8 * es.rb, (uint32_t)es.rround & 1u, wait_ns,
                            blockIdx.x, G, lane))
             es.lost = true;
         const float *red = reinterpret_cast<const float *>(smem + kFRedOff + es.rb * kFRedStride);
-        const bool skip = es.lost && !es.lost_before;
+        const bool skip = false;   // a block whose hand-over ran out still runs its own pipeline to the end
         if (p.epilogue == EPI_QKV_ROPE) {
             // a lane owns a pair of rows: (v0, v1) are rotated together (ApplyRope.java:61-92)
             const int pairs = rs >> 1;
@@ -1107,6 +1109,10 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_layers_kernel(const __
                 }
             }
         }
+        // No copy of this block may still be in flight when its shared memory is handed to the next block: the
+        // consumers have waited for every stage, so these waits return at once unless a wait ran out before.
+        for (int d = max(pr.tail, pr.seq - kFDesc); d < pr.seq; ++d)
+            mbar_wait_bounded(sbase + kFBarFull + 8 * (d % kFDesc), (uint32_t)(d / kFDesc) & 1u, wait_ns);
         if (lane == 0)
             *reinterpret_cast<volatile int *>(smem + kFIssued) = 0x7fffffff;   // lets the prefetch cursor run out
         if (pr.lost && lane == 0)

@@ -415,7 +415,7 @@ __global__ void __launch_bounds__(kRingMaxThreads, 1) matvec_ring_kernel(const _
                 }
                 if (round > 0) {
                     if (!mbar_wait_bounded(sbase + kBarEmpty + 8 * slot, (uint32_t)(round - 1) & 1u,
-                                           lost ? kShortWaitNs : wait_ns))
+                                           wait_ns))
                         lost = true;
                 }
                 const uint32_t full = sbase + kBarFull + 8 * slot;
@@ -559,11 +559,11 @@ __global__ void __launch_bounds__(kRingMaxThreads, 1) matvec_ring_kernel(const _
         // handed the first partial sums to this warp, and it runs while they work on the next stage.
         bool fence_first = LL && p.ll.write_back != nullptr && blockIdx.x == 0;
         for (;;) {
-            if (!mbar_wait_bounded(sbase + kBarRedFull + 8 * rb, (uint32_t)rround & 1u, lost ? kShortWaitNs : wait_ns))
+            if (!mbar_wait_bounded(sbase + kBarRedFull + 8 * rb, (uint32_t)rround & 1u, wait_ns))
                 lost = true;
             const int *rh = reinterpret_cast<const int *>(smem + kRedOff + rb * kRedStride);
             const int seg = rh[0], nrows = rh[2];
-            if (nrows <= 0 || (lost && !lost_before))
+            if (nrows <= 0)
                 break;
             const int row0 = rh[1] + p.seg[p.paired ? 0 : seg].out0;   // index in the output vector
             const float *red = reinterpret_cast<const float *>(rh + 4);
@@ -931,14 +931,16 @@ __global__ void __launch_bounds__(kRingMaxThreads, 1) matvec_ring_kernel(const _
     int slot = 0, round = 0, rb = 0, rround = 0;
     bool first = true;
     for (;;) {
-        if (!mbar_wait_bounded(sbase + kBarFull + 8 * slot, (uint32_t)round & 1u, lost ? kShortWaitNs : wait_ns))
+        if (!mbar_wait_bounded(sbase + kBarFull + 8 * slot, (uint32_t)round & 1u, wait_ns))
             lost = true;
         if (tid == 0 && first) {
             trace_mark(p, 4);
             first = false;
         }
         const StageDesc d = *(reinterpret_cast<const StageDesc *>(smem + kDescOff) + slot);
-        const bool done = d.nrows <= 0 || (lost && !lost_before);
+        // (a block whose input never came still works through its stages: producer, consumers and epilogue warp
+        // stay in step, and no bulk copy is in flight when the block ends)
+        const bool done = d.nrows <= 0;
         const uint8_t *slot_ptr = smem + kSmemHeader + p.xshare_bytes + (size_t)slot * p.slot_bytes;
 
         float v[RT];
@@ -1025,7 +1027,7 @@ __global__ void __launch_bounds__(kRingMaxThreads, 1) matvec_ring_kernel(const _
         if (lane == 0)
             mbar_arrive(sbase + kBarEmpty + 8 * slot);   // this warp is done with the ring slot
         if (rround > 0) {
-            if (!mbar_wait_bounded(sbase + kBarRedEmpty + 8 * rb, (uint32_t)(rround - 1) & 1u, lost ? kShortWaitNs : wait_ns))
+            if (!mbar_wait_bounded(sbase + kBarRedEmpty + 8 * rb, (uint32_t)(rround - 1) & 1u, wait_ns))
                 lost = true;
         }
         int *rh = reinterpret_cast<int *>(smem + kRedOff + rb * kRedStride);
