@@ -518,13 +518,14 @@ def main() -> None:
 
     def barrier():
         dist.barrier(group=host)
-        torch.cuda.synchronize()
+        torch.cuda.synchronize(local_rank)
 
     barrier()
     line = run_group(args, cfg, world) if rank == 0 else None
     barrier()
     # device time of the timed steps, maximum over the ranks (only rank 0 ran kernels of the group)
-    t = torch.tensor([line["ms_per_step"] if line else 0.0], dtype=torch.float64, device="cuda")
+    torch.cuda.set_device(local_rank)   # the group's calls moved rank 0's current device around
+    t = torch.tensor([line["ms_per_step"] if line else 0.0], dtype=torch.float64, device=torch.device("cuda", local_rank))
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     if rank == 0:
         line["ms_per_step"] = float(t.item())

@@ -82,6 +82,7 @@ enum l2j_tensor {
 #define L2J_F_NO_PDL 0x2      /* no programmatic dependent launch between consecutive kernels */
 #define L2J_F_SIMPLE 0x4      /* plain direct-load matvec kernels (cross-check path, slower) */
 #define L2J_F_STEP_KERNELS 0x8 /* one kernel per step of a layer (5 per layer) instead of one persistent kernel per token */
+#define L2J_F_TP_SPLIT_CLASSIFIER 0x10 /* l2j_create_tp: split the classifier's rows over the ranks too (they exchange their best candidates) */
 
 typedef struct l2j_ctx l2j_ctx;
 
@@ -186,11 +187,11 @@ L2J_API int l2j_pipeline_generate_greedy(l2j_ctx *const *stages, int n_stages, c
 
 /* A context that holds every layer but works on rank `tp_rank`'s block of rows of each matrix
  * (whole heads for Wq/Wk/Wv and the attention, hidden_dim / tp_size rows of W1/W3, dim / tp_size
- * rows of Wo/W2; the classifier is computed by every rank unless L2J_TP_CLS_SPLIT=1 is set in the
- * environment, which splits its rows too and lets the ranks exchange their best candidates).
+ * rows of Wo/W2; the classifier is computed by every rank unless L2J_F_TP_SPLIT_CLASSIFIER is given, which
+ * splits its rows too and lets the ranks exchange their best candidates).
  * Each rank sends its results to every rank over the peer links as (value, sequence number) pairs;
- * every output element is computed by one rank in the single-device order, so logits and tokens
- * are bitwise those of one device.  Weights are uploaded to every rank with the usual calls.  n_heads,
+ * every output element is computed by one rank in the order of the single device's per-step kernels, so
+ * logits and tokens are bitwise those of one device created with L2J_F_STEP_KERNELS.  Weights are uploaded to every rank with the usual calls.  n_heads,
  * n_kv_heads and hidden_dim must divide by tp_size (at most 8).  The reference has no such mode
  * (its multi-GPU mode is the layer split above). */
 L2J_API int l2j_create_tp(const l2j_config *cfg, int device, int tp_rank, int tp_size, uint32_t flags, l2j_ctx **ctx);

@@ -813,9 +813,7 @@ static int create_impl(const l2j_config *cfg, int device, int first_layer, int l
     c->tp_size = tp_size;
     // Splitting the classifier's rows as well saves most of its 80 us per token but ends every token with a
     // rendezvous of all ranks; measured it gains 3 % at 2 ranks and loses 11 % at 4 and 8, so it is opt-in.
-    c->cls_split = false;
-    if (const char *e = getenv("L2J_TP_CLS_SPLIT"))
-        c->cls_split = atoi(e) != 0 && tp_size > 1 && cfg->vocab_size % tp_size == 0;
+    c->cls_split = (flags & L2J_F_TP_SPLIT_CLASSIFIER) && tp_size > 1 && cfg->vocab_size % tp_size == 0;
     c->is_first = first_layer == 0;
     c->is_last = last_layer == cfg->n_layers - 1;
     c->dim = cfg->dim;

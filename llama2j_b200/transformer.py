@@ -328,6 +328,10 @@ class TensorParallel:
     def last_generate_us(self) -> float:
         return self.ranks[0].last_generate_us()
 
+    def reset(self) -> None:
+        """l2j_tp_reset: every rank starts a new sequence (their hand-over counters must agree)."""
+        _lib.check(self._lib.l2j_tp_reset(self._arr, len(self.ranks)), self.ranks[0]._ctx)
+
     def close(self) -> None:
         for r in self.ranks:
             r.close()
