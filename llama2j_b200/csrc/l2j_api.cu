@@ -408,9 +408,6 @@ void build_fused_params(l2j_ctx *c)
     F.state = c->state;
     F.timeout_us = c->wait_limit_us;
     F.trace = c->fused_trace;
-    F.l2_ahead_bytes = 384 * 1024;
-    if (const char *e = getenv("L2J_FUSED_L2_AHEAD_KB"))   // diagnostic: A/B of the prefetch distance
-        F.l2_ahead_bytes = atoi(e) * 1024;
     if (const char *e = getenv("L2J_FUSED_NO_COPY"))   // measurement aid: consumers run on whatever the ring holds
         F.debug_no_copy = atoi(e);
 }

@@ -59,7 +59,6 @@ constexpr int kFBarEmpty = 128;         // uint64 empty[16]
 constexpr int kFBarRedFull = 256;       // uint64 red_full[4]
 constexpr int kFBarRedEmpty = 288;      // uint64 red_empty[4]
 constexpr int kFFlag = 320;             // int: result of the poll of a hand-over counter
-constexpr int kFIssued = 324;           // int: bytes of the ring the producer has handed out so far
 constexpr int kFVStart = 3264;          // int vstart[16]: the producer's bookkeeping of where each stage in flight begins
 constexpr int kFScratch = 384;          // float scratch[64]
 constexpr int kFDescOff = 640;          // FStage desc[16]
@@ -210,7 +209,6 @@ struct Producer {
     uint64_t wait_ns;
     int pos;                // the token's position, -1 until the kernel in front has set it
     AttSplit as;
-    int issued;             // bytes of the stages issued so far (what the L2 prefetch cursor paces itself by)
 
     // Room for `bytes` contiguous bytes and a free descriptor; returns the offset in the ring.
     __device__ __forceinline__ uint32_t acquire(uint32_t bytes)
@@ -236,24 +234,7 @@ struct Producer {
     }
 };
 
-// The other cursor over the same sequence of stages, run by a warp of its own ahead of the producer: it asks L2
-// for the stages to come (cp.async.bulk.prefetch.L2).  The ring holds what the copies in flight need to keep
-// HBM busy; it cannot also buffer a phase boundary of several microseconds, so without this HBM idles at every
-// boundary.
-struct Prefetcher {
-    int pos;
-    AttSplit as;
-    int layer, part, idx, limit, rot, bytes;
-};
-
-// Position in the block's sequence of stages: part 0 QKV, 1 attention units, 2 Wo, 3 W1/W3, 4 W2.
-__device__ __forceinline__ int part_matrix(int part)
-{
-    return part == 0 ? 0 : part - 1;
-}
-
-template <typename T>
-__device__ __forceinline__ void producer_learn_pos(T &pr, const FusedParams &P, int grid)
+__device__ __forceinline__ void producer_learn_pos(Producer &pr, const FusedParams &P, int grid)
 {
     if (pr.pos < 0) {
         // The position is set by the kernel in front; everything touched so far was weights.
@@ -261,68 +242,6 @@ __device__ __forceinline__ void producer_learn_pos(T &pr, const FusedParams &P, 
         pr.pos = __ldcg(&P.state->cur_pos);
         pr.as = att_split(P, pr.pos, grid);
     }
-}
-
-// Sets the prefetch cursor to the first item of its current part; empty parts are skipped by the caller.
-__device__ __forceinline__ void prefetch_enter(Prefetcher &pf, const FusedParams &P, int b, int grid)
-{
-    if (pf.part == 1) {
-        producer_learn_pos(pf, P, grid);
-        pf.idx = b < pf.as.ga ? att_first_unit(pf.as, b) : 0;
-        pf.limit = b < pf.as.ga ? att_first_unit(pf.as, b + 1) : 0;
-    } else {
-        pf.idx = first_stage_of(b, pf.rot, grid);
-        pf.limit = P.mv[part_matrix(pf.part)].total_stages;
-    }
-}
-
-// One step of the prefetch cursor: asks L2 for the next stage of the block.  Returns false at the end.
-__device__ __forceinline__ bool prefetch_step(Prefetcher &pf, const FusedParams &P, int b, int grid, int lane)
-{
-    while (pf.idx >= pf.limit) {   // next part
-        if (pf.part != 1)
-            pf.rot = (pf.rot + P.mv[part_matrix(pf.part)].total_stages) % grid;
-        if (++pf.part == 5) {
-            pf.part = 0;
-            if (++pf.layer == P.n_layers)
-                return false;
-        }
-        prefetch_enter(pf, P, b, grid);
-    }
-    if (pf.part == 1) {
-        const AttSplit &a = pf.as;
-        const int h = pf.idx / a.nchunk, c = pf.idx - h * a.nchunk;
-        const int t0 = c * kAttChunk;
-        const int old = min(pf.pos, t0 + kAttChunk) - t0;
-        const uint32_t kbytes = (uint32_t)old * (uint32_t)P.head * 4u;
-        if (old > 0 && lane < 2) {
-            const int64_t row = ((int64_t)(h / P.kv_mul) * P.seq_len + t0) * P.head;
-            bulk_prefetch_l2((lane ? P.mv[0].v_cache : P.mv[0].k_cache) + (int64_t)pf.layer * P.kv_step + row, kbytes);
-        }
-        pf.bytes += 2 * (int)((kbytes + 127u) & ~127u);
-        pf.idx += 1;
-    } else {
-        const int k = part_matrix(pf.part);
-        const MvParams &p = P.mv[k];
-        int seg, row0, nrows;
-        stage_rows(p, pf.idx, seg, row0, nrows);
-        const int h = lane & 1, is_hdr = lane >> 1;
-        const int sg = p.paired ? h : seg;
-        const uint32_t pbytes = (uint32_t)nrows * (uint32_t)p.rowbytes;
-        const int64_t flat = p.seg[sg].flat0 + (int64_t)pf.layer * P.seg_step[k][sg] + (int64_t)row0 * p.n;
-        const int64_t ga = (flat >> 8) & ~(int64_t)1;
-        const int64_t gl = (flat + pbytes - 1) >> 8;
-        const uint32_t hbytes = (uint32_t)(((gl - ga + 2) & ~(int64_t)1) * 8);
-        if (p.paired || h == 0) {
-            if (is_hdr)
-                bulk_prefetch_l2(p.seg[sg].hdr + ga, hbytes);
-            else
-                bulk_prefetch_l2(p.seg[sg].payload + flat, pbytes);
-        }
-        pf.bytes += p.slot_bytes;
-        pf.idx += grid;
-    }
-    return true;
 }
 
 // The producer is the first four lanes of its warp.  All four keep the same bookkeeping; a stage's (up to) four
@@ -365,9 +284,6 @@ __device__ __forceinline__ void produce_ring_stage(Producer &pr, const FusedPara
         mbar_arrive(full);
     }
     ++pr.seq;
-    pr.issued += p.slot_bytes;
-    if (lane == 0)
-        *reinterpret_cast<volatile int *>(pr.smem + kFIssued) = pr.issued;
 }
 
 __device__ __forceinline__ void produce_att_stage(Producer &pr, const FusedParams &P, int layer, int unit, const AttSplit &a, int pos,
@@ -401,9 +317,6 @@ __device__ __forceinline__ void produce_att_stage(Producer &pr, const FusedParam
         mbar_arrive(full);   // only the token's own row: nothing travels through the ring
     }
     ++pr.seq;
-    pr.issued += 2 * (int)voff;
-    if (lane == 0)
-        *reinterpret_cast<volatile int *>(pr.smem + kFIssued) = pr.issued;
 }
 
 // -------------------------------------------------------------------------------------------------
@@ -927,28 +840,7 @@ __device__ __forceinline__ void consume_attention(const FusedParams &P, int laye
 struct Epilogue {
     int rb, rround;
     bool lost, lost_before;
-    Prefetcher pf;      // this warp spends most of its time waiting: it runs the L2 prefetch cursor meanwhile
-    bool pf_on;
 };
-
-// Waits for the consumers' partial sums of the next group; while they are not there, asks L2 for stages ahead.
-__device__ __forceinline__ bool epilogue_wait(const FusedParams &P, Epilogue &es, uint8_t *smem, uint32_t bar, uint32_t parity,
-                                              uint64_t timeout_ns, int b, int grid, int lane)
-{
-    if (mbar_try_wait(bar, parity))
-        return true;
-    const long long c0 = sm_clock();
-    const long long limit = (long long)(2 * timeout_ns);
-    volatile int *issued = reinterpret_cast<volatile int *>(smem + kFIssued);
-    for (;;) {
-        if (mbar_try_wait(bar, parity))
-            return true;
-        if (es.pf_on && es.pf.bytes - *issued < P.l2_ahead_bytes)
-            es.pf_on = prefetch_step(es.pf, P, b, grid, lane);
-        if (sm_clock() - c0 > limit)
-            return false;
-    }
-}
 
 __device__ __forceinline__ void epilogue_phase(const FusedParams &P, const MvParams &p, int layer, int first, int nmine, int pos,
                                                uint8_t *smem, uint32_t sbase, Epilogue &es, uint64_t wait_ns)
@@ -961,8 +853,7 @@ __device__ __forceinline__ void epilogue_phase(const FusedParams &P, const MvPar
     const float *rope_s = rope_c + 64;
     for (int g0 = 0; g0 < nmine; g0 += kFGroup) {
         const int cnt = min(kFGroup, nmine - g0);
-        if (!epilogue_wait(P, es, smem, sbase + kFBarRedFull + 8 * es.rb, (uint32_t)es.rround & 1u, wait_ns,
-                           blockIdx.x, G, lane))
+        if (!mbar_wait_bounded(sbase + kFBarRedFull + 8 * es.rb, (uint32_t)es.rround & 1u, wait_ns))
             es.lost = true;
         const float *red = reinterpret_cast<const float *>(smem + kFRedOff + es.rb * kFRedStride);
         const bool skip = false;   // a block whose hand-over ran out still runs its own pipeline to the end
@@ -1059,8 +950,6 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_layers_kernel(const __
         mbar_init(sbase + kFBarRedFull + 8 * tid, kFusedConsWarps);
         mbar_init(sbase + kFBarRedEmpty + 8 * tid, 1);
     }
-    if (tid == 0)
-        *reinterpret_cast<volatile int *>(smem + kFIssued) = 0;
     if (tid < 32)
         mbar_fence_init();
     __syncthreads();
@@ -1083,7 +972,6 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_layers_kernel(const __
         pr.pos = -1;
         pr.as = AttSplit{};
         pr.off = 0;
-        pr.issued = 0;
         int rot = 0;
         for (int layer = 0; layer < P.n_layers; ++layer) {
 #pragma unroll 1
@@ -1113,8 +1001,6 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_layers_kernel(const __
         // consumers have waited for every stage, so these waits return at once unless a wait ran out before.
         for (int d = max(pr.tail, pr.seq - kFDesc); d < pr.seq; ++d)
             mbar_wait_bounded(sbase + kFBarFull + 8 * (d % kFDesc), (uint32_t)(d / kFDesc) & 1u, wait_ns);
-        if (lane == 0)
-            *reinterpret_cast<volatile int *>(smem + kFIssued) = 0x7fffffff;   // lets the prefetch cursor run out
         if (pr.lost && lane == 0)
             atomicOr(&P.state->status, L2J_DS_WAIT_TIMEOUT);
         return;
@@ -1132,11 +1018,6 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_layers_kernel(const __
         Epilogue es;
         es.rb = es.rround = 0;
         es.lost = es.lost_before = lost_at_entry;
-        es.pf.pos = pos;
-        es.pf.as = as;
-        es.pf.layer = es.pf.part = es.pf.rot = es.pf.bytes = 0;
-        es.pf_on = P.l2_ahead_bytes > 0;
-        prefetch_enter(es.pf, P, b, G);
         {
             float *rope_c = reinterpret_cast<float *>(smem + kFRopeOff);
             const int half = P.head >> 1;

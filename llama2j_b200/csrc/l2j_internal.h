@@ -219,7 +219,6 @@ struct FusedParams {
     SeqState *state;
     int timeout_us;
     unsigned long long *trace; // optional: [block][5 * n_layers][8] global-timer marks, else nullptr
-    int l2_ahead_bytes;        // how far (bytes per block) the producer's L2 prefetch runs ahead of its copies (0: no prefetch)
     int debug_no_copy;         // measurement aid: the producer hands out stages without copying (results are garbage)
 };
 constexpr int kSyncStride = 32;     // unsigned ints between two hand-over counters (128 bytes)
