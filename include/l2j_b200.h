@@ -334,17 +334,14 @@ L2J_API int l2j_k_swiglu(int device, float *hb, const float *hb2, int n);
  * work on `stream` (a cudaStream_t, NULL for the default stream) and does not synchronise; it calls no
  * cudaMalloc / cudaFree.  The first call on a device looks up the scratch array's device address, so
  * make it before any stream capture.  All calls share the one array: two calls whose kernels overlap
- * on the GPU race on it, keep them on one stream or order them yourself. */
+ * on the GPU race on it, keep them on one stream or order them yourself.  `stream` must be a stream of
+ * `device` (or 0); the call makes `device` current for the duration and puts the caller's device back. */
 L2J_API int l2j_k_attention_noalloc(int device, const float *q_dev, const float *k_cache_dev, const float *v_cache_dev,
                                     int pos, int n_heads, int n_kv_heads, int head_size, int seq_len, float *out_dev,
                                     void *stream);
 
 /* Message of the calling thread's most recent l2j_k_attention_noalloc failure ("" if none). */
 L2J_API const char *l2j_noalloc_last_error(void);
-
-/* Copies n bytes device-to-device repeatedly and returns the best time; the denominator check of
- * the roofline (no counterpart in the reference). */
-L2J_API int l2j_k_copy_bandwidth(int device, int64_t bytes, int iters, double *best_gbs);
 
 #ifdef __cplusplus
 }

@@ -54,6 +54,10 @@ struct l2j_ctx {
     float *rms_att = nullptr, *rms_ffn = nullptr, *rms_final = nullptr;   // dequantised
     float *emb = nullptr, *wcls = nullptr;
     int64_t emb_received = 0, wcls_received = 0;
+    // which parts have arrived, as sorted disjoint intervals (groups for the quantised tensors, floats for the
+    // FP32 ones): a part sent twice must not stand in for one that never came
+    std::vector<std::pair<int64_t, int64_t>> got[L2J_T_COUNT];
+    int async_in_flight = 0;       // forwards queued by l2j_forward_stage_async since the last synchronisation
 
     float *x = nullptr, *xb = nullptr, *q = nullptr, *hb = nullptr, *logits = nullptr;
     int reps = 1;                  // copies of x, xb, hb and the RMSNorm weights
@@ -63,7 +67,7 @@ struct l2j_ctx {
     float *rope_cos = nullptr, *rope_sin = nullptr;
     float *attn_part = nullptr;
     unsigned int *attn_counters = nullptr;
-    int nsplit = 1, chunk_max = 1;
+    int nsplit = 1;
     int nsplit_long = 1;           // splits per head of the long-context attention launch
     float *blk_val = nullptr;
     int *blk_idx = nullptr;
@@ -160,6 +164,34 @@ int dev_alloc(l2j_ctx *ctx, T **out, int64_t count, bool zero)
     return L2J_OK;
 }
 
+// Adds [a, b) to the sorted disjoint intervals; false (and nothing added) if it overlaps one of them.
+bool add_interval(std::vector<std::pair<int64_t, int64_t>> &iv, int64_t a, int64_t b)
+{
+    size_t i = 0;
+    while (i < iv.size() && iv[i].second <= a)
+        ++i;
+    if (i < iv.size() && iv[i].first < b)
+        return false;
+    iv.insert(iv.begin() + (long)i, std::make_pair(a, b));
+    for (size_t j = 0; j + 1 < iv.size();) {   // join neighbours that touch
+        if (iv[j].second == iv[j + 1].first) {
+            iv[j].second = iv[j + 1].second;
+            iv.erase(iv.begin() + (long)j + 1);
+        } else {
+            ++j;
+        }
+    }
+    return true;
+}
+
+int64_t covered(const std::vector<std::pair<int64_t, int64_t>> &iv)
+{
+    int64_t n = 0;
+    for (const auto &p : iv)
+        n += p.second - p.first;
+    return n;
+}
+
 bool is_quant_tensor(int t)
 {
     return t == L2J_T_RMS_ATT || t == L2J_T_WQ || t == L2J_T_WK || t == L2J_T_WV || t == L2J_T_WO || t == L2J_T_RMS_FFN ||
@@ -187,19 +219,6 @@ void build_rope_tables(int seq_len, int head, std::vector<float> &cs, std::vecto
             sn[(size_t)pos * half + j] = (float)std::sin((double)val);
         }
     }
-}
-
-int choose_nsplit(int sm_count, int n_heads, int seq_len)
-{
-    int ns = (2 * sm_count + n_heads - 1) / n_heads;
-    if (ns > 32)
-        ns = 32;
-    const int cap = seq_len / 16 > 0 ? seq_len / 16 : 1;
-    if (ns > cap)
-        ns = cap;
-    if (ns < 1)
-        ns = 1;
-    return ns;
 }
 
 // Rows [rank * rows / parts, (rank + 1) * rows / parts) of a matrix of `rows` rows of n elements that starts
@@ -472,7 +491,6 @@ void build_launch_params(l2j_ctx *c)
         t.head = c->head;
         t.seq_len = c->cfg.seq_len;
         t.nsplit = c->nsplit;
-        t.chunk_max = c->chunk_max;
         t.pos_override = -1;
         t.cluster = c->attn_cluster ? 1 : 0;
         t.timeout_us = c->wait_limit_us;
@@ -929,7 +947,6 @@ static int create_impl(const l2j_config *cfg, int device, int first_layer, int l
         c->attn_cluster = atoi(e) != 0;
     if (c->attn_cluster && c->nsplit > 8)
         c->nsplit = 8;   // portable cluster size
-    c->chunk_max = (((cfg->seq_len + c->nsplit - 1) / c->nsplit) + 3) & ~3;   // keeps the float4 scratch behind it aligned
     // A tensor-parallel rank has few heads: the long-context launch splits them further so that its blocks
     // still cover the SMs (its results travel with sequence numbers, no block count is baked in anywhere).
     c->nsplit_long = c->nsplit;
@@ -1123,6 +1140,9 @@ extern "C" int l2j_upload_quant(l2j_ctx *c, int tensor, int64_t float_offset, co
     const int64_t i0 = pg0 > g0 ? pg0 : g0, i1 = pg1 < g1 ? pg1 : g1;
     if (i1 <= i0)
         return L2J_OK;
+    if (!add_interval(c->got[tensor], i0, i1))
+        return fail(c, L2J_E_INVALID, "tensor %d: groups [%lld, %lld) overlap a part that was uploaded before", tensor,
+                    (long long)i0, (long long)i1);
     CK(c, cudaSetDevice(c->device));
     const int64_t count = i1 - i0;
     const uint8_t *src = static_cast<const uint8_t *>(groups) + (i0 - pg0) * kGroupBytes;
@@ -1149,8 +1169,7 @@ extern "C" int l2j_upload_quant(l2j_ctx *c, int tensor, int64_t float_offset, co
             rc = fail(c, L2J_E_CUDA, "upload of tensor %d failed: %s", tensor, cudaGetErrorString(e));
     }
     cudaFree(stage);
-    if (rc == L2J_OK)
-        q.groups_received += count;
+    q.groups_received = covered(c->got[tensor]);
     return rc;
 }
 
@@ -1171,13 +1190,13 @@ extern "C" int l2j_upload_f32(l2j_ctx *c, int tensor, int64_t float_offset, cons
         return fail(c, L2J_E_INVALID, "the classifier is shared with the embedding in this configuration");
     if (!c->needed[tensor])
         return L2J_OK;
+    if (!add_interval(c->got[tensor], float_offset, float_offset + n_floats))
+        return fail(c, L2J_E_INVALID, "tensor %d: floats [%lld, +%lld) overlap a part that was uploaded before", tensor,
+                    (long long)float_offset, (long long)n_floats);
     CK(c, cudaSetDevice(c->device));
     float *dst = tensor == L2J_T_TOKEN_EMBEDDING ? c->emb : c->wcls;
     CK(c, cudaMemcpy(dst + float_offset, data, (size_t)n_floats * sizeof(float), cudaMemcpyHostToDevice));
-    if (tensor == L2J_T_TOKEN_EMBEDDING)
-        c->emb_received += n_floats;
-    else
-        c->wcls_received += n_floats;
+    (tensor == L2J_T_TOKEN_EMBEDDING ? c->emb_received : c->wcls_received) = covered(c->got[tensor]);
     return L2J_OK;
 }
 
@@ -1293,10 +1312,16 @@ extern "C" int l2j_forward_stage_async(l2j_ctx *c, int token, int pos)
         return fail(c, L2J_E_STATE, "forward before finalize");
     if (c->tp_size > 1)
         return fail(c, L2J_E_STATE, "a rank of a tensor-parallel group runs through l2j_tp_forward");
+    std::lock_guard<std::mutex> lock(c->mu);
     int rc = check_range(c, token, pos, c->is_first);
     if (rc != L2J_OK)
         return rc;
     CK(c, cudaSetDevice(c->device));
+    // every queued forward holds a slot of the pinned command ring until its copy has run
+    if (++c->async_in_flight >= kCmdRing) {
+        CK(c, cudaStreamSynchronize(c->stream));
+        c->async_in_flight = 1;
+    }
     rc = post_cmd(c, 1, c->is_first ? token : 0, pos);
     if (rc != L2J_OK)
         return rc;
@@ -1307,9 +1332,11 @@ extern "C" int l2j_sync(l2j_ctx *c)
 {
     if (!c)
         return L2J_E_INVALID;
+    std::lock_guard<std::mutex> lock(c->mu);
     CK(c, cudaSetDevice(c->device));
     CK(c, cudaMemcpyAsync(c->state_host, c->state, sizeof(SeqState), cudaMemcpyDeviceToHost, c->stream));
     CK(c, cudaStreamSynchronize(c->stream));
+    c->async_in_flight = 0;
     return finish_status(c);
 }
 
@@ -2488,7 +2515,6 @@ extern "C" int l2j_k_attention(int device, const float *q, const float *key_cach
     SeqState *st = nullptr;
     AttnParams p{};
     p.nsplit = choose_nsplit(prop.multiProcessorCount, n_heads, seq_len);
-    p.chunk_max = (((seq_len + p.nsplit - 1) / p.nsplit) + 3) & ~3;
     KCK(s.alloc(&dq, (int64_t)n_heads * head_size));
     KCK(s.alloc(&ksrc, used));
     KCK(s.alloc(&vsrc, used));
@@ -2539,39 +2565,5 @@ extern "C" int l2j_k_swiglu(int device, float *hb, const float *hb2, int n)
     KCK(launch_swiglu_plain(nullptr, a, b, n));
     KCK(cudaDeviceSynchronize());
     KCK(cudaMemcpy(hb, a, (size_t)n * sizeof(float), cudaMemcpyDeviceToHost));
-    return L2J_OK;
-}
-
-extern "C" int l2j_k_copy_bandwidth(int device, int64_t bytes, int iters, double *best_gbs)
-{
-    if (bytes <= 0 || iters <= 0 || !best_gbs)
-        return fail(nullptr, L2J_E_INVALID, "bad arguments");
-    int rc = set_device_checked(device);
-    if (rc != L2J_OK)
-        return rc;
-    Scratch s;
-    uint8_t *a = nullptr, *b = nullptr;
-    KCK(s.alloc(&a, bytes, true));
-    KCK(s.alloc(&b, bytes, true));
-    cudaEvent_t e0, e1;
-    KCK(cudaEventCreate(&e0));
-    KCK(cudaEventCreate(&e1));
-    double best = 0.0;
-    for (int i = 0; i < iters + 2; ++i) {
-        cudaEventRecord(e0, nullptr);
-        cudaMemcpyAsync(b, a, (size_t)bytes, cudaMemcpyDeviceToDevice, nullptr);
-        cudaEventRecord(e1, nullptr);
-        cudaEventSynchronize(e1);
-        float ms = 0.f;
-        cudaEventElapsedTime(&ms, e0, e1);
-        if (i >= 2 && ms > 0.f) {
-            const double gbs = 2.0 * (double)bytes / ((double)ms * 1e6);
-            if (gbs > best)
-                best = gbs;
-        }
-    }
-    cudaEventDestroy(e0);
-    cudaEventDestroy(e1);
-    *best_gbs = best;
     return L2J_OK;
 }

@@ -178,7 +178,7 @@ struct AttnParams {
     float *part;             // scratch: [n_heads][nsplit][head + 2]
     unsigned int *counters;  // [n_heads], zero between launches
     SeqState *state;
-    int n_heads, kv_mul, head, seq_len, nsplit, chunk_max;
+    int n_heads, kv_mul, head, seq_len, nsplit;
     int pos_override;        // >= 0: use this position instead of state->cur_pos (tests)
     int cluster;             // 1: the nsplit (<= 8) blocks of a head are launched as one thread-block cluster and merge
                              // their partial results through distributed shared memory instead of `part`
@@ -227,6 +227,21 @@ constexpr int kFusedConsWarps = 18;
 
 cudaError_t prepare_fused(int *max_smem);
 cudaError_t launch_fused(cudaStream_t stream, bool pdl, int grid, int smem_bytes, const FusedParams &p);
+
+// Blocks per head of the stand-alone attention kernel: enough to fill the SMs twice over, at least 16 positions
+// each.  One definition for every entry point, so that they split (and therefore round) alike.
+inline int choose_nsplit(int sm_count, int n_heads, int seq_len)
+{
+    int ns = (2 * sm_count + n_heads - 1) / n_heads;
+    if (ns > 32)
+        ns = 32;
+    const int cap = seq_len / 16 > 0 ? seq_len / 16 : 1;
+    if (ns > cap)
+        ns = cap;
+    if (ns < 1)
+        ns = 1;
+    return ns;
+}
 
 struct MvPlan {
     bool grouped;  // u8 rows of whole groups: four lanes share a group (template selector)

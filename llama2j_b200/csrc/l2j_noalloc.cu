@@ -66,9 +66,25 @@ extern "C" int l2j_k_attention_noalloc(int device, const float *q_dev, const flo
         return na_fail(L2J_E_INVALID, "problem exceeds the fixed scratch: at most 128 heads of at most 128 floats");
     if (device < 0 || device >= kNaMaxDevices)
         return na_fail(L2J_E_INVALID, "device index out of range");
-    cudaError_t e = cudaSetDevice(device);
+    // The launch needs `device` current; the caller's own current device is put back on every way out.
+    struct DeviceGuard {
+        int prev = -1;
+        ~DeviceGuard()
+        {
+            if (prev >= 0)
+                cudaSetDevice(prev);
+        }
+    } guard;
+    int current = -1;
+    cudaError_t e = cudaGetDevice(&current);
     if (e != cudaSuccess)
-        return na_fail(L2J_E_CUDA, "cudaSetDevice failed", e);
+        return na_fail(L2J_E_CUDA, "cudaGetDevice failed", e);
+    if (current != device) {
+        e = cudaSetDevice(device);
+        if (e != cudaSuccess)
+            return na_fail(L2J_E_CUDA, "cudaSetDevice failed", e);
+        guard.prev = current;
+    }
 
     void *scratch = nullptr;
     int sms = 0;
@@ -93,16 +109,8 @@ extern "C" int l2j_k_attention_noalloc(int device, const float *q_dev, const flo
     }
 
     AttnParams p{};
-    int ns = (2 * sms + n_heads - 1) / n_heads;   // enough blocks to fill the GPU twice over
-    if (ns > kNaMaxSplit)
-        ns = kNaMaxSplit;
-    const int cap = seq_len / 16 > 0 ? seq_len / 16 : 1;
-    if (ns > cap)
-        ns = cap;
-    if (ns < 1)
-        ns = 1;
-    p.nsplit = ns;
-    p.chunk_max = 0;
+    p.nsplit = choose_nsplit(sms, n_heads, seq_len);   // the split of l2j_k_attention: same partial sums, same bits
+    static_assert(kNaMaxSplit >= 32, "choose_nsplit returns at most 32 splits");
     p.q = q_dev;
     p.k_cache = k_cache_dev;
     p.v_cache = v_cache_dev;

@@ -91,7 +91,6 @@ _SIGNATURES = {
     "l2j_k_swiglu": (C.c_int, [C.c_int, _P, _P, C.c_int]),
     "l2j_k_attention_noalloc": (C.c_int, [C.c_int, _P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _P, _P]),
     "l2j_noalloc_last_error": (C.c_char_p, []),
-    "l2j_k_copy_bandwidth": (C.c_int, [C.c_int, C.c_int64, C.c_int, C.POINTER(C.c_double)]),
 }
 
 EXPORTED_SYMBOLS = tuple(_SIGNATURES)

@@ -101,3 +101,31 @@ def test_layer_split_needs_the_link():
     with pytest.raises(L.L2jError):
         rest.forward(1, 0)
     a.close()
+
+
+def test_duplicate_part_cannot_stand_in_for_a_missing_one():
+    """A tensor uploaded in parts (the multi-part .quant cache): a part sent twice is refused, and the hole the
+    missing part leaves is seen at finalize (the parts have equal sizes, so a count of groups would not see it)."""
+    cfg = ModelConfig(dim=256, hidden_dim=512, n_layers=2, n_heads=4, n_kv_heads=4, vocab_size=256, seq_len=16,
+                      shared_classifier=True)
+    tensors = syn.synthetic_tensors(cfg, 1)
+    m = Transformer(cfg)
+    for t in L.QUANT_TENSORS:
+        if t != L.T_W1:
+            m.upload_quant(t, tensors[t])
+    m.upload_f32(L.T_TOKEN_EMBEDDING, tensors[L.T_TOKEN_EMBEDDING])
+    per_layer = cfg.hidden_dim * cfg.dim                       # floats of one layer of W1: a multiple of 256
+    part_bytes = per_layer // 256 * 264
+    first = tensors[L.T_W1][:part_bytes]
+    m.upload_quant(L.T_W1, first, n_floats=per_layer, float_offset=0)
+    with pytest.raises(L.L2jError) as e:
+        m.upload_quant(L.T_W1, first, n_floats=per_layer, float_offset=0)      # the same part again
+    assert e.value.code == L.E_INVALID
+    with pytest.raises(L.L2jError) as e:
+        m.finalize()                                                           # layer 1 never came
+    assert e.value.code == L.E_STATE
+    m.upload_quant(L.T_W1, tensors[L.T_W1][part_bytes:], n_floats=per_layer, float_offset=per_layer)
+    m.finalize()
+    lg, _ = m.forward(1, 0)
+    assert np.isfinite(lg).all()
+    m.close()
