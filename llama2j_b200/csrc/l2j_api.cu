@@ -421,7 +421,7 @@ void build_fused_params(l2j_ctx *c)
     const int merge_bytes = kFusedConsWarps * (32 / gw) * (c->head + 4) * 4;
     const int limb_bytes = 3 * (c->dim > c->hidden ? c->dim : c->hidden);
     F.xarea_bytes = ((merge_bytes > limb_bytes ? merge_bytes : limb_bytes) + 127) & ~127;
-    F.ring_bytes = (c->fused_smem - 3840 - F.xarea_bytes) & ~127;
+    F.ring_bytes = (c->fused_smem - kFusedHeaderBytes - F.xarea_bytes) & ~127;
     F.sync = c->chain;
     F.epoch = c->chain + (int64_t)kChainStride * (5 * c->nl + 1);
     F.state = c->state;
@@ -1013,9 +1013,11 @@ static int create_impl(const l2j_config *cfg, int device, int first_layer, int l
     c->use_ring = !(flags & L2J_F_SIMPLE) && c->plan_qkv.ok && c->plan_wo.ok && c->plan_w13.ok && c->plan_hidden.ok &&
                   c->plan_cls.ok && (head % 2 == 0);
     {   // one persistent launch per token where every matrix has rows of whole quantisation groups
-        // (its consumers hold a vector of dim elements in four rounds of 16-byte loads, the hidden vector in eight)
+        // (a consumer warp converts every 18th group of the input vector, three at most; a lane's eight elements of the
+        // attention output lie in one head)
         bool fused = c->use_ring && tp_size == 1 && !(flags & L2J_F_STEP_KERNELS) && c->reps == 1 && c->dim % kGroup == 0 &&
-                     c->hidden % kGroup == 0 && c->dim <= 4 * 4 * kFusedConsWarps * 32 && c->hidden <= 8 * 4 * kFusedConsWarps * 32;
+                     c->hidden % kGroup == 0 && c->dim <= 3 * kFusedConsWarps * kGroup && c->hidden <= 3 * kFusedConsWarps * kGroup &&
+                     head % 8 == 0;
         if (const char *e = getenv("L2J_FUSED"))   // diagnostic: A/B against the per-step kernels
             fused = fused && atoi(e) != 0;
         if (fused) {
@@ -1032,7 +1034,7 @@ static int create_impl(const l2j_config *cfg, int device, int first_layer, int l
             for (int k = 0; k < 4; ++k)
                 largest = c->fplan[k].slot_bytes > largest ? c->fplan[k].slot_bytes : largest;
             const int limb_bytes = 3 * (c->dim > c->hidden ? c->dim : c->hidden);
-            if (c->fused_smem - 3840 - limb_bytes - 4096 < 3 * largest)
+            if (c->fused_smem - kFusedHeaderBytes - limb_bytes - 4096 < 3 * largest)
                 fused = false;   // the ring would not hold three stages
         }
         if (fused) {

@@ -65,11 +65,12 @@ constexpr int kFDescOff = 640;          // FStage desc[16]
 constexpr int kFRedOff = 1152;          // 4 x 132 floats: [stage of the group][row of the stage][warp of the row]
 constexpr int kFRedStride = 528;
 constexpr int kFRopeOff = 3328;         // float cos[64], sin[64] of the token's position
-constexpr int kFHeader = 3840;          // end of the fixed part (128-byte aligned)
+constexpr int kFInvTab = 3840;          // float inv[64]: value of one fixed-point unit of each group of the input vector
+constexpr int kFHeader = kFusedHeaderBytes;   // end of the fixed part (128-byte aligned)
+static_assert(kFInvTab + 64 * 4 <= kFHeader, "header layout");
 constexpr int kFCons = kFusedConsWarps * 32;
-constexpr int kFRounds = 8;             // 16-byte loads of the input vector per consumer thread at most
-constexpr int kAttFastSlots = 4, kAttFastRounds = 2;   // the merge that fetches all partials of a thread's elements at once
-constexpr int kFRmsRounds = 4;          // the same for a vector of dim elements (RMSNorm'd input, merged attention output)
+constexpr int kFGroupRounds = 3;        // quantisation groups of the input vector that one consumer warp converts at most (54 groups)
+constexpr int kAttFastSlots = 4;        // the merge that fetches all partials of a thread's elements at once
 constexpr uint64_t kFShortWaitNs = 2000;
 
 struct FStage {
@@ -373,85 +374,22 @@ __device__ __forceinline__ void consume_ring_phase(const FusedParams &P, const M
     for (int k = 0; k < 4; ++k)
         chunk[k] = g * 16 + 4 * (k ^ ((lane >> 2) & 1)) + (lane & 3);
 
-    float inv = 1.0f;
+    // ---- prologue: the input vector as fixed-point limbs in shared memory.  Every warp owns whole quantisation
+    // groups of the vector (group warp + 18 j in round j; a lane holds elements 4 l..4 l + 3 of each half of the group, so that a warp's loads are two contiguous 512-byte requests) and gives each its own
+    // power-of-two scale from the group's largest element: no block-wide maximum has to be agreed on before the
+    // conversion can start, and the RMSNorm scalar ss = 1 / sqrt(mean(x^2) + eps) is applied to the dot products
+    // at the end (sum_j w_j (r_j ss x_j) = ss sum_j w_j r_j x_j up to rounding), so nothing here waits for the
+    // sum of squares either.
+    float *inv_tab = reinterpret_cast<float *>(smem + kFInvTab);   // value of one fixed-point unit, per group
+    const int ngroups = n >> 8;
     {
-        // All 576 consumer threads share the vector: thread t owns the float4s t, t + 576, ...
-        const int n4 = n >> 2;
         const bool has_rms = rms_w != nullptr;
-        float4 xr[kFRounds], wr[kFRmsRounds];   // the RMSNorm'd vectors have dim elements: kFRmsRounds rounds (host-checked)
-        if (!merge) {
-#pragma unroll
-            for (int j = 0; j < kFRounds; ++j) {
-                const int idx = tid + j * kFCons;
-                xr[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (j < kFRmsRounds)
-                    wr[j] = make_float4(1.f, 1.f, 1.f, 1.f);
-                if (idx < n4) {
-                    xr[j] = ld_cg_f4_issue(p.x_in + (int64_t)idx * 4);
-                    if (j < kFRmsRounds && has_rms)
-                        wr[j] = ld_cg_f4_issue(rms_w + (int64_t)idx * 4);
-                }
-            }
-        } else if (as.np_max <= kAttFastSlots && n4 <= kAttFastRounds * kFCons) {
-            // The partials of head h were written by blocks b0..b1 of the attention phase, one slot each, in block
-            // order; merged here in that order, so the result does not depend on which SM ran what.  Few partials:
-            // every thread fetches those of its elements (weights included) in one round of loads.
-            const int ps = P.head + 4;
-            float4 o4[kAttFastRounds][kAttFastSlots];
-            float2 ml[kAttFastRounds][kAttFastSlots];
-#pragma unroll
-            for (int j = 0; j < kAttFastRounds; ++j) {
-                const int idx = tid + j * kFCons;
-                const int e = min(idx, n4 - 1) * 4;
-                const int h = e / P.head, d = e - h * P.head;
-                const int u0 = h * as.nchunk;
-                const int np = att_block_of(as, u0 + as.nchunk - 1) - att_block_of(as, u0) + 1;
-                const float *hp = P.att_part + (int64_t)h * kAttSlots * ps;
-#pragma unroll
-                for (int s2 = 0; s2 < kAttFastSlots; ++s2) {
-                    o4[j][s2] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    ml[j][s2] = make_float2(-INFINITY, 0.f);
-                    if (s2 < np && idx < n4) {
-                        o4[j][s2] = ld_cg_f4_issue(hp + (int64_t)s2 * ps + d);
-                        ml[j][s2] = __ldcg(reinterpret_cast<const float2 *>(hp + (int64_t)s2 * ps + P.head));
-                    }
-                }
-            }
-#pragma unroll
-            for (int j = 0; j < kFRounds; ++j)
-                xr[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-            for (int j = 0; j < kFRmsRounds; ++j)
-                wr[j] = make_float4(1.f, 1.f, 1.f, 1.f);
-#pragma unroll
-            for (int j = 0; j < kAttFastRounds; ++j) {
-                float gm = -INFINITY;
-#pragma unroll
-                for (int s2 = 0; s2 < kAttFastSlots; ++s2)
-                    gm = fmaxf(gm, ml[j][s2].x);
-                float L = 0.f;
-                float4 O = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-                for (int s2 = 0; s2 < kAttFastSlots; ++s2) {
-                    if (ml[j][s2].y > 0.f) {
-                        const float w = expf(ml[j][s2].x - gm);
-                        L = fmaf(ml[j][s2].y, w, L);
-                        O.x = fmaf(o4[j][s2].x, w, O.x);
-                        O.y = fmaf(o4[j][s2].y, w, O.y);
-                        O.z = fmaf(o4[j][s2].z, w, O.z);
-                        O.w = fmaf(o4[j][s2].w, w, O.w);
-                    }
-                }
-                if (tid + j * kFCons < n4)   // ExpSumNormalize.java:33-37 folded into the weighted sum
-                    xr[j] = make_float4(__fdiv_rn(O.x, L), __fdiv_rn(O.y, L), __fdiv_rn(O.z, L), __fdiv_rn(O.w, L));
-            }
-        } else {
-            // The partials of head h were written by blocks b0..b1 of the attention phase, one slot each, in block
-            // order.  First a table of their weights in shared memory (one thread per head), then every thread
-            // folds the partial outputs of its elements with those weights, in slot order: the result does not
-            // depend on which SM ran what.
-            float *tw = reinterpret_cast<float *>(share);            // [n_heads][kAttSlots] weights, then [n_heads] 1 / sum
-            const int ps = P.head + 4;
+        float xg[kFGroupRounds][8];
+        const int ps = P.head + 4;
+        const bool merge_fast = merge && as.np_max <= kAttFastSlots;
+        if (merge && !merge_fast) {
+            // Many partials per head: first a table of their weights in shared memory (one thread per head).
+            float *tw = reinterpret_cast<float *>(share);            // [n_heads][kAttSlots] weights, then [n_heads] sums
             if (tid < P.n_heads) {
                 const int h = tid;
                 const int u0 = h * as.nchunk;
@@ -481,101 +419,149 @@ __device__ __forceinline__ void consume_ring_phase(const FusedParams &P, const M
                 }
                 tw[P.n_heads * kAttSlots + h] = L;
             }
-#pragma unroll
-            for (int j = 0; j < kFRounds; ++j)
-                xr[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-            for (int j = 0; j < kFRmsRounds; ++j)
-                wr[j] = make_float4(1.f, 1.f, 1.f, 1.f);
             named_barrier_sync(2, kFCons);
+        }
+        // ---- loads of all rounds first (they are independent), then the arithmetic
+        float4 wa[kFGroupRounds], wb[kFGroupRounds];
 #pragma unroll
-            for (int j = 0; j < kFRmsRounds; ++j) {
-                const int idx = tid + j * kFCons;
-                if (idx < n4) {
-                    const int e = idx * 4;
-                    const int h = e / P.head, d = e - h * P.head;
-                    const float *hp = P.att_part + (int64_t)h * kAttSlots * ps + d;
+        for (int j = 0; j < kFGroupRounds; ++j) {
+            const int gi = warp + j * kFusedConsWarps;
+            const int e = gi * 256 + lane * 4;
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+                xg[j][q] = 0.f;
+            wa[j] = wb[j] = make_float4(1.f, 1.f, 1.f, 1.f);
+            if (gi >= ngroups)
+                continue;
+            if (!merge) {
+                const float4 a4 = ld_cg_f4_issue(p.x_in + e), b4 = ld_cg_f4_issue(p.x_in + e + 128);
+                xg[j][0] = a4.x; xg[j][1] = a4.y; xg[j][2] = a4.z; xg[j][3] = a4.w;
+                xg[j][4] = b4.x; xg[j][5] = b4.y; xg[j][6] = b4.z; xg[j][7] = b4.w;
+                if (has_rms) {
+                    wa[j] = ld_cg_f4_issue(rms_w + e);
+                    wb[j] = ld_cg_f4_issue(rms_w + e + 128);
+                }
+            } else {
+                // The partials of head h were written by blocks b0..b1 of the attention phase, one slot each, in
+                // block order; merged here in that order, so the result does not depend on which SM ran what.
+#pragma unroll
+                for (int hw = 0; hw < 2; ++hw) {
+                    const int eh = e + 128 * hw;
+                    const int h = eh / P.head, d = eh - h * P.head;
+                    const float *hp = P.att_part + (int64_t)h * kAttSlots * ps;
                     float4 O = make_float4(0.f, 0.f, 0.f, 0.f);
+                    float L = 0.f;
+                    if (merge_fast) {
+                        const int u0 = h * as.nchunk;
+                        const int np = att_block_of(as, u0 + as.nchunk - 1) - att_block_of(as, u0) + 1;
+                        float4 o4[kAttFastSlots];
+                        float2 ml[kAttFastSlots];
 #pragma unroll
-                    for (int s2 = 0; s2 < kAttSlots; ++s2) {
-                        const float w = tw[h * kAttSlots + s2];
-                        if (w > 0.f) {
-                            const float4 o = ld_cg_f4_issue(hp + (int64_t)s2 * ps);
-                            O.x = fmaf(o.x, w, O.x);
-                            O.y = fmaf(o.y, w, O.y);
-                            O.z = fmaf(o.z, w, O.z);
-                            O.w = fmaf(o.w, w, O.w);
+                        for (int s2 = 0; s2 < kAttFastSlots; ++s2) {
+                            o4[s2] = make_float4(0.f, 0.f, 0.f, 0.f);
+                            ml[s2] = make_float2(-INFINITY, 0.f);
+                            if (s2 < np) {
+                                o4[s2] = ld_cg_f4_issue(hp + (int64_t)s2 * ps + d);
+                                ml[s2] = __ldcg(reinterpret_cast<const float2 *>(hp + (int64_t)s2 * ps + P.head));
+                            }
                         }
+                        float gm = -INFINITY;
+#pragma unroll
+                        for (int s2 = 0; s2 < kAttFastSlots; ++s2)
+                            gm = fmaxf(gm, ml[s2].x);
+#pragma unroll
+                        for (int s2 = 0; s2 < kAttFastSlots; ++s2) {
+                            if (ml[s2].y > 0.f) {
+                                const float w = expf(ml[s2].x - gm);
+                                L = fmaf(ml[s2].y, w, L);
+                                O.x = fmaf(o4[s2].x, w, O.x);
+                                O.y = fmaf(o4[s2].y, w, O.y);
+                                O.z = fmaf(o4[s2].z, w, O.z);
+                                O.w = fmaf(o4[s2].w, w, O.w);
+                            }
+                        }
+                    } else {
+                        const float *tw = reinterpret_cast<const float *>(share);
+#pragma unroll
+                        for (int s2 = 0; s2 < kAttSlots; ++s2) {
+                            const float w = tw[h * kAttSlots + s2];
+                            if (w > 0.f) {
+                                const float4 o = ld_cg_f4_issue(hp + (int64_t)s2 * ps + d);
+                                O.x = fmaf(o.x, w, O.x);
+                                O.y = fmaf(o.y, w, O.y);
+                                O.z = fmaf(o.z, w, O.z);
+                                O.w = fmaf(o.w, w, O.w);
+                            }
+                        }
+                        L = tw[P.n_heads * kAttSlots + h];
                     }
-                    const float L = tw[P.n_heads * kAttSlots + h];
                     // ExpSumNormalize.java:33-37 folded into the weighted sum
-                    xr[j] = make_float4(__fdiv_rn(O.x, L), __fdiv_rn(O.y, L), __fdiv_rn(O.z, L), __fdiv_rn(O.w, L));
+                    xg[j][4 * hw + 0] = __fdiv_rn(O.x, L);
+                    xg[j][4 * hw + 1] = __fdiv_rn(O.y, L);
+                    xg[j][4 * hw + 2] = __fdiv_rn(O.z, L);
+                    xg[j][4 * hw + 3] = __fdiv_rn(O.w, L);
                 }
             }
+        }
+        if (merge && !merge_fast)
             named_barrier_sync(2, kFCons);   // the table's place is taken by the limbs below
-        }
-        float ssq = 0.f, amax = 0.f;
+        float ssq = 0.f;
 #pragma unroll
-        for (int j = 0; j < kFRounds; ++j) {
-            ssq = fmaf(xr[j].x, xr[j].x, ssq);
-            ssq = fmaf(xr[j].y, xr[j].y, ssq);
-            ssq = fmaf(xr[j].z, xr[j].z, ssq);
-            ssq = fmaf(xr[j].w, xr[j].w, ssq);
-            amax = fmaxf(fmaxf(amax, fmaxf(fabsf(xr[j].x), fabsf(xr[j].y))), fmaxf(fabsf(xr[j].z), fabsf(xr[j].w)));
+        for (int j = 0; j < kFGroupRounds; ++j) {
+            const int gi = warp + j * kFusedConsWarps;
+            if (gi >= ngroups)   // warp-uniform
+                continue;
+            float amax = 0.f;
+            const float wv[8] = {wa[j].x, wa[j].y, wa[j].z, wa[j].w, wb[j].x, wb[j].y, wb[j].z, wb[j].w};
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                ssq = fmaf(xg[j][q], xg[j][q], ssq);
+                xg[j][q] = __fmul_rn(wv[q], xg[j][q]);       // RMSNorm weight (1 where the phase has none)
+                amax = fmaxf(amax, fabsf(xg[j][q]));
+            }
+            amax = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(amax)));   // non-negative floats order like their bits
+            // 24-bit fixed point: one power-of-two scale per group, |x * f| <= 2^22
+            int ex = (int)((__float_as_uint(amax) >> 23) & 0xffu) - 126;   // amax < 2^ex for normal numbers
+            if (!(amax > 0.f) || !(amax < 3.0e38f))
+                ex = 0;
+            ex = max(-90, min(126, ex));
+            const float f = __int_as_float((127 + 22 - ex) << 23);
+            if (lane == 0)
+                inv_tab[gi] = __int_as_float((127 + ex - 22) << 23);
+            // three balanced signed byte limbs: after the add-and-flip, bytes 0..2 of z are l0, l1, l2 in
+            // [-128, 127] with X = l0 + 256 l1 + 65536 l2
+            uint32_t z[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+                z[q] = ((uint32_t)__float2int_rn(xg[j][q] * f) + 0x00008080u) ^ 0x00008080u;
+            uint32_t *dst = reinterpret_cast<uint32_t *>(share) + gi * 64 + lane;
+#pragma unroll
+            for (int hw = 0; hw < 2; ++hw) {
+                const uint32_t t0 = __byte_perm(z[4 * hw], z[4 * hw + 1], 0x5140);
+                const uint32_t t2 = __byte_perm(z[4 * hw + 2], z[4 * hw + 3], 0x5140);
+                const uint32_t t1 = __byte_perm(z[4 * hw], z[4 * hw + 1], 0x0062);
+                const uint32_t t3 = __byte_perm(z[4 * hw + 2], z[4 * hw + 3], 0x0062);
+                dst[32 * hw] = __byte_perm(t0, t2, 0x5410);
+                dst[(n >> 2) + 32 * hw] = __byte_perm(t0, t2, 0x7632);
+                dst[(n >> 1) + 32 * hw] = __byte_perm(t1, t3, 0x5410);
+            }
         }
-        if (tid == 0 && (P.debug_no_copy & 8)) fused_trace(P, pidx, 5);
-        ssq = warp_sum(ssq);
-        amax = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(amax)));   // non-negative floats order like their bits
-        if (lane == 0) {
-            scratch[warp] = ssq;
-            scratch[32 + warp] = amax;
-        }
-        named_barrier_sync(2, kFCons);
-        if (tid == 0 && (P.debug_no_copy & 8)) fused_trace(P, pidx, 6);
-        ssq = warp_sum(lane < kFusedConsWarps ? scratch[lane] : 0.f);   // the same order in every warp and block
-        amax = __uint_as_float(__reduce_max_sync(0xffffffffu, lane < kFusedConsWarps ? __float_as_uint(scratch[32 + lane]) : 0u));
         if (has_rms) {
-            float tot = __fdiv_rn(ssq, (float)n);
-            tot = __fadd_rn(tot, 1e-5f);
-            const float ss = __fdiv_rn(1.0f, __fsqrt_rn(tot));
-#pragma unroll
-            for (int j = 0; j < kFRmsRounds; ++j) {
-                xr[j].x = __fmul_rn(wr[j].x, __fmul_rn(ss, xr[j].x));
-                xr[j].y = __fmul_rn(wr[j].y, __fmul_rn(ss, xr[j].y));
-                xr[j].z = __fmul_rn(wr[j].z, __fmul_rn(ss, xr[j].z));
-                xr[j].w = __fmul_rn(wr[j].w, __fmul_rn(ss, xr[j].w));
-            }
-            amax = amax * ss * rms_wmax * 1.000001f;   // bound of |w * (ss * x)| from max|x| and max|w|
-        }
-        // 24-bit fixed point: one power-of-two scale per vector, |x * f| <= 2^22
-        int ex = (int)((__float_as_uint(amax) >> 23) & 0xffu) - 126;   // amax < 2^ex for normal numbers
-        if (!(amax > 0.f) || !(amax < 3.0e38f))
-            ex = 0;
-        ex = max(-90, min(126, ex));
-        const float f = __int_as_float((127 + 22 - ex) << 23);
-        inv = __int_as_float((127 + ex - 22) << 23);
-#pragma unroll
-        for (int j = 0; j < kFRounds; ++j) {
-            const int idx = tid + j * kFCons;
-            if (idx < n4) {
-                // three balanced signed byte limbs: after the add-and-flip, bytes 0..2 of z are l0, l1, l2 in
-                // [-128, 127] with X = l0 + 256 l1 + 65536 l2
-                const uint32_t z0 = ((uint32_t)__float2int_rn(xr[j].x * f) + 0x00008080u) ^ 0x00008080u;
-                const uint32_t z1 = ((uint32_t)__float2int_rn(xr[j].y * f) + 0x00008080u) ^ 0x00008080u;
-                const uint32_t z2 = ((uint32_t)__float2int_rn(xr[j].z * f) + 0x00008080u) ^ 0x00008080u;
-                const uint32_t z3 = ((uint32_t)__float2int_rn(xr[j].w * f) + 0x00008080u) ^ 0x00008080u;
-                const uint32_t t0 = __byte_perm(z0, z1, 0x5140);
-                const uint32_t t2 = __byte_perm(z2, z3, 0x5140);
-                const uint32_t t1 = __byte_perm(z0, z1, 0x0062);
-                const uint32_t t3 = __byte_perm(z2, z3, 0x0062);
-                uint32_t *dst = reinterpret_cast<uint32_t *>(share) + idx;
-                dst[0] = __byte_perm(t0, t2, 0x5410);
-                dst[n >> 2] = __byte_perm(t0, t2, 0x7632);
-                dst[n >> 1] = __byte_perm(t1, t3, 0x5410);
-            }
+            ssq = warp_sum(ssq);
+            if (lane == 0)
+                scratch[warp] = ssq;
         }
     }
     named_barrier_sync(1, kFCons);
+
+    // what a unit of this thread's integer sums is worth: its group's fixed-point unit, times the RMSNorm scalar
+    float unit = gvalid ? inv_tab[g] : 0.f;
+    if (rms_w != nullptr) {
+        const float ssq = warp_sum(lane < kFusedConsWarps ? scratch[lane] : 0.f);   // the same order in every warp and block
+        float tot = __fdiv_rn(ssq, (float)n);
+        tot = __fadd_rn(tot, 1e-5f);
+        unit *= __fdiv_rn(1.0f, __fsqrt_rn(tot));   // RootMeanSquare.java:25-35
+    }
 
     uint32_t xl[4][4][3];
     float xs;
@@ -658,7 +644,7 @@ __device__ __forceinline__ void consume_ring_phase(const FusedParams &P, const M
                 }
                 // |a_l| <= 64 * 255 * 128 < 2^24: the conversions are exact
                 const float dsum = fmaf((float)a2, 65536.0f, fmaf((float)a1, 256.0f, (float)a0));
-                v[t] = fmaf(ms.y, dsum, ms.x * xs);
+                v[t] = fmaf(ms.y, dsum, ms.x * xs) * unit;
             }
             __syncwarp();
             if (lane == 0)
@@ -667,7 +653,7 @@ __device__ __forceinline__ void consume_ring_phase(const FusedParams &P, const M
             parity ^= (e == 0);
             ++cs.seq;
         }
-        const float tot = Fold<kFGroup, 16>::run(v, lane) * inv;   // lane t * (32 / kFGroup) holds the sum of stage t
+        const float tot = Fold<kFGroup, 16>::run(v, lane);   // lane t * (32 / kFGroup) holds the sum of stage t
         if (cs.rround > 0) {
             if (!mbar_wait_bounded(sbase + kFBarRedEmpty + 8 * cs.rb, (uint32_t)(cs.rround - 1) & 1u, wait_ns))
                 cs.lost = true;

@@ -224,6 +224,7 @@ struct FusedParams {
 constexpr int kSyncStride = 32;     // unsigned ints between two hand-over counters (128 bytes)
 constexpr int kFusedThreads = 640;  // 18 consumer warps, the producer warp, the epilogue warp
 constexpr int kFusedConsWarps = 18;
+constexpr int kFusedHeaderBytes = 4096;   // barriers, descriptors, reduction buffers in front of the vector area and the ring
 
 cudaError_t prepare_fused(int *max_smem);
 cudaError_t launch_fused(cudaStream_t stream, bool pdl, int grid, int smem_bytes, const FusedParams &p);
