@@ -82,6 +82,7 @@ enum l2j_tensor {
 #define L2J_F_NO_PDL 0x2      /* no programmatic dependent launch between consecutive kernels */
 #define L2J_F_SIMPLE 0x4      /* plain direct-load matvec kernels (cross-check path, slower) */
 #define L2J_F_STEP_KERNELS 0x8 /* one kernel per step of a layer (5 per layer) instead of one persistent kernel per token */
+#define L2J_F_PERSISTENT 0x20  /* the persistent kernel wherever the shape allows it (default: only where it is the faster one) */
 #define L2J_F_TP_SPLIT_CLASSIFIER 0x10 /* l2j_create_tp: split the classifier's rows over the ranks too (they exchange their best candidates) */
 
 typedef struct l2j_ctx l2j_ctx;

@@ -1018,6 +1018,11 @@ static int create_impl(const l2j_config *cfg, int device, int first_layer, int l
         bool fused = c->use_ring && tp_size == 1 && !(flags & L2J_F_STEP_KERNELS) && c->reps == 1 && c->dim % kGroup == 0 &&
                      c->hidden % kGroup == 0 && c->dim <= 3 * kFusedConsWarps * kGroup && c->hidden <= 3 * kFusedConsWarps * kGroup &&
                      head % 8 == 0;
+        // Measured on B200: with dim a multiple of 2048 (every consumer warp's lanes own a group of the rows:
+        // 7B shape) the persistent kernel is level with the per-step kernels at short contexts and 4 % ahead at
+        // long ones; with 20 groups per row (13B shape) a sixth of the lanes idle and it is 9 % behind.
+        if (!(flags & L2J_F_PERSISTENT) && c->dim % (8 * kGroup) != 0)
+            fused = false;
         if (const char *e = getenv("L2J_FUSED"))   // diagnostic: A/B against the per-step kernels
             fused = fused && atoi(e) != 0;
         if (fused) {

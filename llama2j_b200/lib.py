@@ -13,7 +13,7 @@ from . import build as _build
 
 E_INVALID, E_CUDA, E_STATE, E_DEVICE, E_NOMEM = -1, -2, -3, -4, -5
 DS_WAIT_TIMEOUT, DS_BAD_POS, DS_BAD_TOKEN, DS_BAD_LINK = 0x1, 0x2, 0x4, 0x8
-F_NO_GRAPH, F_NO_PDL, F_SIMPLE, F_STEP_KERNELS, F_TP_SPLIT_CLASSIFIER = 0x1, 0x2, 0x4, 0x8, 0x10
+F_NO_GRAPH, F_NO_PDL, F_SIMPLE, F_STEP_KERNELS, F_TP_SPLIT_CLASSIFIER, F_PERSISTENT = 0x1, 0x2, 0x4, 0x8, 0x10, 0x20
 QUANT_GROUP, QUANT_GROUP_BYTES = 256, 264
 
 (T_TOKEN_EMBEDDING, T_RMS_ATT, T_WQ, T_WK, T_WV, T_WO, T_RMS_FFN, T_W1, T_W2, T_W3, T_RMS_FINAL, T_WCLS) = range(12)

@@ -162,13 +162,16 @@ def test_layer_split_two_stages_equal_one(oracle):
         m.close()
 
 
-def test_config2_stories110m_to_position_1024(oracle):
-    """dim 768 (group-aligned rows), 32-token prompt, greedy decode to position 1024."""
+@pytest.mark.parametrize("flags,persistent", [(0, False), (L.F_PERSISTENT, True)])
+def test_config2_stories110m_to_position_1024(oracle, flags, persistent):
+    """dim 768 (group-aligned rows), 32-token prompt, greedy decode to position 1024: with the per-step kernels
+    (the default at this width) and with all layers in one persistent launch."""
     cfg = syn.SHAPES["stories110M"]
     tensors = syn.synthetic_tensors(cfg, 0)
     prompt = syn.synthetic_prompt(32, 1)
-    toks, worst, flips, mode, _ = _compare_run(oracle, cfg, tensors, prompt, 1024)
-    assert mode["ring"]
+    toks, worst, flips, mode, stats = _compare_run(oracle, cfg, tensors, prompt, 1024, flags)
+    assert mode["ring"] and mode["persistent"] == persistent
+    assert stats.kernels_per_forward == (3 if persistent else 2 + 5 * cfg.n_layers)
     assert worst < TOL, worst
     assert not flips, flips
 

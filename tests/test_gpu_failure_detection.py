@@ -28,7 +28,7 @@ def _build(cfg, tensors, flags=0, first=0, last=None, limit_us=None):
     return m
 
 
-@pytest.mark.parametrize("flags,kernels", [(0, "persistent"), (L.F_STEP_KERNELS, "per-step")])
+@pytest.mark.parametrize("flags,kernels", [(L.F_PERSISTENT, "persistent"), (L.F_STEP_KERNELS, "per-step")])
 def test_wait_runs_out_is_reported_and_reset_recovers(flags, kernels):
     cfg = ModelConfig(dim=512, hidden_dim=1536, n_layers=3, n_heads=8, n_kv_heads=8, vocab_size=2048, seq_len=64,
                       shared_classifier=False)

@@ -39,8 +39,8 @@ def _build(cfg, tensors, flags=0):
     return m
 
 
-def _compare(oracle, cfg, tensors, prompt, steps):
-    gpu = _build(cfg, tensors)
+def _compare(oracle, cfg, tensors, prompt, steps, flags=0):
+    gpu = _build(cfg, tensors, flags)
     toks, logits = run_greedy_host_loop(gpu, prompt, steps, stop_on_bos=False)
     dev_toks = gpu.generate_greedy(prompt, steps)
     status = gpu.stats().device_status
@@ -74,6 +74,13 @@ def test_llama2_13b_full_workload(oracle):
     _compare(oracle, cfg, syn.synthetic_tensors(cfg, 0), syn.synthetic_prompt(32, 1, cfg.vocab_size), 288)
 
 
+def test_llama2_13b_persistent_kernel(oracle):
+    """The 13B shape runs the per-step kernels by default (they are the faster ones there); the persistent kernel
+    on the same shape, asked for by flag: rows of 20 groups leave lanes of every third warp without a group."""
+    cfg = syn.SHAPES["llama2-13b"]
+    _compare(oracle, cfg, syn.synthetic_tensors(cfg, 0), syn.synthetic_prompt(32, 1, cfg.vocab_size), 40, L.F_PERSISTENT)
+
+
 def test_llama2_7b_varied_tokens_and_rms_weights(oracle):
     """A forced random token stream and RMSNorm weights in [0.3, 2): token identity means something here."""
     cfg = syn.SHAPES["llama2-7b"]
@@ -100,7 +107,7 @@ def test_llama2_7b_long_context_same_cache(oracle):
         return np.ascontiguousarray(np.roll(base, 17 * layer, axis=0)) * np.float32(1.0 + 0.01 * layer)
 
     results = {}
-    for name, flags in (("persistent", 0), ("per-step", L.F_STEP_KERNELS)):
+    for name, flags in (("persistent", L.F_PERSISTENT), ("per-step", L.F_STEP_KERNELS)):
         gpu = _build(cfg, tensors, flags)
         for layer in range(cfg.n_layers):
             gpu.kv_write(layer, 0, rows(k0, layer), rows(v0, layer))
@@ -136,7 +143,7 @@ def test_llama2_7b_long_context_prefill_on_device():
     prompt = syn.synthetic_prompt(3840, 1, cfg.vocab_size)
     steps = 3904
     runs = {}
-    for name, flags in (("persistent", 0), ("per-step", L.F_STEP_KERNELS)):
+    for name, flags in (("persistent", L.F_PERSISTENT), ("per-step", L.F_STEP_KERNELS)):
         gpu = _build(cfg, tensors, flags)
         toks = gpu.generate_greedy(prompt, steps)
         logits = gpu.forward(int(toks[steps - 1]), steps)[0].copy()
