@@ -149,6 +149,17 @@ L2J_API int l2j_forward_stage(l2j_ctx *ctx, int token, int pos, const float *x_i
 
 /* Device addresses of the stage's activation vector x (dim floats) and of its logits, for callers
  * that move them with their own device-to-device transport. */
+/* Token selection on the device for --temp > 0 (Run.java:643-665 with Sampler.java:20-44,76-120): the logits
+ * of the last forward are divided by the temperature, turned into probabilities in place exactly as the
+ * reference does it (exp in double, one sequential float sum) and sampled plainly (topp > 0.999) or from the
+ * nucleus, with java.util.Random's 48-bit generator seeded like `new Sampler(seed, vocab)`: from the same
+ * logits the device chooses the token the Java Sampler chooses, and only its id crosses PCIe (call
+ * l2j_forward with logits == NULL).  The ProbIndex array the reference keeps across calls (and sorts whole,
+ * stale entries included) is kept across calls here too.  temperature == 0 returns the arg-max
+ * (Sampler.argmax).  Vocabularies of at most 39,000 tokens (the probabilities live in shared memory). */
+L2J_API int l2j_sampler_seed(l2j_ctx *ctx, int64_t seed);
+L2J_API int l2j_sample(l2j_ctx *ctx, float temperature, float topp, int *token);
+
 L2J_API int l2j_device_buffers(l2j_ctx *ctx, void **x_dev, void **logits_dev);
 
 /* The stage step without host copies: enqueues the kernels on the context's stream and returns.

@@ -57,6 +57,10 @@ struct l2j_ctx {
     // which parts have arrived, as sorted disjoint intervals (groups for the quantised tensors, floats for the
     // FP32 ones): a part sent twice must not stand in for one that never came
     std::vector<std::pair<int64_t, int64_t>> got[L2J_T_COUNT];
+    SamplerState *samp_state = nullptr;   // device sampler (l2j_sampler_seed / l2j_sample), allocated on first use
+    float *samp_prob[2] = {nullptr, nullptr};
+    int *samp_index[2] = {nullptr, nullptr};
+    SamplerState *samp_host = nullptr;     // pinned
     int async_in_flight = 0;       // forwards queued by l2j_forward_stage_async since the last synchronisation
 
     float *x = nullptr, *xb = nullptr, *q = nullptr, *hb = nullptr, *logits = nullptr;
@@ -1104,6 +1108,8 @@ extern "C" void l2j_destroy(l2j_ctx *c)
         cudaFreeHost(c->x_host);
     if (c->state_host)
         cudaFreeHost(c->state_host);
+    if (c->samp_host)
+        cudaFreeHost(c->samp_host);
     if (c->ev0)
         cudaEventDestroy(c->ev0);
     if (c->ev1)
@@ -1397,6 +1403,78 @@ extern "C" int l2j_forward(l2j_ctx *c, int token, int pos, float *logits, int *a
     if (!(c->is_first && c->is_last))
         return fail(c, L2J_E_STATE, "l2j_forward needs a context that holds every layer; use l2j_forward_stage");
     return l2j_forward_stage(c, token, pos, nullptr, nullptr, logits, argmax);
+}
+
+extern "C" int l2j_sampler_seed(l2j_ctx *c, int64_t seed)
+{
+    if (!c)
+        return L2J_E_INVALID;
+    std::lock_guard<std::mutex> lock(c->mu);
+    if (!c->finalized || !c->is_last)
+        return fail(c, L2J_E_STATE, "the sampler belongs to the finalized context that holds the classifier");
+    const int n = c->cfg.vocab_size;
+    if (n < 2 || sample_smem_bytes(n) > 220 * 1024)
+        return fail(c, L2J_E_INVALID, "the device sampler keeps the probabilities in shared memory: vocabulary of 2..%d tokens",
+                    (int)((220 * 1024 - 65536) / 4));
+    CK(c, cudaSetDevice(c->device));
+    if (!c->samp_state) {
+        int rc = dev_alloc(c, &c->samp_state, 1, true);
+        for (int b = 0; b < 2 && rc == L2J_OK; ++b) {
+            rc = dev_alloc(c, &c->samp_prob[b], n, true);
+            if (rc == L2J_OK)
+                rc = dev_alloc(c, &c->samp_index[b], n, true);
+        }
+        if (rc != L2J_OK)
+            return rc;
+        CK(c, cudaHostAlloc((void **)&c->samp_host, sizeof(SamplerState), cudaHostAllocDefault));
+        CK(c, prepare_sampler(n));
+    }
+    CK(c, cudaStreamSynchronize(c->stream));
+    // new Sampler(seed, vocab): every ProbIndex is (0, 0), Random(seed) scrambles the seed (java.util.Random)
+    for (int b = 0; b < 2; ++b) {
+        CK(c, cudaMemset(c->samp_prob[b], 0, sizeof(float) * (size_t)n));
+        CK(c, cudaMemset(c->samp_index[b], 0, sizeof(int) * (size_t)n));
+    }
+    SamplerState init{};
+    init.rng = ((unsigned long long)seed ^ 0x5DEECE66DULL) & ((1ULL << 48) - 1ULL);
+    init.token = 0;
+    CK(c, cudaMemcpy(c->samp_state, &init, sizeof(init), cudaMemcpyHostToDevice));
+    return L2J_OK;
+}
+
+extern "C" int l2j_sample(l2j_ctx *c, float temperature, float topp, int *token)
+{
+    if (!c || !token)
+        return L2J_E_INVALID;
+    std::lock_guard<std::mutex> lock(c->mu);
+    if (!c->finalized || !c->is_last)
+        return fail(c, L2J_E_STATE, "sampling needs the finalized context that holds the classifier");
+    if (!(temperature >= 0.0f) || !(topp >= 0.0f))
+        return fail(c, L2J_E_INVALID, "temperature and topp must not be negative");
+    CK(c, cudaSetDevice(c->device));
+    if (temperature == 0.0f) {   // Run.java:639-642: the arg-max, already chosen on the device by the classifier's launch
+        CK(c, cudaMemcpyAsync(c->state_host, c->state, sizeof(SeqState), cudaMemcpyDeviceToHost, c->stream));
+        CK(c, cudaStreamSynchronize(c->stream));
+        *token = c->state_host->argmax;
+        return finish_status(c);
+    }
+    if (!c->samp_state)
+        return fail(c, L2J_E_STATE, "call l2j_sampler_seed first");
+    SampleParams sp{};
+    sp.logits = c->logits;
+    sp.n = c->cfg.vocab_size;
+    sp.temperature = temperature;
+    sp.topp = topp;
+    sp.st = c->samp_state;
+    for (int b = 0; b < 2; ++b) {
+        sp.prob[b] = c->samp_prob[b];
+        sp.index[b] = c->samp_index[b];
+    }
+    CK(c, launch_sample(c->stream, sp));
+    CK(c, cudaMemcpyAsync(c->samp_host, c->samp_state, sizeof(SamplerState), cudaMemcpyDeviceToHost, c->stream));
+    CK(c, cudaStreamSynchronize(c->stream));
+    *token = c->samp_host->token;
+    return L2J_OK;
 }
 
 extern "C" int l2j_device_buffers(l2j_ctx *c, void **x_dev, void **logits_dev)

@@ -244,6 +244,25 @@ inline int choose_nsplit(int sm_count, int n_heads, int seq_len)
     return ns;
 }
 
+// ---- temperature / top-p sampler on the device (l2j_sampler.cu) ----------------------------------
+struct SamplerState {
+    unsigned long long rng;   // java.util.Random's 48-bit state
+    int token;                // the id chosen by the last launch
+};
+
+struct SampleParams {
+    float *logits;            // vocab logits of the last forward; turned into probabilities in place
+    int n;
+    float temperature, topp;
+    SamplerState *st;
+    float *prob[2];           // the Sampler's ProbIndex array (persistent across calls), and the sort's second buffer
+    int *index[2];
+};
+
+size_t sample_smem_bytes(int n);
+cudaError_t prepare_sampler(int n);
+cudaError_t launch_sample(cudaStream_t stream, const SampleParams &sp);
+
 struct MvPlan {
     bool grouped;  // u8 rows of whole groups: four lanes share a group (template selector)
     int cpt;       // chunks per thread (template selector)

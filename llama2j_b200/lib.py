@@ -55,6 +55,8 @@ _SIGNATURES = {
     "l2j_finalize": (C.c_int, [_P]),
     "l2j_forward": (C.c_int, [_P, C.c_int, C.c_int, _P, C.POINTER(C.c_int)]),
     "l2j_forward_stage": (C.c_int, [_P, C.c_int, C.c_int, _P, _P, _P, C.POINTER(C.c_int)]),
+    "l2j_sampler_seed": (C.c_int, [_P, C.c_int64]),
+    "l2j_sample": (C.c_int, [_P, C.c_float, C.c_float, C.POINTER(C.c_int)]),
     "l2j_device_buffers": (C.c_int, [_P, C.POINTER(_P), C.POINTER(_P)]),
     "l2j_forward_stage_async": (C.c_int, [_P, C.c_int, C.c_int]),
     "l2j_sync": (C.c_int, [_P]),

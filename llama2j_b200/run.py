@@ -1,8 +1,10 @@
 """Command-line run loop with the reference's flags, CUDA mode only.
 
 Mirror of Run.main (Run.java:528-707) and CommandLine (CommandLine.java:12-133) for the decode path:
-`--checkpoint X --mode CUDA --gpuMem a,b --temp 0.0 --steps N`, checkpoint resolved under `models/`,
-quant cache files beside it (TransformerWeights.java:191-232).  The tokenizer stays outside this
+`--checkpoint X --mode CUDA --gpuMem a,b --temp T --topp P --seed S --steps N`, checkpoint resolved under
+`models/`, quant cache files beside it (TransformerWeights.java:191-232).  With --temp > 0 the token is
+chosen on the device by the restatement of Sampler.java (same java.util.Random stream for the same seed),
+and only its id comes back.  The tokenizer stays outside this
 repository, so prompts are token ids (`--promptTokens 5,17,...`, an addition) and the output is ids.
 There is no CPU mode here: `--mode CPU` is refused.
 
@@ -57,8 +59,8 @@ def main(argv=None) -> int:
     args = parse_args(sys.argv[1:] if argv is None else argv)
     if args["--mode"].upper() != "CUDA":
         raise SystemExit("only --mode CUDA exists in this implementation (no CPU path)")
-    if float(args["--temp"]) != 0.0:
-        raise SystemExit("temperature sampling stays in the Java host; run with --temp 0.0")
+    temperature, topp = float(args["--temp"]), float(args["--topp"])
+    seed = int(args["--seed"]) if "--seed" in args else int(time.time())   # Run.java:542-545
     path = os.path.join(MODELS_DIRECTORY, args["--checkpoint"])
     cfg = mf.read_checkpoint_header(path)
     gpu_mem = parse_gpu_mem(args["--gpuMem"]) if args["--gpuMem"] else [180 * 1024 ** 3]
@@ -81,13 +83,22 @@ def main(argv=None) -> int:
     if steps <= 0 or steps > cfg.seq_len:
         steps = cfg.seq_len                                  # Run.java:599-602
     prompt = [int(t) for t in args["--promptTokens"].split(",") if t.strip()]
+    if temperature != 0.0:
+        stages[-1].sampler_seed(seed)                        # Run.java:620
     token, pos, start, out = 1, 0, 0.0, []
     while pos < steps:                                       # Run.java:623-685
         x = None
         for st in stages[:-1]:
             x = st.forward_stage(token, pos, x)
-        logits, _ = stages[-1].forward_stage(token, pos, x) if len(stages) > 1 else stages[0].forward(token, pos)
-        nxt = prompt[pos] if pos < len(prompt) else argmax(logits)
+        want = temperature == 0.0 and pos >= len(prompt)
+        logits, _ = (stages[-1].forward_stage(token, pos, x, want) if len(stages) > 1
+                     else stages[0].forward(token, pos, want))
+        if pos < len(prompt):
+            nxt = prompt[pos]                                # Run.java:635-637
+        elif temperature == 0.0:
+            nxt = argmax(logits)
+        else:
+            nxt = stages[-1].sample(temperature, topp)       # Run.java:643-665, on the device
         pos += 1
         if nxt == 1:
             break

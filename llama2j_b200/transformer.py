@@ -124,6 +124,16 @@ class Transformer:
         _lib.check(rc, self._ctx)
         return x_out
 
+    def sampler_seed(self, seed: int) -> None:
+        """new Sampler(seed, vocab) on the device (Sampler.java:24-31)."""
+        _lib.check(self._lib.l2j_sampler_seed(self._ctx, int(seed)), self._ctx)
+
+    def sample(self, temperature: float, topp: float) -> int:
+        """The token the reference's Sampler would choose from the logits of the last forward (Run.java:639-665)."""
+        tok = C.c_int(-1)
+        _lib.check(self._lib.l2j_sample(self._ctx, C.c_float(temperature), C.c_float(topp), C.byref(tok)), self._ctx)
+        return tok.value
+
     def generate_greedy(self, prompt, steps: int) -> np.ndarray:
         """Greedy run loop on the device; element p is the token chosen after position p."""
         prompt = np.ascontiguousarray(prompt, dtype=np.int32).reshape(-1)

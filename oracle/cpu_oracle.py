@@ -63,6 +63,11 @@ def load():
         "l2jo_model_destroy": (None, [P]),
         "l2jo_model_buffer": (P, [P, I]),
         "l2jo_model_forward": (None, [P, I, I, P]),
+        "l2jo_sampler_create": (P, [I64, I]),
+        "l2jo_sampler_destroy": (None, [P]),
+        "l2jo_sampler_next_int": (C.c_int32, [P]),
+        "l2jo_sampler_next_float": (C.c_float, [P]),
+        "l2jo_sampler_sample": (I, [P, P, I, C.c_float, C.c_float]),
         "l2jo_synth_normal": (None, [P, I64, C.c_uint64, C.c_uint32, I64, C.c_float]),
         "l2jo_synth_quant": (None, [P, I64, C.c_uint64, C.c_uint32, C.c_float]),
     }
@@ -207,6 +212,31 @@ class OracleModel:
             self.close()
         except Exception:
             pass
+
+
+class Sampler:
+    """Sampler.java + java.util.Random restated: temperature / top-p token choice from logits."""
+
+    def __init__(self, seed: int, vocab: int):
+        self.lib = load()
+        self.vocab = vocab
+        self.h = self.lib.l2jo_sampler_create(int(seed), int(vocab))
+
+    def next_int(self) -> int:
+        return int(self.lib.l2jo_sampler_next_int(self.h))
+
+    def next_float(self) -> float:
+        return float(self.lib.l2jo_sampler_next_float(self.h))
+
+    def sample(self, logits: np.ndarray, temperature: float, topp: float) -> int:
+        """Run.java:643-665: the logits are consumed (turned into probabilities in place)."""
+        a = np.ascontiguousarray(logits, dtype=np.float32)
+        return int(self.lib.l2jo_sampler_sample(self.h, a.ctypes.data, a.size, C.c_float(temperature), C.c_float(topp)))
+
+    def close(self):
+        if self.h:
+            self.lib.l2jo_sampler_destroy(self.h)
+            self.h = None
 
 
 def synthetic_tensors(cfg, seed: int = 0) -> dict:

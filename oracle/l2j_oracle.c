@@ -427,6 +427,164 @@ EXPORT int l2jo_argmax(const float *logits, int n)
 }
 
 /* ------------------------------------------------------------------------------------------
+ * Temperature / top-p sampling               (Sampler.java:20-120, Run.java:643-665, java.util.Random)
+ * ---------------------------------------------------------------------------------------- */
+
+/* java.util.Random: 48-bit linear congruential generator.  Random(seed) scrambles the seed with the
+ * multiplier; next(bits) advances and returns the top `bits` bits; nextFloat() = next(24) / 2^24. */
+typedef struct {
+    uint64_t rng;
+    int vocab;
+    float *prob;   /* ProbIndex[vocab]: Sampler keeps ONE array for its lifetime and sorts all of it in every */
+    int *index;    /* call, so entries beyond the current candidates are whatever earlier calls left there */
+    float *tprob;  /* merge-sort scratch */
+    int *tindex;
+} l2jo_sampler;
+
+#define L2JO_RNG_MULT 0x5DEECE66DULL
+#define L2JO_RNG_MASK ((1ULL << 48) - 1ULL)
+
+static int32_t rng_next(l2jo_sampler *s, int bits)
+{
+    s->rng = (s->rng * L2JO_RNG_MULT + 0xBULL) & L2JO_RNG_MASK;
+    return (int32_t)((int64_t)s->rng >> (48 - bits));
+}
+
+EXPORT l2jo_sampler *l2jo_sampler_create(int64_t seed, int vocab)
+{
+    l2jo_sampler *s = (l2jo_sampler *)calloc(1, sizeof(l2jo_sampler));
+    s->rng = ((uint64_t)seed ^ L2JO_RNG_MULT) & L2JO_RNG_MASK;
+    s->vocab = vocab;
+    s->prob = (float *)calloc((size_t)vocab, sizeof(float));    /* new ProbIndex(): prob 0, index 0 */
+    s->index = (int *)calloc((size_t)vocab, sizeof(int));
+    s->tprob = (float *)calloc((size_t)vocab, sizeof(float));
+    s->tindex = (int *)calloc((size_t)vocab, sizeof(int));
+    return s;
+}
+
+EXPORT void l2jo_sampler_destroy(l2jo_sampler *s)
+{
+    if (!s)
+        return;
+    free(s->prob);
+    free(s->index);
+    free(s->tprob);
+    free(s->tindex);
+    free(s);
+}
+
+EXPORT int32_t l2jo_sampler_next_int(l2jo_sampler *s)
+{
+    return rng_next(s, 32);
+}
+
+EXPORT float l2jo_sampler_next_float(l2jo_sampler *s)
+{
+    return (float)rng_next(s, 24) / (float)(1 << 24);
+}
+
+/* Arrays.sort(Object[]) with ProbIndex.compareTo (Sampler.java:60-72): descending by prob, stable (elements
+ * that compare equal keep their order).  Bottom-up merge sort. */
+static void sort_desc_stable(l2jo_sampler *s)
+{
+    const int n = s->vocab;
+    float *ap = s->prob, *bp = s->tprob;
+    int *ai = s->index, *bi = s->tindex;
+    for (int width = 1; width < n; width *= 2) {
+        for (int lo = 0; lo < n; lo += 2 * width) {
+            int mid = lo + width < n ? lo + width : n, hi = lo + 2 * width < n ? lo + 2 * width : n;
+            int i = lo, j = mid, k = lo;
+            while (i < mid && j < hi) {
+                if (ap[j] > ap[i]) {   /* the right element goes first only if it is strictly larger */
+                    bp[k] = ap[j];
+                    bi[k++] = ai[j++];
+                } else {
+                    bp[k] = ap[i];
+                    bi[k++] = ai[i++];
+                }
+            }
+            while (i < mid) {
+                bp[k] = ap[i];
+                bi[k++] = ai[i++];
+            }
+            while (j < hi) {
+                bp[k] = ap[j];
+                bi[k++] = ai[j++];
+            }
+        }
+        float *tp = ap; ap = bp; bp = tp;
+        int *ti = ai; ai = bi; bi = ti;
+    }
+    if (ap != s->prob) {
+        memcpy(s->prob, ap, (size_t)n * sizeof(float));
+        memcpy(s->index, ai, (size_t)n * sizeof(int));
+    }
+}
+
+/* Sampler.sample, Sampler.java:33-44 */
+static int sample_plain(l2jo_sampler *s, const float *p, int n)
+{
+    float r = l2jo_sampler_next_float(s);
+    float cdf = 0.0f;
+    for (int i = 0; i < n; i++) {
+        cdf = cdf + p[i];
+        if (r < cdf)
+            return i;
+    }
+    return n - 1;
+}
+
+/* Sampler.sample_topp, Sampler.java:76-120 */
+static int sample_topp(l2jo_sampler *s, const float *p, int n, float topp)
+{
+    int n0 = 0;
+    const float cutoff = (1.0f - topp) / (float)(n - 1);
+    for (int i = 0; i < n; i++) {
+        if (p[i] >= cutoff) {
+            s->index[n0] = i;
+            s->prob[n0] = p[i];
+            n0++;
+        }
+    }
+    sort_desc_stable(s);
+    float cumulative = 0.0f;
+    int last_idx = n0 - 1;
+    for (int i = 0; i < n0; i++) {
+        cumulative = cumulative + s->prob[i];
+        if (cumulative > topp) {
+            last_idx = i;
+            break;
+        }
+    }
+    float r = l2jo_sampler_next_float(s) * cumulative;
+    float cdf = 0.0f;
+    for (int i = 0; i <= last_idx; i++) {
+        cdf = cdf + s->prob[i];
+        if (r < cdf)
+            return s->index[i];
+    }
+    return s->index[last_idx];
+}
+
+/* The token choice of Run.java:639-665 for temperature > 0: logits are divided by the temperature and turned
+ * into probabilities IN PLACE (FindMax.call, ExpSumNormalize.call), then sampled plainly (topp > 0.999) or from
+ * the nucleus. */
+EXPORT int l2jo_sampler_sample(l2jo_sampler *s, float *logits, int n, float temperature, float topp)
+{
+    for (int q = 0; q < n; q++)
+        logits[q] = logits[q] / temperature;
+    float max_val = logits[0];
+    for (int i = 1; i < n; i++) {
+        if (logits[i] > max_val)
+            max_val = logits[i];
+    }
+    l2jo_exp_sum_normalize(logits, max_val, n);
+    if ((double)topp > 0.999)
+        return sample_plain(s, logits, n);
+    return sample_topp(s, logits, n, topp);
+}
+
+/* ------------------------------------------------------------------------------------------
  * The forward pass                                   (Run.transformerCPU, Run.java:62-169)
  * ---------------------------------------------------------------------------------------- */
 

@@ -135,3 +135,77 @@ def test_golden_regression(oracle):
     toks, lgs = oracle.greedy_run(m, g["prompt"], int(g["steps"]))
     assert np.array_equal(toks, g["tokens"])
     assert np.abs(lgs - g["logits"]).max() <= 1e-6
+
+
+# ---- Sampler.java + java.util.Random restated (token choice for --temp > 0) ------------------------------
+
+def test_java_random_known_answers(oracle):
+    """java.util.Random is specified bit for bit (48-bit LCG, seed scrambled with 0x5DEECE66D); these are the
+    values every JDK prints for new Random(42).nextInt() twice and new Random(0).nextInt()."""
+    s = oracle.Sampler(42, 4)
+    assert s.next_int() == -1170105035
+    assert s.next_int() == 234785527
+    s.close()
+    s = oracle.Sampler(0, 4)
+    assert s.next_int() == -1155484576
+    s.close()
+    s = oracle.Sampler(42, 4)
+    assert abs(s.next_float() - 0.7275637) < 5e-8     # new Random(42).nextFloat()
+    s.close()
+
+
+def _python_java_random(seed):
+    state = (seed ^ 0x5DEECE66D) & ((1 << 48) - 1)
+    while True:
+        state = (state * 0x5DEECE66D + 0xB) & ((1 << 48) - 1)
+        yield np.float32(state >> 24) / np.float32(1 << 24)
+
+
+def test_sampler_plain_follows_the_cumulative_walk(oracle):
+    """Sampler.sample (Sampler.java:33-44) from an independent restatement in numpy float32."""
+    rng = np.random.default_rng(0)
+    n = 500
+    s = oracle.Sampler(2024, n)
+    draws = _python_java_random(2024)
+    for _ in range(50):
+        logits = rng.standard_normal(n).astype(np.float32) * np.float32(3)
+        t = np.float32(0.8)
+        x = logits / t
+        e = np.exp((x - x.max()).astype(np.float64)).astype(np.float32)
+        tot = np.float32(0)
+        for v in e:
+            tot = np.float32(tot + v)
+        p = e / tot
+        r = next(draws)
+        cdf, want = np.float32(0), n - 1
+        for i, v in enumerate(p):
+            cdf = np.float32(cdf + v)
+            if r < cdf:
+                want = i
+                break
+        assert s.sample(logits.copy(), 0.8, 1.0) == want
+    s.close()
+
+
+def test_sampler_top_p_keeps_the_nucleus(oracle):
+    """Sampler.sample_topp (Sampler.java:76-120): only tokens of the smallest prefix (by descending probability)
+    whose mass exceeds topp can be chosen; a one-hot distribution always returns its token."""
+    n = 64
+    s = oracle.Sampler(5, n)
+    logits = np.full(n, -30.0, dtype=np.float32)
+    logits[17] = 10.0
+    for _ in range(20):
+        assert s.sample(logits.copy(), 1.0, 0.9) == 17
+    base = np.linspace(0.0, 6.0, n).astype(np.float32)
+    p = np.exp(base - base.max())
+    p /= p.sum()
+    order = np.argsort(-p, kind="stable")
+    k = int(np.searchsorted(np.cumsum(p[order]), 0.5)) + 1
+    allowed = set(int(i) for i in order[:k + 1])
+    seen = set()
+    for _ in range(300):
+        t = s.sample(base.copy(), 1.0, 0.5)
+        assert t in allowed
+        seen.add(t)
+    assert len(seen) > 1
+    s.close()
