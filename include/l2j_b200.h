@@ -82,6 +82,7 @@ enum l2j_tensor {
 #define L2J_F_NO_PDL 0x2      /* no programmatic dependent launch between consecutive kernels */
 #define L2J_F_SIMPLE 0x4      /* plain direct-load matvec kernels (cross-check path, slower) */
 #define L2J_F_STEP_KERNELS 0x8 /* one kernel per step of a layer (5 per layer) instead of one persistent kernel per token */
+#define L2J_F_NO_TENSOR_PREFILL 0x40  /* l2j_prefill pushes the prompt through the decode step (what shapes the tensor-core path does not take get anyway) */
 #define L2J_F_PERSISTENT 0x20  /* the persistent kernel wherever the shape allows it (default: only where it is the faster one) */
 #define L2J_F_TP_SPLIT_CLASSIFIER 0x10 /* l2j_create_tp: split the classifier's rows over the ranks too (they exchange their best candidates) */
 
@@ -149,6 +150,19 @@ L2J_API int l2j_forward_stage(l2j_ctx *ctx, int token, int pos, const float *x_i
 
 /* Device addresses of the stage's activation vector x (dim floats) and of its logits, for callers
  * that move them with their own device-to-device transport. */
+/* Batched prompt processing (no counterpart in the reference, whose run loop pushes every prompt token through
+ * the decode step, Run.java:623-637): positions pos0 .. pos0 + n - 1 with the input tokens given (tokens[i] is
+ * the token fed at position pos0 + i, i.e. BOS and then the prompt, Run.java:614,635-637), 64 positions per
+ * sweep over the weights, dot products on the tensor cores (u8 weights x s8 limbs of the 24-bit fixed-point
+ * activations, exact integer sums, group (min, scale) applied in FP32 as in the decode kernels).  Leaves the K/V
+ * cache as the decode steps would leave it to FP32 rounding of the row sums (prompt positions are not bitwise
+ * those of the decode kernels); produces no logits: continue with l2j_forward(token, pos0 + n).  Needs a
+ * context that holds every layer.  Shapes the tensor-core path does not take (rows that are not whole
+ * quantisation groups, head sizes other than 64 and 128) go through the decode step, as with
+ * L2J_F_NO_TENSOR_PREFILL; l2j_prefill_launches tells which ran (kernels launched by the batched path so far). */
+L2J_API int l2j_prefill(l2j_ctx *ctx, const int32_t *tokens, int n, int pos0);
+L2J_API uint64_t l2j_prefill_launches(l2j_ctx *ctx);
+
 /* Token selection on the device for --temp > 0 (Run.java:643-665 with Sampler.java:20-44,76-120): the logits
  * of the last forward are divided by the temperature, turned into probabilities in place exactly as the
  * reference does it (exp in double, one sequential float sum) and sampled plainly (topp > 0.999) or from the

@@ -13,7 +13,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_PATH = os.path.join(HERE, "libl2j_b200.so")
-SOURCES = ["l2j_kernels.cu", "l2j_fused.cu", "l2j_sampler.cu", "l2j_api.cu", "l2j_noalloc.cu"]
+SOURCES = ["l2j_kernels.cu", "l2j_fused.cu", "l2j_sampler.cu", "l2j_prefill.cu", "l2j_api.cu", "l2j_noalloc.cu"]
 HEADERS = ["l2j_device.cuh", "l2j_internal.h", os.path.join("..", "..", "include", "l2j_b200.h")]
 
 

@@ -57,6 +57,8 @@ struct l2j_ctx {
     // which parts have arrived, as sorted disjoint intervals (groups for the quantised tensors, floats for the
     // FP32 ones): a part sent twice must not stand in for one that never came
     std::vector<std::pair<int64_t, int64_t>> got[L2J_T_COUNT];
+    Prefill *prefill = nullptr;            // batched prompt path, built on first use where the shape allows it
+    bool prefill_tried = false;
     SamplerState *samp_state = nullptr;   // device sampler (l2j_sampler_seed / l2j_sample), allocated on first use
     float *samp_prob[2] = {nullptr, nullptr};
     int *samp_index[2] = {nullptr, nullptr};
@@ -1110,6 +1112,7 @@ extern "C" void l2j_destroy(l2j_ctx *c)
         cudaFreeHost(c->state_host);
     if (c->samp_host)
         cudaFreeHost(c->samp_host);
+    prefill_destroy(c->prefill);
     if (c->ev0)
         cudaEventDestroy(c->ev0);
     if (c->ev1)
@@ -1403,6 +1406,90 @@ extern "C" int l2j_forward(l2j_ctx *c, int token, int pos, float *logits, int *a
     if (!(c->is_first && c->is_last))
         return fail(c, L2J_E_STATE, "l2j_forward needs a context that holds every layer; use l2j_forward_stage");
     return l2j_forward_stage(c, token, pos, nullptr, nullptr, logits, argmax);
+}
+
+// The batched prompt path works on this context's own weights, caches and tables.
+static PrefillModel prefill_model(l2j_ctx *c)
+{
+    PrefillModel m{};
+    m.dim = c->dim;
+    m.hidden = c->hidden;
+    m.n_layers = c->nl;
+    m.n_heads = c->cfg.n_heads;
+    m.n_kv_heads = c->cfg.n_kv_heads;
+    m.head = c->head;
+    m.seq_len = c->cfg.seq_len;
+    m.vocab = c->cfg.vocab_size;
+    m.emb = c->emb;
+    m.status = reinterpret_cast<unsigned int *>(&c->state->status);
+    m.timeout_us = c->wait_limit_us;
+    auto payload = [](const MvSeg &s) { return s.payload + s.flat0; };
+    auto hdr = [](const MvSeg &s) { return s.hdr + s.flat0 / kGroup; };
+    for (int li = 0; li < c->nl; ++li) {
+        const LayerLaunch &L = c->layers[(size_t)li];
+        PrefillLayerDesc d{};
+        const MvSeg *segs[PF_W_COUNT] = {&L.qkv.seg[0], &L.qkv.seg[1], &L.qkv.seg[2], &L.wo.seg[0], &L.w13.seg[0], &L.w13.seg[1], &L.w2.seg[0]};
+        for (int w = 0; w < PF_W_COUNT; ++w) {
+            d.w[w] = payload(*segs[w]);
+            d.h[w] = hdr(*segs[w]);
+        }
+        d.rms_att = L.qkv.rms_w;
+        d.rms_ffn = L.w13.rms_w;
+        d.kc = L.qkv.k_cache;
+        d.vc = L.qkv.v_cache;
+        m.rope_cos = L.qkv.rope_cos;
+        m.rope_sin = L.qkv.rope_sin;
+        m.layers.push_back(d);
+    }
+    return m;
+}
+
+extern "C" int l2j_prefill(l2j_ctx *c, const int32_t *tokens, int n, int pos0)
+{
+    if (!c || (n > 0 && !tokens))
+        return L2J_E_INVALID;
+    {
+        std::lock_guard<std::mutex> lock(c->mu);
+        if (!c->finalized)
+            return fail(c, L2J_E_STATE, "prefill before finalize");
+        if (!(c->is_first && c->is_last) || c->tp_size > 1)
+            return fail(c, L2J_E_STATE, "l2j_prefill needs a context that holds every layer");
+        if (n < 0 || pos0 < 0 || (int64_t)pos0 + n > c->cfg.seq_len)
+            return fail(c, L2J_E_INVALID, "positions %d..%d outside the sequence length %d", pos0, pos0 + n - 1, c->cfg.seq_len);
+        for (int i = 0; i < n; ++i)
+            if (tokens[i] < 0 || tokens[i] >= c->cfg.vocab_size)
+                return fail(c, L2J_E_INVALID, "token %d outside the vocabulary", tokens[i]);
+        if (n == 0)
+            return L2J_OK;
+        CK(c, cudaSetDevice(c->device));
+        if (!c->prefill_tried) {
+            c->prefill_tried = true;
+            const PrefillModel m = prefill_model(c);
+            if (prefill_supported(m) && !(c->flags & L2J_F_NO_TENSOR_PREFILL))
+                CK(c, prefill_create(&c->prefill, m));
+        }
+        if (c->prefill) {
+            CK(c, prefill_run(c->prefill, c->stream, tokens, n, pos0));
+            CK(c, cudaMemcpyAsync(c->state_host, c->state, sizeof(SeqState), cudaMemcpyDeviceToHost, c->stream));
+            CK(c, cudaStreamSynchronize(c->stream));
+            return finish_status(c);
+        }
+    }
+    // shapes the tensor-core path does not take: the prompt goes through the decode step, as in the reference
+    for (int i = 0; i < n; ++i) {
+        const int rc = l2j_forward_stage_async(c, tokens[i], pos0 + i);
+        if (rc != L2J_OK)
+            return rc;
+    }
+    return l2j_sync(c);
+}
+
+extern "C" uint64_t l2j_prefill_launches(l2j_ctx *c)
+{
+    if (!c)
+        return 0;
+    std::lock_guard<std::mutex> lock(c->mu);
+    return prefill_launches(c->prefill);
 }
 
 extern "C" int l2j_sampler_seed(l2j_ctx *c, int64_t seed)

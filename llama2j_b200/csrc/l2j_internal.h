@@ -5,6 +5,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <vector>
+
 namespace l2j {
 
 constexpr int kGroup = 256;        // elements per quantisation group
@@ -243,6 +245,33 @@ inline int choose_nsplit(int sm_count, int n_heads, int seq_len)
         ns = 1;
     return ns;
 }
+
+// ---- batched prompt processing on the tensor cores (l2j_prefill.cu) ---------------------------------------------
+constexpr int kPrefillTokens = 64;   // positions that share one sweep over the weights
+enum PrefillWeight { PF_WQ = 0, PF_WK, PF_WV, PF_WO, PF_W1, PF_W3, PF_W2, PF_W_COUNT };
+
+struct PrefillLayerDesc {
+    const uint8_t *w[PF_W_COUNT];    // byte payload of the layer's matrix, row-major, rows of whole quantisation groups
+    const float2 *h[PF_W_COUNT];     // (min, scale) of group g of row r at [r * (k / 256) + g]
+    const float *rms_att, *rms_ffn;  // dequantised RMSNorm weights of the layer
+    float *kc, *vc;                  // the layer's K / V cache, [kv_head][seq][head]
+};
+
+struct PrefillModel {
+    int dim, hidden, n_layers, n_heads, n_kv_heads, head, seq_len, vocab;
+    const float *emb;
+    const float *rope_cos, *rope_sin;
+    unsigned int *status;            // device status word of the context
+    int timeout_us;
+    std::vector<PrefillLayerDesc> layers;
+};
+
+struct Prefill;
+bool prefill_supported(const PrefillModel &m);
+cudaError_t prefill_create(Prefill **out, const PrefillModel &m);
+cudaError_t prefill_run(Prefill *pf, cudaStream_t stream, const int *tokens_host, int n, int pos0);
+unsigned long long prefill_launches(const Prefill *pf);
+void prefill_destroy(Prefill *pf);
 
 // ---- temperature / top-p sampler on the device (l2j_sampler.cu) ----------------------------------
 struct SamplerState {

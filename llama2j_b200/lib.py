@@ -14,6 +14,7 @@ from . import build as _build
 E_INVALID, E_CUDA, E_STATE, E_DEVICE, E_NOMEM = -1, -2, -3, -4, -5
 DS_WAIT_TIMEOUT, DS_BAD_POS, DS_BAD_TOKEN, DS_BAD_LINK = 0x1, 0x2, 0x4, 0x8
 F_NO_GRAPH, F_NO_PDL, F_SIMPLE, F_STEP_KERNELS, F_TP_SPLIT_CLASSIFIER, F_PERSISTENT = 0x1, 0x2, 0x4, 0x8, 0x10, 0x20
+F_NO_TENSOR_PREFILL = 0x40
 QUANT_GROUP, QUANT_GROUP_BYTES = 256, 264
 
 (T_TOKEN_EMBEDDING, T_RMS_ATT, T_WQ, T_WK, T_WV, T_WO, T_RMS_FFN, T_W1, T_W2, T_W3, T_RMS_FINAL, T_WCLS) = range(12)
@@ -55,6 +56,8 @@ _SIGNATURES = {
     "l2j_finalize": (C.c_int, [_P]),
     "l2j_forward": (C.c_int, [_P, C.c_int, C.c_int, _P, C.POINTER(C.c_int)]),
     "l2j_forward_stage": (C.c_int, [_P, C.c_int, C.c_int, _P, _P, _P, C.POINTER(C.c_int)]),
+    "l2j_prefill": (C.c_int, [_P, C.POINTER(C.c_int32), C.c_int, C.c_int]),
+    "l2j_prefill_launches": (C.c_uint64, [_P]),
     "l2j_sampler_seed": (C.c_int, [_P, C.c_int64]),
     "l2j_sample": (C.c_int, [_P, C.c_float, C.c_float, C.POINTER(C.c_int)]),
     "l2j_device_buffers": (C.c_int, [_P, C.POINTER(_P), C.POINTER(_P)]),

@@ -124,6 +124,16 @@ class Transformer:
         _lib.check(rc, self._ctx)
         return x_out
 
+    def prefill(self, tokens, pos0: int = 0) -> None:
+        """Positions pos0 .. pos0 + len(tokens) - 1 in batches of 64 on the tensor cores; tokens[i] is the input
+        token of position pos0 + i (BOS, then the prompt: Run.java:614,635-637).  No logits."""
+        t = np.ascontiguousarray(tokens, dtype=np.int32).reshape(-1)
+        ptr = t.ctypes.data_as(C.POINTER(C.c_int32)) if t.size else None
+        _lib.check(self._lib.l2j_prefill(self._ctx, ptr, int(t.size), int(pos0)), self._ctx)
+
+    def prefill_launches(self) -> int:
+        return int(self._lib.l2j_prefill_launches(self._ctx))
+
     def sampler_seed(self, seed: int) -> None:
         """new Sampler(seed, vocab) on the device (Sampler.java:24-31)."""
         _lib.check(self._lib.l2j_sampler_seed(self._ctx, int(seed)), self._ctx)
