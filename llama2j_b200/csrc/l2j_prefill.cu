@@ -26,6 +26,7 @@
 
 #include <cfloat>
 #include <cmath>
+#include <cstdlib>
 #include <mutex>
 #include <vector>
 
@@ -38,11 +39,15 @@ namespace {
 constexpr int kT = kPrefillTokens;          // tokens per chunk
 constexpr int kN = 3 * kT;                  // columns of the B operand: three limbs per token
 constexpr int kTileM = 128;                 // weight rows per tile
-constexpr int kGemmThreads = 256;
-constexpr int kStages = 2;                  // one stage = one quantisation group (K = 256) of A and B
-constexpr int kABytes = kTileM * 128;       // one 128-byte-wide half of the A stage
+constexpr int kGemmThreads = 384;          // producer warp, issue warp, two spare, eight epilogue warps
+constexpr int kEpiWarps = 8;                // warps 4..11: quarter of tensor memory = warp % 4, half of the tokens = (warp - 4) / 4
+constexpr int kTH = kT / 2;                 // tokens per epilogue thread
+constexpr int kStages = 4;                  // ring depth; one stage = half a quantisation group (K = 128) of A and B
+constexpr int kABytes = kTileM * 128;       // the A part of a stage: 128 rows of 128 bytes
 constexpr int kBBytes = kN * 128;
-constexpr int kStageBytes = 2 * kABytes + 2 * kBBytes;
+constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kRingBytes = kStages * kStageBytes;
+constexpr int kMaxParts = 8;                // parts a row sum (or a query's keys) may be dealt into
 constexpr int kAccCols = 256;               // column distance of the two accumulators in tensor memory
 constexpr int kTmemCols = 512;
 
@@ -174,9 +179,12 @@ struct PfGemmParams {
     int nseg;
     int groups;          // K / 256
     const float2 *ux;    // [groups][64]: (value of one unit of the integer sums, sum of the fixed-point activations)
-    float *out;          // [64][ldc]
+    const float *ssq;    // [nssq][64] partial sums of squares of the input rows (RMSNorm in front), or nullptr
+    int nssq;
+    int n;               // elements per input row
+    float *out;          // [ksplit][64][ldc]
     int ldc;
-    int accumulate;      // 1: out += result (the residual stream)
+    int ksplit;          // the groups of a row are dealt to this many blocks; part z goes to out + z * 64 * ldc
     int nvalid;          // tokens of the chunk that exist
     int timeout_us;
     unsigned int *status;
@@ -190,11 +198,12 @@ pf_gemm_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant
     __shared__ __align__(8) unsigned long long s_bar[2 * kStages + 4 + 1];
     __shared__ uint32_t s_tmem;
     __shared__ int s_give_up;
+    __shared__ float s_ss[kT];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t base = (smem_u32(pf_smem_raw) + 1023u) & ~1023u;            // swizzled tiles want 1024-byte alignment
     unsigned char *gen = pf_smem_raw + (base - smem_u32(pf_smem_raw));
-    float2 *s_ux = reinterpret_cast<float2 *>(gen + kStages * kStageBytes);
+    float2 *s_ux = reinterpret_cast<float2 *>(gen + kRingBytes);
     const uint32_t bar_full = smem_u32(&s_bar[0]), bar_empty = smem_u32(&s_bar[kStages]);
     const uint32_t bar_acc_full = smem_u32(&s_bar[2 * kStages]), bar_acc_empty = smem_u32(&s_bar[2 * kStages + 2]);
     const uint32_t bar_fin = smem_u32(&s_bar[2 * kStages + 4]);
@@ -203,7 +212,9 @@ pf_gemm_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant
     int ntiles = 0;
     for (int s = 0; s < p.nseg; ++s)
         ntiles += p.seg[s].rows / kTileM;
+    ntiles *= p.ksplit;                       // work items: (tile, part of the groups)
     const int G = p.groups;
+    const int gper = (G + p.ksplit - 1) / p.ksplit;
 
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -212,7 +223,7 @@ pf_gemm_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(bar_acc_full + 8 * b, 1);
-            mbar_init(bar_acc_empty + 8 * b, 4);
+            mbar_init(bar_acc_empty + 8 * b, kEpiWarps);
         }
         mbar_init(bar_fin, 1);
         mbar_fence_init();
@@ -222,8 +233,24 @@ pf_gemm_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant
         tmem_alloc(smem_u32(&s_tmem), kTmemCols);
         tmem_relinquish();
     }
-    for (int i = tid; i < G * kT; i += kGemmThreads)
-        s_ux[i] = p.ux[i];
+    if (tid < kT) {
+        // RootMeanSquare.java:25-35: the scalar of the RMSNorm in front multiplies every unit of the token
+        float ss = 1.0f;
+        if (p.ssq != nullptr) {
+            float tot = 0.f;
+            for (int y = 0; y < p.nssq; ++y)
+                tot += p.ssq[y * kT + tid];
+            tot = __fdiv_rn(tot, (float)p.n);
+            tot = __fadd_rn(tot, 1e-5f);
+            ss = __fdiv_rn(1.0f, __fsqrt_rn(tot));
+        }
+        s_ss[tid] = ss;
+    }
+    __syncthreads();
+    for (int i = tid; i < G * kT; i += kGemmThreads) {
+        const float2 u = p.ux[i];
+        s_ux[i] = make_float2(u.x * s_ss[i & (kT - 1)], u.y);
+    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -231,28 +258,27 @@ pf_gemm_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant
     volatile int *give_up = &s_give_up;
 
     if (warp == 0) {
-        // ---- producer: one lane feeds the stages
+        // ---- producer: one lane feeds the ring
         if (lane == 0) {
             const uint64_t pol = policy_evict_first();
             long it = 0;
             for (int tile = blockIdx.x; tile < ntiles && !*give_up; tile += gridDim.x) {
-                int sg = 0, m0 = tile * kTileM;
+                int sg = 0, m0 = (tile / p.ksplit) * kTileM;
                 while (m0 >= p.seg[sg].rows) {
                     m0 -= p.seg[sg].rows;
                     ++sg;
                 }
                 const CUtensorMap *ma = sg == 0 ? &map_a0 : (sg == 1 ? &map_a1 : &map_a2);
-                for (int g = 0; g < G; ++g, ++it) {
+                const int g0 = (tile % p.ksplit) * gper, g1 = min(G, g0 + gper);
+                for (int hs = 2 * g0; hs < 2 * g1; ++hs, ++it) {   // half groups
                     const int s = (int)(it % kStages);
                     const uint32_t ph = (uint32_t)((it / kStages) & 1);
                     if (!pf_wait(bar_empty + 8 * s, ph ^ 1u, give_up, limit))
                         break;
                     const uint32_t st = base + (uint32_t)s * kStageBytes;
                     mbar_arrive_expect_tx(bar_full + 8 * s, kStageBytes);
-                    tma_load_2d_hint(st, ma, g * 256, m0, bar_full + 8 * s, pol);
-                    tma_load_2d_hint(st + kABytes, ma, g * 256 + 128, m0, bar_full + 8 * s, pol);
-                    tma_load_2d(st + 2 * kABytes, &map_b, g * 256, 0, bar_full + 8 * s);
-                    tma_load_2d(st + 2 * kABytes + kBBytes, &map_b, g * 256 + 128, 0, bar_full + 8 * s);
+                    tma_load_2d_hint(st, ma, hs * 128, m0, bar_full + 8 * s, pol);
+                    tma_load_2d(st + kABytes, &map_b, hs * 128, 0, bar_full + 8 * s);
                 }
             }
             if (*give_up) {
@@ -271,24 +297,32 @@ pf_gemm_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant
             long it = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
-                for (int g = 0; g < G; ++g, ++it) {
-                    const int s = (int)(it % kStages), b = (int)(it & 1);
-                    const uint32_t ph = (uint32_t)((it / kStages) & 1), pha = (uint32_t)((it >> 1) & 1);
-                    if (!pf_wait(bar_acc_empty + 8 * b, pha ^ 1u, give_up, limit) || !pf_wait(bar_full + 8 * s, ph, give_up, limit)) {
+                const int g0 = (tile % p.ksplit) * gper, g1 = min(G, g0 + gper);
+                for (int g = g0; g < g1 && ok; ++g, ++it) {
+                    const int b = (int)(it & 1);
+                    const uint32_t pha = (uint32_t)((it >> 1) & 1);
+                    if (!pf_wait(bar_acc_empty + 8 * b, pha ^ 1u, give_up, limit)) {
                         ok = false;
                         break;
                     }
-                    tc_fence_after();
-                    const uint32_t st = base + (uint32_t)s * kStageBytes;
                     const uint32_t d = tmem + (uint32_t)b * kAccCols;
+                    for (int half = 0; half < 2; ++half) {
+                        const long hit = 2 * it + half;
+                        const int s = (int)(hit % kStages);
+                        if (!pf_wait(bar_full + 8 * s, (uint32_t)((hit / kStages) & 1), give_up, limit)) {
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after();
+                        const uint32_t ta = base + (uint32_t)s * kStageBytes, tb = ta + kABytes;
 #pragma unroll
-                    for (int kk = 0; kk < 8; ++kk) {
-                        const uint32_t a_addr = st + (uint32_t)(kk >> 2) * kABytes + (uint32_t)(kk & 3) * 32u;
-                        const uint32_t b_addr = st + 2 * kABytes + (uint32_t)(kk >> 2) * kBBytes + (uint32_t)(kk & 3) * 32u;
-                        umma_i8(d, smem_desc_sw128(a_addr), smem_desc_sw128(b_addr), kIdesc, kk > 0 ? 1u : 0u);
+                        for (int kk = 0; kk < 4; ++kk)
+                            umma_i8(d, smem_desc_sw128(ta + (uint32_t)kk * 32u), smem_desc_sw128(tb + (uint32_t)kk * 32u), kIdesc,
+                                    (half | kk) ? 1u : 0u);
+                        umma_commit(bar_empty + 8 * s);        // the stage may be refilled when these have read it
                     }
-                    umma_commit(bar_empty + 8 * s);        // the stage may be refilled when these have read it
-                    umma_commit(bar_acc_full + 8 * b);     // and the group's sums are complete
+                    if (ok)
+                        umma_commit(bar_acc_full + 8 * b);     // the group's sums are complete
                 }
             }
             if (!ok) {
@@ -299,68 +333,64 @@ pf_gemm_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant
             }
         }
     } else if (warp >= 4) {
-        // ---- epilogue: thread = one row of the tile, 64 token sums in registers
+        // ---- epilogue: thread = one row of the tile and half of the tokens, 32 sums in registers
         const int q = warp & 3;                               // the quarter of tensor memory this warp may read
-        const uint32_t trow = tmem + ((uint32_t)(q * 32) << 16);
+        const int th = (warp - 4) >> 2;                       // which half of the tokens
+        const uint32_t trow = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(th * kTH);
         long it = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
-            int sg = 0, m0 = tile * kTileM;
+            int sg = 0, m0 = (tile / p.ksplit) * kTileM;
             while (m0 >= p.seg[sg].rows) {
                 m0 -= p.seg[sg].rows;
                 ++sg;
             }
+            const int z = tile % p.ksplit, g0 = z * gper, g1 = min(G, g0 + gper);
             const int row = m0 + q * 32 + lane;
             const float2 *hrow = p.seg[sg].hdr + (size_t)row * G;
-            float acc[kT];
+            float acc[kTH];
 #pragma unroll
-            for (int t = 0; t < kT; ++t)
+            for (int t = 0; t < kTH; ++t)
                 acc[t] = 0.f;
-            float2 ms = hrow[0];
-            for (int g = 0; g < G; ++g, ++it) {
+            float2 ms = hrow[g0 < G ? g0 : 0];
+            for (int g = g0; g < g1; ++g, ++it) {
                 const int b = (int)(it & 1);
                 const uint32_t pha = (uint32_t)((it >> 1) & 1);
-                const float2 ms_next = hrow[g + 1 < G ? g + 1 : g];
+                const float2 ms_next = hrow[g + 1 < g1 ? g + 1 : g];
                 if (!pf_wait(bar_acc_full + 8 * b, pha, give_up, limit)) {
                     ok = false;
                     break;
                 }
                 tc_fence_after();
                 const uint32_t tacc = trow + (uint32_t)b * kAccCols;
-                const float2 *ux = s_ux + g * kT;
+                // all of the thread's sums of the group in one round trip, then the accumulator is free again
+                uint32_t s0[kTH], s1[kTH], s2[kTH];
 #pragma unroll
-                for (int t0 = 0; t0 < kT; t0 += 16) {
-                    uint32_t s0[16], s1[16], s2[16];
-                    tmem_ld16(tacc + t0, s0);
-                    tmem_ld16(tacc + kT + t0, s1);
-                    tmem_ld16(tacc + 2 * kT + t0, s2);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const float dsum = fmaf((float)(int)s2[j], 65536.0f, fmaf((float)(int)s1[j], 256.0f, (float)(int)s0[j]));
-                        const float2 u = ux[t0 + j];
-                        acc[t0 + j] += fmaf(ms.y, dsum, ms.x * u.y) * u.x;
-                    }
+                for (int c = 0; c < kTH; c += 16) {
+                    tmem_ld16(tacc + c, *reinterpret_cast<uint32_t(*)[16]>(&s0[c]));
+                    tmem_ld16(tacc + kT + c, *reinterpret_cast<uint32_t(*)[16]>(&s1[c]));
+                    tmem_ld16(tacc + 2 * kT + c, *reinterpret_cast<uint32_t(*)[16]>(&s2[c]));
                 }
+                tmem_ld_wait();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0)
                     mbar_arrive(bar_acc_empty + 8 * b);
+                const float2 *ux = s_ux + g * kT + th * kTH;
+#pragma unroll
+                for (int j = 0; j < kTH; ++j) {
+                    const float dsum = fmaf((float)(int)s2[j], 65536.0f, fmaf((float)(int)s1[j], 256.0f, (float)(int)s0[j]));
+                    const float2 u = ux[j];
+                    acc[j] += fmaf(ms.y, dsum, ms.x * u.y) * u.x;
+                }
                 ms = ms_next;
             }
             if (ok) {
-                float *o = p.out + p.seg[sg].col0 + row;
-                if (p.accumulate) {
+                float *o = p.out + (size_t)z * kT * p.ldc + p.seg[sg].col0 + row;
 #pragma unroll
-                    for (int t = 0; t < kT; ++t)
-                        if (t < p.nvalid)
-                            o[(size_t)t * p.ldc] = __fadd_rn(o[(size_t)t * p.ldc], acc[t]);
-                } else {
-#pragma unroll
-                    for (int t = 0; t < kT; ++t)
-                        if (t < p.nvalid)
-                            o[(size_t)t * p.ldc] = acc[t];
-                }
+                for (int t = 0; t < kTH; ++t)
+                    if (th * kTH + t < p.nvalid)
+                        o[(size_t)(th * kTH + t) * p.ldc] = acc[t];
             }
         }
     }
@@ -377,36 +407,66 @@ pf_gemm_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant
 // activations -> limbs
 // ---------------------------------------------------------------------------------------------------------------
 
-enum { PF_IN_NORM = 0, PF_IN_PLAIN = 1, PF_IN_SWIGLU = 2 };
+enum { PF_IN_NORM = 0, PF_IN_ATTN = 1, PF_IN_SWIGLU = 2 };
 
 struct PfLimbParams {
-    const float *a;        // [64][lda]: x (NORM), the vector itself (PLAIN), h1 (SWIGLU)
+    float *a;              // [64][lda]: x (NORM, updated with the parts), h1 (SWIGLU); ATTN: unused
     const float *b;        // NORM: RMSNorm weights [n]; SWIGLU: h3 [64][lda]
+    const float *parts;    // NORM: [nparts][64][lda] partial row sums of the matrix in front, added to x in this order;
+                           // ATTN: [nparts][64][heads][head + 2] partial attention outputs (o, m, l) of the key ranges
+    int nparts;
+    int head;              // ATTN: head size
     int lda;
     int n;                 // elements per token (multiple of 256)
     int nvalid;
     int8_t *limbs;         // [3 * 64][n]
-    float2 *ux;            // [n / 256][64]
+    float2 *ux;            // [n / 256][64]: (value of one fixed-point unit, sum of the fixed-point activations)
+    float *ssq;            // NORM: [gridDim.y][64] partial sums of squares of the rows
 };
 
+constexpr int kLimbWarps = 4, kLimbThreads = 32 * kLimbWarps;
+
 template <int MODE>
-__global__ void __launch_bounds__(256) pf_limbs_kernel(const PfLimbParams p)
+__global__ void __launch_bounds__(kLimbThreads) pf_limbs_kernel(const PfLimbParams p)
 {
-    __shared__ float s_inv[64];     // value of one fixed-point unit per group (up to 16384 elements per row)
-    __shared__ float s_xs[64];
-    __shared__ float s_ssq[8];
+    // one quantisation group per warp, kLimbWarps groups per block: nothing loops, every load of the block is in
+    // flight at once
+    __shared__ float s_ssq[kLimbWarps];
     const int t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = p.n >> 8;
     const bool live = t < p.nvalid;
     float ssq = 0.f;
-    for (int gi = warp; gi < G; gi += 8) {
+    const int gi = blockIdx.y * kLimbWarps + warp;
+    if (gi < G) {
         float v[8];
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             const int e = gi * 256 + h * 128 + lane * 4;
             float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (live)
+            if (live && MODE != PF_IN_ATTN)
                 x = *reinterpret_cast<const float4 *>(p.a + (size_t)t * p.lda + e);
+            if (MODE == PF_IN_ATTN && live) {
+                // the key ranges' partial results of this element's head, merged in a fixed order
+                const int hd = e / p.head, d = e - hd * p.head, heads = p.n / p.head, rec = p.head + 2;
+                float mx = -FLT_MAX;
+                for (int z = 0; z < p.nparts; ++z)
+                    mx = fmaxf(mx, p.parts[((size_t)(z * kT + t) * heads + hd) * rec + p.head]);
+                float lsum = 0.f;
+                for (int z = 0; z < p.nparts; ++z) {
+                    const float *r = p.parts + ((size_t)(z * kT + t) * heads + hd) * rec;
+                    const float w = expf(r[p.head] - mx);
+                    lsum = fmaf(w, r[p.head + 1], lsum);
+                    x.x = fmaf(w, r[d], x.x); x.y = fmaf(w, r[d + 1], x.y); x.z = fmaf(w, r[d + 2], x.z); x.w = fmaf(w, r[d + 3], x.w);
+                }
+                x.x = __fdiv_rn(x.x, lsum); x.y = __fdiv_rn(x.y, lsum); x.z = __fdiv_rn(x.z, lsum); x.w = __fdiv_rn(x.w, lsum);
+            }
+            if (MODE == PF_IN_NORM && live && p.nparts > 0) {
+                for (int z = 0; z < p.nparts; ++z) {
+                    const float4 d4 = *reinterpret_cast<const float4 *>(p.parts + ((size_t)z * kT + t) * p.lda + e);
+                    x.x = __fadd_rn(x.x, d4.x); x.y = __fadd_rn(x.y, d4.y); x.z = __fadd_rn(x.z, d4.z); x.w = __fadd_rn(x.w, d4.w);
+                }
+                *reinterpret_cast<float4 *>(p.a + (size_t)t * p.lda + e) = x;   // the residual stream after the matrix in front
+            }
             if (MODE == PF_IN_NORM) {
                 const float4 w = *reinterpret_cast<const float4 *>(p.b + e);
                 ssq = fmaf(x.x, x.x, ssq); ssq = fmaf(x.y, x.y, ssq); ssq = fmaf(x.z, x.z, ssq); ssq = fmaf(x.w, x.w, ssq);
@@ -458,27 +518,24 @@ __global__ void __launch_bounds__(256) pf_limbs_kernel(const PfLimbParams p)
         s1 = __reduce_add_sync(0xffffffffu, s1);
         s2 = __reduce_add_sync(0xffffffffu, s2);
         if (lane == 0) {
-            s_inv[gi] = __int_as_float((127 + ex - 22) << 23);
-            s_xs[gi] = fmaf((float)s2, 65536.0f, fmaf((float)s1, 256.0f, (float)s0));
+            const float inv = __int_as_float((127 + ex - 22) << 23);   // value of one fixed-point unit
+            const float xs = fmaf((float)s2, 65536.0f, fmaf((float)s1, 256.0f, (float)s0));
+            p.ux[(size_t)gi * kT + t] = live ? make_float2(inv, xs) : make_float2(0.f, 0.f);
         }
     }
     if (MODE == PF_IN_NORM) {
+        // the row's sum of squares: per block here, summed in block order by the matrix kernel that needs it
         ssq = warp_sum(ssq);
         if (lane == 0)
             s_ssq[warp] = ssq;
+        __syncthreads();
+        if (tid == 0) {
+            float tot = 0.f;
+            for (int w = 0; w < kLimbWarps; ++w)
+                tot += s_ssq[w];
+            p.ssq[(size_t)blockIdx.y * kT + t] = tot;
+        }
     }
-    __syncthreads();
-    float ss = 1.0f;
-    if (MODE == PF_IN_NORM) {
-        float tot = 0.f;
-        for (int w = 0; w < 8; ++w)
-            tot += s_ssq[w];
-        tot = __fdiv_rn(tot, (float)p.n);
-        tot = __fadd_rn(tot, 1e-5f);
-        ss = __fdiv_rn(1.0f, __fsqrt_rn(tot));   // RootMeanSquare.java:25-35
-    }
-    for (int gi = tid; gi < G; gi += 256)
-        p.ux[(size_t)gi * kT + t] = live ? make_float2(s_inv[gi] * ss, s_xs[gi]) : make_float2(0.f, 0.f);
 }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -512,7 +569,8 @@ __global__ void pf_rope_kv_kernel(const PfRopeParams p)
     const int pos = p.pos0 + t, half = p.head >> 1;
     const float *row = p.qkv + (size_t)t * (p.dim + 2 * p.kv_dim);
     const float *cs = p.rope_cos + (size_t)pos * half, *sn = p.rope_sin + (size_t)pos * half;
-    for (int i = threadIdx.x; i < (p.dim + 2 * p.kv_dim) / 2; i += blockDim.x) {
+    const int i = blockIdx.y * blockDim.x + threadIdx.x;      // one pair per thread
+    if (i < (p.dim + 2 * p.kv_dim) / 2) {
         const int e = 2 * i;
         const float v0 = row[e], v1 = row[e + 1];
         if (e < p.dim + p.kv_dim) {
@@ -545,34 +603,53 @@ __global__ void pf_rope_kv_kernel(const PfRopeParams p)
 struct PfAttnParams {
     const float *q;        // [64][dim] after RoPE
     const float *k_cache, *v_cache;
-    float *out;            // [64][dim]
-    int dim, head, kv_mul, seq_len, pos0, nvalid;
+    float *parts;          // [nsplit][64][heads][head + 2]: unnormalised output, running maximum, sum of the key range
+    int dim, head, kv_mul, seq_len, pos0, nvalid, nsplit;
 };
 
-constexpr int kAttnQ = 16;       // queries per block
+constexpr int kAttnQ = 32;       // queries per block
 constexpr int kAttnKeys = 64;    // keys per tile
 constexpr int kAttnThreads = 128;
 
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src)
+{
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+
+__device__ __forceinline__ void cp_async_wait_all()
+{
+    asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
+}
+
+// Block = (head, 32 queries, one range of key tiles); thread = 4 queries x 4 keys of a tile for the scores and
+// 4 queries x HEAD / 16 elements for the output.  The K and V rows of a tile come into shared memory with
+// asynchronous 16-byte copies (no registers, no load-to-store dependency per row); two blocks share an SM.
 template <int HEAD>
-__global__ void __launch_bounds__(kAttnThreads) pf_attention_kernel(const PfAttnParams p)
+__global__ void __launch_bounds__(kAttnThreads, 2) pf_attention_kernel(const PfAttnParams p)
 {
     constexpr int LD = HEAD + 4;             // row pitch in floats: consecutive rows start 4 banks apart
-    constexpr int DV = HEAD / 16;            // output elements per thread and query
+    constexpr int NV4 = HEAD / 64;           // float4 chunks of the output per thread and query
     extern __shared__ __align__(16) float pf_att_smem[];
     float *sK = pf_att_smem;                 // [64][LD]
     float *sV = sK + kAttnKeys * LD;
-    float *sQ = sV + kAttnKeys * LD;         // [16][LD]
-    float *sP = sQ + kAttnQ * LD;            // [16][64]
+    float *sQ = sV + kAttnKeys * LD;         // [32][LD]
+    float *sP = sQ + kAttnQ * LD;            // [32][64]
 
-    const int h = blockIdx.x, q0 = blockIdx.y * kAttnQ, tid = threadIdx.x;
+    const int h = blockIdx.x, q0 = blockIdx.y * kAttnQ, z = blockIdx.z, tid = threadIdx.x;
     if (q0 >= p.nvalid)
         return;
     const int kvh = h / p.kv_mul;
     const float *kbase = p.k_cache + (size_t)kvh * p.seq_len * HEAD;
     const float *vbase = p.v_cache + (size_t)kvh * p.seq_len * HEAD;
-    const int qa = (tid >> 4) * 2;           // this thread's two queries
-    const int kb = tid & 15;                 // its keys are kb, kb + 16, kb + 32, kb + 48 of a tile; its outputs DV from kb * DV
+    const int qa = (tid >> 4) * 4;           // this thread's four queries
+    const int kb = tid & 15;                 // its keys are kb, kb + 16, kb + 32, kb + 48 of a tile
     const float root = sqrtf((float)HEAD);   // AttentionLoop: score / sqrt(head_size)
+
+    const int last_q = min(q0 + kAttnQ, p.nvalid) - 1;
+    const int nkeys = p.pos0 + last_q + 1;                      // keys 0 .. position of the block's last query
+    const int tiles = (nkeys + kAttnKeys - 1) / kAttnKeys;
+    const int tper = (tiles + p.nsplit - 1) / p.nsplit;
+    const int t_lo = z * tper, t_hi = min(tiles, t_lo + tper);
 
     for (int i = tid; i < kAttnQ * (HEAD / 4); i += kAttnThreads) {
         const int r = i / (HEAD / 4), c = i % (HEAD / 4);
@@ -581,47 +658,50 @@ __global__ void __launch_bounds__(kAttnThreads) pf_attention_kernel(const PfAttn
             v = *reinterpret_cast<const float4 *>(p.q + (size_t)(q0 + r) * p.dim + h * HEAD + c * 4);
         *reinterpret_cast<float4 *>(sQ + r * LD + c * 4) = v;
     }
-    float m[2] = {-FLT_MAX, -FLT_MAX}, l[2] = {0.f, 0.f};
-    float o[2][DV];
+    float m[4], l[4];
+    float4 o[4][NV4];
 #pragma unroll
-    for (int i = 0; i < 2; ++i)
+    for (int i = 0; i < 4; ++i) {
+        m[i] = -FLT_MAX;
+        l[i] = 0.f;
 #pragma unroll
-        for (int d = 0; d < DV; ++d)
-            o[i][d] = 0.f;
+        for (int c = 0; c < NV4; ++c)
+            o[i][c] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
 
-    const int last_q = min(q0 + kAttnQ, p.nvalid) - 1;
-    const int nkeys = p.pos0 + last_q + 1;                      // keys 0 .. position of the block's last query
-    for (int k0 = 0; k0 < nkeys; k0 += kAttnKeys) {
+    for (int tile = t_lo; tile < t_hi; ++tile) {
+        const int k0 = tile * kAttnKeys;
         __syncthreads();
         for (int i = tid; i < kAttnKeys * (HEAD / 4); i += kAttnThreads) {
             const int r = i / (HEAD / 4), c = i % (HEAD / 4);
-            float4 kv = make_float4(0.f, 0.f, 0.f, 0.f), vv = kv;
             if (k0 + r < nkeys) {
-                kv = *reinterpret_cast<const float4 *>(kbase + (size_t)(k0 + r) * HEAD + c * 4);
-                vv = *reinterpret_cast<const float4 *>(vbase + (size_t)(k0 + r) * HEAD + c * 4);
+                cp_async16(smem_u32(sK + r * LD + c * 4), kbase + (size_t)(k0 + r) * HEAD + c * 4);
+                cp_async16(smem_u32(sV + r * LD + c * 4), vbase + (size_t)(k0 + r) * HEAD + c * 4);
+            } else {
+                *reinterpret_cast<float4 *>(sK + r * LD + c * 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+                *reinterpret_cast<float4 *>(sV + r * LD + c * 4) = make_float4(0.f, 0.f, 0.f, 0.f);
             }
-            *reinterpret_cast<float4 *>(sK + r * LD + c * 4) = kv;
-            *reinterpret_cast<float4 *>(sV + r * LD + c * 4) = vv;
         }
+        cp_async_wait_all();
         __syncthreads();
-        // scores of 2 queries x 4 keys
-        float s[2][4];
+        // scores of 4 queries x 4 keys
+        float s[4][4];
 #pragma unroll
-        for (int i = 0; i < 2; ++i)
+        for (int i = 0; i < 4; ++i)
 #pragma unroll
             for (int j = 0; j < 4; ++j)
                 s[i][j] = 0.f;
-#pragma unroll 4
+#pragma unroll 2
         for (int d = 0; d < HEAD; d += 4) {
-            float4 qv[2], kv[4];
+            float4 qv[4], kv[4];
 #pragma unroll
-            for (int i = 0; i < 2; ++i)
+            for (int i = 0; i < 4; ++i)
                 qv[i] = *reinterpret_cast<const float4 *>(sQ + (qa + i) * LD + d);
 #pragma unroll
             for (int j = 0; j < 4; ++j)
                 kv[j] = *reinterpret_cast<const float4 *>(sK + (kb + 16 * j) * LD + d);
 #pragma unroll
-            for (int i = 0; i < 2; ++i)
+            for (int i = 0; i < 4; ++i)
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     s[i][j] = fmaf(qv[i].x, kv[j].x, s[i][j]);
@@ -630,9 +710,8 @@ __global__ void __launch_bounds__(kAttnThreads) pf_attention_kernel(const PfAttn
                     s[i][j] = fmaf(qv[i].w, kv[j].w, s[i][j]);
                 }
         }
-        float alpha[2];
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < 4; ++i) {
             const int qpos = p.pos0 + q0 + qa + i;
             float mx = -FLT_MAX;
 #pragma unroll
@@ -645,7 +724,7 @@ __global__ void __launch_bounds__(kAttnThreads) pf_attention_kernel(const PfAttn
             for (int o2 = 1; o2 < 16; o2 <<= 1)
                 mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o2));
             const float mn = fmaxf(m[i], mx);
-            alpha[i] = expf(m[i] - mn);
+            const float alpha = expf(m[i] - mn);
             float sum = 0.f;
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
@@ -656,35 +735,50 @@ __global__ void __launch_bounds__(kAttnThreads) pf_attention_kernel(const PfAttn
 #pragma unroll
             for (int o2 = 1; o2 < 16; o2 <<= 1)
                 sum += __shfl_xor_sync(0xffffffffu, sum, o2);
-            l[i] = l[i] * alpha[i] + sum;
+            l[i] = l[i] * alpha + sum;
             m[i] = mn;
 #pragma unroll
-            for (int d = 0; d < DV; ++d)
-                o[i][d] *= alpha[i];
+            for (int c = 0; c < NV4; ++c) {
+                o[i][c].x *= alpha; o[i][c].y *= alpha; o[i][c].z *= alpha; o[i][c].w *= alpha;
+            }
         }
         __syncthreads();
-        const int kmax = min(kAttnKeys, nkeys - k0);
-        for (int j = 0; j < kmax; ++j) {
-            const float p0 = sP[qa * kAttnKeys + j], p1 = sP[(qa + 1) * kAttnKeys + j];
-            const float *vr = sV + j * LD + kb * DV;
+        const int kmax = (min(kAttnKeys, nkeys - k0) + 3) & ~3;   // rows past the last key hold zeros and weigh zero
+        for (int j = 0; j < kmax; j += 4) {
+            float4 pj[4];
 #pragma unroll
-            for (int d = 0; d < DV; d += 4) {
-                const float4 vv = *reinterpret_cast<const float4 *>(vr + d);
-                o[0][d] = fmaf(p0, vv.x, o[0][d]); o[0][d + 1] = fmaf(p0, vv.y, o[0][d + 1]);
-                o[0][d + 2] = fmaf(p0, vv.z, o[0][d + 2]); o[0][d + 3] = fmaf(p0, vv.w, o[0][d + 3]);
-                o[1][d] = fmaf(p1, vv.x, o[1][d]); o[1][d + 1] = fmaf(p1, vv.y, o[1][d + 1]);
-                o[1][d + 2] = fmaf(p1, vv.z, o[1][d + 2]); o[1][d + 3] = fmaf(p1, vv.w, o[1][d + 3]);
+            for (int i = 0; i < 4; ++i)
+                pj[i] = *reinterpret_cast<const float4 *>(sP + (qa + i) * kAttnKeys + j);
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) {
+#pragma unroll
+                for (int c = 0; c < NV4; ++c) {
+                    const float4 vv = *reinterpret_cast<const float4 *>(sV + (j + jj) * LD + c * 64 + kb * 4);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float w = jj == 0 ? pj[i].x : (jj == 1 ? pj[i].y : (jj == 2 ? pj[i].z : pj[i].w));
+                        o[i][c].x = fmaf(w, vv.x, o[i][c].x); o[i][c].y = fmaf(w, vv.y, o[i][c].y);
+                        o[i][c].z = fmaf(w, vv.z, o[i][c].z); o[i][c].w = fmaf(w, vv.w, o[i][c].w);
+                    }
+                }
             }
         }
     }
+    const int heads = p.dim / HEAD;
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < 4; ++i) {
         const int qi = q0 + qa + i;
         if (qi < p.nvalid) {
-            float *dst = p.out + (size_t)qi * p.dim + h * HEAD + kb * DV;
+            float *rec = p.parts + ((size_t)(z * kT + qi) * heads + h) * (HEAD + 2);
 #pragma unroll
-            for (int d = 0; d < DV; ++d)
-                dst[d] = __fdiv_rn(o[i][d], l[i]);
+            for (int c = 0; c < NV4; ++c) {   // records are 8-byte aligned (HEAD + 2 floats each)
+                *reinterpret_cast<float2 *>(rec + c * 64 + kb * 4) = make_float2(o[i][c].x, o[i][c].y);
+                *reinterpret_cast<float2 *>(rec + c * 64 + kb * 4 + 2) = make_float2(o[i][c].z, o[i][c].w);
+            }
+            if (kb == 0) {
+                rec[HEAD] = m[i];
+                rec[HEAD + 1] = l[i];
+            }
         }
     }
 }
@@ -714,7 +808,7 @@ EncodeTiledFn encode_tiled_fn()
 }
 
 // Byte matrix [rows][k] (row pitch k), tiles of box_rows x 128 bytes, 128-byte swizzled in shared memory.
-bool encode_bytes_2d(CUtensorMap *map, const void *base, int rows, int k, int box_rows)
+bool encode_bytes_2d(CUtensorMap *map, const void *base, int rows, int k, int box_rows, bool from_hbm)
 {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn)
@@ -724,7 +818,7 @@ bool encode_bytes_2d(CUtensorMap *map, const void *base, int rows, int k, int bo
     const cuuint32_t box[2] = {128u, (cuuint32_t)box_rows};
     const cuuint32_t estride[2] = {1u, 1u};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), gdim, gstride, box, estride, CU_TENSOR_MAP_INTERLEAVE_NONE,
-              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+              CU_TENSOR_MAP_SWIZZLE_128B, from_hbm ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 }  // namespace
@@ -735,9 +829,12 @@ struct Prefill {
     std::vector<CUtensorMap> maps;   // [layer][PF_W_COUNT]
     CUtensorMap map_b_dim, map_b_hidden;
     int *tokens = nullptr;
-    float *x = nullptr, *qkv = nullptr, *q = nullptr, *ao = nullptr, *h1 = nullptr, *h3 = nullptr;
+    float *x = nullptr, *qkv = nullptr, *q = nullptr, *h13 = nullptr;
+    float *parts = nullptr;      // [kMaxParts][64][dim]: partial row sums of Wo / W2, or the attention's key ranges
+    int ksplit_o = 1, ksplit_2 = 1;
     int8_t *limbs = nullptr;
     float2 *ux = nullptr;
+    float *ssq = nullptr;         // [groups / 4][64]
     int token_cap = 0;
     size_t gemm_smem_dim = 0, gemm_smem_hidden = 0, attn_smem = 0;
     std::vector<void *> owned;
@@ -789,11 +886,11 @@ cudaError_t prefill_create(Prefill **out, const PrefillModel &m)
     if (e == cudaSuccess) e = pf_alloc(pf, &pf->x, (size_t)kT * m.dim);
     if (e == cudaSuccess) e = pf_alloc(pf, &pf->qkv, (size_t)kT * pf->qkv_ld);
     if (e == cudaSuccess) e = pf_alloc(pf, &pf->q, (size_t)kT * m.dim);
-    if (e == cudaSuccess) e = pf_alloc(pf, &pf->ao, (size_t)kT * m.dim);
-    if (e == cudaSuccess) e = pf_alloc(pf, &pf->h1, (size_t)kT * m.hidden);
-    if (e == cudaSuccess) e = pf_alloc(pf, &pf->h3, (size_t)kT * m.hidden);
+    if (e == cudaSuccess) e = pf_alloc(pf, &pf->h13, (size_t)kT * 2 * m.hidden);
+    if (e == cudaSuccess) e = pf_alloc(pf, &pf->parts, (size_t)kMaxParts * kT * (m.dim + 2 * m.n_heads));
     if (e == cudaSuccess) e = pf_alloc(pf, &pf->limbs, (size_t)kN * kmax);
     if (e == cudaSuccess) e = pf_alloc(pf, &pf->ux, (size_t)(kmax / 256) * kT);
+    if (e == cudaSuccess) e = pf_alloc(pf, &pf->ssq, (size_t)(kmax / 256) * kT);
     if (e != cudaSuccess) {
         prefill_destroy(pf);
         return e;
@@ -804,18 +901,28 @@ cudaError_t prefill_create(Prefill **out, const PrefillModel &m)
     bool ok = true;
     for (int l = 0; l < m.n_layers && ok; ++l)
         for (int w = 0; w < PF_W_COUNT && ok; ++w)
-            ok = encode_bytes_2d(&pf->maps[(size_t)l * PF_W_COUNT + w], m.layers[(size_t)l].w[w], rows[w], ks[w], kTileM);
-    ok = ok && encode_bytes_2d(&pf->map_b_dim, pf->limbs, kN, m.dim, kN) && encode_bytes_2d(&pf->map_b_hidden, pf->limbs, kN, m.hidden, kN);
+            ok = encode_bytes_2d(&pf->maps[(size_t)l * PF_W_COUNT + w], m.layers[(size_t)l].w[w], rows[w], ks[w], kTileM, true);
+    ok = ok && encode_bytes_2d(&pf->map_b_dim, pf->limbs, kN, m.dim, kN, false) &&
+         encode_bytes_2d(&pf->map_b_hidden, pf->limbs, kN, m.hidden, kN, false);
     if (!ok) {
         prefill_destroy(pf);
         return cudaErrorNotSupported;
     }
-    pf->gemm_smem_dim = (size_t)kStages * kStageBytes + (size_t)(m.dim / 256) * kT * sizeof(float2) + 1024;
-    pf->gemm_smem_hidden = (size_t)kStages * kStageBytes + (size_t)(m.hidden / 256) * kT * sizeof(float2) + 1024;
+    pf->gemm_smem_dim = (size_t)kRingBytes + (size_t)(m.dim / 256) * kT * sizeof(float2) + 1024;
+    pf->gemm_smem_hidden = (size_t)kRingBytes + (size_t)(m.hidden / 256) * kT * sizeof(float2) + 1024;
     const size_t gmax = pf->gemm_smem_dim > pf->gemm_smem_hidden ? pf->gemm_smem_dim : pf->gemm_smem_hidden;
     e = cudaFuncSetAttribute(pf_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gmax);
     const int ld = m.head + 4;
     pf->attn_smem = (size_t)(2 * kAttnKeys * ld + kAttnQ * ld + kAttnQ * kAttnKeys) * sizeof(float);
+    // matrices with few row tiles (Wo, W2: dim / 128) deal the groups of a row to several blocks
+    auto split_for = [&](int rows, int groups) {
+        int ks = 1;
+        while (ks < kMaxParts && (rows / kTileM) * ks * 2 <= pf->sms && groups / (ks * 2) >= 2)
+            ks *= 2;
+        return ks;
+    };
+    pf->ksplit_o = split_for(m.dim, m.dim / 256);
+    pf->ksplit_2 = split_for(m.dim, m.hidden / 256);
     if (e == cudaSuccess)
         e = m.head == 128 ? cudaFuncSetAttribute(pf_attention_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pf->attn_smem)
                           : cudaFuncSetAttribute(pf_attention_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pf->attn_smem);
@@ -830,7 +937,7 @@ cudaError_t prefill_create(Prefill **out, const PrefillModel &m)
 namespace {
 
 cudaError_t launch_gemm(Prefill *pf, cudaStream_t st, int layer, const int *w, int nw, int k, float *out, int ldc, const int *col0,
-                        int accumulate, int nvalid)
+                        int ksplit, int nvalid, bool normed)
 {
     const PrefillModel &m = pf->m;
     const int rows_of[PF_W_COUNT] = {m.dim, pf->kv_dim, pf->kv_dim, m.dim, m.hidden, m.hidden, m.dim};
@@ -847,7 +954,10 @@ cudaError_t launch_gemm(Prefill *pf, cudaStream_t st, int layer, const int *w, i
     p.ux = pf->ux;
     p.out = out;
     p.ldc = ldc;
-    p.accumulate = accumulate;
+    p.ksplit = ksplit;
+    p.ssq = normed ? pf->ssq : nullptr;
+    p.nssq = (k / 256 + kLimbWarps - 1) / kLimbWarps;
+    p.n = k;
     p.nvalid = nvalid;
     p.timeout_us = m.timeout_us;
     p.status = m.status;
@@ -855,24 +965,29 @@ cudaError_t launch_gemm(Prefill *pf, cudaStream_t st, int layer, const int *w, i
     const CUtensorMap &a0 = base[w[0]], &a1 = base[w[nw > 1 ? 1 : 0]], &a2 = base[w[nw > 2 ? 2 : 0]];
     const CUtensorMap &b = k == m.dim ? pf->map_b_dim : pf->map_b_hidden;
     const size_t smem = k == m.dim ? pf->gemm_smem_dim : pf->gemm_smem_hidden;
-    const int grid = tiles < pf->sms ? tiles : pf->sms;
+    const int grid = tiles * ksplit < pf->sms ? tiles * ksplit : pf->sms;
     pf_gemm_kernel<<<grid, kGemmThreads, smem, st>>>(a0, a1, a2, b, p);
     ++pf->launches;
     return cudaGetLastError();
 }
 
 template <int MODE>
-cudaError_t launch_limbs(Prefill *pf, cudaStream_t st, const float *a, const float *b, int lda, int n, int nvalid)
+cudaError_t launch_limbs(Prefill *pf, cudaStream_t st, float *a, const float *b, const float *parts, int nparts, int lda, int n, int nvalid)
 {
     PfLimbParams p{};
     p.a = a;
     p.b = b;
+    p.parts = parts;
+    p.nparts = nparts;
+    p.head = pf->m.head;
     p.lda = lda;
     p.n = n;
     p.nvalid = nvalid;
     p.limbs = pf->limbs;
     p.ux = pf->ux;
-    pf_limbs_kernel<MODE><<<kT, 256, 0, st>>>(p);
+    p.ssq = pf->ssq;
+    const dim3 grid((unsigned)kT, (unsigned)((n / 256 + kLimbWarps - 1) / kLimbWarps));
+    pf_limbs_kernel<MODE><<<grid, kLimbThreads, 0, st>>>(p);
     ++pf->launches;
     return cudaGetLastError();
 }
@@ -906,27 +1021,33 @@ cudaError_t prefill_run(Prefill *pf, cudaStream_t st, const int *tokens_host, in
         pf_embed_kernel<<<kT, 256, 0, st>>>(pf->tokens + c0, nv, m.emb, dim, m.vocab, pf->x);
         ++pf->launches;
         PF_CK(cudaGetLastError());
+        int pending = 0;     // partial row sums in `parts` that the next RMSNorm adds to x
         for (int l = 0; l < m.n_layers; ++l) {
             const PrefillLayerDesc &L = m.layers[(size_t)l];
-            PF_CK(launch_limbs<PF_IN_NORM>(pf, st, pf->x, L.rms_att, dim, dim, nv));
+            PF_CK(launch_limbs<PF_IN_NORM>(pf, st, pf->x, L.rms_att, pf->parts, pending, dim, dim, nv));
             {
                 const int w[3] = {PF_WQ, PF_WK, PF_WV}, col0[3] = {0, dim, dim + kvd};
-                PF_CK(launch_gemm(pf, st, l, w, 3, dim, pf->qkv, pf->qkv_ld, col0, 0, nv));
+                PF_CK(launch_gemm(pf, st, l, w, 3, dim, pf->qkv, pf->qkv_ld, col0, 1, nv, true));
             }
             {
                 PfRopeParams r{};
                 r.qkv = pf->qkv; r.q = pf->q; r.k_cache = L.kc; r.v_cache = L.vc;
                 r.rope_cos = m.rope_cos; r.rope_sin = m.rope_sin;
                 r.dim = dim; r.kv_dim = kvd; r.head = m.head; r.seq_len = m.seq_len; r.pos0 = pos0 + c0; r.nvalid = nv;
-                pf_rope_kv_kernel<<<kT, 256, 0, st>>>(r);
+                const dim3 grid((unsigned)kT, (unsigned)((pf->qkv_ld / 2 + 255) / 256));
+                pf_rope_kv_kernel<<<grid, 256, 0, st>>>(r);
                 ++pf->launches;
                 PF_CK(cudaGetLastError());
             }
+            int nsplit = 1;
             {
+                const int tiles = (pos0 + c0 + nv + kAttnKeys - 1) / kAttnKeys;
+                nsplit = tiles / 4 < 1 ? 1 : (tiles / 4 > kMaxParts ? kMaxParts : tiles / 4);
                 PfAttnParams a{};
-                a.q = pf->q; a.k_cache = L.kc; a.v_cache = L.vc; a.out = pf->ao;
+                a.q = pf->q; a.k_cache = L.kc; a.v_cache = L.vc; a.parts = pf->parts;
                 a.dim = dim; a.head = m.head; a.kv_mul = m.n_heads / m.n_kv_heads; a.seq_len = m.seq_len; a.pos0 = pos0 + c0; a.nvalid = nv;
-                const dim3 grid((unsigned)m.n_heads, (unsigned)((nv + kAttnQ - 1) / kAttnQ));
+                a.nsplit = nsplit;
+                const dim3 grid((unsigned)m.n_heads, (unsigned)((nv + kAttnQ - 1) / kAttnQ), (unsigned)nsplit);
                 if (m.head == 128)
                     pf_attention_kernel<128><<<grid, kAttnThreads, pf->attn_smem, st>>>(a);
                 else
@@ -934,22 +1055,22 @@ cudaError_t prefill_run(Prefill *pf, cudaStream_t st, const int *tokens_host, in
                 ++pf->launches;
                 PF_CK(cudaGetLastError());
             }
-            PF_CK(launch_limbs<PF_IN_PLAIN>(pf, st, pf->ao, nullptr, dim, dim, nv));
+            PF_CK(launch_limbs<PF_IN_ATTN>(pf, st, nullptr, nullptr, pf->parts, nsplit, dim, dim, nv));
             {
                 const int w[1] = {PF_WO}, col0[1] = {0};
-                PF_CK(launch_gemm(pf, st, l, w, 1, dim, pf->x, dim, col0, 1, nv));
+                PF_CK(launch_gemm(pf, st, l, w, 1, dim, pf->parts, dim, col0, pf->ksplit_o, nv, false));
             }
-            PF_CK(launch_limbs<PF_IN_NORM>(pf, st, pf->x, L.rms_ffn, dim, dim, nv));
+            PF_CK(launch_limbs<PF_IN_NORM>(pf, st, pf->x, L.rms_ffn, pf->parts, pf->ksplit_o, dim, dim, nv));
             {
-                const int w1[1] = {PF_W1}, w3[1] = {PF_W3}, col0[1] = {0};
-                PF_CK(launch_gemm(pf, st, l, w1, 1, dim, pf->h1, hidden, col0, 0, nv));
-                PF_CK(launch_gemm(pf, st, l, w3, 1, dim, pf->h3, hidden, col0, 0, nv));
+                const int w[2] = {PF_W1, PF_W3}, col0[2] = {0, hidden};
+                PF_CK(launch_gemm(pf, st, l, w, 2, dim, pf->h13, 2 * hidden, col0, 1, nv, true));
             }
-            PF_CK(launch_limbs<PF_IN_SWIGLU>(pf, st, pf->h1, pf->h3, hidden, hidden, nv));
+            PF_CK(launch_limbs<PF_IN_SWIGLU>(pf, st, pf->h13, pf->h13 + hidden, nullptr, 0, 2 * hidden, hidden, nv));
             {
                 const int w[1] = {PF_W2}, col0[1] = {0};
-                PF_CK(launch_gemm(pf, st, l, w, 1, hidden, pf->x, dim, col0, 1, nv));
+                PF_CK(launch_gemm(pf, st, l, w, 1, hidden, pf->parts, dim, col0, pf->ksplit_2, nv, false));
             }
+            pending = pf->ksplit_2;
         }
     }
     return cudaSuccess;
