@@ -266,6 +266,18 @@ def long_context_account(cfg, model, tensors, device: int, peak: float) -> dict:
         out["attention"] = {"pos": pos_mid, "us_per_layer": a["us"], "bytes_per_layer": a["bytes"], "gbs": a["gbs"],
                             "frac": a["gbs"] / peak, "where": "attention phase of the persistent kernel, in situ"}
         out["us_per_layer"] = split["us_per_layer"]
+    # the same prompt through l2j_prefill (64 positions per weight sweep on the tensor cores) beside the decode path
+    inputs = np.concatenate([[1], prompt[:n_prompt - 1]]).astype(np.int32)   # BOS, then the prompt: what each position is fed
+    model.prefill(inputs, 0)
+    import torch
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    model.prefill(inputs, 0)
+    pf_s = time.perf_counter() - t0
+    out["prefill"] = {"tokens": int(n_prompt), "batched_s": pf_s, "batched_tok_s": n_prompt / pf_s,
+                      "decode_path_s": t_head * 1e-6, "speedup": t_head * 1e-6 / pf_s,
+                      "tensor_core_path": model.prefill_launches() > 0,
+                      "timing": "host wall clock around one blocking l2j_prefill call, tokens copied from host memory"}
     return out
 
 

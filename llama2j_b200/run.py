@@ -86,6 +86,11 @@ def main(argv=None) -> int:
     if temperature != 0.0:
         stages[-1].sampler_seed(seed)                        # Run.java:620
     token, pos, start, out = 1, 0, 0.0, []
+    if len(stages) == 1 and 1 < len(prompt) < steps and 1 not in prompt:
+        # positions 0 .. len(prompt) - 1 (fed BOS, then the prompt) in one batched call instead of one decode step
+        # per token (Run.java:623-637 takes the steps); their forced results are the prompt itself
+        stages[0].prefill([1] + prompt[:-1], 0)
+        out, token, pos, start = list(prompt), prompt[-1], len(prompt), time.time()
     while pos < steps:                                       # Run.java:623-685
         x = None
         for st in stages[:-1]:
