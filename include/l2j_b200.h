@@ -163,6 +163,20 @@ L2J_API int l2j_forward_stage(l2j_ctx *ctx, int token, int pos, const float *x_i
 L2J_API int l2j_prefill(l2j_ctx *ctx, const int32_t *tokens, int n, int pos0);
 L2J_API uint64_t l2j_prefill_launches(l2j_ctx *ctx);
 
+/* Concurrent sequences on one sweep over the weights (the reference's roadmap item "parallel processing of
+ * multiple queries", README.md:347,355-360; it has no such path).  l2j_batch_create gives the context K/V caches
+ * for n_seq independent sequences of seq_len positions (beside the cache of the single sequence, which
+ * l2j_forward keeps using).  l2j_batch_forward runs ONE decode step for up to 64 entries (sequence seq[i] is fed
+ * tokens[i] at position pos[i]): every weight byte is read once for all of them, dot products on the tensor
+ * cores as in l2j_prefill, attention per entry over its own sequence's cache, FP32 classifier for all entries.
+ * logits (n x vocab floats) and argmax (n ints, first maximum) may be NULL.  A sequence may appear with several
+ * positions in one call (a prompt in slices of 64): their K/V rows are written before any attention runs.
+ * Per entry the arithmetic is the decode step's with the row sums in another order (agreement to rounding, not
+ * bit for bit, with l2j_forward). */
+L2J_API int l2j_batch_create(l2j_ctx *ctx, int n_seq, int seq_len);
+L2J_API int l2j_batch_forward(l2j_ctx *ctx, int n, const int32_t *seq, const int32_t *pos, const int32_t *tokens, float *logits,
+                              int32_t *argmax);
+
 /* Token selection on the device for --temp > 0 (Run.java:643-665 with Sampler.java:20-44,76-120): the logits
  * of the last forward are divided by the temperature, turned into probabilities in place exactly as the
  * reference does it (exp in double, one sequential float sum) and sampled plainly (topp > 0.999) or from the

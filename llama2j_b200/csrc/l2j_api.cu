@@ -1421,6 +1421,8 @@ static PrefillModel prefill_model(l2j_ctx *c)
     m.seq_len = c->cfg.seq_len;
     m.vocab = c->cfg.vocab_size;
     m.emb = c->emb;
+    m.wcls = c->wcls;
+    m.rms_final = c->rms_final;
     m.status = reinterpret_cast<unsigned int *>(&c->state->status);
     m.timeout_us = c->wait_limit_us;
     auto payload = [](const MvSeg &s) { return s.payload + s.flat0; };
@@ -1444,6 +1446,20 @@ static PrefillModel prefill_model(l2j_ctx *c)
     return m;
 }
 
+// Builds the batched path of a whole-model context on first use; L2J_E_INVALID where the shape is outside it.
+static int ensure_prefill(l2j_ctx *c, bool required)
+{
+    if (!c->prefill_tried) {
+        c->prefill_tried = true;
+        const PrefillModel m = prefill_model(c);
+        if (prefill_supported(m) && !(c->flags & L2J_F_NO_TENSOR_PREFILL))
+            CK(c, prefill_create(&c->prefill, m));
+    }
+    if (required && !c->prefill)
+        return fail(c, L2J_E_INVALID, "the batched path needs rows of whole quantisation groups and a head size of 64 or 128");
+    return L2J_OK;
+}
+
 extern "C" int l2j_prefill(l2j_ctx *c, const int32_t *tokens, int n, int pos0)
 {
     if (!c || (n > 0 && !tokens))
@@ -1462,12 +1478,9 @@ extern "C" int l2j_prefill(l2j_ctx *c, const int32_t *tokens, int n, int pos0)
         if (n == 0)
             return L2J_OK;
         CK(c, cudaSetDevice(c->device));
-        if (!c->prefill_tried) {
-            c->prefill_tried = true;
-            const PrefillModel m = prefill_model(c);
-            if (prefill_supported(m) && !(c->flags & L2J_F_NO_TENSOR_PREFILL))
-                CK(c, prefill_create(&c->prefill, m));
-        }
+        const int rc = ensure_prefill(c, false);
+        if (rc != L2J_OK)
+            return rc;
         if (c->prefill) {
             CK(c, prefill_run(c->prefill, c->stream, tokens, n, pos0));
             CK(c, cudaMemcpyAsync(c->state_host, c->state, sizeof(SeqState), cudaMemcpyDeviceToHost, c->stream));
@@ -1482,6 +1495,58 @@ extern "C" int l2j_prefill(l2j_ctx *c, const int32_t *tokens, int n, int pos0)
             return rc;
     }
     return l2j_sync(c);
+}
+
+extern "C" int l2j_batch_create(l2j_ctx *c, int n_seq, int seq_len)
+{
+    if (!c)
+        return L2J_E_INVALID;
+    std::lock_guard<std::mutex> lock(c->mu);
+    if (!c->finalized)
+        return fail(c, L2J_E_STATE, "batch before finalize");
+    if (!(c->is_first && c->is_last) || c->tp_size > 1)
+        return fail(c, L2J_E_STATE, "concurrent sequences need a context that holds every layer");
+    if (n_seq < 1 || seq_len < 1 || seq_len > c->cfg.seq_len)
+        return fail(c, L2J_E_INVALID, "n_seq >= 1 and 1 <= seq_len <= %d", c->cfg.seq_len);
+    CK(c, cudaSetDevice(c->device));
+    const int rc = ensure_prefill(c, true);
+    if (rc != L2J_OK)
+        return rc;
+    CK(c, cudaStreamSynchronize(c->stream));
+    const cudaError_t e = prefill_batch_create(c->prefill, n_seq, seq_len);
+    if (e == cudaErrorMemoryAllocation) {
+        cudaGetLastError();
+        return fail(c, L2J_E_NOMEM, "no device memory for the caches of %d sequences of %d positions", n_seq, seq_len);
+    }
+    CK(c, e);
+    return L2J_OK;
+}
+
+extern "C" int l2j_batch_forward(l2j_ctx *c, int n, const int32_t *seq, const int32_t *pos, const int32_t *tokens, float *logits,
+                                 int32_t *argmax)
+{
+    if (!c || n < 0 || (n > 0 && (!seq || !pos || !tokens)))
+        return L2J_E_INVALID;
+    std::lock_guard<std::mutex> lock(c->mu);
+    if (!c->prefill || prefill_batch_sequences(c->prefill) == 0)
+        return fail(c, L2J_E_STATE, "call l2j_batch_create first");
+    if (n > kPrefillTokens)
+        return fail(c, L2J_E_INVALID, "at most %d (sequence, position) pairs per call", kPrefillTokens);
+    for (int i = 0; i < n; ++i) {
+        if (seq[i] < 0 || seq[i] >= prefill_batch_sequences(c->prefill) || pos[i] < 0 || pos[i] >= prefill_batch_seq_len(c->prefill) ||
+            tokens[i] < 0 || tokens[i] >= c->cfg.vocab_size)
+            return fail(c, L2J_E_INVALID, "entry %d: sequence %d, position %d or token %d out of range", i, seq[i], pos[i], tokens[i]);
+        for (int j = 0; j < i; ++j)
+            if (seq[j] == seq[i] && pos[j] == pos[i])
+                return fail(c, L2J_E_INVALID, "entries %d and %d name the same position of sequence %d", j, i, seq[i]);
+    }
+    if (n == 0)
+        return L2J_OK;
+    CK(c, cudaSetDevice(c->device));
+    CK(c, prefill_batch_forward(c->prefill, c->stream, tokens, pos, seq, n, logits, argmax));
+    CK(c, cudaMemcpyAsync(c->state_host, c->state, sizeof(SeqState), cudaMemcpyDeviceToHost, c->stream));
+    CK(c, cudaStreamSynchronize(c->stream));
+    return finish_status(c);
 }
 
 extern "C" uint64_t l2j_prefill_launches(l2j_ctx *c)

@@ -260,6 +260,8 @@ struct PrefillLayerDesc {
 struct PrefillModel {
     int dim, hidden, n_layers, n_heads, n_kv_heads, head, seq_len, vocab;
     const float *emb;
+    const float *wcls;               // FP32 classifier [vocab][dim] (the embedding table when shared)
+    const float *rms_final;          // dequantised final RMSNorm weights
     const float *rope_cos, *rope_sin;
     unsigned int *status;            // device status word of the context
     int timeout_us;
@@ -270,6 +272,11 @@ struct Prefill;
 bool prefill_supported(const PrefillModel &m);
 cudaError_t prefill_create(Prefill **out, const PrefillModel &m);
 cudaError_t prefill_run(Prefill *pf, cudaStream_t stream, const int *tokens_host, int n, int pos0);
+cudaError_t prefill_batch_create(Prefill *pf, int n_seq, int seq_len);
+cudaError_t prefill_batch_forward(Prefill *pf, cudaStream_t stream, const int *tokens, const int *pos, const int *seq, int n, float *logits_out,
+                                  int *argmax_out);
+int prefill_batch_sequences(const Prefill *pf);
+int prefill_batch_seq_len(const Prefill *pf);
 unsigned long long prefill_launches(const Prefill *pf);
 void prefill_destroy(Prefill *pf);
 

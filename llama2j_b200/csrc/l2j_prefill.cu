@@ -27,6 +27,7 @@
 #include <cfloat>
 #include <cmath>
 #include <cstdlib>
+#include <cstring>
 #include <mutex>
 #include <vector>
 
@@ -559,14 +560,20 @@ struct PfRopeParams {
     float *k_cache, *v_cache;   // layer base, [kv_head][seq][head]
     const float *rope_cos, *rope_sin;   // [seq][head / 2]
     int dim, kv_dim, head, seq_len, pos0, nvalid;
+    const int *pos_of, *seq_of;         // concurrent sequences: position and sequence of every token (else pos0 + t, one cache)
+    long long seq_stride;               // floats between the caches of two sequences
 };
 
-__global__ void pf_rope_kv_kernel(const PfRopeParams p)
+__global__ void pf_rope_kv_kernel(PfRopeParams p)
 {
     const int t = blockIdx.x;
     if (t >= p.nvalid)
         return;
-    const int pos = p.pos0 + t, half = p.head >> 1;
+    const int pos = p.pos_of ? p.pos_of[t] : p.pos0 + t, half = p.head >> 1;
+    if (p.seq_of) {
+        p.k_cache += (size_t)p.seq_of[t] * p.seq_stride;
+        p.v_cache += (size_t)p.seq_of[t] * p.seq_stride;
+    }
     const float *row = p.qkv + (size_t)t * (p.dim + 2 * p.kv_dim);
     const float *cs = p.rope_cos + (size_t)pos * half, *sn = p.rope_sin + (size_t)pos * half;
     const int i = blockIdx.y * blockDim.x + threadIdx.x;      // one pair per thread
@@ -784,6 +791,242 @@ __global__ void __launch_bounds__(kAttnThreads, 2) pf_attention_kernel(const PfA
 }
 
 // ---------------------------------------------------------------------------------------------------------------
+// concurrent sequences: one decode step of up to 64 (sequence, position) pairs on one sweep over the weights
+// ---------------------------------------------------------------------------------------------------------------
+
+struct BdAttnParams {
+    const float *q;                     // [64][dim] after RoPE
+    const float *k_cache, *v_cache;     // layer base of sequence 0, [kv_head][seq][head]
+    long long seq_stride;
+    const int *pos_of, *seq_of;
+    float *parts;                       // [64][heads][head + 2]: unnormalised output, maximum, sum (one key range)
+    int dim, kv_mul, seq_len, nvalid;
+};
+
+// Block = (head, token): every token has its own cache and length.  Warp w takes keys 32 (w + 4 i) + lane: the
+// lane's dot product with q (shared memory, broadcast), online softmax per warp, then the weighted V rows
+// (a row is one coalesced 16-byte load per lane); the four warps merge at the end.
+template <int HEAD>
+__global__ void __launch_bounds__(128) bd_attention_kernel(const BdAttnParams p)
+{
+    constexpr int DL = HEAD / 32;       // output elements per lane
+    __shared__ __align__(16) float sq[HEAD];
+    __shared__ float s_m[4], s_l[4];
+    __shared__ __align__(16) float s_o[4][HEAD];
+    const int h = blockIdx.x, t = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (t >= p.nvalid)
+        return;
+    const int pos = p.pos_of[t];
+    const size_t cache = (size_t)p.seq_of[t] * p.seq_stride + (size_t)(h / p.kv_mul) * p.seq_len * HEAD;
+    const float *kbase = p.k_cache + cache, *vbase = p.v_cache + cache;
+    if (tid < HEAD)
+        sq[tid] = p.q[(size_t)t * p.dim + h * HEAD + tid];
+    __syncthreads();
+    const float root = sqrtf((float)HEAD);
+    float m = -FLT_MAX, l = 0.f;
+    float o[DL];
+#pragma unroll
+    for (int d = 0; d < DL; ++d)
+        o[d] = 0.f;
+    for (int k0 = warp * 32; k0 <= pos; k0 += 128) {
+        const int key = k0 + lane;
+        float sc = -FLT_MAX;
+        if (key <= pos) {
+            const float4 *kr = reinterpret_cast<const float4 *>(kbase + (size_t)key * HEAD);
+            float a = 0.f;
+#pragma unroll 8
+            for (int d = 0; d < HEAD / 4; ++d) {
+                const float4 kv = kr[d];
+                const float4 qv = *reinterpret_cast<const float4 *>(sq + 4 * d);
+                a = fmaf(qv.x, kv.x, a); a = fmaf(qv.y, kv.y, a); a = fmaf(qv.z, kv.z, a); a = fmaf(qv.w, kv.w, a);
+            }
+            sc = __fdiv_rn(a, root);
+        }
+        const float mx = warp_max(sc);
+        const float mn = fmaxf(m, mx);
+        const float alpha = expf(m - mn);
+        const float pv = sc > -FLT_MAX ? expf(sc - mn) : 0.f;
+        l = l * alpha + warp_sum(pv);
+        m = mn;
+#pragma unroll
+        for (int d = 0; d < DL; ++d)
+            o[d] *= alpha;
+        const int kn = min(32, pos + 1 - k0);
+        for (int j = 0; j < kn; ++j) {
+            const float w = __shfl_sync(0xffffffffu, pv, j);
+            const float *vr = vbase + (size_t)(k0 + j) * HEAD + lane * DL;
+#pragma unroll
+            for (int d = 0; d < DL; ++d)
+                o[d] = fmaf(w, vr[d], o[d]);
+        }
+    }
+    if (lane == 0) {
+        s_m[warp] = m;
+        s_l[warp] = l;
+    }
+#pragma unroll
+    for (int d = 0; d < DL; ++d)
+        s_o[warp][lane * DL + d] = o[d];
+    __syncthreads();
+    const float mt = fmaxf(fmaxf(s_m[0], s_m[1]), fmaxf(s_m[2], s_m[3]));
+    float *rec = p.parts + ((size_t)t * (p.dim / HEAD) + h) * (HEAD + 2);
+    if (tid < HEAD) {
+        float acc = 0.f;
+        for (int w = 0; w < 4; ++w)
+            acc = fmaf(expf(s_m[w] - mt), s_o[w][tid], acc);
+        rec[tid] = acc;
+    }
+    if (tid == 0) {
+        float lt = 0.f;
+        for (int w = 0; w < 4; ++w)
+            lt = fmaf(expf(s_m[w] - mt), s_l[w], lt);
+        rec[HEAD] = mt;
+        rec[HEAD + 1] = lt;
+    }
+}
+
+// x after the last layer (with the partial row sums of its W2), RMSNorm with the final weights
+// (RootMeanSquare.java:25-35, WeightNormalizeAndScale.java:71-74): [64][dim] FP32 for the classifier.
+__global__ void __launch_bounds__(256) bd_final_norm_kernel(const float *x, const float *parts, int nparts, const float *w, int dim, int nvalid,
+                                                            float *out)
+{
+    __shared__ float s_red[8];
+    const int t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    float ssq = 0.f;
+    for (int i = tid; i < dim; i += 256) {
+        float v = t < nvalid ? x[(size_t)t * dim + i] : 0.f;
+        for (int z = 0; z < nparts && t < nvalid; ++z)
+            v = __fadd_rn(v, parts[((size_t)z * kT + t) * dim + i]);
+        out[(size_t)t * dim + i] = v;
+        ssq = fmaf(v, v, ssq);
+    }
+    ssq = warp_sum(ssq);
+    if (lane == 0)
+        s_red[warp] = ssq;
+    __syncthreads();
+    float tot = 0.f;
+    for (int k = 0; k < 8; ++k)
+        tot += s_red[k];
+    tot = __fdiv_rn(tot, (float)dim);
+    tot = __fadd_rn(tot, 1e-5f);
+    const float ss = __fdiv_rn(1.0f, __fsqrt_rn(tot));
+    for (int i = tid; i < dim; i += 256)
+        out[(size_t)t * dim + i] = __fmul_rn(w[i], __fmul_rn(ss, out[(size_t)t * dim + i]));
+}
+
+// logits[t][v] = sum_k wcls[v][k] * xn[t][k] for 64 tokens: FP32 on the CUDA cores (the classifier is not
+// quantised, TransformerWeights.java:25,41,122), 128 vocabulary rows x 64 tokens per block, K in chunks of 32
+// double-buffered with asynchronous copies, 8 rows x 4 tokens per thread.
+constexpr int kClsRows = 128, kClsK = 32, kClsLd = kClsK + 4, kClsThreads = 256;
+constexpr int kClsStage = (kClsRows + kT) * kClsLd;      // floats per stage
+
+__global__ void __launch_bounds__(kClsThreads) bd_classifier_kernel(const float *wcls, const float *xn, int vocab, int dim, float *logits)
+{
+    extern __shared__ __align__(16) float cls_smem[];
+    const int tid = threadIdx.x, v0 = blockIdx.x * kClsRows;
+    const int rg = tid >> 4, tg = tid & 15;          // rows rg + 16 i (i < 8), tokens tg + 16 j (j < 4)
+    float acc[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            acc[i][j] = 0.f;
+    auto load_stage = [&](int st, int k0) {
+        float *sw = cls_smem + st * kClsStage, *sx = sw + kClsRows * kClsLd;
+        for (int i = tid; i < (kClsRows + kT) * (kClsK / 4); i += kClsThreads) {
+            const int r = i / (kClsK / 4), c = i % (kClsK / 4);
+            if (r < kClsRows) {
+                const int v = min(v0 + r, vocab - 1);
+                cp_async16(smem_u32(sw + r * kClsLd + c * 4), wcls + (size_t)v * dim + k0 + c * 4);
+            } else {
+                cp_async16(smem_u32(sx + (r - kClsRows) * kClsLd + c * 4), xn + (size_t)(r - kClsRows) * dim + k0 + c * 4);
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    const int nk = dim / kClsK;
+    load_stage(0, 0);
+    for (int kc = 0; kc < nk; ++kc) {
+        if (kc + 1 < nk) {
+            load_stage((kc + 1) & 1, (kc + 1) * kClsK);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();
+        const float *sw = cls_smem + (kc & 1) * kClsStage, *sx = sw + kClsRows * kClsLd;
+#pragma unroll
+        for (int k = 0; k < kClsK; k += 4) {
+            float4 wv[8], xv[4];
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                wv[i] = *reinterpret_cast<const float4 *>(sw + (rg + 16 * i) * kClsLd + k);
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                xv[j] = *reinterpret_cast<const float4 *>(sx + (tg + 16 * j) * kClsLd + k);
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    acc[i][j] = fmaf(wv[i].x, xv[j].x, acc[i][j]);
+                    acc[i][j] = fmaf(wv[i].y, xv[j].y, acc[i][j]);
+                    acc[i][j] = fmaf(wv[i].z, xv[j].z, acc[i][j]);
+                    acc[i][j] = fmaf(wv[i].w, xv[j].w, acc[i][j]);
+                }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int v = v0 + rg + 16 * i;
+        if (v < vocab)
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                logits[(size_t)(tg + 16 * j) * vocab + v] = acc[i][j];
+    }
+}
+
+// First maximum of every token's logits (Sampler.java:46-57).
+__global__ void __launch_bounds__(256) bd_argmax_kernel(const float *logits, int vocab, int nvalid, int *out)
+{
+    __shared__ float s_v[8];
+    __shared__ int s_i[8];
+    const int t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (t >= nvalid)
+        return;
+    float bv = -FLT_MAX;
+    int bi = 0x7fffffff;
+    for (int i = tid; i < vocab; i += 256) {
+        const float v = logits[(size_t)t * vocab + i];
+        if (v > bv) {
+            bv = v;
+            bi = i;
+        }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) {
+            bv = ov;
+            bi = oi;
+        }
+    }
+    if (lane == 0) {
+        s_v[warp] = bv;
+        s_i[warp] = bi;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        for (int w = 1; w < 8; ++w)
+            if (s_v[w] > bv || (s_v[w] == bv && s_i[w] < bi)) {
+                bv = s_v[w];
+                bi = s_i[w];
+            }
+        out[t] = bi;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------------------------
 
@@ -839,6 +1082,13 @@ struct Prefill {
     size_t gemm_smem_dim = 0, gemm_smem_hidden = 0, attn_smem = 0;
     std::vector<void *> owned;
     unsigned long long launches = 0;
+    // concurrent sequences
+    int n_seq = 0, seq_len_b = 0;
+    float *bkc = nullptr, *bvc = nullptr;      // [sequence][layer][kv_head][seq_len_b][head]
+    int *meta = nullptr;                       // device: tokens[64], positions[64], sequences[64], arg-max[64]
+    float *xn = nullptr, *logits = nullptr;    // [64][dim], [64][vocab]
+    int *meta_host = nullptr;                  // pinned, 4 x 64
+    float *logits_host = nullptr;              // pinned, [64][vocab]
 };
 
 bool prefill_supported(const PrefillModel &m)
@@ -852,6 +1102,10 @@ void prefill_destroy(Prefill *pf)
 {
     if (!pf)
         return;
+    if (pf->meta_host)
+        cudaFreeHost(pf->meta_host);
+    if (pf->logits_host)
+        cudaFreeHost(pf->logits_host);
     for (void *p : pf->owned)
         cudaFree(p);
     delete pf;
@@ -1074,6 +1328,142 @@ cudaError_t prefill_run(Prefill *pf, cudaStream_t st, const int *tokens_host, in
         }
     }
     return cudaSuccess;
+}
+
+// Caches for n_seq sequences of seq_len positions each (replaces an earlier set).
+cudaError_t prefill_batch_create(Prefill *pf, int n_seq, int seq_len)
+{
+    const PrefillModel &m = pf->m;
+    if (n_seq < 1 || seq_len < 1 || seq_len > m.seq_len)
+        return cudaErrorInvalidValue;
+    const size_t per_seq = (size_t)m.n_layers * m.n_kv_heads * seq_len * m.head;
+    auto drop = [&](void *ptr) {
+        for (size_t i = 0; i < pf->owned.size(); ++i)
+            if (pf->owned[i] == ptr) {
+                cudaFree(ptr);
+                pf->owned.erase(pf->owned.begin() + (long)i);
+                return;
+            }
+    };
+    if (pf->bkc) {
+        drop(pf->bkc);
+        drop(pf->bvc);
+        pf->bkc = pf->bvc = nullptr;
+        pf->n_seq = 0;
+    }
+    PF_CK(pf_alloc(pf, &pf->bkc, per_seq * n_seq));
+    PF_CK(pf_alloc(pf, &pf->bvc, per_seq * n_seq));
+    if (!pf->meta) {
+        PF_CK(pf_alloc(pf, &pf->meta, (size_t)4 * kT));
+        PF_CK(pf_alloc(pf, &pf->xn, (size_t)kT * m.dim));
+        PF_CK(pf_alloc(pf, &pf->logits, (size_t)kT * m.vocab));
+        PF_CK(cudaHostAlloc(reinterpret_cast<void **>(&pf->meta_host), sizeof(int) * 4 * kT, cudaHostAllocDefault));
+        PF_CK(cudaHostAlloc(reinterpret_cast<void **>(&pf->logits_host), sizeof(float) * (size_t)kT * m.vocab, cudaHostAllocDefault));
+        PF_CK(cudaFuncSetAttribute(bd_classifier_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(2 * kClsStage * sizeof(float))));
+    }
+    pf->n_seq = n_seq;
+    pf->seq_len_b = seq_len;
+    return cudaSuccess;
+}
+
+// One decode step of n <= 64 (sequence, position, token) triples on one sweep over the weights; a sequence
+// may appear several times with different positions (their K/V rows are all written before the attention).
+// logits_out [n][vocab] and argmax_out [n] are host pointers (either may be null); blocks until done.
+cudaError_t prefill_batch_forward(Prefill *pf, cudaStream_t st, const int *tokens, const int *pos, const int *seq, int n, float *logits_out,
+                                  int *argmax_out)
+{
+    const PrefillModel &m = pf->m;
+    const int dim = m.dim, hidden = m.hidden, kvd = pf->kv_dim, nv = n;
+    for (int i = 0; i < kT; ++i) {
+        pf->meta_host[i] = i < n ? tokens[i] : 0;
+        pf->meta_host[kT + i] = i < n ? pos[i] : 0;
+        pf->meta_host[2 * kT + i] = i < n ? seq[i] : 0;
+    }
+    PF_CK(cudaMemcpyAsync(pf->meta, pf->meta_host, sizeof(int) * 3 * kT, cudaMemcpyHostToDevice, st));
+    const int *d_tok = pf->meta, *d_pos = pf->meta + kT, *d_seq = pf->meta + 2 * kT;
+    int *d_arg = pf->meta + 3 * kT;
+    const long long layer_stride = (long long)m.n_kv_heads * pf->seq_len_b * m.head;
+    const long long seq_stride = layer_stride * m.n_layers;
+    pf_embed_kernel<<<kT, 256, 0, st>>>(d_tok, nv, m.emb, dim, m.vocab, pf->x);
+    ++pf->launches;
+    PF_CK(cudaGetLastError());
+    int pending = 0;
+    for (int l = 0; l < m.n_layers; ++l) {
+        const PrefillLayerDesc &L = m.layers[(size_t)l];
+        PF_CK(launch_limbs<PF_IN_NORM>(pf, st, pf->x, L.rms_att, pf->parts, pending, dim, dim, nv));
+        {
+            const int w[3] = {PF_WQ, PF_WK, PF_WV}, col0[3] = {0, dim, dim + kvd};
+            PF_CK(launch_gemm(pf, st, l, w, 3, dim, pf->qkv, pf->qkv_ld, col0, 1, nv, true));
+        }
+        {
+            PfRopeParams r{};
+            r.qkv = pf->qkv; r.q = pf->q; r.k_cache = pf->bkc + l * layer_stride; r.v_cache = pf->bvc + l * layer_stride;
+            r.rope_cos = m.rope_cos; r.rope_sin = m.rope_sin;
+            r.dim = dim; r.kv_dim = kvd; r.head = m.head; r.seq_len = pf->seq_len_b; r.pos0 = 0; r.nvalid = nv;
+            r.pos_of = d_pos; r.seq_of = d_seq; r.seq_stride = seq_stride;
+            const dim3 grid((unsigned)kT, (unsigned)((pf->qkv_ld / 2 + 255) / 256));
+            pf_rope_kv_kernel<<<grid, 256, 0, st>>>(r);
+            ++pf->launches;
+            PF_CK(cudaGetLastError());
+        }
+        {
+            BdAttnParams a{};
+            a.q = pf->q; a.k_cache = pf->bkc + l * layer_stride; a.v_cache = pf->bvc + l * layer_stride; a.seq_stride = seq_stride;
+            a.pos_of = d_pos; a.seq_of = d_seq; a.parts = pf->parts;
+            a.dim = dim; a.kv_mul = m.n_heads / m.n_kv_heads; a.seq_len = pf->seq_len_b; a.nvalid = nv;
+            const dim3 grid((unsigned)m.n_heads, (unsigned)nv);
+            if (m.head == 128)
+                bd_attention_kernel<128><<<grid, 128, 0, st>>>(a);
+            else
+                bd_attention_kernel<64><<<grid, 128, 0, st>>>(a);
+            ++pf->launches;
+            PF_CK(cudaGetLastError());
+        }
+        PF_CK(launch_limbs<PF_IN_ATTN>(pf, st, nullptr, nullptr, pf->parts, 1, dim, dim, nv));
+        {
+            const int w[1] = {PF_WO}, col0[1] = {0};
+            PF_CK(launch_gemm(pf, st, l, w, 1, dim, pf->parts, dim, col0, pf->ksplit_o, nv, false));
+        }
+        PF_CK(launch_limbs<PF_IN_NORM>(pf, st, pf->x, L.rms_ffn, pf->parts, pf->ksplit_o, dim, dim, nv));
+        {
+            const int w[2] = {PF_W1, PF_W3}, col0[2] = {0, hidden};
+            PF_CK(launch_gemm(pf, st, l, w, 2, dim, pf->h13, 2 * hidden, col0, 1, nv, true));
+        }
+        PF_CK(launch_limbs<PF_IN_SWIGLU>(pf, st, pf->h13, pf->h13 + hidden, nullptr, 0, 2 * hidden, hidden, nv));
+        {
+            const int w[1] = {PF_W2}, col0[1] = {0};
+            PF_CK(launch_gemm(pf, st, l, w, 1, hidden, pf->parts, dim, col0, pf->ksplit_2, nv, false));
+        }
+        pending = pf->ksplit_2;
+    }
+    bd_final_norm_kernel<<<kT, 256, 0, st>>>(pf->x, pf->parts, pending, m.rms_final, dim, nv, pf->xn);
+    PF_CK(cudaGetLastError());
+    bd_classifier_kernel<<<(m.vocab + kClsRows - 1) / kClsRows, kClsThreads, 2 * kClsStage * sizeof(float), st>>>(m.wcls, pf->xn, m.vocab, dim,
+                                                                                                                 pf->logits);
+    PF_CK(cudaGetLastError());
+    bd_argmax_kernel<<<nv, 256, 0, st>>>(pf->logits, m.vocab, nv, d_arg);
+    PF_CK(cudaGetLastError());
+    pf->launches += 3;
+    PF_CK(cudaMemcpyAsync(pf->meta_host + 3 * kT, d_arg, sizeof(int) * kT, cudaMemcpyDeviceToHost, st));
+    if (logits_out)
+        PF_CK(cudaMemcpyAsync(pf->logits_host, pf->logits, sizeof(float) * (size_t)nv * m.vocab, cudaMemcpyDeviceToHost, st));
+    PF_CK(cudaStreamSynchronize(st));
+    if (logits_out)
+        memcpy(logits_out, pf->logits_host, sizeof(float) * (size_t)nv * m.vocab);
+    if (argmax_out)
+        for (int i = 0; i < n; ++i)
+            argmax_out[i] = pf->meta_host[3 * kT + i];
+    return cudaSuccess;
+}
+
+int prefill_batch_sequences(const Prefill *pf)
+{
+    return pf ? pf->n_seq : 0;
+}
+
+int prefill_batch_seq_len(const Prefill *pf)
+{
+    return pf ? pf->seq_len_b : 0;
 }
 
 unsigned long long prefill_launches(const Prefill *pf)

@@ -58,6 +58,9 @@ _SIGNATURES = {
     "l2j_forward_stage": (C.c_int, [_P, C.c_int, C.c_int, _P, _P, _P, C.POINTER(C.c_int)]),
     "l2j_prefill": (C.c_int, [_P, C.POINTER(C.c_int32), C.c_int, C.c_int]),
     "l2j_prefill_launches": (C.c_uint64, [_P]),
+    "l2j_batch_create": (C.c_int, [_P, C.c_int, C.c_int]),
+    "l2j_batch_forward": (C.c_int, [_P, C.c_int, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.c_void_p,
+                                   C.POINTER(C.c_int32)]),
     "l2j_sampler_seed": (C.c_int, [_P, C.c_int64]),
     "l2j_sample": (C.c_int, [_P, C.c_float, C.c_float, C.POINTER(C.c_int)]),
     "l2j_device_buffers": (C.c_int, [_P, C.POINTER(_P), C.POINTER(_P)]),

@@ -134,6 +134,26 @@ class Transformer:
     def prefill_launches(self) -> int:
         return int(self._lib.l2j_prefill_launches(self._ctx))
 
+    def batch_create(self, n_seq: int, seq_len: int) -> None:
+        """K/V caches for n_seq concurrent sequences of seq_len positions."""
+        _lib.check(self._lib.l2j_batch_create(self._ctx, int(n_seq), int(seq_len)), self._ctx)
+
+    def batch_forward(self, seq, pos, tokens, want_logits: bool = True):
+        """One decode step for up to 64 (sequence, position, token) entries on one sweep over the weights;
+        returns (logits [n, vocab] or None, arg-max [n])."""
+        sq = np.ascontiguousarray(seq, dtype=np.int32).reshape(-1)
+        ps = np.ascontiguousarray(pos, dtype=np.int32).reshape(-1)
+        tk = np.ascontiguousarray(tokens, dtype=np.int32).reshape(-1)
+        n = int(sq.size)
+        assert ps.size == n and tk.size == n
+        logits = np.empty((n, self.cfg.vocab_size), dtype=np.float32) if want_logits else None
+        am = np.zeros(n, dtype=np.int32)
+        ip = C.POINTER(C.c_int32)
+        rc = self._lib.l2j_batch_forward(self._ctx, n, sq.ctypes.data_as(ip), ps.ctypes.data_as(ip), tk.ctypes.data_as(ip),
+                                         logits.ctypes.data if want_logits else None, am.ctypes.data_as(ip))
+        _lib.check(rc, self._ctx)
+        return logits, am
+
     def sampler_seed(self, seed: int) -> None:
         """new Sampler(seed, vocab) on the device (Sampler.java:24-31)."""
         _lib.check(self._lib.l2j_sampler_seed(self._ctx, int(seed)), self._ctx)
