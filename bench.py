@@ -281,6 +281,24 @@ def long_context_account(cfg, model, tensors, device: int, peak: float) -> dict:
     return out
 
 
+def concurrent_account(cfg, model, single_tok_s: float) -> dict:
+    """64 sequences decoded together (l2j_batch_forward): one sweep over the weights per step for all of them.
+    Greedy from BOS, every sequence fed its own arg-max; host wall clock per blocking step (ids in, ids out)."""
+    n_seq, seq_len, steps, skip = 64, 256, 72, 8
+    model.batch_create(n_seq, seq_len)
+    toks = np.ones(n_seq, dtype=np.int32)
+    seq = np.arange(n_seq, dtype=np.int32)
+    times = []
+    for p in range(steps):
+        t0 = time.perf_counter()
+        _, toks = model.batch_forward(seq, np.full(n_seq, p, dtype=np.int32), toks, want_logits=False)
+        times.append(time.perf_counter() - t0)
+    per = float(np.mean(times[skip:]))
+    return {"sequences": n_seq, "positions": [skip, steps - 1], "ms_per_step": per * 1e3, "aggregate_tok_s": n_seq / per,
+            "vs_one_sequence": n_seq / per / single_tok_s,
+            "note": "each step reads every weight once for 64 sequences; attention and K/V traffic grow with the positions"}
+
+
 def run_single(args, cfg, local_rank: int) -> dict:
     from llama2j_b200 import synthetic as syn
     from llama2j_b200.transformer import Transformer, run_greedy_host_loop
@@ -371,6 +389,8 @@ def run_single(args, cfg, local_rank: int) -> dict:
         if cfg.seq_len >= 4096:
             accounts["long_context"] = long_context_account(cfg, model, tensors, local_rank, peak)
             model.reset()
+        if model.prefill_launches() > 0:
+            accounts["concurrent_sequences"] = concurrent_account(cfg, model, value)
 
     line = {
         "metric": "batch-1 decode tok/s (forwards per second)", "value": value, "unit": "tok/s", "n_gpus": 1,

@@ -43,11 +43,12 @@ constexpr int kTileM = 128;                 // weight rows per tile
 constexpr int kGemmThreads = 384;          // producer warp, issue warp, two spare, eight epilogue warps
 constexpr int kEpiWarps = 8;                // warps 4..11: quarter of tensor memory = warp % 4, half of the tokens = (warp - 4) / 4
 constexpr int kTH = kT / 2;                 // tokens per epilogue thread
-constexpr int kStages = 4;                  // ring depth; one stage = half a quantisation group (K = 128) of A and B
+constexpr int kMaxStages = 4;                // ring depth; one stage = half a quantisation group (K = 128) of A and B.
+                                            // Measured: a fifth stage, or separate rings for A and B, are slower; the kernel
+                                            // sits on the kind::i8 issue rate (about 380 cycles per 128 x 192 x 32 MMA)
 constexpr int kABytes = kTileM * 128;       // the A part of a stage: 128 rows of 128 bytes
 constexpr int kBBytes = kN * 128;
 constexpr int kStageBytes = kABytes + kBBytes;
-constexpr int kRingBytes = kStages * kStageBytes;
 constexpr int kMaxParts = 8;                // parts a row sum (or a query's keys) may be dealt into
 constexpr int kAccCols = 256;               // column distance of the two accumulators in tensor memory
 constexpr int kTmemCols = 512;
@@ -185,6 +186,7 @@ struct PfGemmParams {
     int n;               // elements per input row
     float *out;          // [ksplit][64][ldc]
     int ldc;
+    int stages;          // ring depth (<= kMaxStages)
     int ksplit;          // the groups of a row are dealt to this many blocks; part z goes to out + z * 64 * ldc
     int nvalid;          // tokens of the chunk that exist
     int timeout_us;
@@ -196,7 +198,7 @@ pf_gemm_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant
                const __grid_constant__ CUtensorMap map_a2, const __grid_constant__ CUtensorMap map_b, const PfGemmParams p)
 {
     extern __shared__ unsigned char pf_smem_raw[];
-    __shared__ __align__(8) unsigned long long s_bar[2 * kStages + 4 + 1];
+    __shared__ __align__(8) unsigned long long s_bar[2 * kMaxStages + 4 + 1];
     __shared__ uint32_t s_tmem;
     __shared__ int s_give_up;
     __shared__ float s_ss[kT];
@@ -204,10 +206,11 @@ pf_gemm_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t base = (smem_u32(pf_smem_raw) + 1023u) & ~1023u;            // swizzled tiles want 1024-byte alignment
     unsigned char *gen = pf_smem_raw + (base - smem_u32(pf_smem_raw));
-    float2 *s_ux = reinterpret_cast<float2 *>(gen + kRingBytes);
-    const uint32_t bar_full = smem_u32(&s_bar[0]), bar_empty = smem_u32(&s_bar[kStages]);
-    const uint32_t bar_acc_full = smem_u32(&s_bar[2 * kStages]), bar_acc_empty = smem_u32(&s_bar[2 * kStages + 2]);
-    const uint32_t bar_fin = smem_u32(&s_bar[2 * kStages + 4]);
+    const int kStages = p.stages;
+    float2 *s_ux = reinterpret_cast<float2 *>(gen + (size_t)kStages * kStageBytes);
+    const uint32_t bar_full = smem_u32(&s_bar[0]), bar_empty = smem_u32(&s_bar[kMaxStages]);
+    const uint32_t bar_acc_full = smem_u32(&s_bar[2 * kMaxStages]), bar_acc_empty = smem_u32(&s_bar[2 * kMaxStages + 2]);
+    const uint32_t bar_fin = smem_u32(&s_bar[2 * kMaxStages + 4]);
     const long long limit = 2000ll * (long long)p.timeout_us;
 
     int ntiles = 0;
@@ -353,38 +356,57 @@ pf_gemm_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant
 #pragma unroll
             for (int t = 0; t < kTH; ++t)
                 acc[t] = 0.f;
-            float2 ms = hrow[g0 < G ? g0 : 0];
-            for (int g = g0; g < g1; ++g, ++it) {
-                const int b = (int)(it & 1);
-                const uint32_t pha = (uint32_t)((it >> 1) & 1);
-                const float2 ms_next = hrow[g + 1 < g1 ? g + 1 : g];
-                if (!pf_wait(bar_acc_full + 8 * b, pha, give_up, limit)) {
-                    ok = false;
-                    break;
-                }
-                tc_fence_after();
-                const uint32_t tacc = trow + (uint32_t)b * kAccCols;
-                // all of the thread's sums of the group in one round trip, then the accumulator is free again
-                uint32_t s0[kTH], s1[kTH], s2[kTH];
+            // The (min, scale) pairs of the row come from HBM, 8 bytes per group and row: they are asked for four
+            // groups ahead, or every group would wait one memory latency for its own pair.
+            const int glast = g1 > g0 ? g1 - 1 : 0;
+            float2 msq[4];
 #pragma unroll
-                for (int c = 0; c < kTH; c += 16) {
-                    tmem_ld16(tacc + c, *reinterpret_cast<uint32_t(*)[16]>(&s0[c]));
-                    tmem_ld16(tacc + kT + c, *reinterpret_cast<uint32_t(*)[16]>(&s1[c]));
-                    tmem_ld16(tacc + 2 * kT + c, *reinterpret_cast<uint32_t(*)[16]>(&s2[c]));
-                }
-                tmem_ld_wait();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0)
-                    mbar_arrive(bar_acc_empty + 8 * b);
-                const float2 *ux = s_ux + g * kT + th * kTH;
+            for (int j = 0; j < 4; ++j)
+                msq[j] = hrow[min(g0 + j, glast)];
+            for (int gb = g0; gb < g1 && ok; gb += 4) {
+                float2 nxt[4];
 #pragma unroll
-                for (int j = 0; j < kTH; ++j) {
-                    const float dsum = fmaf((float)(int)s2[j], 65536.0f, fmaf((float)(int)s1[j], 256.0f, (float)(int)s0[j]));
-                    const float2 u = ux[j];
-                    acc[j] += fmaf(ms.y, dsum, ms.x * u.y) * u.x;
+                for (int j = 0; j < 4; ++j)
+                    nxt[j] = hrow[min(gb + 4 + j, glast)];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int g = gb + j;
+                    if (g >= g1 || !ok)
+                        continue;
+                    const float2 ms = msq[j];
+                    const int b = (int)(it & 1);
+                    const uint32_t pha = (uint32_t)((it >> 1) & 1);
+                    if (!pf_wait(bar_acc_full + 8 * b, pha, give_up, limit)) {
+                        ok = false;
+                        continue;
+                    }
+                    tc_fence_after();
+                    const uint32_t tacc = trow + (uint32_t)b * kAccCols;
+                    // all of the thread's sums of the group in one round trip, then the accumulator is free again
+                    uint32_t s0[kTH], s1[kTH], s2[kTH];
+#pragma unroll
+                    for (int c = 0; c < kTH; c += 16) {
+                        tmem_ld16(tacc + c, *reinterpret_cast<uint32_t(*)[16]>(&s0[c]));
+                        tmem_ld16(tacc + kT + c, *reinterpret_cast<uint32_t(*)[16]>(&s1[c]));
+                        tmem_ld16(tacc + 2 * kT + c, *reinterpret_cast<uint32_t(*)[16]>(&s2[c]));
+                    }
+                    tmem_ld_wait();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0)
+                        mbar_arrive(bar_acc_empty + 8 * b);
+                    const float2 *ux = s_ux + g * kT + th * kTH;
+#pragma unroll
+                    for (int k = 0; k < kTH; ++k) {
+                        const float dsum = fmaf((float)(int)s2[k], 65536.0f, fmaf((float)(int)s1[k], 256.0f, (float)(int)s0[k]));
+                        const float2 u = ux[k];
+                        acc[k] += fmaf(ms.y, dsum, ms.x * u.y) * u.x;
+                    }
+                    ++it;
                 }
-                ms = ms_next;
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    msq[j] = nxt[j];
             }
             if (ok) {
                 float *o = p.out + (size_t)z * kT * p.ldc + p.seg[sg].col0 + row;
@@ -1080,6 +1102,7 @@ struct Prefill {
     float *ssq = nullptr;         // [groups / 4][64]
     int token_cap = 0;
     size_t gemm_smem_dim = 0, gemm_smem_hidden = 0, attn_smem = 0;
+    int stages_dim = 4, stages_hidden = 4;
     std::vector<void *> owned;
     unsigned long long launches = 0;
     // concurrent sequences
@@ -1162,8 +1185,21 @@ cudaError_t prefill_create(Prefill **out, const PrefillModel &m)
         prefill_destroy(pf);
         return cudaErrorNotSupported;
     }
-    pf->gemm_smem_dim = (size_t)kRingBytes + (size_t)(m.dim / 256) * kT * sizeof(float2) + 1024;
-    pf->gemm_smem_hidden = (size_t)kRingBytes + (size_t)(m.hidden / 256) * kT * sizeof(float2) + 1024;
+    int max_smem = 0;
+    e = cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+    if (e != cudaSuccess) {
+        prefill_destroy(pf);
+        return e;
+    }
+    auto fit = [&](int k, int *stages) {
+        const size_t table = (size_t)(k / 256) * kT * sizeof(float2) + 1024 + 512;   // unit table, alignment slack, static part
+        *stages = kMaxStages;
+        while (*stages > 2 && (size_t)*stages * kStageBytes + table > (size_t)max_smem)
+            --*stages;
+        return (size_t)*stages * kStageBytes + table - 512;
+    };
+    pf->gemm_smem_dim = fit(m.dim, &pf->stages_dim);
+    pf->gemm_smem_hidden = fit(m.hidden, &pf->stages_hidden);
     const size_t gmax = pf->gemm_smem_dim > pf->gemm_smem_hidden ? pf->gemm_smem_dim : pf->gemm_smem_hidden;
     e = cudaFuncSetAttribute(pf_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gmax);
     const int ld = m.head + 4;
@@ -1209,6 +1245,7 @@ cudaError_t launch_gemm(Prefill *pf, cudaStream_t st, int layer, const int *w, i
     p.out = out;
     p.ldc = ldc;
     p.ksplit = ksplit;
+    p.stages = k == m.dim ? pf->stages_dim : pf->stages_hidden;
     p.ssq = normed ? pf->ssq : nullptr;
     p.nssq = (k / 256 + kLimbWarps - 1) / kLimbWarps;
     p.n = k;
