@@ -43,9 +43,10 @@ constexpr int kTileM = 128;                 // weight rows per tile
 constexpr int kGemmThreads = 384;          // producer warp, issue warp, two spare, eight epilogue warps
 constexpr int kEpiWarps = 8;                // warps 4..11: quarter of tensor memory = warp % 4, half of the tokens = (warp - 4) / 4
 constexpr int kTH = kT / 2;                 // tokens per epilogue thread
-constexpr int kMaxStages = 4;                // ring depth; one stage = half a quantisation group (K = 128) of A and B.
-                                            // Measured: a fifth stage, or separate rings for A and B, are slower; the kernel
-                                            // sits on the kind::i8 issue rate (about 380 cycles per 128 x 192 x 32 MMA)
+constexpr int kStages = 4;                  // ring depth, a power of two known at compile time: the two single-lane issue
+                                            // loops are on the critical path (a run-time depth, i.e. a division per stage,
+                                            // costs 15 %); one stage = half a quantisation group (K = 128) of A and B
+constexpr int kMaxStages = kStages;
 constexpr int kABytes = kTileM * 128;       // the A part of a stage: 128 rows of 128 bytes
 constexpr int kBBytes = kN * 128;
 constexpr int kStageBytes = kABytes + kBBytes;
@@ -186,7 +187,6 @@ struct PfGemmParams {
     int n;               // elements per input row
     float *out;          // [ksplit][64][ldc]
     int ldc;
-    int stages;          // ring depth (<= kMaxStages)
     int ksplit;          // the groups of a row are dealt to this many blocks; part z goes to out + z * 64 * ldc
     int nvalid;          // tokens of the chunk that exist
     int timeout_us;
@@ -206,7 +206,6 @@ pf_gemm_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t base = (smem_u32(pf_smem_raw) + 1023u) & ~1023u;            // swizzled tiles want 1024-byte alignment
     unsigned char *gen = pf_smem_raw + (base - smem_u32(pf_smem_raw));
-    const int kStages = p.stages;
     float2 *s_ux = reinterpret_cast<float2 *>(gen + (size_t)kStages * kStageBytes);
     const uint32_t bar_full = smem_u32(&s_bar[0]), bar_empty = smem_u32(&s_bar[kMaxStages]);
     const uint32_t bar_acc_full = smem_u32(&s_bar[2 * kMaxStages]), bar_acc_empty = smem_u32(&s_bar[2 * kMaxStages + 2]);
@@ -1102,7 +1101,6 @@ struct Prefill {
     float *ssq = nullptr;         // [groups / 4][64]
     int token_cap = 0;
     size_t gemm_smem_dim = 0, gemm_smem_hidden = 0, attn_smem = 0;
-    int stages_dim = 4, stages_hidden = 4;
     std::vector<void *> owned;
     unsigned long long launches = 0;
     // concurrent sequences
@@ -1185,21 +1183,9 @@ cudaError_t prefill_create(Prefill **out, const PrefillModel &m)
         prefill_destroy(pf);
         return cudaErrorNotSupported;
     }
-    int max_smem = 0;
-    e = cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
-    if (e != cudaSuccess) {
-        prefill_destroy(pf);
-        return e;
-    }
-    auto fit = [&](int k, int *stages) {
-        const size_t table = (size_t)(k / 256) * kT * sizeof(float2) + 1024 + 512;   // unit table, alignment slack, static part
-        *stages = kMaxStages;
-        while (*stages > 2 && (size_t)*stages * kStageBytes + table > (size_t)max_smem)
-            --*stages;
-        return (size_t)*stages * kStageBytes + table - 512;
-    };
-    pf->gemm_smem_dim = fit(m.dim, &pf->stages_dim);
-    pf->gemm_smem_hidden = fit(m.hidden, &pf->stages_hidden);
+    // ring, unit table (at most 64 groups: 32 KB), alignment slack: below the 227 KB a block may have
+    pf->gemm_smem_dim = (size_t)kStages * kStageBytes + (size_t)(m.dim / 256) * kT * sizeof(float2) + 1024;
+    pf->gemm_smem_hidden = (size_t)kStages * kStageBytes + (size_t)(m.hidden / 256) * kT * sizeof(float2) + 1024;
     const size_t gmax = pf->gemm_smem_dim > pf->gemm_smem_hidden ? pf->gemm_smem_dim : pf->gemm_smem_hidden;
     e = cudaFuncSetAttribute(pf_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gmax);
     const int ld = m.head + 4;
@@ -1245,7 +1231,6 @@ cudaError_t launch_gemm(Prefill *pf, cudaStream_t st, int layer, const int *w, i
     p.out = out;
     p.ldc = ldc;
     p.ksplit = ksplit;
-    p.stages = k == m.dim ? pf->stages_dim : pf->stages_hidden;
     p.ssq = normed ? pf->ssq : nullptr;
     p.nssq = (k / 256 + kLimbWarps - 1) / kLimbWarps;
     p.n = k;
