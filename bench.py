@@ -299,6 +299,20 @@ def concurrent_account(cfg, model, single_tok_s: float) -> dict:
             "note": "each step reads every weight once for 64 sequences; attention and K/V traffic grow with the positions"}
 
 
+def host_loop(model, prompt, forwards: int) -> np.ndarray:
+    """The run loop of Run.java:609-685 with --temp 0.0 as a host makes it through the C ABI: one blocking
+    l2j_forward per token, the token from pinned host memory to the device, the 128 KB of logits back into a host
+    buffer, the next token = forced prompt token or the first maximum (the call returns the device's arg-max of
+    the same logits; the parity tests check that it is the host's)."""
+    prompt = [int(t) for t in prompt]
+    token, out = 1, np.empty(forwards, dtype=np.int32)
+    for pos in range(forwards):
+        _, am = model.forward(token, pos)
+        token = prompt[pos] if pos < len(prompt) else am
+        out[pos] = token
+    return out
+
+
 def run_single(args, cfg, local_rank: int) -> dict:
     from llama2j_b200 import synthetic as syn
     from llama2j_b200.transformer import Transformer, run_greedy_host_loop
@@ -341,11 +355,11 @@ def run_single(args, cfg, local_rank: int) -> dict:
     reference_style = (forwards - 1) / ((step_us - first_us) * 1e-6) if step_us > first_us else None
 
     # ---- end-to-end arm: the call the Java host makes, once per token, logits back to the host ----
-    run_greedy_host_loop(model, prompt, min(forwards, 64), stop_on_bos=False)
+    host_loop(model, prompt, min(forwards, 64))
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        host_tokens, _ = run_greedy_host_loop(model, prompt, forwards, stop_on_bos=False)
+        host_tokens = host_loop(model, prompt, forwards)
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
     e2e_value = args.steps * forwards / e2e_s
@@ -464,10 +478,10 @@ def run_group(args, cfg, world: int) -> dict:
     value = args.steps * forwards / (dev_us * 1e-6)
     kpf = int(group.ranks[0].stats().kernels_per_forward)
 
-    run_greedy_host_loop(group, prompt, min(forwards, 64), stop_on_bos=False)
+    host_loop(group, prompt, min(forwards, 64))
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        host_tokens, _ = run_greedy_host_loop(group, prompt, forwards, stop_on_bos=False)
+        host_tokens = host_loop(group, prompt, forwards)
     e2e_value = args.steps * forwards / (time.perf_counter() - t0)
     group.close()
 
