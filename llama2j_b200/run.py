@@ -22,7 +22,7 @@ from . import lib as _lib
 from . import model_files as mf
 from . import synthetic as syn
 from .layer_allocation import LayerAllocation, parse_gpu_mem
-from .transformer import Transformer, argmax
+from .transformer import LinkedStages, Transformer, argmax
 
 MODELS_DIRECTORY = "models"   # Run.java:34
 
@@ -85,6 +85,15 @@ def main(argv=None) -> int:
     prompt = [int(t) for t in args["--promptTokens"].split(",") if t.strip()]
     if temperature != 0.0:
         stages[-1].sampler_seed(seed)                        # Run.java:620
+    # several devices: the stages hand x over the peer links (l2j_pipeline_*), the host sees one forward per token;
+    # without peer access between the devices the link is refused and x travels through the host array, as in the
+    # reference (Run.java:368-413)
+    linked = None
+    if len(stages) > 1:
+        try:
+            linked = LinkedStages(stages)
+        except _lib.L2jError as e:
+            print(f"INFO: stages not linked ({e}); hand-over through the host")
     token, pos, start, out = 1, 0, 0.0, []
     if len(stages) == 1 and 1 < len(prompt) < steps and 1 not in prompt:
         # positions 0 .. len(prompt) - 1 (fed BOS, then the prompt) in one batched call instead of one decode step
@@ -92,12 +101,16 @@ def main(argv=None) -> int:
         stages[0].prefill([1] + prompt[:-1], 0)
         out, token, pos, start = list(prompt), prompt[-1], len(prompt), time.time()
     while pos < steps:                                       # Run.java:623-685
-        x = None
-        for st in stages[:-1]:
-            x = st.forward_stage(token, pos, x)
         want = temperature == 0.0 and pos >= len(prompt)
-        logits, _ = (stages[-1].forward_stage(token, pos, x, want) if len(stages) > 1
-                     else stages[0].forward(token, pos, want))
+        if linked is not None:
+            logits, _ = linked.forward(token, pos, want)
+        elif len(stages) > 1:
+            x = None
+            for st in stages[:-1]:
+                x = st.forward_stage(token, pos, x)
+            logits, _ = stages[-1].forward_stage(token, pos, x, want)
+        else:
+            logits, _ = stages[0].forward(token, pos, want)
         if pos < len(prompt):
             nxt = prompt[pos]                                # Run.java:635-637
         elif temperature == 0.0:

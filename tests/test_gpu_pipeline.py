@@ -92,3 +92,33 @@ def test_link_rejects_gaps_and_wrong_order():
         LinkedStages([b, a])
     a.close()
     b.close()
+
+
+def test_command_line_loop_over_two_devices(tmp_path, monkeypatch, capsys):
+    """`--gpuMem a,b` (LayerAllocation.java:54-95) splits the layers over two devices; the command-line loop links
+    the stages and must print the tokens of the single-device run."""
+    if _device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import numpy as np
+
+    from llama2j_b200 import model_files as mf
+    from llama2j_b200 import run as cli
+    from llama2j_b200.model_files import ModelConfig
+    cfg = ModelConfig(dim=256, hidden_dim=768, n_layers=6, n_heads=4, n_kv_heads=4, vocab_size=400, seq_len=64,
+                      shared_classifier=True)
+    rng = np.random.default_rng(21)
+    fp32 = {t: rng.normal(0, 0.05, cfg.tensor_floats(t)).astype(np.float32) for t in range(11)}
+    for t in (L.T_RMS_ATT, L.T_RMS_FFN, L.T_RMS_FINAL):
+        fp32[t] = rng.uniform(0.5, 1.5, cfg.tensor_floats(t)).astype(np.float32)
+    (tmp_path / "models").mkdir()
+    mf.write_checkpoint(str(tmp_path / "models" / "tiny.bin"), cfg, fp32)
+    monkeypatch.chdir(tmp_path)
+    base = ["--checkpoint", "tiny.bin", "--temp", "0.0", "--steps", "40", "--promptTokens", "5,17,200,3",
+            "--mode", "CUDA"]
+    assert cli.main(base) == 0
+    one = capsys.readouterr().out.strip().splitlines()
+    assert cli.main(base + ["--gpuMem", "1,1"]) == 0      # equal budgets: three layers on each device
+    two = capsys.readouterr().out.strip().splitlines()
+    tokens = lambda lines: [ln for ln in lines if ln and ln[0].isdigit()][0]
+    assert tokens(two) == tokens(one)
+    assert not any("not linked" in ln for ln in two)
