@@ -112,12 +112,15 @@ __device__ __forceinline__ void umma_commit(uint32_t bar)
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16])
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32])
 {
     asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, "
+        "%20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
         : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
-          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+          "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]),
+          "=r"(r[30]), "=r"(r[31])
         : "r"(taddr)
         : "memory");
 }
@@ -383,12 +386,10 @@ pf_gemm_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant
                     const uint32_t tacc = trow + (uint32_t)b * kAccCols;
                     // all of the thread's sums of the group in one round trip, then the accumulator is free again
                     uint32_t s0[kTH], s1[kTH], s2[kTH];
-#pragma unroll
-                    for (int c = 0; c < kTH; c += 16) {
-                        tmem_ld16(tacc + c, *reinterpret_cast<uint32_t(*)[16]>(&s0[c]));
-                        tmem_ld16(tacc + kT + c, *reinterpret_cast<uint32_t(*)[16]>(&s1[c]));
-                        tmem_ld16(tacc + 2 * kT + c, *reinterpret_cast<uint32_t(*)[16]>(&s2[c]));
-                    }
+                    static_assert(kTH == 32, "one 32-column load per limb");
+                    tmem_ld32(tacc, s0);
+                    tmem_ld32(tacc + kT, s1);
+                    tmem_ld32(tacc + 2 * kT, s2);
                     tmem_ld_wait();
                     tc_fence_before();
                     __syncwarp();
