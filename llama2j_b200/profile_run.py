@@ -5,6 +5,7 @@ decodes a few tokens on the device and prints per-kernel event timings.
   python -m llama2j_b200.profile_run --shape llama2-7b --layers 4 --forwards 4
   python -m llama2j_b200.profile_run --shape llama2-7b --layers 4 --forwards 0 --prefill 128 --pos0 1024
   python -m llama2j_b200.profile_run --shape llama2-7b --layers 4 --forwards 0 --concurrent 64 --steps 3
+  python -m llama2j_b200.profile_run --shape llama2-7b --layers 2 --forwards 0 --flags 8 --prefill 3840 --decode 3
 
 Meant to be run plainly first and then under `ncu --clock-control none ...`.
 """
@@ -29,6 +30,7 @@ def main() -> None:
     ap.add_argument("--time-kernels", type=int, default=0, help="position for the per-kernel event timing (0: skip)")
     ap.add_argument("--prefill", type=int, default=0, help="tokens to push through l2j_prefill, twice (0: skip)")
     ap.add_argument("--pos0", type=int, default=0, help="first position of the prefill")
+    ap.add_argument("--decode", type=int, default=0, help="decode steps after the prefill, from the position behind it (0: skip)")
     ap.add_argument("--concurrent", type=int, default=0, help="sequences to decode together with l2j_batch_forward (0: skip)")
     ap.add_argument("--steps", type=int, default=3, help="steps of the concurrent run")
     args = ap.parse_args()
@@ -50,6 +52,9 @@ def main() -> None:
             m.prefill(inputs, args.pos0)
             m.prefill(inputs, args.pos0)
             out["prefill_launches"] = m.prefill_launches()
+            tok = 7
+            for i in range(args.decode):          # long-context decode steps over the cache the prefill left
+                _, tok = m.forward(tok, args.pos0 + args.prefill + i, want_logits=False)
         if args.concurrent > 0:
             m.batch_create(args.concurrent, 64)
             toks = np.ones(args.concurrent, dtype=np.int32)
