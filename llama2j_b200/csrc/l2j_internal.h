@@ -231,11 +231,13 @@ constexpr int kFusedHeaderBytes = 4096;   // barriers, descriptors, reduction bu
 cudaError_t prepare_fused(int *max_smem);
 cudaError_t launch_fused(cudaStream_t stream, bool pdl, int grid, int smem_bytes, const FusedParams &p);
 
-// Blocks per head of the stand-alone attention kernel: enough to fill the SMs twice over, at least 16 positions
-// each.  One definition for every entry point, so that they split (and therefore round) alike.
+// Blocks per head of the stand-alone attention kernel: as many as fit on the device at once (two blocks per SM are
+// resident; one block more than that and a few SMs scan a third key range while the others wait: 40 heads x 8
+// splits were 320 blocks on 296 places), at least 16 positions each.  One definition for every entry point, so
+// that they split (and therefore round) alike.
 inline int choose_nsplit(int sm_count, int n_heads, int seq_len)
 {
-    int ns = (2 * sm_count + n_heads - 1) / n_heads;
+    int ns = (2 * sm_count) / n_heads;
     if (ns > 32)
         ns = 32;
     const int cap = seq_len / 16 > 0 ? seq_len / 16 : 1;
