@@ -50,7 +50,7 @@ constexpr int kMaxStages = kStages;
 constexpr int kABytes = kTileM * 128;       // the A part of a stage: 128 rows of 128 bytes
 constexpr int kBBytes = kN * 128;
 constexpr int kStageBytes = kABytes + kBBytes;
-constexpr int kMaxParts = 8;                // parts a row sum (or a query's keys) may be dealt into
+constexpr int kMaxParts = 12;               // parts a row sum (or a query's keys) may be dealt into
 constexpr int kAccCols = 256;               // column distance of the two accumulators in tensor memory
 constexpr int kTmemCols = 512;
 
@@ -1319,7 +1319,20 @@ cudaError_t prefill_run(Prefill *pf, cudaStream_t st, const int *tokens_host, in
             int nsplit = 1;
             {
                 const int tiles = (pos0 + c0 + nv + kAttnKeys - 1) / kAttnKeys;
-                nsplit = tiles / 4 < 1 ? 1 : (tiles / 4 > kMaxParts ? kMaxParts : tiles / 4);
+                // key ranges per (head, 32 queries): the count that needs the fewest rounds of key tiles, with two
+                // blocks resident per SM (each block pays about half a tile for its set-up and the merge of a part)
+                {
+                    const int base = m.n_heads * ((nv + kAttnQ - 1) / kAttnQ), places = 2 * pf->sms;
+                    float best = 0.f;
+                    for (int ns = 1; ns <= kMaxParts && ns <= tiles; ++ns) {
+                        const int waves = (base * ns + places - 1) / places;
+                        const float cost = (float)waves * ((float)((tiles + ns - 1) / ns) + 0.5f);
+                        if (ns == 1 || cost < best) {
+                            best = cost;
+                            nsplit = ns;
+                        }
+                    }
+                }
                 PfAttnParams a{};
                 a.q = pf->q; a.k_cache = L.kc; a.v_cache = L.vc; a.parts = pf->parts;
                 a.dim = dim; a.head = m.head; a.kv_mul = m.n_heads / m.n_kv_heads; a.seq_len = m.seq_len; a.pos0 = pos0 + c0; a.nvalid = nv;
