@@ -51,6 +51,7 @@ constexpr int kABytes = kTileM * 128;       // the A part of a stage: 128 rows o
 constexpr int kBBytes = kN * 128;
 constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kMaxParts = 12;               // parts a row sum (or a query's keys) may be dealt into
+constexpr int kWideParts = 3;               // at most this many parts for the wide outputs (QKV, W1/W3): their sums are read back
 constexpr int kAccCols = 256;               // column distance of the two accumulators in tensor memory
 constexpr int kTmemCols = 512;
 
@@ -498,6 +499,12 @@ __global__ void __launch_bounds__(kLimbThreads) pf_limbs_kernel(const PfLimbPara
                 float4 y = make_float4(0.f, 0.f, 0.f, 0.f);
                 if (live)
                     y = *reinterpret_cast<const float4 *>(p.b + (size_t)t * p.lda + e);
+                for (int z = 1; z < p.nparts && live; ++z) {   // split-K parts of h1 and h3, in order
+                    const float4 xz = *reinterpret_cast<const float4 *>(p.a + ((size_t)z * kT + t) * p.lda + e);
+                    const float4 yz = *reinterpret_cast<const float4 *>(p.b + ((size_t)z * kT + t) * p.lda + e);
+                    x.x = __fadd_rn(x.x, xz.x); x.y = __fadd_rn(x.y, xz.y); x.z = __fadd_rn(x.z, xz.z); x.w = __fadd_rn(x.w, xz.w);
+                    y.x = __fadd_rn(y.x, yz.x); y.y = __fadd_rn(y.y, yz.y); y.z = __fadd_rn(y.z, yz.z); y.w = __fadd_rn(y.w, yz.w);
+                }
                 // Silu.java:122-132 order: (value * sigmoid) * hb2
                 x.x = __fmul_rn(__fmul_rn(x.x, sigmoid_accurate(x.x)), y.x);
                 x.y = __fmul_rn(__fmul_rn(x.y, sigmoid_accurate(x.y)), y.y);
@@ -582,6 +589,7 @@ struct PfRopeParams {
     float *k_cache, *v_cache;   // layer base, [kv_head][seq][head]
     const float *rope_cos, *rope_sin;   // [seq][head / 2]
     int dim, kv_dim, head, seq_len, pos0, nvalid;
+    int nparts;                         // split-K parts of qkv ([nparts][64][dim + 2 kv_dim]), summed here in order
     const int *pos_of, *seq_of;         // concurrent sequences: position and sequence of every token (else pos0 + t, one cache)
     long long seq_stride;               // floats between the caches of two sequences
 };
@@ -601,7 +609,12 @@ __global__ void pf_rope_kv_kernel(PfRopeParams p)
     const int i = blockIdx.y * blockDim.x + threadIdx.x;      // one pair per thread
     if (i < (p.dim + 2 * p.kv_dim) / 2) {
         const int e = 2 * i;
-        const float v0 = row[e], v1 = row[e + 1];
+        float v0 = row[e], v1 = row[e + 1];
+        for (int z = 1; z < p.nparts; ++z) {
+            const float *rz = row + (size_t)z * kT * (p.dim + 2 * p.kv_dim);
+            v0 = __fadd_rn(v0, rz[e]);
+            v1 = __fadd_rn(v1, rz[e + 1]);
+        }
         if (e < p.dim + p.kv_dim) {
             const int r = e < p.dim ? e : e - p.dim;
             const int d = r % p.head;
@@ -1096,7 +1109,7 @@ struct Prefill {
     int *tokens = nullptr;
     float *x = nullptr, *qkv = nullptr, *q = nullptr, *h13 = nullptr;
     float *parts = nullptr;      // [kMaxParts][64][dim]: partial row sums of Wo / W2, or the attention's key ranges
-    int ksplit_o = 1, ksplit_2 = 1;
+    int ksplit_o = 1, ksplit_2 = 1, ksplit_qkv = 1, ksplit_13 = 1;
     int8_t *limbs = nullptr;
     float2 *ux = nullptr;
     float *ssq = nullptr;         // [groups / 4][64]
@@ -1160,9 +1173,9 @@ cudaError_t prefill_create(Prefill **out, const PrefillModel &m)
         e = cudaDeviceGetAttribute(&pf->sms, cudaDevAttrMultiProcessorCount, dev);
     const int kmax = m.dim > m.hidden ? m.dim : m.hidden;
     if (e == cudaSuccess) e = pf_alloc(pf, &pf->x, (size_t)kT * m.dim);
-    if (e == cudaSuccess) e = pf_alloc(pf, &pf->qkv, (size_t)kT * pf->qkv_ld);
+    if (e == cudaSuccess) e = pf_alloc(pf, &pf->qkv, (size_t)kWideParts * kT * pf->qkv_ld);
     if (e == cudaSuccess) e = pf_alloc(pf, &pf->q, (size_t)kT * m.dim);
-    if (e == cudaSuccess) e = pf_alloc(pf, &pf->h13, (size_t)kT * 2 * m.hidden);
+    if (e == cudaSuccess) e = pf_alloc(pf, &pf->h13, (size_t)kWideParts * kT * 2 * m.hidden);
     if (e == cudaSuccess) e = pf_alloc(pf, &pf->parts, (size_t)kMaxParts * kT * (m.dim + 2 * m.n_heads));
     if (e == cudaSuccess) e = pf_alloc(pf, &pf->limbs, (size_t)kN * kmax);
     if (e == cudaSuccess) e = pf_alloc(pf, &pf->ux, (size_t)(kmax / 256) * kT);
@@ -1200,6 +1213,20 @@ cudaError_t prefill_create(Prefill **out, const PrefillModel &m)
     };
     pf->ksplit_o = split_for(m.dim, m.dim / 256);
     pf->ksplit_2 = split_for(m.dim, m.hidden / 256);
+    // the wide matrices have more tiles than SMs or nearly so: the part count that needs the fewest rounds of groups
+    auto rounds_split = [&](int tiles, int groups) {
+        int best = 1, best_cost = 1 << 30;
+        for (int ks = 1; ks <= kWideParts && ks <= groups; ++ks) {
+            const int cost = ((tiles * ks + pf->sms - 1) / pf->sms) * ((groups + ks - 1) / ks);
+            if (cost < best_cost) {
+                best_cost = cost;
+                best = ks;
+            }
+        }
+        return best;
+    };
+    pf->ksplit_qkv = 1;   // measured: three parts for QKV (96 tiles at the 7B shape) gain nothing and cost the RoPE kernel two more reads
+    pf->ksplit_13 = rounds_split(2 * m.hidden / kTileM, m.dim / 256);
     if (e == cudaSuccess)
         e = m.head == 128 ? cudaFuncSetAttribute(pf_attention_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pf->attn_smem)
                           : cudaFuncSetAttribute(pf_attention_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pf->attn_smem);
@@ -1304,13 +1331,14 @@ cudaError_t prefill_run(Prefill *pf, cudaStream_t st, const int *tokens_host, in
             PF_CK(launch_limbs<PF_IN_NORM>(pf, st, pf->x, L.rms_att, pf->parts, pending, dim, dim, nv));
             {
                 const int w[3] = {PF_WQ, PF_WK, PF_WV}, col0[3] = {0, dim, dim + kvd};
-                PF_CK(launch_gemm(pf, st, l, w, 3, dim, pf->qkv, pf->qkv_ld, col0, 1, nv, true));
+                PF_CK(launch_gemm(pf, st, l, w, 3, dim, pf->qkv, pf->qkv_ld, col0, pf->ksplit_qkv, nv, true));
             }
             {
                 PfRopeParams r{};
                 r.qkv = pf->qkv; r.q = pf->q; r.k_cache = L.kc; r.v_cache = L.vc;
                 r.rope_cos = m.rope_cos; r.rope_sin = m.rope_sin;
                 r.dim = dim; r.kv_dim = kvd; r.head = m.head; r.seq_len = m.seq_len; r.pos0 = pos0 + c0; r.nvalid = nv;
+                r.nparts = pf->ksplit_qkv;
                 const dim3 grid((unsigned)kT, (unsigned)((pf->qkv_ld / 2 + 255) / 256));
                 pf_rope_kv_kernel<<<grid, 256, 0, st>>>(r);
                 ++pf->launches;
@@ -1353,9 +1381,9 @@ cudaError_t prefill_run(Prefill *pf, cudaStream_t st, const int *tokens_host, in
             PF_CK(launch_limbs<PF_IN_NORM>(pf, st, pf->x, L.rms_ffn, pf->parts, pf->ksplit_o, dim, dim, nv));
             {
                 const int w[2] = {PF_W1, PF_W3}, col0[2] = {0, hidden};
-                PF_CK(launch_gemm(pf, st, l, w, 2, dim, pf->h13, 2 * hidden, col0, 1, nv, true));
+                PF_CK(launch_gemm(pf, st, l, w, 2, dim, pf->h13, 2 * hidden, col0, pf->ksplit_13, nv, true));
             }
-            PF_CK(launch_limbs<PF_IN_SWIGLU>(pf, st, pf->h13, pf->h13 + hidden, nullptr, 0, 2 * hidden, hidden, nv));
+            PF_CK(launch_limbs<PF_IN_SWIGLU>(pf, st, pf->h13, pf->h13 + hidden, nullptr, pf->ksplit_13, 2 * hidden, hidden, nv));
             {
                 const int w[1] = {PF_W2}, col0[1] = {0};
                 PF_CK(launch_gemm(pf, st, l, w, 1, hidden, pf->parts, dim, col0, pf->ksplit_2, nv, false));
@@ -1429,13 +1457,14 @@ cudaError_t prefill_batch_forward(Prefill *pf, cudaStream_t st, const int *token
         PF_CK(launch_limbs<PF_IN_NORM>(pf, st, pf->x, L.rms_att, pf->parts, pending, dim, dim, nv));
         {
             const int w[3] = {PF_WQ, PF_WK, PF_WV}, col0[3] = {0, dim, dim + kvd};
-            PF_CK(launch_gemm(pf, st, l, w, 3, dim, pf->qkv, pf->qkv_ld, col0, 1, nv, true));
+            PF_CK(launch_gemm(pf, st, l, w, 3, dim, pf->qkv, pf->qkv_ld, col0, pf->ksplit_qkv, nv, true));
         }
         {
             PfRopeParams r{};
             r.qkv = pf->qkv; r.q = pf->q; r.k_cache = pf->bkc + l * layer_stride; r.v_cache = pf->bvc + l * layer_stride;
             r.rope_cos = m.rope_cos; r.rope_sin = m.rope_sin;
             r.dim = dim; r.kv_dim = kvd; r.head = m.head; r.seq_len = pf->seq_len_b; r.pos0 = 0; r.nvalid = nv;
+            r.nparts = pf->ksplit_qkv;
             r.pos_of = d_pos; r.seq_of = d_seq; r.seq_stride = seq_stride;
             const dim3 grid((unsigned)kT, (unsigned)((pf->qkv_ld / 2 + 255) / 256));
             pf_rope_kv_kernel<<<grid, 256, 0, st>>>(r);
@@ -1463,9 +1492,9 @@ cudaError_t prefill_batch_forward(Prefill *pf, cudaStream_t st, const int *token
         PF_CK(launch_limbs<PF_IN_NORM>(pf, st, pf->x, L.rms_ffn, pf->parts, pf->ksplit_o, dim, dim, nv));
         {
             const int w[2] = {PF_W1, PF_W3}, col0[2] = {0, hidden};
-            PF_CK(launch_gemm(pf, st, l, w, 2, dim, pf->h13, 2 * hidden, col0, 1, nv, true));
+            PF_CK(launch_gemm(pf, st, l, w, 2, dim, pf->h13, 2 * hidden, col0, pf->ksplit_13, nv, true));
         }
-        PF_CK(launch_limbs<PF_IN_SWIGLU>(pf, st, pf->h13, pf->h13 + hidden, nullptr, 0, 2 * hidden, hidden, nv));
+        PF_CK(launch_limbs<PF_IN_SWIGLU>(pf, st, pf->h13, pf->h13 + hidden, nullptr, pf->ksplit_13, 2 * hidden, hidden, nv));
         {
             const int w[1] = {PF_W2}, col0[1] = {0};
             PF_CK(launch_gemm(pf, st, l, w, 1, hidden, pf->parts, dim, col0, pf->ksplit_2, nv, false));
