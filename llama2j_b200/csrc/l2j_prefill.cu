@@ -28,6 +28,7 @@
 #include <cmath>
 #include <cstdlib>
 #include <cstring>
+#include <map>
 #include <mutex>
 #include <vector>
 
@@ -1124,6 +1125,9 @@ struct Prefill {
     float *xn = nullptr, *logits = nullptr;    // [64][dim], [64][vocab]
     int *meta_host = nullptr;                  // pinned, 4 x 64
     float *logits_host = nullptr;              // pinned, [64][vocab]
+    std::map<int, cudaGraphExec_t> step_graphs; // captured step per entry count
+    unsigned long long step_launches = 0;
+    bool no_graph = false;
 };
 
 bool prefill_supported(const PrefillModel &m)
@@ -1137,6 +1141,8 @@ void prefill_destroy(Prefill *pf)
 {
     if (!pf)
         return;
+    for (auto &g : pf->step_graphs)
+        cudaGraphExecDestroy(g.second);
     if (pf->meta_host)
         cudaFreeHost(pf->meta_host);
     if (pf->logits_host)
@@ -1409,6 +1415,9 @@ cudaError_t prefill_batch_create(Prefill *pf, int n_seq, int seq_len)
                 return;
             }
     };
+    for (auto &g : pf->step_graphs)
+        cudaGraphExecDestroy(g.second);
+    pf->step_graphs.clear();
     if (pf->bkc) {
         drop(pf->bkc);
         drop(pf->bvc);
@@ -1433,16 +1442,12 @@ cudaError_t prefill_batch_create(Prefill *pf, int n_seq, int seq_len)
 // One decode step of n <= 64 (sequence, position, token) triples on one sweep over the weights; a sequence
 // may appear several times with different positions (their K/V rows are all written before the attention).
 // logits_out [n][vocab] and argmax_out [n] are host pointers (either may be null); blocks until done.
-cudaError_t prefill_batch_forward(Prefill *pf, cudaStream_t st, const int *tokens, const int *pos, const int *seq, int n, float *logits_out,
-                                  int *argmax_out)
+// Everything one step of n entries puts on the stream: tokens / positions / sequences in, all layers, classifier,
+// arg-max ids out (pinned buffers on both ends, so the whole step can be captured into a graph).
+static cudaError_t batch_enqueue(Prefill *pf, cudaStream_t st, int nv)
 {
     const PrefillModel &m = pf->m;
-    const int dim = m.dim, hidden = m.hidden, kvd = pf->kv_dim, nv = n;
-    for (int i = 0; i < kT; ++i) {
-        pf->meta_host[i] = i < n ? tokens[i] : 0;
-        pf->meta_host[kT + i] = i < n ? pos[i] : 0;
-        pf->meta_host[2 * kT + i] = i < n ? seq[i] : 0;
-    }
+    const int dim = m.dim, hidden = m.hidden, kvd = pf->kv_dim;
     PF_CK(cudaMemcpyAsync(pf->meta, pf->meta_host, sizeof(int) * 3 * kT, cudaMemcpyHostToDevice, st));
     const int *d_tok = pf->meta, *d_pos = pf->meta + kT, *d_seq = pf->meta + 2 * kT;
     int *d_arg = pf->meta + 3 * kT;
@@ -1510,6 +1515,54 @@ cudaError_t prefill_batch_forward(Prefill *pf, cudaStream_t st, const int *token
     PF_CK(cudaGetLastError());
     pf->launches += 3;
     PF_CK(cudaMemcpyAsync(pf->meta_host + 3 * kT, d_arg, sizeof(int) * kT, cudaMemcpyDeviceToHost, st));
+    return cudaSuccess;
+}
+
+cudaError_t prefill_batch_forward(Prefill *pf, cudaStream_t st, const int *tokens, const int *pos, const int *seq, int n, float *logits_out,
+                                  int *argmax_out)
+{
+    const PrefillModel &m = pf->m;
+    const int nv = n;
+    for (int i = 0; i < kT; ++i) {
+        pf->meta_host[i] = i < n ? tokens[i] : 0;
+        pf->meta_host[kT + i] = i < n ? pos[i] : 0;
+        pf->meta_host[2 * kT + i] = i < n ? seq[i] : 0;
+    }
+    // The step is about 330 launches of kernels that mostly run for a few microseconds: replayed as one graph per
+    // entry count (grids and parameters depend on it; the caches and buffers stay where they are until
+    // prefill_batch_create runs again).
+    cudaGraphExec_t exec = nullptr;
+    auto it = pf->step_graphs.find(nv);
+    if (it != pf->step_graphs.end()) {
+        exec = it->second;
+    } else if (!pf->no_graph) {
+        cudaGraph_t graph = nullptr;
+        const unsigned long long before = pf->launches;
+        if (cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal) == cudaSuccess) {
+            const cudaError_t ce = batch_enqueue(pf, st, nv);
+            const cudaError_t ee = cudaStreamEndCapture(st, &graph);
+            if (ce == cudaSuccess && ee == cudaSuccess && graph && cudaGraphInstantiate(&exec, graph, 0) == cudaSuccess) {
+                pf->step_graphs[nv] = exec;
+                pf->step_launches = pf->launches - before;
+            } else {
+                exec = nullptr;
+                pf->no_graph = true;      // direct launches from now on
+                cudaGetLastError();
+            }
+            if (graph)
+                cudaGraphDestroy(graph);
+        } else {
+            pf->no_graph = true;
+            cudaGetLastError();
+        }
+        pf->launches = before;
+    }
+    if (exec) {
+        PF_CK(cudaGraphLaunch(exec, st));
+        pf->launches += pf->step_launches;
+    } else {
+        PF_CK(batch_enqueue(pf, st, nv));
+    }
     if (logits_out)
         PF_CK(cudaMemcpyAsync(pf->logits_host, pf->logits, sizeof(float) * (size_t)nv * m.vocab, cudaMemcpyDeviceToHost, st));
     PF_CK(cudaStreamSynchronize(st));
